@@ -1,0 +1,192 @@
+"""gpt_b200 -- Python binding of libgptb200, the sm_100a replacement for the dense linear-layer path of
+Filipeak/gpt (the operators its CUDA backend sends to cuBLAS, src/backend/cuda/kernels/linear.cu and
+src/backend/cuda/kernels/embedding.cu:47-63,140-170).
+
+The binding is a ctypes view of include/gptb200.h.  `Backend` mirrors the reference's operator names
+(IGPTBackend, src/backend/backend_interface.h) so that a test written against the reference reads the
+same here.  Tensors are passed as raw device addresses (ints) or as objects with a `data_ptr()` method
+(torch CUDA tensors); nothing is copied or converted on the way.
+
+There is no fallback: if the shared library has not been built, or no sm_100 device is present,
+constructing a Backend raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Any
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libgptb200.so")
+
+MODE_3XTF32 = 0
+MODE_TF32 = 1
+
+# Every symbol include/gptb200.h declares (checked by the CPU test-suite against the built library).
+EXPORTED_SYMBOLS = [
+    "gptb200_ctx_create", "gptb200_ctx_destroy", "gptb200_ctx_set_mode", "gptb200_ctx_get_mode",
+    "gptb200_ctx_set_stream", "gptb200_ctx_set_option", "gptb200_ctx_synchronize", "gptb200_ctx_launch_count",
+    "gptb200_status_string", "gptb200_last_error",
+    "gptb200_linear_forward", "gptb200_linear_backward", "gptb200_gelu_backward",
+    "gptb200_unembed_forward", "gptb200_unembed_backward",
+    "gptb200_malloc", "gptb200_free", "gptb200_memset", "gptb200_memcpy_h2d", "gptb200_memcpy_d2h",
+]
+
+
+class GptB200Error(RuntimeError):
+    def __init__(self, status: int, what: str, detail: str = ""):
+        self.status = status
+        super().__init__(f"{what}: status {status}" + (f" ({detail})" if detail else ""))
+
+
+_lib = None
+
+
+def load_library(path: str | None = None) -> ctypes.CDLL:
+    """dlopen libgptb200.so and declare the argument types of its entry points."""
+    global _lib
+    if _lib is not None and path is None:
+        return _lib
+    p = path or LIB_PATH
+    if not os.path.exists(p):
+        raise FileNotFoundError(f"{p} is missing: build it with `python -m gpt_b200.build` (there is no fallback path)")
+    lib = ctypes.CDLL(p)
+    vp, i, fp = ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p
+    sig = {
+        "gptb200_ctx_create": (i, [ctypes.POINTER(vp), i, vp, i]),
+        "gptb200_ctx_destroy": (i, [vp]),
+        "gptb200_ctx_set_mode": (i, [vp, i]),
+        "gptb200_ctx_get_mode": (i, [vp]),
+        "gptb200_ctx_set_stream": (i, [vp, vp]),
+        "gptb200_ctx_set_option": (i, [vp, ctypes.c_char_p, i]),
+        "gptb200_ctx_synchronize": (i, [vp]),
+        "gptb200_ctx_launch_count": (ctypes.c_longlong, [vp]),
+        "gptb200_status_string": (ctypes.c_char_p, [i]),
+        "gptb200_last_error": (ctypes.c_char_p, [vp]),
+        "gptb200_linear_forward": (i, [vp, fp, fp, fp, fp, fp, i, i, i, i]),
+        "gptb200_linear_backward": (i, [vp, fp, fp, fp, fp, fp, fp, i, i, i]),
+        "gptb200_gelu_backward": (i, [vp, fp, fp, fp, i, i]),
+        "gptb200_unembed_forward": (i, [vp, fp, fp, fp, i, i, i]),
+        "gptb200_unembed_backward": (i, [vp, fp, fp, fp, fp, fp, i, i, i]),
+        "gptb200_malloc": (i, [vp, ctypes.POINTER(vp), ctypes.c_size_t]),
+        "gptb200_free": (i, [vp, vp]),
+        "gptb200_memset": (i, [vp, vp, i, ctypes.c_size_t]),
+        "gptb200_memcpy_h2d": (i, [vp, vp, vp, ctypes.c_size_t]),
+        "gptb200_memcpy_d2h": (i, [vp, vp, vp, ctypes.c_size_t]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    if path is None:
+        _lib = lib
+    return lib
+
+
+def _ptr(t: Any) -> int | None:
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return t
+    return int(t.data_ptr())
+
+
+class Backend:
+    """Host-side mirror of the linear-path operators of the reference's IGPTBackend.
+
+    Method names and argument order follow src/backend/backend_interface.h (lines 42-51, 70-82, 120-159);
+    `batch_size` and `seq_len` only ever enter as their product, as in the reference.
+    """
+
+    def __init__(self, device: int = 0, stream: int | None = None, mode: int = MODE_3XTF32):
+        self._lib = load_library()
+        self._ctx = ctypes.c_void_p()
+        rc = self._lib.gptb200_ctx_create(ctypes.byref(self._ctx), device, ctypes.c_void_p(stream or 0), mode)
+        if rc != 0:
+            raise GptB200Error(rc, "gptb200_ctx_create", self._lib.gptb200_status_string(rc).decode())
+
+    # ---- context
+    def close(self) -> None:
+        if self._ctx:
+            self._lib.gptb200_ctx_destroy(self._ctx)
+            self._ctx = ctypes.c_void_p()
+
+    def __del__(self):  # pragma: no cover - best effort
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc: int, what: str) -> None:
+        if rc != 0:
+            raise GptB200Error(rc, what, self._lib.gptb200_last_error(self._ctx).decode())
+
+    @property
+    def handle(self) -> ctypes.c_void_p:
+        return self._ctx
+
+    @property
+    def lib(self) -> ctypes.CDLL:
+        return self._lib
+
+    def set_mode(self, mode: int) -> None:
+        self._check(self._lib.gptb200_ctx_set_mode(self._ctx, mode), "gptb200_ctx_set_mode")
+
+    def set_stream(self, stream: int) -> None:
+        self._check(self._lib.gptb200_ctx_set_stream(self._ctx, ctypes.c_void_p(stream)), "gptb200_ctx_set_stream")
+
+    def set_option(self, key: str, value: int) -> None:
+        self._check(self._lib.gptb200_ctx_set_option(self._ctx, key.encode(), value), "gptb200_ctx_set_option")
+
+    def synchronize(self) -> None:
+        self._check(self._lib.gptb200_ctx_synchronize(self._ctx), "gptb200_ctx_synchronize")
+
+    def launch_count(self) -> int:
+        return int(self._lib.gptb200_ctx_launch_count(self._ctx))
+
+    # ---- operators (names of the reference interface)
+    def device_linear_activation_fused_forward(self, y, act, x, w, b, activation: bool, batch_size: int, seq_len: int,
+                                               input_size: int, output_size: int) -> None:
+        self._check(self._lib.gptb200_linear_forward(self._ctx, _ptr(y), _ptr(act), _ptr(x), _ptr(w), _ptr(b),
+                                                     1 if activation else 0, batch_size * seq_len, input_size, output_size),
+                    "gptb200_linear_forward")
+
+    def device_linear_backward(self, grad_x, grad_w, grad_b, grad_y, x, w, batch_size: int, seq_len: int, input_size: int,
+                               output_size: int) -> None:
+        self._check(self._lib.gptb200_linear_backward(self._ctx, _ptr(grad_x), _ptr(grad_w), _ptr(grad_b), _ptr(grad_y),
+                                                      _ptr(x), _ptr(w), batch_size * seq_len, input_size, output_size),
+                    "gptb200_linear_backward")
+
+    def device_activation_backward(self, grad_x, grad_y, x, batch_size: int, seq_len: int, output_size: int) -> None:
+        self._check(self._lib.gptb200_gelu_backward(self._ctx, _ptr(grad_x), _ptr(grad_y), _ptr(x), batch_size * seq_len,
+                                                    output_size), "gptb200_gelu_backward")
+
+    def device_unembedding_forward(self, y, x, wte, batch_size: int, seq_len: int, hidden_size: int, vocab_size: int) -> None:
+        self._check(self._lib.gptb200_unembed_forward(self._ctx, _ptr(y), _ptr(x), _ptr(wte), batch_size * seq_len,
+                                                      hidden_size, vocab_size), "gptb200_unembed_forward")
+
+    def device_unembedding_backward(self, grad_x, grad_wte, grad_y, x, wte, batch_size: int, seq_len: int, hidden_size: int,
+                                    vocab_size_padded: int) -> None:
+        self._check(self._lib.gptb200_unembed_backward(self._ctx, _ptr(grad_x), _ptr(grad_wte), _ptr(grad_y), _ptr(x),
+                                                       _ptr(wte), batch_size * seq_len, hidden_size, vocab_size_padded),
+                    "gptb200_unembed_backward")
+
+    # ---- memory operators (device_malloc / device_free / device_memset / device_memcpy_*)
+    def device_malloc(self, nbytes: int) -> int:
+        p = ctypes.c_void_p()
+        self._check(self._lib.gptb200_malloc(self._ctx, ctypes.byref(p), nbytes), "gptb200_malloc")
+        return int(p.value or 0)
+
+    def device_free(self, ptr: int) -> None:
+        self._check(self._lib.gptb200_free(self._ctx, ctypes.c_void_p(ptr)), "gptb200_free")
+
+    def device_memset(self, ptr: int, value: int, nbytes: int) -> None:
+        self._check(self._lib.gptb200_memset(self._ctx, ctypes.c_void_p(ptr), value, nbytes), "gptb200_memset")
+
+    def device_memcpy_h2d(self, dst: int, src: int, nbytes: int) -> None:
+        self._check(self._lib.gptb200_memcpy_h2d(self._ctx, ctypes.c_void_p(dst), ctypes.c_void_p(src), nbytes),
+                    "gptb200_memcpy_h2d")
+
+    def device_memcpy_d2h(self, dst: int, src: int, nbytes: int) -> None:
+        self._check(self._lib.gptb200_memcpy_d2h(self._ctx, ctypes.c_void_p(dst), ctypes.c_void_p(src), nbytes),
+                    "gptb200_memcpy_d2h")

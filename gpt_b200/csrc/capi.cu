@@ -1,0 +1,511 @@
+// extern "C" layer of libgptb200: context, operand checks, tensor-map construction, tile / split-K
+// selection and kernel launches.  No cuBLAS, no CPU fallback: a call either runs CUDA kernels of this
+// library on the context's stream or returns an error code.
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <algorithm>
+#include <set>
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "../../include/gptb200.h"
+#include "gemm_sm100.cuh"
+#include "kernels_misc.cuh"
+
+using namespace gptb200;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct gptb200_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    int mode = GPTB200_MODE_3XTF32;
+    int num_sms = 0;
+    int tile_n = 0;      // 0 = automatic
+    int max_splits = 0;  // 0 = automatic
+    int *d_status = nullptr;
+    float *ws = nullptr;  // scratch: split-K partial tiles, bias-gradient partial rows
+    size_t ws_bytes = 0;
+    size_t ws_limit = size_t(1) << 30;
+    EncodeTiledFn encode = nullptr;
+    long long launches = 0;
+    std::set<const void *> configured;  // kernels whose dynamic shared-memory limit has been raised
+    char last_error[512] = {0};
+};
+
+namespace {
+
+int fail(gptb200_ctx *ctx, int code, const char *fmt, ...)
+{
+    if (ctx) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(ctx->last_error, sizeof(ctx->last_error), fmt, ap);
+        va_end(ap);
+    }
+    return code;
+}
+
+#define CUDA_TRY(ctx, expr)                                                                                \
+    do {                                                                                                   \
+        cudaError_t e_ = (expr);                                                                           \
+        if (e_ != cudaSuccess)                                                                             \
+            return fail(ctx, GPTB200_ERR_CUDA, "%s:%d %s -> %s", __FILE__, __LINE__, #expr, cudaGetErrorString(e_)); \
+    } while (0)
+
+int ensure_workspace(gptb200_ctx *ctx, size_t bytes)
+{
+    if (bytes <= ctx->ws_bytes) return GPTB200_OK;
+    if (bytes > ctx->ws_limit) return fail(ctx, GPTB200_ERR_WORKSPACE, "scratch request of %zu bytes exceeds limit %zu", bytes, ctx->ws_limit);
+    // Growing the scratch buffer waits for queued work: earlier kernels may still read the old one.
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    if (ctx->ws) CUDA_TRY(ctx, cudaFree(ctx->ws));
+    ctx->ws = nullptr;
+    ctx->ws_bytes = 0;
+    const size_t rounded = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+    CUDA_TRY(ctx, cudaMalloc(&ctx->ws, rounded));
+    ctx->ws_bytes = rounded;
+    return GPTB200_OK;
+}
+
+// One GEMM operand as stored: `rows` x `cols` fp32, row pitch `cols`.
+// K-major operand: rows = free extent (M or N), cols = reduction extent.
+// MN-major operand: rows = reduction extent, cols = free extent.
+int make_tmap(gptb200_ctx *ctx, CUtensorMap *map, const float *base, long long rows, long long cols, int box_cols, int box_rows)
+{
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * sizeof(float)};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+    cuuint32_t estr[2] = {1, 1};
+    const CUresult r = ctx->encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, estr,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(ctx, GPTB200_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) rows=%lld cols=%lld box=%dx%d", int(r), rows, cols, box_rows, box_cols);
+    return GPTB200_OK;
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+struct GemmCall {
+    int M, N, K;
+    const float *a;  // K-major: [M][K]; MN-major: [K][M]
+    bool a_mn;
+    const float *b;  // K-major: [N][K]; MN-major: [K][N]
+    bool b_mn;
+    float *out;      // [M][N]
+    float *act;      // optional
+    const float *bias;
+    bool accumulate;  // out += result
+};
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool X3>
+cudaError_t launch_instance(gptb200_ctx *ctx, const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, int grid)
+{
+    constexpr int smem = gemm_smem_bytes<BN, STAGES, X3>();
+    constexpr int threads = (2 + kNumEpilogueWarps + (X3 ? kNumConvertWarps : 0)) * 32;
+    auto kernel = gemm_tcgen05_kernel<BN, STAGES, A_MN, B_MN, X3>;
+    const void *key = reinterpret_cast<const void *>(kernel);
+    if (!ctx->configured.count(key)) {  // the attribute is per device, the context is bound to one device
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        ctx->configured.insert(key);
+    }
+    kernel<<<grid, threads, smem, ctx->stream>>>(ta, tb, p);
+    return cudaGetLastError();
+}
+
+template <int BN, bool X3>
+cudaError_t launch_majors(gptb200_ctx *ctx, bool a_mn, bool b_mn, const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, int grid)
+{
+    // Ring depth: as many stages as fit in 227 KiB of shared memory.
+    constexpr int STAGES = X3 ? (BN == 256 ? 2 : 3) : (BN == 256 ? 4 : 6);
+    if (!a_mn && b_mn) return launch_instance<BN, STAGES, false, true, X3>(ctx, ta, tb, p, grid);
+    if (!a_mn && !b_mn) return launch_instance<BN, STAGES, false, false, X3>(ctx, ta, tb, p, grid);
+    if (a_mn && b_mn) return launch_instance<BN, STAGES, true, true, X3>(ctx, ta, tb, p, grid);
+    return cudaErrorInvalidValue;  // (MN, K) does not occur on this path
+}
+
+int pick_splits(const gptb200_ctx *ctx, long long tiles, int num_kb, bool allowed, size_t bytes_per_split)
+{
+    if (!allowed) return 1;
+    const int sms = ctx->num_sms;
+    int cap = ctx->max_splits > 0 ? ctx->max_splits : 16;
+    cap = std::min(cap, std::max(1, num_kb / 8));  // at least 8 k-blocks per split
+    if (bytes_per_split > 0) cap = static_cast<int>(std::min<size_t>(cap, std::max<size_t>(1, (ctx->ws_limit / 2) / bytes_per_split)));
+    if (ctx->max_splits > 0) return std::max(1, cap);
+    int best = 1;
+    double best_eff = 0.0;
+    for (int s = 1; s <= cap; ++s) {
+        const long long items = tiles * s;
+        const long long waves = (items + sms - 1) / sms;
+        const double eff = double(items) / double(waves * sms);
+        if (eff > best_eff + 0.04) {  // take a larger split only for a real gain in SM occupancy
+            best_eff = eff;
+            best = s;
+        }
+    }
+    return best;
+}
+
+int run_gemm(gptb200_ctx *ctx, const GemmCall &c)
+{
+    if (c.M == 0 || c.N == 0) return GPTB200_OK;
+    const long long lda = c.a_mn ? c.M : c.K;
+    const long long ldb = c.b_mn ? c.N : c.K;
+    const bool tma_ok = c.K > 0 && aligned16(c.a) && aligned16(c.b) && aligned16(c.out) && (!c.act || aligned16(c.act)) &&
+                        (lda % 4 == 0) && (ldb % 4 == 0) && (c.N % 4 == 0) && !(c.a_mn && !c.b_mn);
+    if (!tma_ok) {
+        // Plain SIMT kernel for the shapes TMA cannot address.
+        const long long a_rs = c.a_mn ? 1 : c.K, a_cs = c.a_mn ? c.M : 1;
+        const long long b_rs = c.b_mn ? c.N : 1, b_cs = c.b_mn ? 1 : c.K;
+        dim3 block(32, 8);
+        dim3 grid((c.N + 31) / 32, (c.M + 31) / 32);
+        simt_gemm_kernel<<<grid, block, 0, ctx->stream>>>(c.M, c.N, c.K, c.a, a_rs, a_cs, c.b, b_rs, b_cs, c.out, c.act, c.bias, c.N,
+                                                          c.accumulate ? EPI_ACCUM : EPI_STORE);
+        ctx->launches++;
+        CUDA_TRY(ctx, cudaGetLastError());
+        return GPTB200_OK;
+    }
+
+    const bool x3 = ctx->mode == GPTB200_MODE_3XTF32;
+    int bn = ctx->tile_n;
+    if (bn != 128 && bn != 256) {
+        const long long tiles256 = 1LL * ((c.M + kBM - 1) / kBM) * ((c.N + 255) / 256);
+        bn = (c.N <= 128 || tiles256 < ctx->num_sms / 2) ? 128 : 256;
+    }
+
+    GemmParams p{};
+    p.M = c.M;
+    p.N = c.N;
+    p.K = c.K;
+    p.tiles_m = (c.M + kBM - 1) / kBM;
+    p.tiles_n = (c.N + bn - 1) / bn;
+    p.num_kb = (c.K + kBK - 1) / kBK;
+    p.status = ctx->d_status;
+    const long long tiles = 1LL * p.tiles_m * p.tiles_n;
+    const bool split_allowed = !c.bias && !c.act;
+    const size_t bytes_per_split = size_t(c.M) * size_t(c.N) * sizeof(float);
+    int splits = pick_splits(ctx, tiles, p.num_kb, split_allowed, bytes_per_split);
+    p.kb_per_split = (p.num_kb + splits - 1) / splits;
+    splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
+    p.splits = splits;
+
+    if (splits > 1) {
+        const int rc = ensure_workspace(ctx, bytes_per_split * splits);
+        if (rc != GPTB200_OK) return rc;
+        p.out = ctx->ws;
+        p.act = nullptr;
+        p.bias = nullptr;
+        p.ldo = c.N;
+        p.epi_mode = EPI_PARTIAL;
+    } else {
+        p.out = c.out;
+        p.act = c.act;
+        p.bias = c.bias;
+        p.ldo = c.N;
+        p.epi_mode = c.accumulate ? EPI_ACCUM : EPI_STORE;
+    }
+
+    CUtensorMap ta, tb;
+    int rc;
+    if (c.a_mn)
+        rc = make_tmap(ctx, &ta, c.a, c.K, c.M, 32, kBK);
+    else
+        rc = make_tmap(ctx, &ta, c.a, c.M, c.K, kBK, kBM);
+    if (rc != GPTB200_OK) return rc;
+    if (c.b_mn)
+        rc = make_tmap(ctx, &tb, c.b, c.K, c.N, 32, kBK);
+    else
+        rc = make_tmap(ctx, &tb, c.b, c.N, c.K, kBK, bn);
+    if (rc != GPTB200_OK) return rc;
+
+    const long long items = tiles * splits;
+    const int grid = static_cast<int>(std::min<long long>(items, ctx->num_sms));
+    cudaError_t e;
+    if (bn == 256)
+        e = x3 ? launch_majors<256, true>(ctx, c.a_mn, c.b_mn, ta, tb, p, grid) : launch_majors<256, false>(ctx, c.a_mn, c.b_mn, ta, tb, p, grid);
+    else
+        e = x3 ? launch_majors<128, true>(ctx, c.a_mn, c.b_mn, ta, tb, p, grid) : launch_majors<128, false>(ctx, c.a_mn, c.b_mn, ta, tb, p, grid);
+    ctx->launches++;
+    CUDA_TRY(ctx, e);
+
+    if (splits > 1) {
+        const long long n4 = (1LL * c.M * c.N) >> 2;
+        const int blocks = static_cast<int>(std::min<long long>((n4 + 255) / 256, 1LL * ctx->num_sms * 8));
+        splitk_reduce_kernel<<<blocks, 256, 0, ctx->stream>>>(c.out, ctx->ws, n4, splits, c.accumulate ? 1 : 0);
+        ctx->launches++;
+        CUDA_TRY(ctx, cudaGetLastError());
+    }
+    return GPTB200_OK;
+}
+
+int run_bias_grad(gptb200_ctx *ctx, float *gb, const float *gy, int M, int N)
+{
+    if (M == 0 || N == 0) return GPTB200_OK;
+    const int col_groups = (N + 31) / 32;
+    int chunks = std::max(1, std::min((ctx->num_sms * 6 + col_groups - 1) / col_groups, (M + 63) / 64));
+    chunks = std::min(chunks, 65535);
+    const int rows_per_chunk = (M + chunks - 1) / chunks;
+    chunks = (M + rows_per_chunk - 1) / rows_per_chunk;
+    const int rc = ensure_workspace(ctx, size_t(chunks) * N * sizeof(float));
+    if (rc != GPTB200_OK) return rc;
+    bias_grad_partial_kernel<<<dim3(col_groups, chunks), dim3(32, 8), 0, ctx->stream>>>(ctx->ws, gy, M, N, rows_per_chunk);
+    ctx->launches++;
+    CUDA_TRY(ctx, cudaGetLastError());
+    bias_grad_final_kernel<<<(N + 127) / 128, 128, 0, ctx->stream>>>(gb, ctx->ws, N, chunks);
+    ctx->launches++;
+    CUDA_TRY(ctx, cudaGetLastError());
+    return GPTB200_OK;
+}
+
+int check_dims(gptb200_ctx *ctx, int m, int a, int b)
+{
+    if (!ctx) return GPTB200_ERR_INVALID_ARG;
+    if (m < 0 || a < 0 || b < 0) return fail(ctx, GPTB200_ERR_INVALID_ARG, "negative dimension (%d, %d, %d)", m, a, b);
+    // The reference indexes with int (src/backend/common/tensor_utils.h:3-5); keep its m*n < 2^31 limit explicit.
+    if (1LL * m * a > 0x7fffffffLL || 1LL * m * b > 0x7fffffffLL || 1LL * a * b > 0x7fffffffLL)
+        return fail(ctx, GPTB200_ERR_INVALID_ARG, "tensor with more than 2^31-1 elements (%d, %d, %d)", m, a, b);
+    return GPTB200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *gptb200_status_string(int status)
+{
+    switch (status) {
+        case GPTB200_OK: return "ok";
+        case GPTB200_ERR_INVALID_ARG: return "invalid argument";
+        case GPTB200_ERR_CUDA: return "CUDA call failed";
+        case GPTB200_ERR_NO_DEVICE: return "no sm_100 device";
+        case GPTB200_ERR_DEVICE_TIMEOUT: return "bounded wait inside a kernel ran out";
+        case GPTB200_ERR_WORKSPACE: return "scratch request beyond limit";
+        case GPTB200_ERR_TOO_LARGE: return "size beyond the entry point's maximum";
+        default: return "unknown status";
+    }
+}
+
+const char *gptb200_last_error(const gptb200_ctx *ctx) { return ctx ? ctx->last_error : "null context"; }
+
+int gptb200_ctx_create(gptb200_ctx **out, int device, void *cuda_stream, int mode)
+{
+    if (!out) return GPTB200_ERR_INVALID_ARG;
+    *out = nullptr;
+    if (mode != GPTB200_MODE_3XTF32 && mode != GPTB200_MODE_TF32) return GPTB200_ERR_INVALID_ARG;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) return GPTB200_ERR_NO_DEVICE;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return GPTB200_ERR_CUDA;
+    if (prop.major != 10) return GPTB200_ERR_NO_DEVICE;
+    if (cudaSetDevice(device) != cudaSuccess) return GPTB200_ERR_CUDA;
+
+    gptb200_ctx *ctx = new gptb200_ctx();
+    ctx->device = device;
+    ctx->stream = static_cast<cudaStream_t>(cuda_stream);
+    ctx->mode = mode;
+    ctx->num_sms = prop.multiProcessorCount;
+
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn ||
+        qres != cudaDriverEntryPointSuccess) {
+        delete ctx;
+        return GPTB200_ERR_CUDA;
+    }
+    ctx->encode = reinterpret_cast<EncodeTiledFn>(fn);
+    if (cudaMalloc(&ctx->d_status, sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_status, 0, sizeof(int)) != cudaSuccess) {
+        delete ctx;
+        return GPTB200_ERR_CUDA;
+    }
+    *out = ctx;
+    return GPTB200_OK;
+}
+
+int gptb200_ctx_destroy(gptb200_ctx *ctx)
+{
+    if (!ctx) return GPTB200_ERR_INVALID_ARG;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    if (ctx->ws) cudaFree(ctx->ws);
+    if (ctx->d_status) cudaFree(ctx->d_status);
+    delete ctx;
+    return GPTB200_OK;
+}
+
+int gptb200_ctx_set_mode(gptb200_ctx *ctx, int mode)
+{
+    if (!ctx || (mode != GPTB200_MODE_3XTF32 && mode != GPTB200_MODE_TF32)) return GPTB200_ERR_INVALID_ARG;
+    ctx->mode = mode;
+    return GPTB200_OK;
+}
+
+int gptb200_ctx_get_mode(const gptb200_ctx *ctx) { return ctx ? ctx->mode : -1; }
+
+int gptb200_ctx_set_stream(gptb200_ctx *ctx, void *cuda_stream)
+{
+    if (!ctx) return GPTB200_ERR_INVALID_ARG;
+    ctx->stream = static_cast<cudaStream_t>(cuda_stream);
+    return GPTB200_OK;
+}
+
+int gptb200_ctx_set_option(gptb200_ctx *ctx, const char *key, int value)
+{
+    if (!ctx || !key) return GPTB200_ERR_INVALID_ARG;
+    if (!strcmp(key, "tile_n")) {
+        if (value != 0 && value != 128 && value != 256) return fail(ctx, GPTB200_ERR_INVALID_ARG, "tile_n must be 0, 128 or 256");
+        ctx->tile_n = value;
+        return GPTB200_OK;
+    }
+    if (!strcmp(key, "max_splits")) {
+        if (value < 0 || value > 64) return fail(ctx, GPTB200_ERR_INVALID_ARG, "max_splits must be in [0, 64]");
+        ctx->max_splits = value;
+        return GPTB200_OK;
+    }
+    return fail(ctx, GPTB200_ERR_INVALID_ARG, "unknown option '%s'", key);
+}
+
+int gptb200_ctx_synchronize(gptb200_ctx *ctx)
+{
+    if (!ctx) return GPTB200_ERR_INVALID_ARG;
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    int st = 0;
+    CUDA_TRY(ctx, cudaMemcpy(&st, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (st != 0) {
+        cudaMemset(ctx->d_status, 0, sizeof(int));
+        return fail(ctx, GPTB200_ERR_DEVICE_TIMEOUT, "device status %d: a bounded wait inside a kernel ran out", st);
+    }
+    return GPTB200_OK;
+}
+
+long long gptb200_ctx_launch_count(const gptb200_ctx *ctx) { return ctx ? ctx->launches : -1; }
+
+int gptb200_linear_forward(gptb200_ctx *ctx, float *y, float *act, const float *x, const float *w, const float *b, int activation,
+                           int m, int k, int n)
+{
+    int rc = check_dims(ctx, m, k, n);
+    if (rc) return rc;
+    if (m == 0 || n == 0) return GPTB200_OK;
+    if (!y || !x || !w || !b || (activation && !act)) return fail(ctx, GPTB200_ERR_INVALID_ARG, "null tensor pointer");
+    GemmCall c{m, n, k, x, false, w, true, y, activation ? act : nullptr, b, false};
+    return run_gemm(ctx, c);
+}
+
+int gptb200_linear_backward(gptb200_ctx *ctx, float *grad_x, float *grad_w, float *grad_b, const float *grad_y, const float *x,
+                            const float *w, int m, int k, int n)
+{
+    int rc = check_dims(ctx, m, k, n);
+    if (rc) return rc;
+    if (!grad_x || !grad_w || !grad_b || !grad_y || !x || !w) return fail(ctx, GPTB200_ERR_INVALID_ARG, "null tensor pointer");
+    // grad_x[m x k] = grad_y[m x n] . w^T : A = grad_y (K-major), B = w stored [k x n] = [N' x K'] (K-major)
+    if (m > 0 && k > 0) {
+        if (n == 0) {
+            CUDA_TRY(ctx, cudaMemsetAsync(grad_x, 0, size_t(m) * k * sizeof(float), ctx->stream));
+        } else {
+            GemmCall dx{m, k, n, grad_y, false, w, false, grad_x, nullptr, nullptr, false};
+            rc = run_gemm(ctx, dx);
+            if (rc) return rc;
+        }
+    }
+    // grad_w[k x n] += x^T . grad_y : A = x stored [m x k] = [K' x M'] (MN-major), B = grad_y [m x n] = [K' x N'] (MN-major)
+    if (m > 0 && k > 0 && n > 0) {
+        GemmCall dw{k, n, m, x, true, grad_y, true, grad_w, nullptr, nullptr, true};
+        rc = run_gemm(ctx, dw);
+        if (rc) return rc;
+    }
+    return run_bias_grad(ctx, grad_b, grad_y, m, n);
+}
+
+int gptb200_gelu_backward(gptb200_ctx *ctx, float *grad_x, const float *grad_y, const float *x, int m, int n)
+{
+    int rc = check_dims(ctx, m, n, 1);
+    if (rc) return rc;
+    const long long total = 1LL * m * n;
+    if (total == 0) return GPTB200_OK;
+    if (!grad_x || !grad_y || !x) return fail(ctx, GPTB200_ERR_INVALID_ARG, "null tensor pointer");
+    const int blocks = static_cast<int>(std::min<long long>((total / 4 + 255) / 256 + 1, 1LL * ctx->num_sms * 16));
+    gelu_backward_kernel<<<blocks, 256, 0, ctx->stream>>>(grad_x, grad_y, x, total);
+    ctx->launches++;
+    CUDA_TRY(ctx, cudaGetLastError());
+    return GPTB200_OK;
+}
+
+int gptb200_unembed_forward(gptb200_ctx *ctx, float *y, const float *x, const float *wte, int m, int d, int vp)
+{
+    int rc = check_dims(ctx, m, d, vp);
+    if (rc) return rc;
+    if (m == 0 || vp == 0) return GPTB200_OK;
+    if (!y || !x || !wte) return fail(ctx, GPTB200_ERR_INVALID_ARG, "null tensor pointer");
+    if (d == 0) {
+        CUDA_TRY(ctx, cudaMemsetAsync(y, 0, size_t(m) * vp * sizeof(float), ctx->stream));
+        return GPTB200_OK;
+    }
+    // y[m x vp] = x[m x d] . wte^T : A = x (K-major), B = wte stored [vp x d] = [N' x K'] (K-major)
+    GemmCall c{m, vp, d, x, false, wte, false, y, nullptr, nullptr, false};
+    return run_gemm(ctx, c);
+}
+
+int gptb200_unembed_backward(gptb200_ctx *ctx, float *grad_x, float *grad_wte, const float *grad_y, const float *x, const float *wte,
+                             int m, int d, int vp)
+{
+    int rc = check_dims(ctx, m, d, vp);
+    if (rc) return rc;
+    if (!grad_x || !grad_wte || !grad_y || !x || !wte) return fail(ctx, GPTB200_ERR_INVALID_ARG, "null tensor pointer");
+    if (m == 0 || d == 0) return GPTB200_OK;
+    if (vp == 0) {
+        CUDA_TRY(ctx, cudaMemsetAsync(grad_x, 0, size_t(m) * d * sizeof(float), ctx->stream));
+        return GPTB200_OK;
+    }
+    // grad_x[m x d] = grad_y[m x vp] . wte : A = grad_y (K-major), B = wte stored [vp x d] = [K' x N'] (MN-major)
+    GemmCall dx{m, d, vp, grad_y, false, wte, true, grad_x, nullptr, nullptr, false};
+    rc = run_gemm(ctx, dx);
+    if (rc) return rc;
+    // grad_wte[vp x d] += grad_y^T . x : A = grad_y stored [m x vp] = [K' x M'] (MN-major), B = x [m x d] = [K' x N'] (MN-major)
+    GemmCall dw{vp, d, m, grad_y, true, x, true, grad_wte, nullptr, nullptr, true};
+    return run_gemm(ctx, dw);
+}
+
+int gptb200_malloc(gptb200_ctx *ctx, void **ptr, size_t bytes)
+{
+    if (!ctx || !ptr) return GPTB200_ERR_INVALID_ARG;
+    CUDA_TRY(ctx, cudaMalloc(ptr, bytes));
+    return GPTB200_OK;
+}
+
+int gptb200_free(gptb200_ctx *ctx, void *ptr)
+{
+    if (!ctx) return GPTB200_ERR_INVALID_ARG;
+    CUDA_TRY(ctx, cudaFree(ptr));
+    return GPTB200_OK;
+}
+
+int gptb200_memset(gptb200_ctx *ctx, void *ptr, int value, size_t bytes)
+{
+    if (!ctx) return GPTB200_ERR_INVALID_ARG;
+    CUDA_TRY(ctx, cudaMemsetAsync(ptr, value, bytes, ctx->stream));
+    return GPTB200_OK;
+}
+
+int gptb200_memcpy_h2d(gptb200_ctx *ctx, void *dst, const void *src, size_t bytes)
+{
+    if (!ctx) return GPTB200_ERR_INVALID_ARG;
+    CUDA_TRY(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    return GPTB200_OK;
+}
+
+int gptb200_memcpy_d2h(gptb200_ctx *ctx, void *dst, const void *src, size_t bytes)
+{
+    if (!ctx) return GPTB200_ERR_INVALID_ARG;
+    CUDA_TRY(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    return GPTB200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,399 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a:  D[M x N] = A[M x K] * B[K x N], fp32 in HBM,
+// TF32 tensor-core math with fp32 accumulation in TMEM.
+//
+// One kernel covers the six GEMM forms of the linear layers.  Each operand is described by the way it
+// is *stored* (row-major, last dimension contiguous):
+//   K-major  operand: the reduction index is the contiguous one   (x in y = x.w, grad_y in grad_x = grad_y.w^T, wte in logits = x.wte^T)
+//   MN-major operand: the free (M or N) index is the contiguous one (w in y = x.w, both operands of grad_w += x^T.grad_y)
+// so no operand is ever transposed in memory: the UMMA shared-memory descriptors express the major-ness.
+//
+// Roles per CTA (one CTA per SM, static round-robin over work items):
+//   warp 0      TMA producer: fills a STAGES-deep ring of 128-byte-swizzled operand tiles
+//   warp 1      MMA issuer (one thread): tcgen05.mma kind::tf32 into a double-buffered TMEM accumulator
+//   warps 2-5   epilogue: tcgen05.ld, bias / GELU / accumulate, stores to HBM (overlaps the next tile's main loop)
+//   warps 6-9   (3xTF32 only) split each landed tile into its low-order part  lo = a - trunc_tf32(a)
+//
+// 3xTF32: the tensor core reads only the top 19 bits of an fp32 word, so the raw tile *is* the high
+// part; the converter warps write the low parts at the same (swizzled) offsets in a second buffer and the
+// MMA thread issues  lo.hi + hi.lo + hi.hi  per k-step.
+#pragma once
+
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "ptx_sm100.cuh"
+
+namespace gptb200 {
+
+// Device status codes written (first writer wins) to the context's status word.
+enum DeviceStatus : int {
+    DEV_OK = 0,
+    DEV_TIMEOUT_PRODUCER = 101,   // producer gave up waiting for a free stage
+    DEV_TIMEOUT_MMA_FULL = 102,   // MMA thread gave up waiting for a landed stage
+    DEV_TIMEOUT_MMA_CONV = 103,   // MMA thread gave up waiting for the low-part tiles
+    DEV_TIMEOUT_MMA_TMEM = 104,   // MMA thread gave up waiting for a drained accumulator
+    DEV_TIMEOUT_EPILOGUE = 105,   // epilogue gave up waiting for a finished accumulator
+    DEV_TIMEOUT_CONVERT = 106,    // converter gave up waiting for a landed stage
+    DEV_TIMEOUT_DRAIN = 107,      // teardown gave up waiting for outstanding MMAs
+};
+
+enum EpilogueMode : int {
+    EPI_STORE = 0,    // out = acc (+ bias); optionally act = gelu_tanh(out)
+    EPI_ACCUM = 1,    // out += acc
+    EPI_PARTIAL = 2,  // workspace[split] = acc   (reduced by splitk_reduce_kernel)
+};
+
+struct GemmParams {
+    int M, N, K;         // D[M x N] = A[M x K] . B[K x N]
+    float *out;          // EPI_STORE / EPI_ACCUM: [M x N] with row pitch ldo; EPI_PARTIAL: workspace [splits][M][N]
+    float *act;          // optional second output (GELU of out), same pitch
+    const float *bias;   // optional [N]
+    long long ldo;       // row pitch of out / act in elements
+    int tiles_m, tiles_n;
+    int splits;          // split-K factor (1 = none)
+    int kb_per_split;    // k-blocks (of 32) per split
+    int num_kb;          // ceil(K / 32)
+    int epi_mode;
+    int *status;         // device status word
+};
+
+constexpr int kBM = 128;
+constexpr int kBK = 32;                       // 32 fp32 = one 128-byte swizzle row
+constexpr int kUmmaK = 8;                     // K per tcgen05.mma kind::tf32
+constexpr int kATileBytes = kBM * kBK * 4;    // 16 KiB
+constexpr int kBoxBytesMN = kBK * 32 * 4;     // one [32 k-rows x 32 floats] box of an MN-major operand
+constexpr int kNumEpilogueWarps = 4;
+constexpr int kNumConvertWarps = 4;
+constexpr long long kWaitTimeoutCycles = 2000000000LL;  // about one second
+
+template <int BN, bool X3>
+struct GemmSmem {
+    static constexpr int kBTileBytes = BN * kBK * 4;
+    static constexpr int kHiBytes = kATileBytes + kBTileBytes;
+    static constexpr int kStageBytes = X3 ? 2 * kHiBytes : kHiBytes;
+};
+
+template <int BN, int STAGES, bool X3>
+constexpr int gemm_smem_bytes()
+{
+    // tiles (1024-aligned) + barriers + slack for manual alignment
+    return STAGES * GemmSmem<BN, X3>::kStageBytes + 1024 + 256;
+}
+
+__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, int *status, int code)
+{
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (true) {
+        if (ptx::mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 31u) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > kWaitTimeoutCycles) {
+                *abort_flag = 1u;
+                atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+// GELU (tanh form) written as x * sigmoid(2u), u = 0.79788456 (x + 0.044715 x^3):
+// identical to 0.5 x (1 + tanh u) and needs one exp and one divide.
+__device__ __forceinline__ float gelu_tanh(float x)
+{
+    const float u = 0.79788456f * (x + 0.044715f * x * x * x);
+    return x / (1.0f + __expf(-2.0f * u));
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool X3>
+__global__ void __launch_bounds__((2 + kNumEpilogueWarps + (X3 ? kNumConvertWarps : 0)) * 32, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p)
+{
+    using S = GemmSmem<BN, X3>;
+    constexpr int kTmemCols = 2 * BN;  // two accumulator buffers (power of two: 256 or 512)
+    constexpr int kBoxesA = A_MN ? kBM / 32 : 1;
+    constexpr int kBoxesB = B_MN ? BN / 32 : 1;
+    constexpr uint32_t kIdesc = ptx::make_idesc_tf32(kBM, BN, A_MN, B_MN);
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+
+    // barrier block sits after the tile ring
+    const uint32_t bar_base = smem_base + STAGES * S::kStageBytes;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto conv_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
+    auto tmem_full_bar = [&](int b) { return bar_base + 8u * (3 * STAGES + b); };
+    auto tmem_empty_bar = [&](int b) { return bar_base + 8u * (3 * STAGES + 2 + b); };
+    const uint32_t drain_bar = bar_base + 8u * (3 * STAGES + 4);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_gen + STAGES * S::kStageBytes + 8 * (3 * STAGES + 5));
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(full_bar(s), 1);
+            ptx::mbar_init(empty_bar(s), 1);
+            ptx::mbar_init(conv_bar(s), kNumConvertWarps * 32);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(tmem_full_bar(b), 1);
+            ptx::mbar_init(tmem_empty_bar(b), kNumEpilogueWarps * 32);
+        }
+        ptx::mbar_init(drain_bar, 1);
+        *abort_flag = 0u;
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&tmap_a);
+        ptx::prefetch_tensormap(&tmap_b);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const long long num_items = 1LL * p.tiles_m * p.tiles_n * p.splits;
+
+    auto decode = [&](long long w, int &tm, int &tn, int &kb0, int &kb1, int &split) {
+        tm = static_cast<int>(w % p.tiles_m);
+        const long long r = w / p.tiles_m;
+        tn = static_cast<int>(r % p.tiles_n);
+        split = static_cast<int>(r / p.tiles_n);
+        kb0 = split * p.kb_per_split;
+        kb1 = min(kb0 + p.kb_per_split, p.num_kb);
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        uint32_t it = 0;
+        bool ok = true;
+        for (long long w = blockIdx.x; ok && w < num_items; w += gridDim.x) {
+            int tm, tn, kb0, kb1, split;
+            decode(w, tm, tn, kb0, kb1, split);
+            const int m0 = tm * kBM, n0 = tn * BN;
+            for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                const int s = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1u;
+                if (!bounded_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) {
+                    ok = false;
+                    break;
+                }
+                if (lane == 0) ptx::mbar_arrive_expect_tx(full_bar(s), S::kHiBytes);
+                __syncwarp();
+                const uint32_t a_dst = smem_base + s * S::kStageBytes;
+                const uint32_t b_dst = a_dst + kATileBytes;
+                const int k0 = kb * kBK;
+                if (lane < kBoxesA) {
+                    if (A_MN)
+                        ptx::tma_load_2d(a_dst + lane * kBoxBytesMN, &tmap_a, m0 + 32 * lane, k0, full_bar(s));
+                    else
+                        ptx::tma_load_2d(a_dst, &tmap_a, k0, m0, full_bar(s));
+                } else if (lane < kBoxesA + kBoxesB) {
+                    const int j = lane - kBoxesA;
+                    if (B_MN)
+                        ptx::tma_load_2d(b_dst + j * kBoxBytesMN, &tmap_b, n0 + 32 * j, k0, full_bar(s));
+                    else
+                        ptx::tma_load_2d(b_dst, &tmap_b, k0, n0, full_bar(s));
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            uint32_t it = 0;
+            uint32_t t = 0;
+            bool ok = true;
+            for (long long w = blockIdx.x; ok && w < num_items; w += gridDim.x, ++t) {
+                int tm, tn, kb0, kb1, split;
+                decode(w, tm, tn, kb0, kb1, split);
+                const uint32_t buf = t & 1u;
+                const uint32_t use = (t >> 1) & 1u;
+                if (!bounded_wait(tmem_empty_bar(buf), use ^ 1u, abort_flag, p.status, DEV_TIMEOUT_MMA_TMEM)) {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                uint32_t accumulate = 0;
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    if (!bounded_wait(full_bar(s), ph, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL)) {
+                        ok = false;
+                        break;
+                    }
+                    if (X3) {
+                        if (!bounded_wait(conv_bar(s), ph, abort_flag, p.status, DEV_TIMEOUT_MMA_CONV)) {
+                            ok = false;
+                            break;
+                        }
+                    }
+                    ptx::tc_fence_after();
+                    const uint32_t a_hi = smem_base + s * S::kStageBytes;
+                    const uint32_t b_hi = a_hi + kATileBytes;
+                    const uint32_t a_lo = a_hi + S::kHiBytes;
+                    const uint32_t b_lo = b_hi + S::kHiBytes;
+#pragma unroll
+                    for (int k = 0; k < kBK / kUmmaK; ++k) {
+                        // K-major: a k-step is 32 bytes along the swizzled row; 8-row groups are 1024 B apart.
+                        // MN-major: a k-step is 8 rows of 128 B; 32-float column groups are one 4 KiB box apart.
+                        const uint32_t a_off = A_MN ? k * 1024 : k * 32;
+                        const uint32_t b_off = B_MN ? k * 1024 : k * 32;
+                        const uint32_t a_lbo = A_MN ? kBoxBytesMN : 16;
+                        const uint32_t b_lbo = B_MN ? kBoxBytesMN : 16;
+                        const uint64_t da_hi = ptx::make_smem_desc_sw128(a_hi + a_off, a_lbo, 1024);
+                        const uint64_t db_hi = ptx::make_smem_desc_sw128(b_hi + b_off, b_lbo, 1024);
+                        if (X3) {
+                            const uint64_t da_lo = ptx::make_smem_desc_sw128(a_lo + a_off, a_lbo, 1024);
+                            const uint64_t db_lo = ptx::make_smem_desc_sw128(b_lo + b_off, b_lbo, 1024);
+                            ptx::mma_tf32_ss(d_tmem, da_lo, db_hi, kIdesc, accumulate);
+                            ptx::mma_tf32_ss(d_tmem, da_hi, db_lo, kIdesc, 1u);
+                            ptx::mma_tf32_ss(d_tmem, da_hi, db_hi, kIdesc, 1u);
+                        } else {
+                            ptx::mma_tf32_ss(d_tmem, da_hi, db_hi, kIdesc, accumulate);
+                        }
+                        accumulate = 1u;
+                    }
+                    ptx::mma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
+                }
+                if (ok) ptx::mma_commit(tmem_full_bar(buf));
+            }
+            // Do not leave with MMAs still running: they write TMEM that is about to be released.
+            ptx::mma_commit(drain_bar);
+            bounded_wait(drain_bar, 0u, abort_flag, p.status, DEV_TIMEOUT_DRAIN);
+        }
+        __syncwarp();
+    } else if (warp < 2 + kNumEpilogueWarps) {
+        // ------------------------------------------------------------ epilogue
+        const int q = warp & 3;  // TMEM lane quarter this warp may read
+        uint32_t t = 0;
+        bool ok = true;
+        for (long long w = blockIdx.x; ok && w < num_items; w += gridDim.x, ++t) {
+            int tm, tn, kb0, kb1, split;
+            decode(w, tm, tn, kb0, kb1, split);
+            const uint32_t buf = t & 1u;
+            const uint32_t use = (t >> 1) & 1u;
+            if (!bounded_wait(tmem_full_bar(buf), use, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE)) {
+                ok = false;
+                break;
+            }
+            ptx::tc_fence_after();
+            const long long row = 1LL * tm * kBM + q * 32 + lane;
+            const int n0 = tn * BN;
+            const bool row_ok = row < p.M;
+            float *out = p.out;
+            if (p.epi_mode == EPI_PARTIAL) out += 1LL * split * p.M * p.ldo;
+            float *out_row = out + row * p.ldo;
+            float *act_row = p.act ? p.act + row * p.ldo : nullptr;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                ptx::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + c * 32, v);
+                ptx::tmem_ld_wait();
+                const int col0 = n0 + c * 32;
+                if (row_ok && col0 < p.N) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int col = col0 + 4 * j;
+                        if (col < p.N) {  // N is a multiple of 4 on this path
+                            float4 r = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                   __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                            if (p.epi_mode == EPI_ACCUM) {
+                                const float4 o = *reinterpret_cast<const float4 *>(out_row + col);
+                                r.x += o.x; r.y += o.y; r.z += o.z; r.w += o.w;
+                            } else if (p.bias) {
+                                r.x += __ldg(p.bias + col);
+                                r.y += __ldg(p.bias + col + 1);
+                                r.z += __ldg(p.bias + col + 2);
+                                r.w += __ldg(p.bias + col + 3);
+                            }
+                            *reinterpret_cast<float4 *>(out_row + col) = r;
+                            if (act_row) {
+                                *reinterpret_cast<float4 *>(act_row + col) =
+                                    make_float4(gelu_tanh(r.x), gelu_tanh(r.y), gelu_tanh(r.z), gelu_tanh(r.w));
+                            }
+                        }
+                    }
+                }
+            }
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(tmem_empty_bar(buf));
+        }
+    } else if (X3) {
+        // ------------------------------------------------------------ 3xTF32 converter
+        const int ctid = threadIdx.x - (2 + kNumEpilogueWarps) * 32;
+        uint32_t it = 0;
+        bool ok = true;
+        for (long long w = blockIdx.x; ok && w < num_items; w += gridDim.x) {
+            int tm, tn, kb0, kb1, split;
+            decode(w, tm, tn, kb0, kb1, split);
+            for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                const int s = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1u;
+                if (!bounded_wait(full_bar(s), ph, abort_flag, p.status, DEV_TIMEOUT_CONVERT)) {
+                    ok = false;
+                    break;
+                }
+                const float4 *hi = reinterpret_cast<const float4 *>(smem_gen + s * S::kStageBytes);
+                float4 *lo = reinterpret_cast<float4 *>(smem_gen + s * S::kStageBytes + S::kHiBytes);
+                constexpr int kVec = S::kHiBytes / 16;
+#pragma unroll 4
+                for (int i = ctid; i < kVec; i += kNumConvertWarps * 32) {
+                    const float4 h = hi[i];
+                    float4 l;
+                    l.x = h.x - __uint_as_float(__float_as_uint(h.x) & 0xFFFFE000u);
+                    l.y = h.y - __uint_as_float(__float_as_uint(h.y) & 0xFFFFE000u);
+                    l.z = h.z - __uint_as_float(__float_as_uint(h.z) & 0xFFFFE000u);
+                    l.w = h.w - __uint_as_float(__float_as_uint(h.w) & 0xFFFFE000u);
+                    lo[i] = l;
+                }
+                ptx::fence_proxy_async_smem();
+                ptx::mbar_arrive(conv_bar(s));
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // A wait ran out somewhere: give copies still in flight time to land before the CTA's
+        // shared memory and TMEM are handed to the next CTA.
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// out[i] (+)= sum_s ws[s][i], fixed order s = 0..splits-1 (deterministic split-K reduction).
+__global__ void splitk_reduce_kernel(float *__restrict__ out, const float *__restrict__ ws, long long n4, int splits, int accumulate)
+{
+    const long long stride = 1LL * gridDim.x * blockDim.x;
+    for (long long i = 1LL * blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        float4 acc = reinterpret_cast<const float4 *>(ws)[i];
+        for (int s = 1; s < splits; ++s) {
+            const float4 v = reinterpret_cast<const float4 *>(ws)[1LL * s * n4 + i];
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        float4 *o = reinterpret_cast<float4 *>(out) + i;
+        if (accumulate) {
+            const float4 prev = *o;
+            acc.x += prev.x; acc.y += prev.y; acc.z += prev.z; acc.w += prev.w;
+        }
+        *o = acc;
+    }
+}
+
+}  // namespace gptb200

@@ -1,0 +1,103 @@
+/*
+ * gptb200 -- C ABI of the B200 (sm_100a) replacement for the dense linear-layer path of Filipeak/gpt.
+ *
+ * The reference routes these operators through a cuBLAS handle owned by its CUDA backend
+ * (src/backend/cuda/core/cuda_backend.cu:4-13, src/backend/cuda/cuda_backend.h:40).  Here the handle is a
+ * gptb200_ctx; each operator of the reference's IGPTBackend that belongs to the linear path has one entry
+ * point with the same tensor meaning, the same overwrite/accumulate behaviour and plain pointers + ints.
+ *
+ * Conventions (same as the reference's interface, src/backend/backend_interface.h):
+ *   - every tensor is fp32, row-major, last dimension contiguous, and lives in device memory owned by
+ *     the caller; no operator allocates, frees or aliases caller memory;
+ *   - `m` is batch_size * seq_len (the reference only ever uses the product);
+ *   - y / act / grad_x are overwritten; grad_w / grad_b / grad_wte are accumulated into (+=);
+ *   - operators are enqueued on the context's stream and return without waiting for the GPU;
+ *   - every function returns 0 on success or a gptb200_status code; nothing aborts the process.
+ *
+ * There is no cuBLAS and no CPU fallback behind these calls.
+ */
+#ifndef GPTB200_H
+#define GPTB200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct gptb200_ctx gptb200_ctx;
+
+typedef enum gptb200_status {
+    GPTB200_OK = 0,
+    GPTB200_ERR_INVALID_ARG = 1,   /* null pointer, negative dimension, m*n overflow */
+    GPTB200_ERR_CUDA = 2,          /* a CUDA runtime / driver call failed; see gptb200_last_error */
+    GPTB200_ERR_NO_DEVICE = 3,     /* no sm_100 device behind the requested ordinal */
+    GPTB200_ERR_DEVICE_TIMEOUT = 4,/* a bounded wait inside a kernel ran out; results are invalid */
+    GPTB200_ERR_WORKSPACE = 5,     /* scratch request beyond the configured limit */
+    GPTB200_ERR_TOO_LARGE = 6      /* size beyond a fixed maximum of the called entry point */
+} gptb200_status;
+
+/* Precision of the tensor-core path.  Replaces cublasSetMathMode(CUBLAS_TF32_TENSOR_OP_MATH)
+ * (src/backend/cuda/core/cuda_backend.cu:7). */
+typedef enum gptb200_mode {
+    GPTB200_MODE_3XTF32 = 0,  /* default: split operands, three MMAs per step, fp32-level accuracy */
+    GPTB200_MODE_TF32 = 1     /* single-pass TF32 */
+} gptb200_mode;
+
+/* ---- context: stands in for cublasCreate / cublasDestroy (cuda_backend.cu:6, :17) ---- */
+int gptb200_ctx_create(gptb200_ctx **out, int device, void *cuda_stream, int mode);
+int gptb200_ctx_destroy(gptb200_ctx *ctx);
+int gptb200_ctx_set_mode(gptb200_ctx *ctx, int mode);
+int gptb200_ctx_get_mode(const gptb200_ctx *ctx);
+int gptb200_ctx_set_stream(gptb200_ctx *ctx, void *cuda_stream);
+/* Tuning knobs, for benchmarking: key "tile_n" (0 = automatic, 128, 256), "max_splits" (0 = automatic). */
+int gptb200_ctx_set_option(gptb200_ctx *ctx, const char *key, int value);
+/* Waits for the context's stream and reports a device-side timeout recorded by any earlier kernel. */
+int gptb200_ctx_synchronize(gptb200_ctx *ctx);
+/* Number of kernels this context has launched so far. */
+long long gptb200_ctx_launch_count(const gptb200_ctx *ctx);
+const char *gptb200_status_string(int status);
+const char *gptb200_last_error(const gptb200_ctx *ctx);
+
+/* ---- IGPTBackend::device_linear_activation_fused_forward
+ *      (backend_interface.h:120-132, cuda/kernels/linear.cu:36-66, cpu/cpu_backend.cpp:213-239)
+ *   y[m x n] = x[m x k] . w[k x n] + b[n];  if activation: act = gelu_tanh(y) and y keeps the pre-activation.
+ *   act may be NULL when activation == 0. */
+int gptb200_linear_forward(gptb200_ctx *ctx, float *y, float *act, const float *x, const float *w, const float *b,
+                           int activation, int m, int k, int n);
+
+/* ---- IGPTBackend::device_linear_backward
+ *      (backend_interface.h:134-148, cuda/kernels/linear.cu:116-159, cpu/cpu_backend.cpp:241-266)
+ *   grad_x[m x k] = grad_y[m x n] . w^T;  grad_w[k x n] += x^T . grad_y;  grad_b[n] += column sums of grad_y. */
+int gptb200_linear_backward(gptb200_ctx *ctx, float *grad_x, float *grad_w, float *grad_b, const float *grad_y,
+                            const float *x, const float *w, int m, int k, int n);
+
+/* ---- IGPTBackend::device_activation_backward
+ *      (backend_interface.h:150-159, cuda/kernels/linear.cu:162-203, cpu/cpu_backend.cpp:268-287)
+ *   grad_x = grad_y * gelu_tanh'(x), all [m x n]. */
+int gptb200_gelu_backward(gptb200_ctx *ctx, float *grad_x, const float *grad_y, const float *x, int m, int n);
+
+/* ---- IGPTBackend::device_unembedding_forward
+ *      (backend_interface.h:42-51, cuda/kernels/embedding.cu:47-63, cpu/cpu_backend.cpp:81-100)
+ *   y[m x vp] = x[m x d] . wte^T, wte is [vp x d] (vp = padded vocabulary). */
+int gptb200_unembed_forward(gptb200_ctx *ctx, float *y, const float *x, const float *wte, int m, int d, int vp);
+
+/* ---- IGPTBackend::device_unembedding_backward
+ *      (backend_interface.h:70-82, cuda/kernels/embedding.cu:140-170, cpu/cpu_backend.cpp:119-140)
+ *   grad_x[m x d] = grad_y[m x vp] . wte;  grad_wte[vp x d] += grad_y^T . x. */
+int gptb200_unembed_backward(gptb200_ctx *ctx, float *grad_x, float *grad_wte, const float *grad_y, const float *x,
+                             const float *wte, int m, int d, int vp);
+
+/* ---- memory operators of IGPTBackend (backend_interface.h:10-24, cuda/core/cuda_memory.cu:4-64) so that a
+ *      host program can drive the whole path through this library: malloc / free / memset / blocking copies. */
+int gptb200_malloc(gptb200_ctx *ctx, void **ptr, size_t bytes);
+int gptb200_free(gptb200_ctx *ctx, void *ptr);
+int gptb200_memset(gptb200_ctx *ctx, void *ptr, int value, size_t bytes);
+int gptb200_memcpy_h2d(gptb200_ctx *ctx, void *dst, const void *src, size_t bytes);
+int gptb200_memcpy_d2h(gptb200_ctx *ctx, void *dst, const void *src, size_t bytes);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* GPTB200_H */

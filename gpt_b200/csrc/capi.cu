@@ -76,14 +76,17 @@ int ensure_workspace(gptb200_ctx *ctx, size_t bytes)
 // One GEMM operand as stored: `rows` x `cols` fp32, row pitch `cols`.
 // K-major operand: rows = free extent (M or N), cols = reduction extent.
 // MN-major operand: rows = reduction extent, cols = free extent.
-int make_tmap(gptb200_ctx *ctx, CUtensorMap *map, const float *base, long long rows, long long cols, int box_cols, int box_rows)
+// `mn_major` picks the shared-memory swizzle the tensor core expects for that major-ness: 16-byte chunks
+// for K-major tiles, 32-byte chunks for MN-major tiles of 32-bit elements.
+int make_tmap(gptb200_ctx *ctx, CUtensorMap *map, const float *base, long long rows, long long cols, int box_cols, int box_rows, bool mn_major)
 {
     cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
     cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * sizeof(float)};
     cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
     cuuint32_t estr[2] = {1, 1};
     const CUresult r = ctx->encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, estr,
-                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(ctx, GPTB200_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) rows=%lld cols=%lld box=%dx%d", int(r), rows, cols, box_rows, box_cols);
@@ -215,14 +218,14 @@ int run_gemm(gptb200_ctx *ctx, const GemmCall &c)
     CUtensorMap ta, tb;
     int rc;
     if (c.a_mn)
-        rc = make_tmap(ctx, &ta, c.a, c.K, c.M, 32, kBK);
+        rc = make_tmap(ctx, &ta, c.a, c.K, c.M, 32, kBK, true);
     else
-        rc = make_tmap(ctx, &ta, c.a, c.M, c.K, kBK, kBM);
+        rc = make_tmap(ctx, &ta, c.a, c.M, c.K, kBK, kBM, false);
     if (rc != GPTB200_OK) return rc;
     if (c.b_mn)
-        rc = make_tmap(ctx, &tb, c.b, c.K, c.N, 32, kBK);
+        rc = make_tmap(ctx, &tb, c.b, c.K, c.N, 32, kBK, true);
     else
-        rc = make_tmap(ctx, &tb, c.b, c.N, c.K, kBK, bn);
+        rc = make_tmap(ctx, &tb, c.b, c.N, c.K, kBK, bn, false);
     if (rc != GPTB200_OK) return rc;
 
     const long long items = tiles * splits;

@@ -244,17 +244,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     const uint32_t b_lo = b_hi + S::kHiBytes;
 #pragma unroll
                     for (int k = 0; k < kBK / kUmmaK; ++k) {
-                        // K-major: a k-step is 32 bytes along the swizzled row; 8-row groups are 1024 B apart.
-                        // MN-major: a k-step is 8 rows of 128 B; 32-float column groups are one 4 KiB box apart.
+                        // K-major tile: rows of 128 B (32 k), 16-byte-chunk swizzle over 8-row atoms of 1024 B;
+                        //   a k-step (8 floats) is 32 bytes along the row, 8-row groups are 1024 B apart (SBO).
+                        // MN-major tile: boxes of [32 k-rows x 32 floats], 32-byte-chunk swizzle over 4-row atoms
+                        //   of 512 B; a k-step is 8 rows = 1024 B, 4-row groups are 512 B apart (SBO) and the
+                        //   32-float column groups are one 4 KiB box apart (LBO).
                         const uint32_t a_off = A_MN ? k * 1024 : k * 32;
                         const uint32_t b_off = B_MN ? k * 1024 : k * 32;
-                        const uint32_t a_lbo = A_MN ? kBoxBytesMN : 16;
-                        const uint32_t b_lbo = B_MN ? kBoxBytesMN : 16;
-                        const uint64_t da_hi = ptx::make_smem_desc_sw128(a_hi + a_off, a_lbo, 1024);
-                        const uint64_t db_hi = ptx::make_smem_desc_sw128(b_hi + b_off, b_lbo, 1024);
+                        constexpr uint32_t a_lbo = A_MN ? kBoxBytesMN : 16, a_sbo = A_MN ? 512 : 1024;
+                        constexpr uint32_t b_lbo = B_MN ? kBoxBytesMN : 16, b_sbo = B_MN ? 512 : 1024;
+                        constexpr uint32_t a_lay = A_MN ? ptx::kLayoutSw128Base32B : ptx::kLayoutSw128;
+                        constexpr uint32_t b_lay = B_MN ? ptx::kLayoutSw128Base32B : ptx::kLayoutSw128;
+                        const uint64_t da_hi = ptx::make_smem_desc(a_hi + a_off, a_lbo, a_sbo, a_lay);
+                        const uint64_t db_hi = ptx::make_smem_desc(b_hi + b_off, b_lbo, b_sbo, b_lay);
                         if (X3) {
-                            const uint64_t da_lo = ptx::make_smem_desc_sw128(a_lo + a_off, a_lbo, 1024);
-                            const uint64_t db_lo = ptx::make_smem_desc_sw128(b_lo + b_off, b_lbo, 1024);
+                            const uint64_t da_lo = ptx::make_smem_desc(a_lo + a_off, a_lbo, a_sbo, a_lay);
+                            const uint64_t db_lo = ptx::make_smem_desc(b_lo + b_off, b_lbo, b_sbo, b_lay);
                             ptx::mma_tf32_ss(d_tmem, da_lo, db_hi, kIdesc, accumulate);
                             ptx::mma_tf32_ss(d_tmem, da_hi, db_lo, kIdesc, 1u);
                             ptx::mma_tf32_ss(d_tmem, da_hi, db_hi, kIdesc, 1u);

@@ -180,17 +180,24 @@ __device__ __forceinline__ void tmem_ld_wait()
 
 // ---------------------------------------------------------------- descriptors
 
-// Shared-memory matrix descriptor, 128-byte swizzle.  Fields are in 16-byte units:
+// Shared-memory matrix descriptor.  Fields are in 16-byte units:
 //   [0,14) start address, [16,30) leading-dimension byte offset, [32,46) stride byte offset,
-//   [46,48) descriptor version (1 on sm_100), [61,64) layout type (2 = 128B swizzle).
-__device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes)
+//   [46,48) descriptor version (1 on sm_100), [61,64) layout type.
+// Layout types used here:
+//   2 = 128-byte swizzle of 16-byte chunks (8-row atoms): K-major operands;
+//   1 = 128-byte swizzle of 32-byte chunks (4-row atoms): the only swizzled layout the tensor core
+//       accepts for MN-major 32-bit operands.
+constexpr uint32_t kLayoutSw128 = 2;
+constexpr uint32_t kLayoutSw128Base32B = 1;
+
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout_type)
 {
     uint64_t d = 0;
     d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu);
     d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
     d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
     d |= static_cast<uint64_t>(1) << 46;
-    d |= static_cast<uint64_t>(2) << 61;
+    d |= static_cast<uint64_t>(layout_type) << 61;
     return d;
 }
 

@@ -107,31 +107,45 @@ struct GemmCall {
     bool accumulate;  // out += result
 };
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, bool X3>
-cudaError_t launch_instance(gptb200_ctx *ctx, const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, int grid)
+template <int BN, bool A_MN, bool B_MN, bool X3>
+cudaError_t launch_instance(gptb200_ctx *ctx, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &to, const CUtensorMap &tact,
+                            const GemmParams &p, int grid)
 {
-    constexpr int smem = gemm_smem_bytes<BN, STAGES, X3>();
-    constexpr int threads = (2 + kNumEpilogueWarps + (X3 ? kNumConvertWarps : 0)) * 32;
-    auto kernel = gemm_tcgen05_kernel<BN, STAGES, A_MN, B_MN, X3>;
+    using C = GemmCfg<BN, X3>;
+    auto kernel = gemm_tcgen05_kernel<BN, A_MN, B_MN, X3>;
     const void *key = reinterpret_cast<const void *>(kernel);
     if (!ctx->configured.count(key)) {  // the attribute is per device, the context is bound to one device
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
         if (e != cudaSuccess) return e;
         ctx->configured.insert(key);
     }
-    kernel<<<grid, threads, smem, ctx->stream>>>(ta, tb, p);
+    kernel<<<grid, C::kThreads, C::kSmemBytes, ctx->stream>>>(ta, tb, to, tact, p);
     return cudaGetLastError();
 }
 
 template <int BN, bool X3>
-cudaError_t launch_majors(gptb200_ctx *ctx, bool a_mn, bool b_mn, const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, int grid)
+cudaError_t launch_majors(gptb200_ctx *ctx, bool a_mn, bool b_mn, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &to,
+                          const CUtensorMap &tact, const GemmParams &p, int grid)
 {
-    // Ring depth: as many stages as fit in 227 KiB of shared memory.
-    constexpr int STAGES = X3 ? (BN == 256 ? 2 : 3) : (BN == 256 ? 4 : 6);
-    if (!a_mn && b_mn) return launch_instance<BN, STAGES, false, true, X3>(ctx, ta, tb, p, grid);
-    if (!a_mn && !b_mn) return launch_instance<BN, STAGES, false, false, X3>(ctx, ta, tb, p, grid);
-    if (a_mn && b_mn) return launch_instance<BN, STAGES, true, true, X3>(ctx, ta, tb, p, grid);
+    if (!a_mn && b_mn) return launch_instance<BN, false, true, X3>(ctx, ta, tb, to, tact, p, grid);
+    if (!a_mn && !b_mn) return launch_instance<BN, false, false, X3>(ctx, ta, tb, to, tact, p, grid);
+    if (a_mn && b_mn) return launch_instance<BN, true, true, X3>(ctx, ta, tb, to, tact, p, grid);
     return cudaErrorInvalidValue;  // (MN, K) does not occur on this path
+}
+
+// Output tensor [depth][rows][cols] (depth > 1 only for split-K partial tiles), written in
+// [32 x 32] pieces from 128-byte-swizzled staging tiles.
+int make_out_tmap(gptb200_ctx *ctx, CUtensorMap *map, float *base, long long depth, long long rows, long long cols)
+{
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(depth)};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(cols) * sizeof(float), static_cast<cuuint64_t>(rows) * cols * sizeof(float)};
+    cuuint32_t box[3] = {32, 32, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = ctx->encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(ctx, GPTB200_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed (%d) depth=%lld rows=%lld cols=%lld", int(r), depth, rows, cols);
+    return GPTB200_OK;
 }
 
 int pick_splits(const gptb200_ctx *ctx, long long tiles, int num_kb, bool allowed, size_t bytes_per_split)
@@ -199,24 +213,29 @@ int run_gemm(gptb200_ctx *ctx, const GemmCall &c)
     splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
     p.splits = splits;
 
+    float *out_base = c.out;
     if (splits > 1) {
         const int rc = ensure_workspace(ctx, bytes_per_split * splits);
         if (rc != GPTB200_OK) return rc;
-        p.out = ctx->ws;
-        p.act = nullptr;
+        out_base = ctx->ws;
+        p.has_act = 0;
         p.bias = nullptr;
-        p.ldo = c.N;
         p.epi_mode = EPI_PARTIAL;
     } else {
-        p.out = c.out;
-        p.act = c.act;
+        p.has_act = c.act ? 1 : 0;
         p.bias = c.bias;
-        p.ldo = c.N;
         p.epi_mode = c.accumulate ? EPI_ACCUM : EPI_STORE;
     }
 
-    CUtensorMap ta, tb;
-    int rc;
+    CUtensorMap ta, tb, to, tact;
+    int rc = make_out_tmap(ctx, &to, out_base, splits, c.M, c.N);
+    if (rc != GPTB200_OK) return rc;
+    if (p.has_act) {
+        rc = make_out_tmap(ctx, &tact, c.act, 1, c.M, c.N);
+        if (rc != GPTB200_OK) return rc;
+    } else {
+        tact = to;
+    }
     if (c.a_mn)
         rc = make_tmap(ctx, &ta, c.a, c.K, c.M, 32, kBK, true);
     else
@@ -232,9 +251,11 @@ int run_gemm(gptb200_ctx *ctx, const GemmCall &c)
     const int grid = static_cast<int>(std::min<long long>(items, ctx->num_sms));
     cudaError_t e;
     if (bn == 256)
-        e = x3 ? launch_majors<256, true>(ctx, c.a_mn, c.b_mn, ta, tb, p, grid) : launch_majors<256, false>(ctx, c.a_mn, c.b_mn, ta, tb, p, grid);
+        e = x3 ? launch_majors<256, true>(ctx, c.a_mn, c.b_mn, ta, tb, to, tact, p, grid)
+               : launch_majors<256, false>(ctx, c.a_mn, c.b_mn, ta, tb, to, tact, p, grid);
     else
-        e = x3 ? launch_majors<128, true>(ctx, c.a_mn, c.b_mn, ta, tb, p, grid) : launch_majors<128, false>(ctx, c.a_mn, c.b_mn, ta, tb, p, grid);
+        e = x3 ? launch_majors<128, true>(ctx, c.a_mn, c.b_mn, ta, tb, to, tact, p, grid)
+               : launch_majors<128, false>(ctx, c.a_mn, c.b_mn, ta, tb, to, tact, p, grid);
     ctx->launches++;
     CUDA_TRY(ctx, e);
 

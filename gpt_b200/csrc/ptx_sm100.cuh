@@ -86,13 +86,23 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tmap, int3
         : "memory");
 }
 
-// 2-D tiled store shared -> global (bulk async group).
-__device__ __forceinline__ void tma_store_2d(const void *tmap, int32_t x, int32_t y, uint32_t src)
+// 3-D tiled store shared -> global (bulk async group); elements outside the tensor are dropped.
+__device__ __forceinline__ void tma_store_3d(const void *tmap, int32_t x, int32_t y, int32_t z, uint32_t src)
 {
     asm volatile(
-        "cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+        "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
         :
-        : "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(src)
+        : "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(z), "r"(src)
+        : "memory");
+}
+
+// 3-D tiled reduction shared -> global: global += shared (element type from the tensor map).
+__device__ __forceinline__ void tma_reduce_add_3d(const void *tmap, int32_t x, int32_t y, int32_t z, uint32_t src)
+{
+    asm volatile(
+        "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
+        :
+        : "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(z), "r"(src)
         : "memory");
 }
 
@@ -111,6 +121,19 @@ template <int N>
 __device__ __forceinline__ void tma_store_wait_all()
 {
     asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Move registers between the warpgroups of a CTA (all four warps of a warpgroup execute it).
+template <int N>
+__device__ __forceinline__ void reg_dec()
+{
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+template <int N>
+__device__ __forceinline__ void reg_inc()
+{
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
 }
 
 // ---------------------------------------------------------------- tcgen05 / TMEM

@@ -1,0 +1,316 @@
+#!/usr/bin/env python
+"""Benchmark of the linear-layer hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--mode 3xtf32|tf32] [--impl ours|reference]
+
+Workload (BASELINE.json configs[1]): one GPT-2 124M FFN fc layer at M = 8192 tokens per GPU --
+x [8192 x 768], w [768 x 3072], bias, GELU-tanh -- forward, then backward (grad_x, grad_w +=, grad_b +=) with an
+upstream gradient [8192 x 3072].  One step = forward + backward = 6*M*K*N algorithmic flops.  Synthetic
+N(0,1) / N(0,0.02) data, seeded.  The step's buffers rotate through 4 sets (about 1.5 GB, larger than the
+126 MB L2) so no step finds its inputs in cache.
+
+N > 1 (launched by torch.distributed.run, one rank per GPU): the batch (M) is sharded, every rank runs the same
+per-GPU workload (weak scaling) and the weight gradients (grad_w, grad_b) are all-reduced with NCCL inside the
+timed region, as in a data-parallel training step.
+
+`value` is timed with CUDA events on the launching stream, inputs resident in HBM, max over ranks.  `e2e` is
+the same step through the C ABI starting from pinned HOST buffers: x and the upstream gradient are copied to
+the device, and act / grad_x / grad_w / grad_b are copied back, inside the timed region.
+
+--impl reference times the reference's own CPU implementation (unmodified sources, oracle/_ref) of the same
+step on the host, on a bounded row sample per step (its cost is exactly linear in M).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import shutil
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M_PER_GPU, K_IN, N_OUT = 8192, 768, 3072
+FLOPS_PER_STEP = 6.0 * M_PER_GPU * K_IN * N_OUT          # forward + dX + dW, 2*M*K*N each
+METRIC = "linear_layer_tflops"
+UNIT = "TFLOP/s"
+WORKLOAD = "GPT-2 124M FFN fc (x[8192x768].w[768x3072]+b, GELU-tanh) forward+backward per GPU"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        # TF32 tensor rate is half the bf16 rate; the driver measures bf16 with cuBLAS.
+        return dict(tf32_tflops=p["bf16_tflops"] / 2.0, tf32_tflops_sustained=p["bf16_tflops_sustained"] / 2.0, hbm_gbs=p["hbm_gbs"],
+                    source="of measured (MEASURED_PEAKS.json bf16 cuBLAS burst / 2: TF32 issues at half the bf16 rate)")
+    return dict(tf32_tflops=1590.0 / 2.0, tf32_tflops_sustained=1400.0 / 2.0, hbm_gbs=6650.0,
+                source="of fallback (1.59 PFLOP/s bf16 / 2)")
+
+
+class ClockSampler:
+    """Samples nvidia-smi during the timed region (read-only query)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc = None
+        self.path = None
+        self.gpu = gpu_index
+        exe = shutil.which("nvidia-smi")
+        if exe:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen([exe, f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(gpu_index)],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+
+    def stop(self):
+        if not self.proc:
+            return None
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], 0.0, set()
+        for line in open(self.path):
+            f = [s.strip() for s in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax = max(smax, float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if not sm:
+            return None
+        busy = [c for c in sm if c > 0.5 * max(sm)] or sm
+        return dict(sm_mhz=statistics.median(busy), sm_max_mhz=smax, reasons=sorted(reasons), samples=len(sm))
+
+
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import gpt_b200
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    mode = gpt_b200.MODE_TF32 if args.mode == "tf32" else gpt_b200.MODE_3XTF32
+    stream = torch.cuda.current_stream()
+    be = gpt_b200.Backend(local_rank, stream.cuda_stream, mode)
+    M, K, N = M_PER_GPU, K_IN, N_OUT
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    NSETS = 4
+    sets = []
+    for _ in range(NSETS):
+        sets.append(dict(x=torch.randn(M, K, device=dev, generator=gen), gy=torch.randn(M, N, device=dev, generator=gen),
+                         y=torch.empty(M, N, device=dev), act=torch.empty(M, N, device=dev), gx=torch.empty(M, K, device=dev)))
+    w = torch.randn(K, N, device=dev, generator=torch.Generator(device=dev).manual_seed(7)) * 0.02
+    b = torch.randn(N, device=dev, generator=torch.Generator(device=dev).manual_seed(8)) * 0.02
+    gw = torch.zeros(K, N, device=dev)
+    gb = torch.zeros(N, device=dev)
+
+    def step(i):
+        s = sets[i % NSETS]
+        be.device_linear_activation_fused_forward(s["y"], s["act"], s["x"], w, b, True, 1, M, K, N)
+        be.device_linear_backward(s["gx"], gw, gb, s["gy"], s["x"], w, 1, M, K, N)
+        if world > 1:
+            dist.all_reduce(gw)
+            dist.all_reduce(gb)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    be.synchronize()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    launches0 = be.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(args.steps):
+        step(i)
+    ev1.record()
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    launches = be.launch_count() - launches0
+    be.synchronize()
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    clocks = sampler.stop() if sampler else None
+
+    # ---- per-kernel timing of the dominant kernels (forward GEMM, dX GEMM, dW GEMM), same stream
+    peaks = measured_peaks()
+    kern = {}
+    for name, fn, flops in (
+        ("forward_gemm_bias_gelu", lambda s: be.device_linear_activation_fused_forward(s["y"], s["act"], s["x"], w, b, True, 1, M, K, N), 2.0 * M * K * N),
+        ("backward_dx_dw_db", lambda s: be.device_linear_backward(s["gx"], gw, gb, s["gy"], s["x"], w, 1, M, K, N), 4.0 * M * K * N),
+    ):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = max(4, args.steps)
+        fn(sets[0])
+        e0.record()
+        for i in range(reps):
+            fn(sets[i % NSETS])
+        e1.record()
+        torch.cuda.synchronize()
+        t_ms = e0.elapsed_time(e1) / reps
+        kern[name] = dict(ms=t_ms, tflops=flops / t_ms / 1e9)
+    be.synchronize()
+
+    # ---- end to end from pinned host buffers through the C ABI (rank-local; max over ranks)
+    hx = torch.randn(M, K).pin_memory()
+    hgy = torch.randn(M, N).pin_memory()
+    hact, hgx = torch.empty(M, N).pin_memory(), torch.empty(M, K).pin_memory()
+    hgw, hgb = torch.empty(K, N).pin_memory(), torch.empty(N).pin_memory()
+    s0 = sets[0]
+    h2d = (hx.numel() + hgy.numel()) * 4
+    d2h = (hact.numel() + hgx.numel() + hgw.numel() + hgb.numel()) * 4
+
+    def e2e_step():
+        be.device_memcpy_h2d(s0["x"].data_ptr(), hx.data_ptr(), hx.numel() * 4)
+        be.device_memcpy_h2d(s0["gy"].data_ptr(), hgy.data_ptr(), hgy.numel() * 4)
+        be.device_linear_activation_fused_forward(s0["y"], s0["act"], s0["x"], w, b, True, 1, M, K, N)
+        be.device_linear_backward(s0["gx"], gw, gb, s0["gy"], s0["x"], w, 1, M, K, N)
+        if world > 1:
+            dist.all_reduce(gw)
+            dist.all_reduce(gb)
+        be.device_memcpy_d2h(hact.data_ptr(), s0["act"].data_ptr(), hact.numel() * 4)
+        be.device_memcpy_d2h(hgx.data_ptr(), s0["gx"].data_ptr(), hgx.numel() * 4)
+        be.device_memcpy_d2h(hgw.data_ptr(), gw.data_ptr(), hgw.numel() * 4)
+        be.device_memcpy_d2h(hgb.data_ptr(), gb.data_ptr(), hgb.numel() * 4)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    be.synchronize()
+
+    if rank == 0:
+        ms_per_step = ms / args.steps
+        value = FLOPS_PER_STEP * world / (ms_per_step * 1e-3) / 1e12
+        x3 = mode == gpt_b200.MODE_3XTF32
+        fwd = kern["forward_gemm_bias_gelu"]
+        roof = dict(bound="tensor", achieved=fwd["tflops"], peak=peaks["tf32_tflops"], unit="TFLOP/s", frac=fwd["tflops"] / peaks["tf32_tflops"],
+                    traffic=None, kernel="gemm_tcgen05_kernel (forward: x.w + bias, GELU)", peak_source=peaks["source"],
+                    issued_tflops=fwd["tflops"] * (3 if x3 else 1),
+                    issued_frac=fwd["tflops"] * (3 if x3 else 1) / peaks["tf32_tflops"],
+                    note="achieved = 2*M*K*N algorithmic flops per launch / CUDA-event launch time; in 3xTF32 mode the tensor pipe "
+                         "executes 3 MMAs per algorithmic MMA (issued_tflops)")
+        out = dict(metric=METRIC, value=value, unit=UNIT, n_gpus=world, steps=args.steps, warmup=args.warmup, ms_per_step=ms_per_step,
+                   higher_is_better=True, scaling="weak", vs_baseline=None, dtype="tf32x3 (fp32-accurate split)" if x3 else "tf32",
+                   data="synthetic", impl="ours",
+                   config=dict(workload=WORKLOAD, m_per_gpu=M, k=K, n=N, mode=args.mode, l2="4 rotating buffer sets (1.5 GB) > 126 MB L2",
+                               parallelism=f"dp{world}" if world > 1 else "single", allreduce="grad_w+grad_b (NCCL)" if world > 1 else None),
+                   tokens_per_s=M * world / (ms_per_step * 1e-3), kernels=kern, roofline=roof, gpu_launches=int(launches),
+                   e2e=dict(value=FLOPS_PER_STEP * world / (e2e_s / e2e_steps) / 1e12, unit=UNIT, h2d_bytes_per_step=h2d,
+                            d2h_bytes_per_step=d2h, ms_per_step=e2e_s / e2e_steps * 1e3, steps=e2e_steps),
+                   clocks=clocks)
+        if world == 1 and not args.no_cpu_baseline:
+            out["cpu_baseline"] = cpu_reference_sample(rows=args.cpu_rows)
+        print(json.dumps(out), flush=True)
+    be.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_reference_sample(rows: int):
+    """The reference CPU backend (unmodified sources behind oracle/_ref, one thread -- it has no threading) on
+    `rows` rows of the workload; falls back to the oracle port when the reference library was not prebuilt."""
+    import numpy as np
+    from oracle.oracle import Oracle, Reference, reference_available
+    rng = np.random.default_rng(0)
+    K, N = K_IN, N_OUT
+    x = rng.standard_normal((rows, K), dtype=np.float32)
+    w = (0.02 * rng.standard_normal((K, N))).astype(np.float32)
+    b = (0.02 * rng.standard_normal(N)).astype(np.float32)
+    gy = rng.standard_normal((rows, N), dtype=np.float32)
+    if reference_available():
+        impl, kind, cores = Reference(), "reference", 1
+    else:
+        impl, kind = Oracle(), "port"
+        cores = impl.num_threads()
+    t0 = time.perf_counter()
+    impl.linear_forward(x, w, b, True)
+    impl.linear_backward(gy, x, w)
+    dt = time.perf_counter() - t0
+    flops = 6.0 * rows * K * N
+    return dict(value=flops / dt / 1e12, unit=UNIT, cores=cores, kind=kind, host_cores=os.cpu_count(), seconds=dt,
+                sample=f"{rows} of {M_PER_GPU} rows of the same step (cost is linear in rows), forward+backward")
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    rows = args.ref_rows
+    # warm-up and timed steps, each a bounded row sample
+    for _ in range(min(args.warmup, 1)):
+        cpu_reference_sample(rows)
+    t = []
+    base = None
+    for _ in range(args.steps):
+        base = cpu_reference_sample(rows)
+        t.append(base["seconds"])
+    sec = statistics.mean(t)
+    value = 6.0 * rows * K_IN * N_OUT / sec / 1e12
+    base["value"] = value
+    out = dict(metric=METRIC, value=value, unit=UNIT, n_gpus=args.gpus, steps=args.steps, warmup=min(args.warmup, 1),
+               ms_per_step=sec * 1e3, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic", impl="reference",
+               config=dict(workload=WORKLOAD, m_per_gpu=M_PER_GPU, k=K_IN, n=N_OUT, sample_rows_per_step=rows),
+               cpu_baseline=base, e2e=dict(value=value, unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
+    print(json.dumps(out), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--mode", choices=["3xtf32", "tf32"], default="3xtf32")
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--cpu-rows", type=int, default=256, help="rows of the workload the cpu_baseline leg runs")
+    ap.add_argument("--ref-rows", type=int, default=32, help="rows per step of the --impl reference arm")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -55,7 +55,7 @@ def measured_peaks():
 
 class ClockSampler:
     """Samples nvidia-smi during the timed region (read-only query)."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    Q = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
@@ -66,10 +66,12 @@ class ClockSampler:
         if exe:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
-            self.proc = subprocess.Popen([exe, f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(gpu_index)],
+            self.proc = subprocess.Popen([exe, f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50", "-i", str(gpu_index)],
                                          stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
 
-    def stop(self):
+    def stop(self, t_begin: float, t_end: float):
+        """Summary of the samples taken between the two time.time() stamps (the timed region and the
+        measurement loops that follow it)."""
         if not self.proc:
             return None
         self.proc.terminate()
@@ -77,24 +79,28 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, smax, reasons = [], 0.0, set()
+        sm, smax, reasons, n_all = [], 0.0, set(), 0
         for line in open(self.path):
             f = [s.strip() for s in line.split(",")]
-            if len(f) < 9:
+            if len(f) < 10:
                 continue
+            n_all += 1
             try:
-                sm.append(float(f[1]))
-                smax = max(smax, float(f[2]))
-            except ValueError:
+                ts = time.mktime(time.strptime(f[0].split(".")[0], "%Y/%m/%d %H:%M:%S")) + float("0." + f[0].split(".")[1])
+                clk, cmax = float(f[2]), float(f[3])
+            except (ValueError, IndexError):
                 continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+            if ts < t_begin - 0.2 or ts > t_end + 0.2:
+                continue
+            sm.append(clk)
+            smax = max(smax, cmax)
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[6:10]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
         os.unlink(self.path)
         if not sm:
-            return None
-        busy = [c for c in sm if c > 0.5 * max(sm)] or sm
-        return dict(sm_mhz=statistics.median(busy), sm_max_mhz=smax, reasons=sorted(reasons), samples=len(sm))
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0, samples_total=n_all)
+        return dict(sm_mhz=statistics.median(sm), sm_max_mhz=smax, reasons=sorted(reasons), samples=len(sm), samples_total=n_all)
 
 
 def run_ours(args):
@@ -117,7 +123,8 @@ def run_ours(args):
     mode = gpt_b200.MODE_TF32 if args.mode == "tf32" else gpt_b200.MODE_3XTF32
     stream = torch.cuda.current_stream()
     be = gpt_b200.Backend(local_rank, stream.cuda_stream, mode)
-    M, K, N = M_PER_GPU, K_IN, N_OUT
+    M, K, N = args.m_per_gpu, K_IN, N_OUT
+    flops_per_step = 6.0 * M * K * N
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
     NSETS = 4
     sets = []
@@ -142,11 +149,12 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local_rank) if rank == 0 else None
     for i in range(args.warmup):
         step(i)
     be.synchronize()
     barrier()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
+    t_begin = time.time()
     launches0 = be.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
@@ -161,7 +169,6 @@ def run_ours(args):
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-    clocks = sampler.stop() if sampler else None
 
     # ---- per-kernel timing of the dominant kernels (forward GEMM, dX GEMM, dW GEMM), same stream
     peaks = measured_peaks()
@@ -171,7 +178,7 @@ def run_ours(args):
         ("backward_dx_dw_db", lambda s: be.device_linear_backward(s["gx"], gw, gb, s["gy"], s["x"], w, 1, M, K, N), 4.0 * M * K * N),
     ):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        reps = max(4, args.steps)
+        reps = 1 if args.profile else max(4, args.steps)
         fn(sets[0])
         e0.record()
         for i in range(reps):
@@ -204,8 +211,8 @@ def run_ours(args):
         be.device_memcpy_d2h(hgw.data_ptr(), gw.data_ptr(), hgw.numel() * 4)
         be.device_memcpy_d2h(hgb.data_ptr(), gb.data_ptr(), hgb.numel() * 4)
 
-    e2e_steps = max(3, min(args.steps, 10))
-    for _ in range(2):
+    e2e_steps = 0 if args.profile else max(3, min(args.steps, 10))
+    for _ in range(0 if args.profile else 2):
         e2e_step()
     barrier()
     t0 = time.perf_counter()
@@ -218,10 +225,16 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
     be.synchronize()
+    # keep the same load running for about a second so that the 50 ms clock samples cover it (not part of any
+    # number); the iteration count derives from the rank-reduced step time, so every rank runs the same count
+    for i in range(0 if args.profile else int(min(5000, max(10, 1000.0 / (ms / args.steps))))):
+        step(i)
+    torch.cuda.synchronize()
+    clocks = sampler.stop(t_begin, time.time()) if sampler else None
 
     if rank == 0:
         ms_per_step = ms / args.steps
-        value = FLOPS_PER_STEP * world / (ms_per_step * 1e-3) / 1e12
+        value = flops_per_step * world / (ms_per_step * 1e-3) / 1e12
         x3 = mode == gpt_b200.MODE_3XTF32
         fwd = kern["forward_gemm_bias_gelu"]
         roof = dict(bound="tensor", achieved=fwd["tflops"], peak=peaks["tf32_tflops"], unit="TFLOP/s", frac=fwd["tflops"] / peaks["tf32_tflops"],
@@ -233,13 +246,14 @@ def run_ours(args):
         out = dict(metric=METRIC, value=value, unit=UNIT, n_gpus=world, steps=args.steps, warmup=args.warmup, ms_per_step=ms_per_step,
                    higher_is_better=True, scaling="weak", vs_baseline=None, dtype="tf32x3 (fp32-accurate split)" if x3 else "tf32",
                    data="synthetic", impl="ours",
-                   config=dict(workload=WORKLOAD, m_per_gpu=M, k=K, n=N, mode=args.mode, l2="4 rotating buffer sets (1.5 GB) > 126 MB L2",
+                   config=dict(workload=WORKLOAD if M == M_PER_GPU else WORKLOAD.replace("8192", str(M)), m_per_gpu=M, k=K, n=N, mode=args.mode, l2="4 rotating buffer sets (1.5 GB) > 126 MB L2",
                                parallelism=f"dp{world}" if world > 1 else "single", allreduce="grad_w+grad_b (NCCL)" if world > 1 else None),
                    tokens_per_s=M * world / (ms_per_step * 1e-3), kernels=kern, roofline=roof, gpu_launches=int(launches),
-                   e2e=dict(value=FLOPS_PER_STEP * world / (e2e_s / e2e_steps) / 1e12, unit=UNIT, h2d_bytes_per_step=h2d,
-                            d2h_bytes_per_step=d2h, ms_per_step=e2e_s / e2e_steps * 1e3, steps=e2e_steps),
+                   e2e=None if not e2e_steps else dict(value=flops_per_step * world / (e2e_s / e2e_steps) / 1e12, unit=UNIT,
+                                                       h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
+                                                       ms_per_step=e2e_s / e2e_steps * 1e3, steps=e2e_steps),
                    clocks=clocks)
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and not args.profile:
             out["cpu_baseline"] = cpu_reference_sample(rows=args.cpu_rows)
         print(json.dumps(out), flush=True)
     be.close()
@@ -305,6 +319,8 @@ def main():
     ap.add_argument("--cpu-rows", type=int, default=256, help="rows of the workload the cpu_baseline leg runs")
     ap.add_argument("--ref-rows", type=int, default=32, help="rows per step of the --impl reference arm")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--m-per-gpu", type=int, default=M_PER_GPU, help="tokens per GPU (smaller for profiler captures)")
+    ap.add_argument("--profile", action="store_true", help="only the timed steps: no end-to-end, clock-load or CPU legs")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -416,7 +416,8 @@ int gptb200_linear_forward(gptb200_ctx *ctx, float *y, float *act, const float *
     int rc = check_dims(ctx, m, k, n);
     if (rc) return rc;
     if (m == 0 || n == 0) return GPTB200_OK;
-    if (!y || !x || !w || !b || (activation && !act)) return fail(ctx, GPTB200_ERR_INVALID_ARG, "null tensor pointer");
+    // a tensor without elements (k == 0) may come as a null pointer
+    if (!y || !b || (activation && !act) || (k > 0 && (!x || !w))) return fail(ctx, GPTB200_ERR_INVALID_ARG, "null tensor pointer");
     GemmCall c{m, n, k, x, false, w, true, y, activation ? act : nullptr, b, false};
     return run_gemm(ctx, c);
 }
@@ -426,7 +427,8 @@ int gptb200_linear_backward(gptb200_ctx *ctx, float *grad_x, float *grad_w, floa
 {
     int rc = check_dims(ctx, m, k, n);
     if (rc) return rc;
-    if (!grad_x || !grad_w || !grad_b || !grad_y || !x || !w) return fail(ctx, GPTB200_ERR_INVALID_ARG, "null tensor pointer");
+    if ((1LL * m * k > 0 && (!grad_x || !x)) || (1LL * k * n > 0 && (!grad_w || !w)) || (n > 0 && !grad_b) || (1LL * m * n > 0 && !grad_y))
+        return fail(ctx, GPTB200_ERR_INVALID_ARG, "null tensor pointer");
     // grad_x[m x k] = grad_y[m x n] . w^T : A = grad_y (K-major), B = w stored [k x n] = [N' x K'] (K-major)
     if (m > 0 && k > 0) {
         if (n == 0) {
@@ -465,7 +467,7 @@ int gptb200_unembed_forward(gptb200_ctx *ctx, float *y, const float *x, const fl
     int rc = check_dims(ctx, m, d, vp);
     if (rc) return rc;
     if (m == 0 || vp == 0) return GPTB200_OK;
-    if (!y || !x || !wte) return fail(ctx, GPTB200_ERR_INVALID_ARG, "null tensor pointer");
+    if (!y || (d > 0 && (!x || !wte))) return fail(ctx, GPTB200_ERR_INVALID_ARG, "null tensor pointer");
     if (d == 0) {
         CUDA_TRY(ctx, cudaMemsetAsync(y, 0, size_t(m) * vp * sizeof(float), ctx->stream));
         return GPTB200_OK;
@@ -480,8 +482,8 @@ int gptb200_unembed_backward(gptb200_ctx *ctx, float *grad_x, float *grad_wte, c
 {
     int rc = check_dims(ctx, m, d, vp);
     if (rc) return rc;
-    if (!grad_x || !grad_wte || !grad_y || !x || !wte) return fail(ctx, GPTB200_ERR_INVALID_ARG, "null tensor pointer");
     if (m == 0 || d == 0) return GPTB200_OK;
+    if (!grad_x || !x || (vp > 0 && (!grad_wte || !grad_y || !wte))) return fail(ctx, GPTB200_ERR_INVALID_ARG, "null tensor pointer");
     if (vp == 0) {
         CUDA_TRY(ctx, cudaMemsetAsync(grad_x, 0, size_t(m) * d * sizeof(float), ctx->stream));
         return GPTB200_OK;

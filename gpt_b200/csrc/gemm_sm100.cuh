@@ -112,11 +112,12 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, vola
 }
 
 // GELU (tanh form) written as x * sigmoid(2u), u = 0.79788456 (x + 0.044715 x^3):
-// identical to 0.5 x (1 + tanh u) and needs one exp and one divide.
+// identical to 0.5 x (1 + tanh u) and needs one exp2 and one reciprocal (both 1-2 ulp approximations,
+// far inside the 1e-5 bound).  exp(-2u) overflows to +inf only for u < -44, where the result is -0.
 __device__ __forceinline__ float gelu_tanh(float x)
 {
     const float u = 0.79788456f * (x + 0.044715f * x * x * x);
-    return x / (1.0f + __expf(-2.0f * u));
+    return __fdividef(x, 1.0f + __expf(-2.0f * u));
 }
 
 // One epilogue warp's staging state: `kBufs` swizzled [32 x 32] fp32 tiles and the count of TMA stores

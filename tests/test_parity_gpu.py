@@ -42,11 +42,20 @@ def rel_err(a, ref):
     return float(np.abs(a - ref).max() / denom) if ref.size else 0.0
 
 
-def check(name, got, ref, mode, absolute=False):
+def check(name, got, ref, mode, absolute=False, exact=None):
+    """`exact` (float64, optional) is the exactly-rounded result.  For reductions tens of thousands of terms
+    long the oracle's own sequential fp32 sum is several 1e-6 away from it, so a miss of the 1e-5 bound
+    against the oracle is attributed: it still passes if the GPU result is within 1e-5 of the exact result
+    AND at least as close to it as the oracle is."""
     assert got.shape == ref.shape, name
     assert np.isfinite(got).all(), f"{name}: non-finite output"
     e = rel_err(got, ref)
-    assert e <= TOL[mode], f"{name} [{MODE_NAME[mode]}]: rel err {e:.3e} > {TOL[mode]:.0e}"
+    if e > TOL[mode] and exact is not None:
+        e_gpu, e_oracle = rel_err(got, exact), rel_err(ref, exact)
+        assert e_gpu <= TOL[mode] and e_gpu <= e_oracle, (
+            f"{name} [{MODE_NAME[mode]}]: vs oracle {e:.3e}, GPU vs exact {e_gpu:.3e}, oracle vs exact {e_oracle:.3e}")
+    else:
+        assert e <= TOL[mode], f"{name} [{MODE_NAME[mode]}]: rel err {e:.3e} > {TOL[mode]:.0e}"
     if absolute and mode == 0:
         assert np.abs(got.astype(np.float64) - ref).max() <= 1e-5, f"{name}: fails the reference's absolute 1e-5 check"
 
@@ -167,7 +176,8 @@ def test_unembed_ops_against_oracle_seeded(be, torch, oracle, m, d, vp, v):
     dv.check_canaries()
     rgx, rgw = oracle.unembed_backward(gy, x, wte, gw0)
     check("logits", y.cpu().numpy(), logits, be.mode)
-    check("grad_x", gx.cpu().numpy(), rgx, be.mode)
+    exact_gx = gy.astype(np.float64) @ wte.astype(np.float64) if vp > 10000 else None  # 50304-term sums
+    check("grad_x", gx.cpu().numpy(), rgx, be.mode, exact=exact_gx)
     check("grad_wte", gw.cpu().numpy(), rgw, be.mode)
     assert np.all(y.cpu().numpy()[:, v:] == 0.0)  # zeroed padding rows of wte give exactly zero logits
 

@@ -30,6 +30,10 @@ EXPORTED_SYMBOLS = [
     "gptb200_linear_forward", "gptb200_linear_backward", "gptb200_gelu_backward",
     "gptb200_unembed_forward", "gptb200_unembed_backward",
     "gptb200_malloc", "gptb200_free", "gptb200_memset", "gptb200_memcpy_h2d", "gptb200_memcpy_d2h",
+    "gptb200_fill_normal", "gptb200_fill_const", "gptb200_embedding_forward", "gptb200_embedding_backward",
+    "gptb200_layernorm_forward", "gptb200_layernorm_backward", "gptb200_attention_forward", "gptb200_attention_backward",
+    "gptb200_softmax_forward", "gptb200_cross_entropy_softmax_backward", "gptb200_cross_entropy_loss",
+    "gptb200_adamw_step", "gptb200_scale_and_clip_grad", "gptb200_memory_info",
 ]
 
 
@@ -74,6 +78,27 @@ def load_library(path: str | None = None) -> ctypes.CDLL:
         "gptb200_memcpy_h2d": (i, [vp, vp, vp, ctypes.c_size_t]),
         "gptb200_memcpy_d2h": (i, [vp, vp, vp, ctypes.c_size_t]),
     }
+    f32, sz, ull = ctypes.c_float, ctypes.c_size_t, ctypes.c_ulonglong
+    sig.update({
+        "gptb200_fill_normal": (i, [vp, fp, f32, f32, sz, ull, ull]),
+        "gptb200_fill_const": (i, [vp, fp, f32, sz]),
+        "gptb200_embedding_forward": (i, [vp, fp, fp, fp, fp, i, i, i]),
+        "gptb200_embedding_backward": (i, [vp, fp, fp, fp, fp, i, i, i]),
+        "gptb200_layernorm_forward": (i, [vp, fp, fp, fp, fp, fp, fp, fp, i, i]),
+        "gptb200_layernorm_backward": (i, [vp, fp, fp, fp, fp, fp, fp, fp, fp, fp, i, i]),
+        "gptb200_attention_forward": (i, [vp, fp, fp, fp, i, i, i, i]),
+        "gptb200_attention_backward": (i, [vp, fp, fp, fp, fp, fp, fp, i, i, i, i]),
+        "gptb200_softmax_forward": (i, [vp, fp, fp, i, i, i]),
+        "gptb200_cross_entropy_softmax_backward": (i, [vp, fp, fp, fp, i, i, i]),
+        "gptb200_cross_entropy_loss": (i, [vp, fp, fp, fp, i, i]),
+        "gptb200_adamw_step": (i, [vp, fp, fp, fp, fp, sz, f32, f32, f32, f32, f32, i]),
+        "gptb200_scale_and_clip_grad": (i, [vp, fp, sz, f32, i]),
+        "gptb200_memory_info": (i, [vp, ctypes.POINTER(f32), ctypes.POINTER(f32)]),
+        # C++ object factory: an IGPTBackend* for host programs written against the reference's interface
+        "gptb200_backend_create": (vp, [ctypes.c_ulong, i, vp, i]),
+        "gptb200_backend_destroy": (None, [vp]),
+        "gptb200_backend_context": (vp, [vp]),
+    })
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
         fn.restype = res

@@ -1,0 +1,220 @@
+// extern "C" entry points of the operators that are not on the linear-layer hot path (see backend_ops.cuh).
+#include <algorithm>
+#include <cmath>
+
+#include "ctx_internal.h"
+#include "backend_ops.cuh"
+
+using namespace gptb200;
+
+namespace {
+
+int blocks_for(const gptb200_ctx *ctx, size_t n, int threads)
+{
+    const size_t want = (n + threads - 1) / threads;
+    return static_cast<int>(std::max<size_t>(1, std::min<size_t>(want, size_t(ctx->num_sms) * 16)));
+}
+
+int launched(gptb200_ctx *ctx, int n = 1)
+{
+    ctx->launches += n;
+    CUDA_TRY(ctx, cudaGetLastError());
+    return GPTB200_OK;
+}
+
+template <int HD, int TPR>
+int attention_forward_t(gptb200_ctx *ctx, float *y, float *lse, const float *qkv, int batch, int seq_len, int d, int heads)
+{
+    dim3 grid((seq_len + ops::kAttnRowsPerBlock - 1) / ops::kAttnRowsPerBlock, heads, batch);
+    ops::attention_forward_kernel<HD, TPR><<<grid, ops::kAttnRowsPerBlock * TPR, 0, ctx->stream>>>(y, lse, qkv, seq_len, d, heads);
+    return launched(ctx);
+}
+
+template <int HD, int TPR>
+int attention_backward_t(gptb200_ctx *ctx, float *gqkv, float *dcache, const float *lse, const float *gy, const float *qkv, int batch,
+                         int seq_len, int d, int heads)
+{
+    dim3 grid((seq_len + ops::kAttnRowsPerBlock - 1) / ops::kAttnRowsPerBlock, heads, batch);
+    ops::attention_backward_dq_kernel<HD, TPR><<<grid, ops::kAttnRowsPerBlock * TPR, 0, ctx->stream>>>(gqkv, dcache, lse, gy, qkv, seq_len, d, heads);
+    ops::attention_backward_dkv_kernel<HD, TPR><<<grid, ops::kAttnRowsPerBlock * TPR, 0, ctx->stream>>>(gqkv, dcache, lse, gy, qkv, seq_len, d, heads);
+    return launched(ctx, 2);
+}
+
+}  // namespace
+
+#define NEED(ctx, cond)                                                                        \
+    do {                                                                                       \
+        if (!(ctx)) return GPTB200_ERR_INVALID_ARG;                                            \
+        if (!(cond)) return fail(ctx, GPTB200_ERR_INVALID_ARG, "%s: invalid argument (%s)", __func__, #cond); \
+    } while (0)
+
+extern "C" {
+
+int gptb200_fill_normal(gptb200_ctx *ctx, float *ptr, float mean, float stddev, size_t count, unsigned long long seed,
+                        unsigned long long offset)
+{
+    NEED(ctx, ptr || count == 0);
+    if (count == 0) return GPTB200_OK;
+    ops::fill_normal_kernel<<<blocks_for(ctx, count, 256), 256, 0, ctx->stream>>>(ptr, mean, stddev, count, seed, offset);
+    return launched(ctx);
+}
+
+int gptb200_fill_const(gptb200_ctx *ctx, float *ptr, float value, size_t count)
+{
+    NEED(ctx, ptr || count == 0);
+    if (count == 0) return GPTB200_OK;
+    ops::fill_const_kernel<<<blocks_for(ctx, count, 256), 256, 0, ctx->stream>>>(ptr, value, count);
+    return launched(ctx);
+}
+
+int gptb200_embedding_forward(gptb200_ctx *ctx, float *y, const float *wte, const float *wpe, const int *tokens, int batch, int seq_len,
+                              int d)
+{
+    NEED(ctx, batch >= 0 && seq_len >= 0 && d >= 0);
+    const long long rows = 1LL * batch * seq_len;
+    if (rows == 0 || d == 0) return GPTB200_OK;
+    NEED(ctx, y && wte && wpe && tokens && rows <= 0x7fffffffLL);
+    ops::embedding_forward_kernel<<<static_cast<unsigned>(rows), 256, 0, ctx->stream>>>(y, wte, wpe, tokens, static_cast<int>(rows), seq_len, d);
+    return launched(ctx);
+}
+
+int gptb200_embedding_backward(gptb200_ctx *ctx, float *grad_wte, float *grad_wpe, const float *grad_y, const int *tokens, int batch,
+                               int seq_len, int d)
+{
+    NEED(ctx, batch >= 0 && seq_len >= 0 && d >= 0);
+    if (1LL * batch * seq_len == 0 || d == 0) return GPTB200_OK;
+    NEED(ctx, grad_wte && grad_wpe && grad_y && tokens);
+    ops::embedding_backward_kernel<<<seq_len, 256, 0, ctx->stream>>>(grad_wte, grad_wpe, grad_y, tokens, batch, seq_len, d);
+    return launched(ctx);
+}
+
+int gptb200_layernorm_forward(gptb200_ctx *ctx, float *y, float *means, float *vars, float *x, const float *residual, const float *gamma,
+                              const float *beta, int rows, int d)
+{
+    NEED(ctx, rows >= 0 && d >= 0);
+    if (rows == 0 || d == 0) return GPTB200_OK;
+    NEED(ctx, y && means && vars && x && gamma && beta);
+    const int threads = std::min(1024, std::max(32, ((d + 31) / 32) * 32));
+    ops::layernorm_forward_kernel<<<rows, threads, 0, ctx->stream>>>(y, means, vars, x, residual, gamma, beta, d);
+    return launched(ctx);
+}
+
+int gptb200_layernorm_backward(gptb200_ctx *ctx, float *grad_x, float *grad_gamma, float *grad_beta, const float *grad_y,
+                               const float *grad_residual, const float *x, const float *means, const float *vars, const float *gamma,
+                               int rows, int d)
+{
+    NEED(ctx, rows >= 0 && d >= 0);
+    if (rows == 0 || d == 0) return GPTB200_OK;
+    NEED(ctx, grad_x && grad_gamma && grad_beta && grad_y && x && means && vars && gamma);
+    const int threads = std::min(1024, std::max(32, ((d + 31) / 32) * 32));
+    ops::layernorm_backward_dx_kernel<<<rows, threads, 0, ctx->stream>>>(grad_x, grad_y, grad_residual, x, means, vars, gamma, d);
+    const int col_groups = (d + 31) / 32;
+    int chunks = std::max(1, std::min((ctx->num_sms * 4 + col_groups - 1) / col_groups, (rows + 63) / 64));
+    const int rows_per_chunk = (rows + chunks - 1) / chunks;
+    chunks = (rows + rows_per_chunk - 1) / rows_per_chunk;
+    const int rc = ensure_workspace(ctx, size_t(2) * chunks * d * sizeof(float));
+    if (rc) return rc;
+    float *wg = ctx->ws, *wb = ctx->ws + size_t(chunks) * d;
+    ops::layernorm_backward_params_partial_kernel<<<dim3(col_groups, chunks), dim3(32, 8), 0, ctx->stream>>>(wg, wb, grad_y, x, means, vars,
+                                                                                                             rows, d, rows_per_chunk);
+    ops::layernorm_backward_params_final_kernel<<<(d + 127) / 128, 128, 0, ctx->stream>>>(grad_gamma, grad_beta, wg, wb, d, chunks);
+    return launched(ctx, 3);
+}
+
+int gptb200_attention_forward(gptb200_ctx *ctx, float *y, float *logsumexp, const float *qkv, int batch, int seq_len, int d, int heads)
+{
+    NEED(ctx, batch >= 0 && seq_len >= 0 && d >= 0 && heads > 0 && d % heads == 0);
+    if (1LL * batch * seq_len * d == 0) return GPTB200_OK;
+    NEED(ctx, y && logsumexp && qkv && batch <= 65535 && heads <= 65535);
+    switch (d / heads) {
+        case 8: return attention_forward_t<8, 1>(ctx, y, logsumexp, qkv, batch, seq_len, d, heads);
+        case 16: return attention_forward_t<16, 1>(ctx, y, logsumexp, qkv, batch, seq_len, d, heads);
+        case 32: return attention_forward_t<32, 1>(ctx, y, logsumexp, qkv, batch, seq_len, d, heads);
+        case 64: return attention_forward_t<64, 2>(ctx, y, logsumexp, qkv, batch, seq_len, d, heads);
+        case 128: return attention_forward_t<128, 4>(ctx, y, logsumexp, qkv, batch, seq_len, d, heads);
+        default: return fail(ctx, GPTB200_ERR_INVALID_ARG, "attention: head size %d not in {8,16,32,64,128}", d / heads);
+    }
+}
+
+int gptb200_attention_backward(gptb200_ctx *ctx, float *grad_qkv, float *d_cache, const float *logsumexp, const float *grad_y,
+                               const float *y, const float *qkv, int batch, int seq_len, int d, int heads)
+{
+    NEED(ctx, batch >= 0 && seq_len >= 0 && d >= 0 && heads > 0 && d % heads == 0);
+    if (1LL * batch * seq_len * d == 0) return GPTB200_OK;
+    NEED(ctx, grad_qkv && d_cache && logsumexp && grad_y && y && qkv && batch <= 65535 && heads <= 65535);
+    const long long rh = 1LL * batch * seq_len * heads;
+    ops::attention_rowsum_kernel<<<static_cast<unsigned>((rh + 255) / 256), 256, 0, ctx->stream>>>(d_cache, grad_y, y, batch * seq_len, d, heads);
+    ctx->launches++;
+    switch (d / heads) {
+        case 8: return attention_backward_t<8, 1>(ctx, grad_qkv, d_cache, logsumexp, grad_y, qkv, batch, seq_len, d, heads);
+        case 16: return attention_backward_t<16, 1>(ctx, grad_qkv, d_cache, logsumexp, grad_y, qkv, batch, seq_len, d, heads);
+        case 32: return attention_backward_t<32, 1>(ctx, grad_qkv, d_cache, logsumexp, grad_y, qkv, batch, seq_len, d, heads);
+        case 64: return attention_backward_t<64, 2>(ctx, grad_qkv, d_cache, logsumexp, grad_y, qkv, batch, seq_len, d, heads);
+        case 128: return attention_backward_t<128, 4>(ctx, grad_qkv, d_cache, logsumexp, grad_y, qkv, batch, seq_len, d, heads);
+        default: return fail(ctx, GPTB200_ERR_INVALID_ARG, "attention: head size %d not in {8,16,32,64,128}", d / heads);
+    }
+}
+
+int gptb200_softmax_forward(gptb200_ctx *ctx, float *y, const float *x, int rows, int vocab, int vocab_padded)
+{
+    NEED(ctx, rows >= 0 && vocab >= 0 && vocab_padded >= vocab);
+    if (rows == 0 || vocab_padded == 0) return GPTB200_OK;
+    NEED(ctx, y && x);
+    ops::softmax_forward_kernel<<<rows, 1024, 0, ctx->stream>>>(y, x, vocab, vocab_padded);
+    return launched(ctx);
+}
+
+int gptb200_cross_entropy_softmax_backward(gptb200_ctx *ctx, float *grad_x, const float *probs, const int *labels, int rows, int vocab,
+                                           int vocab_padded)
+{
+    NEED(ctx, rows >= 0 && vocab >= 0 && vocab_padded >= vocab);
+    if (rows == 0 || vocab == 0) return GPTB200_OK;
+    NEED(ctx, grad_x && probs && labels);
+    ops::cross_entropy_softmax_backward_kernel<<<rows, 1024, 0, ctx->stream>>>(grad_x, probs, labels, rows, vocab, vocab_padded);
+    return launched(ctx);
+}
+
+int gptb200_cross_entropy_loss(gptb200_ctx *ctx, float *loss, const float *probs, const int *labels, int rows, int vocab_padded)
+{
+    NEED(ctx, rows >= 0 && vocab_padded >= 0 && loss);
+    NEED(ctx, rows == 0 || (probs && labels));
+    ops::cross_entropy_loss_kernel<<<1, 1024, 0, ctx->stream>>>(loss, probs, labels, rows, vocab_padded);
+    return launched(ctx);
+}
+
+int gptb200_adamw_step(gptb200_ctx *ctx, float *params, const float *g, float *m, float *v, size_t count, float lr, float beta1,
+                       float beta2, float eps, float weight_decay, int step)
+{
+    NEED(ctx, count == 0 || (params && g && m && v));
+    if (count == 0) return GPTB200_OK;
+    const float bc1 = 1.0f - powf(beta1, static_cast<float>(step));
+    const float bc2 = 1.0f - powf(beta2, static_cast<float>(step));
+    ops::adamw_kernel<<<blocks_for(ctx, count, 256), 256, 0, ctx->stream>>>(params, g, m, v, count, lr, beta1, beta2, eps, weight_decay, bc1, bc2);
+    return launched(ctx);
+}
+
+int gptb200_scale_and_clip_grad(gptb200_ctx *ctx, float *g, size_t count, float max_norm, int accum_steps)
+{
+    NEED(ctx, (count == 0 || g) && accum_steps > 0);
+    if (count == 0) return GPTB200_OK;
+    const int blocks = std::min<size_t>(size_t(ctx->num_sms) * 8, (count + 1023) / 1024);
+    const int rc = ensure_workspace(ctx, (size_t(blocks) + 1) * sizeof(float));
+    if (rc) return rc;
+    float *partial = ctx->ws, *factor = ctx->ws + blocks;
+    ops::clip_scale_partial_kernel<<<blocks, 256, 0, ctx->stream>>>(g, partial, count, 1.0f / static_cast<float>(accum_steps));
+    ops::clip_factor_kernel<<<1, 32, 0, ctx->stream>>>(factor, partial, blocks, max_norm);
+    ops::clip_apply_kernel<<<blocks_for(ctx, count, 256), 256, 0, ctx->stream>>>(g, factor, count);
+    return launched(ctx, 3);
+}
+
+int gptb200_memory_info(gptb200_ctx *ctx, float *free_mb, float *total_mb)
+{
+    NEED(ctx, free_mb && total_mb);
+    size_t f = 0, t = 0;
+    CUDA_TRY(ctx, cudaMemGetInfo(&f, &t));
+    *free_mb = static_cast<float>(f / (1024.0 * 1024.0));
+    *total_mb = static_cast<float>(t / (1024.0 * 1024.0));
+    return GPTB200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,547 @@
+// Plain fp32 CUDA kernels for the operators of the reference's backend interface that are NOT on the
+// linear-layer hot path (embedding, LayerNorm + residual, causal attention, softmax, cross-entropy, AdamW,
+// gradient clipping, fills).  They exist so that a whole forward/backward step can run on the GPU behind
+// the same interface; they follow the arithmetic of the reference CPU backend
+// (src/backend/cpu/cpu_backend.cpp) and use no library.  Reductions that feed gradients are done in a fixed
+// order (two-stage partial sums), except the token-embedding scatter which uses red.global.add like the
+// reference's CUDA backend (src/backend/cuda/kernels/embedding.cu:92-110).
+#pragma once
+
+#include <cfloat>
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace gptb200 {
+namespace ops {
+
+// ------------------------------------------------------------------------------------------------ helpers
+
+__device__ __forceinline__ float warp_sum(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum; every thread gets the result.  `red` holds 32 floats.
+__device__ __forceinline__ float block_sum(float v, float *red)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = (lane < nwarps) ? red[lane] : 0.0f;
+    t = warp_sum(t);
+    return t;
+}
+
+__device__ __forceinline__ float block_max(float v, float *red)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = (lane < nwarps) ? red[lane] : -FLT_MAX;
+    t = warp_max(t);
+    return t;
+}
+
+// ------------------------------------------------------------------------------------------------ fills
+
+__global__ void fill_const_kernel(float *p, float value, size_t n)
+{
+    const size_t stride = size_t(gridDim.x) * blockDim.x;
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) p[i] = value;
+}
+
+__device__ __forceinline__ uint32_t mix32(uint64_t x)
+{
+    // splitmix64 finaliser, upper half
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    x ^= x >> 31;
+    return static_cast<uint32_t>(x >> 32);
+}
+
+// Counter-based normal fill (Box-Muller on two hashed uniforms per element): reproducible for a given
+// (seed, offset) regardless of launch shape.
+__global__ void fill_normal_kernel(float *p, float mean, float stddev, size_t n, uint64_t seed, uint64_t offset)
+{
+    const size_t stride = size_t(gridDim.x) * blockDim.x;
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const uint64_t c = (offset + i) * 2ull;
+        const float u1 = (mix32(seed ^ (c * 0xD1342543DE82EF95ull)) + 1.0f) * (1.0f / 4294967808.0f);  // (0, 1]
+        const float u2 = mix32(seed ^ ((c + 1ull) * 0xD1342543DE82EF95ull)) * (1.0f / 4294967296.0f);
+        p[i] = sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2) * stddev + mean;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ embedding
+
+// y[r, :] = wte[token[r], :] + wpe[r % seq_len, :]          (cpu_backend.cpp:65-79)
+__global__ void embedding_forward_kernel(float *__restrict__ y, const float *__restrict__ wte, const float *__restrict__ wpe,
+                                         const int *__restrict__ tokens, int rows, int seq_len, int d)
+{
+    const int r = blockIdx.x;
+    if (r >= rows) return;
+    const int tok = tokens[r];
+    const int s = r % seq_len;
+    for (int h = threadIdx.x; h < d; h += blockDim.x) y[size_t(r) * d + h] = wte[size_t(tok) * d + h] + wpe[size_t(s) * d + h];
+}
+
+// grad_wpe[s, h] += sum_b grad_y[b, s, h]  (b ascending);  grad_wte[token, h] += grad_y[r, h] (red.add)
+__global__ void embedding_backward_kernel(float *__restrict__ grad_wte, float *__restrict__ grad_wpe, const float *__restrict__ grad_y,
+                                          const int *__restrict__ tokens, int batch, int seq_len, int d)
+{
+    const int s = blockIdx.x;
+    for (int h = threadIdx.x; h < d; h += blockDim.x) {
+        float acc = 0.0f;
+        for (int b = 0; b < batch; ++b) {
+            const size_t r = size_t(b) * seq_len + s;
+            const float g = grad_y[r * d + h];
+            acc += g;
+            atomicAdd(grad_wte + size_t(tokens[r]) * d + h, g);
+        }
+        grad_wpe[size_t(s) * d + h] += acc;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ LayerNorm
+
+// x += residual (in place); mean, biased variance; y = (x - mean) / sqrt(var + 1e-5) * gamma + beta
+// (cpu_backend.cpp:142-175; `vars` holds the variance, as in the CPU backend).  One block per row.
+__global__ void layernorm_forward_kernel(float *__restrict__ y, float *__restrict__ means, float *__restrict__ vars, float *__restrict__ x,
+                                         const float *__restrict__ residual, const float *__restrict__ gamma,
+                                         const float *__restrict__ beta, int d)
+{
+    __shared__ float red[32];
+    const size_t r = blockIdx.x;
+    float *xr = x + r * d;
+    float s = 0.0f;
+    for (int h = threadIdx.x; h < d; h += blockDim.x) {
+        float v = xr[h];
+        if (residual) {
+            v += residual[r * d + h];
+            xr[h] = v;
+        }
+        s += v;
+    }
+    const float mean = block_sum(s, red) / d;
+    float q = 0.0f;
+    for (int h = threadIdx.x; h < d; h += blockDim.x) {
+        const float diff = xr[h] - mean;
+        q += diff * diff;
+    }
+    const float var = block_sum(q, red) / d;
+    if (threadIdx.x == 0) {
+        means[r] = mean;
+        vars[r] = var;
+    }
+    const float sd = sqrtf(var + 1e-5f);
+    for (int h = threadIdx.x; h < d; h += blockDim.x) y[r * d + h] = ((xr[h] - mean) / sd) * gamma[h] + beta[h];
+}
+
+// grad_x = inv_std * (gy*gamma - mean(gy*gamma) - x_hat * mean(gy*gamma*x_hat)) + grad_residual   (cpu_backend.cpp:177-211)
+__global__ void layernorm_backward_dx_kernel(float *__restrict__ grad_x, const float *__restrict__ grad_y,
+                                             const float *__restrict__ grad_residual, const float *__restrict__ x,
+                                             const float *__restrict__ means, const float *__restrict__ vars,
+                                             const float *__restrict__ gamma, int d)
+{
+    __shared__ float red[32];
+    const size_t r = blockIdx.x;
+    const float mean = means[r];
+    const float inv_std = 1.0f / sqrtf(vars[r] + 1e-5f);
+    float s1 = 0.0f, s2 = 0.0f;
+    for (int h = threadIdx.x; h < d; h += blockDim.x) {
+        const float xh = (x[r * d + h] - mean) * inv_std;
+        const float gg = grad_y[r * d + h] * gamma[h];
+        s1 += gg;
+        s2 += gg * xh;
+    }
+    s1 = block_sum(s1, red) / d;
+    s2 = block_sum(s2, red) / d;
+    for (int h = threadIdx.x; h < d; h += blockDim.x) {
+        const float xh = (x[r * d + h] - mean) * inv_std;
+        float g = inv_std * (grad_y[r * d + h] * gamma[h] - s1 - xh * s2);
+        if (grad_residual) g += grad_residual[r * d + h];
+        grad_x[r * d + h] = g;
+    }
+}
+
+// Stage 1 of grad_gamma / grad_beta: block (32, 8) covers 32 columns x one chunk of rows.
+__global__ void layernorm_backward_params_partial_kernel(float *__restrict__ ws_gamma, float *__restrict__ ws_beta,
+                                                         const float *__restrict__ grad_y, const float *__restrict__ x,
+                                                         const float *__restrict__ means, const float *__restrict__ vars, int rows, int d,
+                                                         int rows_per_chunk)
+{
+    __shared__ float rg[8][33], rb[8][33];
+    const int col = blockIdx.x * 32 + threadIdx.x;
+    const int chunk = blockIdx.y;
+    const int r0 = chunk * rows_per_chunk, r1 = min(r0 + rows_per_chunk, rows);
+    float sg = 0.0f, sb = 0.0f;
+    if (col < d) {
+        for (int r = r0 + threadIdx.y; r < r1; r += 8) {
+            const float inv_std = 1.0f / sqrtf(vars[r] + 1e-5f);
+            const float g = grad_y[size_t(r) * d + col];
+            sg += g * ((x[size_t(r) * d + col] - means[r]) * inv_std);
+            sb += g;
+        }
+    }
+    rg[threadIdx.y][threadIdx.x] = sg;
+    rb[threadIdx.y][threadIdx.x] = sb;
+    __syncthreads();
+    if (threadIdx.y == 0 && col < d) {
+        float tg = 0.0f, tb = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            tg += rg[i][threadIdx.x];
+            tb += rb[i][threadIdx.x];
+        }
+        ws_gamma[size_t(chunk) * d + col] = tg;
+        ws_beta[size_t(chunk) * d + col] = tb;
+    }
+}
+
+__global__ void layernorm_backward_params_final_kernel(float *__restrict__ grad_gamma, float *__restrict__ grad_beta,
+                                                       const float *__restrict__ ws_gamma, const float *__restrict__ ws_beta, int d, int chunks)
+{
+    const int col = blockIdx.x * blockDim.x + threadIdx.x;
+    if (col >= d) return;
+    float sg = 0.0f, sb = 0.0f;
+    for (int c = 0; c < chunks; ++c) {
+        sg += ws_gamma[size_t(c) * d + col];
+        sb += ws_beta[size_t(c) * d + col];
+    }
+    grad_gamma[col] += sg;
+    grad_beta[col] += sb;
+}
+
+// ------------------------------------------------------------------------------------------------ attention
+//
+// Causal softmax attention on the packed qkv[B, T, 3*D] layout (cpu_backend.cpp:290-433), fp32 throughout.
+// A query (or key) row is owned by TPR adjacent lanes, each holding HD/TPR head dimensions in registers;
+// dot products are completed with TPR-wide shuffles.  K/V (or Q/dO) rows stream through shared memory in
+// tiles of kTile rows and are read as warp-wide broadcasts.
+
+constexpr int kAttnTile = 32;
+constexpr int kAttnRowsPerBlock = 64;  // rows (queries or keys) per block
+
+template <int TPR>
+__device__ __forceinline__ float row_sum(float v)
+{
+#pragma unroll
+    for (int o = TPR / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// y[b, s1, h*HD + :] = softmax_{s2 <= s1}(q.k / sqrt(HD)) . v ;  logsumexp[b, s1, h] = max + log(sum)
+template <int HD, int TPR>
+__global__ void __launch_bounds__(kAttnRowsPerBlock *TPR)
+attention_forward_kernel(float *__restrict__ y, float *__restrict__ logsumexp, const float *__restrict__ qkv, int seq_len, int d_model,
+                         int num_heads)
+{
+    constexpr int DPT = HD / TPR;
+    __shared__ float ks[kAttnTile][HD];
+    __shared__ float vs[kAttnTile][HD];
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int row = blockIdx.x * kAttnRowsPerBlock + threadIdx.x / TPR;  // query index s1
+    const int part = threadIdx.x % TPR;
+    const int stride = 3 * d_model;
+    const float scale = 1.0f / sqrtf(static_cast<float>(HD));
+    const float *base = qkv + size_t(b) * seq_len * stride + h * HD;
+    const bool valid = row < seq_len;
+
+    float q[DPT], acc[DPT];
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+        q[i] = valid ? base[size_t(row) * stride + part * DPT + i] : 0.0f;
+        acc[i] = 0.0f;
+    }
+    float m = -FLT_MAX, l = 0.0f;
+    const int last_row = min(seq_len, (blockIdx.x + 1) * kAttnRowsPerBlock) - 1;  // largest query in this block
+    for (int t0 = 0; t0 <= last_row; t0 += kAttnTile) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < kAttnTile * HD; i += blockDim.x) {
+            const int r = i / HD, c = i % HD;
+            const int s2 = t0 + r;
+            ks[r][c] = s2 < seq_len ? base[size_t(s2) * stride + d_model + c] : 0.0f;
+            vs[r][c] = s2 < seq_len ? base[size_t(s2) * stride + 2 * d_model + c] : 0.0f;
+        }
+        __syncthreads();
+        const int tend = row - t0 + 1;                               // this row uses keys s2 <= row
+        const int tmax = min(kAttnTile, last_row - t0 + 1);          // block-uniform bound: shuffles stay convergent
+        for (int r = 0; r < tmax; ++r) {
+            float sc = 0.0f;
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) sc += q[i] * ks[r][part * DPT + i];
+            sc = row_sum<TPR>(sc) * scale;
+            if (r >= tend) continue;
+            const float m_new = fmaxf(m, sc);
+            const float corr = expf(m - m_new);
+            const float p = expf(sc - m_new);
+            l = l * corr + p;
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) acc[i] = acc[i] * corr + p * vs[r][part * DPT + i];
+            m = m_new;
+        }
+    }
+    if (valid) {
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) y[(size_t(b) * seq_len + row) * d_model + h * HD + part * DPT + i] = acc[i] / l;
+        if (part == 0) logsumexp[(size_t(b) * seq_len + row) * num_heads + h] = m + logf(l);
+    }
+}
+
+// D[b, s, h] = sum_d grad_y * y  (per head)
+__global__ void attention_rowsum_kernel(float *__restrict__ dcache, const float *__restrict__ grad_y, const float *__restrict__ y,
+                                        int rows, int d_model, int num_heads)
+{
+    const int hd = d_model / num_heads;
+    const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;  // (row, head)
+    if (idx >= size_t(rows) * num_heads) return;
+    const size_t r = idx / num_heads;
+    const int h = idx % num_heads;
+    float s = 0.0f;
+    for (int d = 0; d < hd; ++d) s += grad_y[r * d_model + h * hd + d] * y[r * d_model + h * hd + d];
+    dcache[idx] = s;
+}
+
+// grad_q[s1] = sum_{s2 <= s1} dS . k[s2],  dS = p (dP - D) / sqrt(HD), p = exp(q.k/sqrt(HD) - L), dP = dO . v
+template <int HD, int TPR>
+__global__ void __launch_bounds__(kAttnRowsPerBlock *TPR)
+attention_backward_dq_kernel(float *__restrict__ grad_qkv, const float *__restrict__ dcache, const float *__restrict__ logsumexp,
+                             const float *__restrict__ grad_y, const float *__restrict__ qkv, int seq_len, int d_model, int num_heads)
+{
+    constexpr int DPT = HD / TPR;
+    __shared__ float ks[kAttnTile][HD];
+    __shared__ float vs[kAttnTile][HD];
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int row = blockIdx.x * kAttnRowsPerBlock + threadIdx.x / TPR;
+    const int part = threadIdx.x % TPR;
+    const int stride = 3 * d_model;
+    const float scale = 1.0f / sqrtf(static_cast<float>(HD));
+    const float *base = qkv + size_t(b) * seq_len * stride + h * HD;
+    const bool valid = row < seq_len;
+    float q[DPT], go[DPT], dq[DPT];
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+        q[i] = valid ? base[size_t(row) * stride + part * DPT + i] : 0.0f;
+        go[i] = valid ? grad_y[(size_t(b) * seq_len + row) * d_model + h * HD + part * DPT + i] : 0.0f;
+        dq[i] = 0.0f;
+    }
+    const float L = valid ? logsumexp[(size_t(b) * seq_len + row) * num_heads + h] : 0.0f;
+    const float Dv = valid ? dcache[(size_t(b) * seq_len + row) * num_heads + h] : 0.0f;
+    const int last_row = min(seq_len, (blockIdx.x + 1) * kAttnRowsPerBlock) - 1;
+    for (int t0 = 0; t0 <= last_row; t0 += kAttnTile) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < kAttnTile * HD; i += blockDim.x) {
+            const int r = i / HD, c = i % HD;
+            const int s2 = t0 + r;
+            ks[r][c] = s2 < seq_len ? base[size_t(s2) * stride + d_model + c] : 0.0f;
+            vs[r][c] = s2 < seq_len ? base[size_t(s2) * stride + 2 * d_model + c] : 0.0f;
+        }
+        __syncthreads();
+        const int tend = row - t0 + 1;
+        const int tmax = min(kAttnTile, last_row - t0 + 1);
+        for (int r = 0; r < tmax; ++r) {
+            float sc = 0.0f, dp = 0.0f;
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) {
+                sc += q[i] * ks[r][part * DPT + i];
+                dp += go[i] * vs[r][part * DPT + i];
+            }
+            sc = row_sum<TPR>(sc);
+            dp = row_sum<TPR>(dp);
+            if (r >= tend) continue;
+            const float p = expf(sc * scale - L);
+            const float ds = p * (dp - Dv) * scale;
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) dq[i] += ds * ks[r][part * DPT + i];
+        }
+    }
+    if (valid) {
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) grad_qkv[(size_t(b) * seq_len + row) * stride + h * HD + part * DPT + i] = dq[i];
+    }
+}
+
+// grad_k[s2] = sum_{s1 >= s2} dS . q[s1],  grad_v[s2] = sum_{s1 >= s2} p . dO[s1]
+template <int HD, int TPR>
+__global__ void __launch_bounds__(kAttnRowsPerBlock *TPR)
+attention_backward_dkv_kernel(float *__restrict__ grad_qkv, const float *__restrict__ dcache, const float *__restrict__ logsumexp,
+                              const float *__restrict__ grad_y, const float *__restrict__ qkv, int seq_len, int d_model, int num_heads)
+{
+    constexpr int DPT = HD / TPR;
+    __shared__ float qs[kAttnTile][HD];
+    __shared__ float gs[kAttnTile][HD];
+    __shared__ float Ls[kAttnTile], Ds[kAttnTile];
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int row = blockIdx.x * kAttnRowsPerBlock + threadIdx.x / TPR;  // key index s2
+    const int part = threadIdx.x % TPR;
+    const int stride = 3 * d_model;
+    const float scale = 1.0f / sqrtf(static_cast<float>(HD));
+    const float *base = qkv + size_t(b) * seq_len * stride + h * HD;
+    const bool valid = row < seq_len;
+    float k[DPT], v[DPT], dk[DPT], dv[DPT];
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+        k[i] = valid ? base[size_t(row) * stride + d_model + part * DPT + i] : 0.0f;
+        v[i] = valid ? base[size_t(row) * stride + 2 * d_model + part * DPT + i] : 0.0f;
+        dk[i] = 0.0f;
+        dv[i] = 0.0f;
+    }
+    const int first_row = blockIdx.x * kAttnRowsPerBlock;  // smallest key in this block
+    for (int t0 = (first_row / kAttnTile) * kAttnTile; t0 < seq_len; t0 += kAttnTile) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < kAttnTile * HD; i += blockDim.x) {
+            const int r = i / HD, c = i % HD;
+            const int s1 = t0 + r;
+            qs[r][c] = s1 < seq_len ? base[size_t(s1) * stride + c] : 0.0f;
+            gs[r][c] = s1 < seq_len ? grad_y[(size_t(b) * seq_len + s1) * d_model + h * HD + c] : 0.0f;
+        }
+        for (int r = threadIdx.x; r < kAttnTile; r += blockDim.x) {
+            const int s1 = t0 + r;
+            Ls[r] = s1 < seq_len ? logsumexp[(size_t(b) * seq_len + s1) * num_heads + h] : 0.0f;
+            Ds[r] = s1 < seq_len ? dcache[(size_t(b) * seq_len + s1) * num_heads + h] : 0.0f;
+        }
+        __syncthreads();
+        const int rbeg = max(0, first_row - t0);              // block-uniform bounds: shuffles stay convergent
+        const int rend = min(kAttnTile, seq_len - t0);
+        for (int r = rbeg; r < rend; ++r) {
+            float sc = 0.0f, dp = 0.0f;
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) {
+                sc += qs[r][part * DPT + i] * k[i];
+                dp += gs[r][part * DPT + i] * v[i];
+            }
+            sc = row_sum<TPR>(sc);
+            dp = row_sum<TPR>(dp);
+            if (t0 + r < row) continue;                       // this key only sees queries s1 >= row
+            const float p = expf(sc * scale - Ls[r]);
+            const float ds = p * (dp - Ds[r]) * scale;
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) {
+                dk[i] += ds * qs[r][part * DPT + i];
+                dv[i] += p * gs[r][part * DPT + i];
+            }
+        }
+    }
+    if (valid) {
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) {
+            grad_qkv[(size_t(b) * seq_len + row) * stride + d_model + h * HD + part * DPT + i] = dk[i];
+            grad_qkv[(size_t(b) * seq_len + row) * stride + 2 * d_model + h * HD + part * DPT + i] = dv[i];
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ softmax / cross-entropy
+
+// y[r, :V] = softmax(x[r, :V]); y[r, V:Vp] = 0       (cpu_backend.cpp:435-472).  One block per row.
+__global__ void softmax_forward_kernel(float *__restrict__ y, const float *__restrict__ x, int v, int vp)
+{
+    __shared__ float red[32];
+    const size_t r = blockIdx.x;
+    const float *xr = x + r * vp;
+    float *yr = y + r * vp;
+    float m = -FLT_MAX;
+    for (int i = threadIdx.x; i < v; i += blockDim.x) m = fmaxf(m, xr[i]);
+    m = block_max(m, red);
+    float s = 0.0f;
+    for (int i = threadIdx.x; i < v; i += blockDim.x) {
+        const float e = expf(xr[i] - m);
+        yr[i] = e;
+        s += e;
+    }
+    s = block_sum(s, red);
+    for (int i = threadIdx.x; i < v; i += blockDim.x) yr[i] /= s;
+    for (int i = v + threadIdx.x; i < vp; i += blockDim.x) yr[i] = 0.0f;
+}
+
+// grad_x[r, :V] = (p - onehot(label)) / rows; padding columns are left as they are   (cpu_backend.cpp:474-491)
+__global__ void cross_entropy_softmax_backward_kernel(float *__restrict__ grad_x, const float *__restrict__ probs,
+                                                      const int *__restrict__ labels, int rows, int v, int vp)
+{
+    const size_t r = blockIdx.x;
+    const int label = labels[r];
+    const float inv = static_cast<float>(rows);
+    for (int i = threadIdx.x; i < v; i += blockDim.x) grad_x[r * vp + i] = (probs[r * vp + i] - (i == label ? 1.0f : 0.0f)) / inv;
+}
+
+// loss = -(1/rows) sum_r log(p[r, label[r]] + 1e-8)   (cpu_backend.cpp:493-509).  Single block, fixed order per thread.
+__global__ void cross_entropy_loss_kernel(float *__restrict__ loss, const float *__restrict__ probs, const int *__restrict__ labels, int rows,
+                                          int vp)
+{
+    __shared__ float red[32];
+    float s = 0.0f;
+    for (int r = threadIdx.x; r < rows; r += blockDim.x) s -= logf(probs[size_t(r) * vp + labels[r]] + 1e-8f);
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) *loss = s / static_cast<float>(rows);
+}
+
+// ------------------------------------------------------------------------------------------------ optimiser
+
+// AdamW with decoupled weight decay (cpu_backend.cpp:511-526); the bias-correction powers come from the host.
+__global__ void adamw_kernel(float *__restrict__ p, const float *__restrict__ g, float *__restrict__ m, float *__restrict__ v, size_t n,
+                             float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2)
+{
+    const size_t stride = size_t(gridDim.x) * blockDim.x;
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float gi = g[i];
+        const float mi = beta1 * m[i] + (1.0f - beta1) * gi;
+        const float vi = beta2 * v[i] + (1.0f - beta2) * gi * gi;
+        m[i] = mi;
+        v[i] = vi;
+        const float m_hat = mi / bc1;
+        const float v_hat = vi / bc2;
+        p[i] -= lr * (m_hat / (sqrtf(v_hat) + eps) + wd * p[i]);
+    }
+}
+
+// Gradient scaling and global-norm clipping (cpu_backend.cpp:528-556) without a host round trip:
+// stage 1 scales by 1/accum_steps and writes per-block sums of squares, stage 2 adds them in order and
+// stores the clip factor, stage 3 applies it when the norm exceeds max_norm.
+__global__ void clip_scale_partial_kernel(float *__restrict__ g, float *__restrict__ partial, size_t n, float inv_accum)
+{
+    __shared__ float red[32];
+    const size_t per = (n + gridDim.x - 1) / gridDim.x;
+    const size_t i0 = size_t(blockIdx.x) * per, i1 = min(n, i0 + per);
+    float s = 0.0f;
+    for (size_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
+        const float v = g[i] * inv_accum;
+        g[i] = v;
+        s += v * v;
+    }
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) partial[blockIdx.x] = s;
+}
+
+__global__ void clip_factor_kernel(float *__restrict__ factor, const float *__restrict__ partial, int blocks, float max_norm)
+{
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    float s = 0.0f;
+    for (int i = 0; i < blocks; ++i) s += partial[i];
+    const float norm = sqrtf(s);
+    *factor = norm <= max_norm ? 1.0f : max_norm / (norm + 1e-6f);
+}
+
+__global__ void clip_apply_kernel(float *__restrict__ g, const float *__restrict__ factor, size_t n)
+{
+    const float f = *factor;
+    if (f == 1.0f) return;
+    const size_t stride = size_t(gridDim.x) * blockDim.x;
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) g[i] *= f;
+}
+
+}  // namespace ops
+}  // namespace gptb200

@@ -1,0 +1,58 @@
+// Internal definition of the context behind include/gptb200.h, shared by the translation units of
+// libgptb200 (never installed, never seen by callers).
+#pragma once
+
+#include <cstdarg>
+#include <cstdio>
+#include <set>
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "../../include/gptb200.h"
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct gptb200_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    int mode = GPTB200_MODE_3XTF32;
+    int num_sms = 0;
+    int tile_n = 0;      // 0 = automatic
+    int max_splits = 0;  // 0 = automatic
+    int *d_status = nullptr;
+    float *ws = nullptr;  // scratch: split-K partial tiles, partial rows of column reductions
+    size_t ws_bytes = 0;
+    size_t ws_limit = size_t(1) << 30;
+    EncodeTiledFn encode = nullptr;
+    long long launches = 0;
+    std::set<const void *> configured;  // kernels whose dynamic shared-memory limit has been raised
+    char last_error[512] = {0};
+};
+
+namespace gptb200 {
+
+inline int fail(gptb200_ctx *ctx, int code, const char *fmt, ...)
+{
+    if (ctx) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(ctx->last_error, sizeof(ctx->last_error), fmt, ap);
+        va_end(ap);
+    }
+    return code;
+}
+
+// Grows the context's scratch buffer to at least `bytes` (waits for queued work before replacing it).
+int ensure_workspace(gptb200_ctx *ctx, size_t bytes);
+
+}  // namespace gptb200
+
+#define CUDA_TRY(ctx, expr)                                                                                          \
+    do {                                                                                                             \
+        cudaError_t e_ = (expr);                                                                                     \
+        if (e_ != cudaSuccess)                                                                                       \
+            return gptb200::fail(ctx, GPTB200_ERR_CUDA, "%s:%d %s -> %s", __FILE__, __LINE__, #expr, cudaGetErrorString(e_)); \
+    } while (0)

@@ -96,6 +96,34 @@ int gptb200_memset(gptb200_ctx *ctx, void *ptr, int value, size_t bytes);
 int gptb200_memcpy_h2d(gptb200_ctx *ctx, void *dst, const void *src, size_t bytes);
 int gptb200_memcpy_d2h(gptb200_ctx *ctx, void *dst, const void *src, size_t bytes);
 
+/* ---- the remaining operators of IGPTBackend (backend_interface.h:26-40, 53-68, 84-118, 161-237), as plain
+ *      kernels so that a whole training step can run behind the interface on the GPU.  They are not on the
+ *      linear-layer hot path; arithmetic follows the reference CPU backend (cpu/cpu_backend.cpp).
+ *      rows = batch_size * seq_len wherever only the product matters. */
+int gptb200_fill_normal(gptb200_ctx *ctx, float *ptr, float mean, float stddev, size_t count, unsigned long long seed,
+                        unsigned long long offset);
+int gptb200_fill_const(gptb200_ctx *ctx, float *ptr, float value, size_t count);
+int gptb200_embedding_forward(gptb200_ctx *ctx, float *y, const float *wte, const float *wpe, const int *tokens, int batch, int seq_len,
+                              int d);
+int gptb200_embedding_backward(gptb200_ctx *ctx, float *grad_wte, float *grad_wpe, const float *grad_y, const int *tokens, int batch,
+                               int seq_len, int d);
+int gptb200_layernorm_forward(gptb200_ctx *ctx, float *y, float *means, float *vars, float *x, const float *residual, const float *gamma,
+                              const float *beta, int rows, int d);
+int gptb200_layernorm_backward(gptb200_ctx *ctx, float *grad_x, float *grad_gamma, float *grad_beta, const float *grad_y,
+                               const float *grad_residual, const float *x, const float *means, const float *vars, const float *gamma,
+                               int rows, int d);
+int gptb200_attention_forward(gptb200_ctx *ctx, float *y, float *logsumexp, const float *qkv, int batch, int seq_len, int d, int heads);
+int gptb200_attention_backward(gptb200_ctx *ctx, float *grad_qkv, float *d_cache, const float *logsumexp, const float *grad_y,
+                               const float *y, const float *qkv, int batch, int seq_len, int d, int heads);
+int gptb200_softmax_forward(gptb200_ctx *ctx, float *y, const float *x, int rows, int vocab, int vocab_padded);
+int gptb200_cross_entropy_softmax_backward(gptb200_ctx *ctx, float *grad_x, const float *probs, const int *labels, int rows, int vocab,
+                                           int vocab_padded);
+int gptb200_cross_entropy_loss(gptb200_ctx *ctx, float *loss, const float *probs, const int *labels, int rows, int vocab_padded);
+int gptb200_adamw_step(gptb200_ctx *ctx, float *params, const float *g, float *m, float *v, size_t count, float lr, float beta1,
+                       float beta2, float eps, float weight_decay, int step);
+int gptb200_scale_and_clip_grad(gptb200_ctx *ctx, float *g, size_t count, float max_norm, int accum_steps);
+int gptb200_memory_info(gptb200_ctx *ctx, float *free_mb, float *total_mb);
+
 #ifdef __cplusplus
 }
 #endif

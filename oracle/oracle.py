@@ -132,6 +132,8 @@ class Reference(_Ops):
         self.lib.ref_cross_entropy_softmax_backward.restype = None
         self.lib.ref_gpt_forward_backward.argtypes = [_i, _f, ctypes.c_longlong, _i, _i, _c, _c, _c, _f, _f, ctypes.c_void_p]
         self.lib.ref_gpt_forward_backward.restype = _c
+        self.lib.ref_gpt_forward_backward_on.argtypes = [ctypes.c_void_p, _i, _f, ctypes.c_longlong, _i, _i, _c, _c, _f, _f, ctypes.c_void_p]
+        self.lib.ref_gpt_forward_backward_on.restype = _c
 
     def softmax_forward(self, logits, vocab_size: int):
         logits = _f32(logits)
@@ -150,8 +152,9 @@ class Reference(_Ops):
         return g
 
     def gpt_forward_backward(self, cfg: dict, weights, inputs, labels, batch: int, seq: int, restated_ops: bool = False,
-                             want_logits: bool = False):
-        """One zero_grad/forward/backward/loss of the reference GPT class.  Returns (grads, loss, logits|None)."""
+                             want_logits: bool = False, backend_ptr: int | None = None):
+        """One zero_grad/forward/backward/loss of the reference GPT class.  Returns (grads, loss, logits|None).
+        `backend_ptr`: address of an IGPTBackend object to run on instead of the reference CPU backend."""
         c = np.array([cfg[k] for k in ("max_seq_len", "vocab_size", "vocab_size_padded", "num_layers", "num_heads", "d_model", "d_ffn")],
                      dtype=np.int32)
         weights = _f32(weights)
@@ -160,8 +163,12 @@ class Reference(_Ops):
         grads = np.empty_like(weights)
         loss = np.zeros(1, np.float32)
         logits = np.empty((batch * seq, cfg["vocab_size_padded"]), np.float32) if want_logits else None
-        rc = self.lib.ref_gpt_forward_backward(c, weights, weights.size, inputs, labels, batch, seq, int(restated_ops), grads, loss,
-                                               logits.ctypes.data if want_logits else None)
+        if backend_ptr is not None:
+            rc = self.lib.ref_gpt_forward_backward_on(ctypes.c_void_p(backend_ptr), c, weights, weights.size, inputs, labels, batch, seq, grads,
+                                                      loss, logits.ctypes.data if want_logits else None)
+        else:
+            rc = self.lib.ref_gpt_forward_backward(c, weights, weights.size, inputs, labels, batch, seq, int(restated_ops), grads, loss,
+                                                   logits.ctypes.data if want_logits else None)
         if rc != 0:
             raise RuntimeError(f"ref_gpt_forward_backward failed with code {rc}")
         return grads, float(loss[0]), logits

@@ -86,11 +86,20 @@ int run_gpt(IGPTBackend *be, const int *cfg, const float *weights, long long n_w
     if (!ok) return 4;
 
     model.set_size(batch, seq);
+    // tokens live in the backend's memory space (src/model/gpt_test.cpp:128-137)
+    int *d_inputs = nullptr, *d_labels = nullptr;
+    const size_t tok_bytes = (size_t)batch * seq * sizeof(int);
+    be->device_malloc((void **)&d_inputs, tok_bytes);
+    be->device_malloc((void **)&d_labels, tok_bytes);
+    be->device_memcpy_h2d(d_inputs, inputs, tok_bytes);
+    be->device_memcpy_h2d(d_labels, labels, tok_bytes);
     // same sequence as src/model/gpt_test.cpp:148-164
     model.zero_grad();
-    model.forward(inputs);
-    model.backward(inputs, labels);
-    const float loss = model.loss(labels);
+    model.forward(d_inputs);
+    model.backward(d_inputs, d_labels);
+    const float loss = model.loss(d_labels);
+    be->device_free(d_inputs);
+    be->device_free(d_labels);
     if (loss_out) *loss_out = loss;
     if (grads_out) be->device_memcpy_d2h(grads_out, model.grad_weights()->buffer_, (size_t)n_weights * sizeof(float));
     if (logits_out)
@@ -155,6 +164,14 @@ int ref_gpt_forward_backward(const int *cfg, const float *weights, long long n_w
     }
     CPUBackend be;
     return run_gpt(&be, cfg, weights, n_weights, inputs, labels, batch, seq, grads_out, loss_out, logits_out);
+}
+
+// The same forward+backward of the reference's GPT class on a backend object supplied by the caller (an
+// IGPTBackend* made elsewhere, e.g. by the product library's factory): the drop-in check.
+int ref_gpt_forward_backward_on(void *backend, const int *cfg, const float *weights, long long n_weights, const int *inputs,
+                                const int *labels, int batch, int seq, float *grads_out, float *loss_out, float *logits_out)
+{
+    return run_gpt(static_cast<IGPTBackend *>(backend), cfg, weights, n_weights, inputs, labels, batch, seq, grads_out, loss_out, logits_out);
 }
 
 }  // extern "C"

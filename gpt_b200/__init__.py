@@ -215,3 +215,152 @@ class Backend:
     def device_memcpy_d2h(self, dst: int, src: int, nbytes: int) -> None:
         self._check(self._lib.gptb200_memcpy_d2h(self._ctx, ctypes.c_void_p(dst), ctypes.c_void_p(src), nbytes),
                     "gptb200_memcpy_d2h")
+
+
+PARAM_NAMES = ["wte", "wpe", "ln_1_w", "ln_1_b", "qkv_proj_w", "qkv_proj_b", "attn_proj_w", "attn_proj_b", "ln_2_w", "ln_2_b",
+               "ffn_up_w", "ffn_up_b", "ffn_down_w", "ffn_down_b", "ln_f_w", "ln_f_b"]
+CONFIG_KEYS = ["max_seq_len", "vocab_size", "vocab_size_padded", "num_layers", "num_heads", "d_model", "d_ffn"]
+GPT2_124M = dict(max_seq_len=256, vocab_size=50257, vocab_size_padded=50304, num_layers=12, num_heads=12, d_model=768, d_ffn=3072)
+
+_LAYER_DONE = ctypes.CFUNCTYPE(None, ctypes.c_int, ctypes.c_void_p)
+
+
+def _declare_model(lib: ctypes.CDLL) -> None:
+    if getattr(lib, "_model_declared", False):
+        return
+    vp, i, f32, ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+    sig = {
+        "gptb200_model_create": (i, [ctypes.POINTER(vp), ctypes.POINTER(i), i, vp, i, ctypes.c_ulong, i]),
+        "gptb200_model_destroy": (i, [vp]),
+        "gptb200_model_context": (vp, [vp]),
+        "gptb200_model_num_params": (ll, [vp]),
+        "gptb200_model_weights": (vp, [vp]),
+        "gptb200_model_grads": (vp, [vp]),
+        "gptb200_model_logits": (vp, [vp]),
+        "gptb200_model_param_offsets": (i, [vp, ctypes.POINTER(ll)]),
+        "gptb200_model_init": (i, [vp, f32, f32]),
+        "gptb200_model_load_weights": (i, [vp, vp, ll]),
+        "gptb200_model_read": (i, [vp, vp, ll, i]),
+        "gptb200_model_load_checkpoint": (i, [vp, ctypes.c_char_p]),
+        "gptb200_model_save_checkpoint": (i, [vp, ctypes.c_char_p]),
+        "gptb200_model_set_size": (i, [vp, i, i]),
+        "gptb200_model_zero_grad": (i, [vp]),
+        "gptb200_model_forward": (i, [vp, vp]),
+        "gptb200_model_backward": (i, [vp, vp, vp, _LAYER_DONE, vp]),
+        "gptb200_model_loss": (i, [vp, vp, ctypes.POINTER(f32)]),
+        "gptb200_model_clip": (i, [vp, f32, i]),
+        "gptb200_model_optimizer_step": (i, [vp, f32, f32, f32, f32]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    lib._model_declared = True
+
+
+class Model:
+    """Host-side mirror of the reference's GPT class (src/model/gpt.h:135-173) over the B200 backend: same method
+    names, same parameter packing, raw-fp32 checkpoints interchangeable with the reference's."""
+
+    def __init__(self, config: dict, device: int = 0, stream: int | None = None, mode: int = MODE_3XTF32, seed: int = 42,
+                 use_grad: bool = True):
+        self._lib = load_library()
+        _declare_model(self._lib)
+        self.config = dict(config)
+        cfg = (ctypes.c_int * 7)(*[int(config[k]) for k in CONFIG_KEYS])
+        self._m = ctypes.c_void_p()
+        rc = self._lib.gptb200_model_create(ctypes.byref(self._m), cfg, device, ctypes.c_void_p(stream or 0), mode, seed, int(use_grad))
+        if rc != 0:
+            raise GptB200Error(rc, "gptb200_model_create", self._lib.gptb200_status_string(rc).decode())
+        self.num_params = int(self._lib.gptb200_model_num_params(self._m))
+        off = (ctypes.c_longlong * 16)()
+        self._check(self._lib.gptb200_model_param_offsets(self._m, off))
+        self.param_offsets = dict(zip(PARAM_NAMES, [int(v) for v in off]))
+        self._cb_keepalive = None
+
+    def _check(self, rc: int) -> None:
+        if rc != 0:
+            ctx = self._lib.gptb200_model_context(self._m)
+            raise GptB200Error(rc, "gptb200_model", self._lib.gptb200_last_error(ctx).decode() if ctx else "")
+
+    def close(self) -> None:
+        if self._m:
+            self._lib.gptb200_model_destroy(self._m)
+            self._m = ctypes.c_void_p()
+
+    def __del__(self):  # pragma: no cover
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def context(self) -> int:
+        return int(self._lib.gptb200_model_context(self._m))
+
+    @property
+    def weights_ptr(self) -> int:
+        return int(self._lib.gptb200_model_weights(self._m))
+
+    @property
+    def grads_ptr(self) -> int:
+        return int(self._lib.gptb200_model_grads(self._m))
+
+    @property
+    def logits_ptr(self) -> int:
+        return int(self._lib.gptb200_model_logits(self._m))
+
+    def launch_count(self) -> int:
+        return int(self._lib.gptb200_ctx_launch_count(ctypes.c_void_p(self.context)))
+
+    def synchronize(self) -> None:
+        self._check(self._lib.gptb200_ctx_synchronize(ctypes.c_void_p(self.context)))
+
+    def init(self, mean: float = 0.0, stddev: float = 0.02) -> None:
+        self._check(self._lib.gptb200_model_init(self._m, mean, stddev))
+
+    def load_weights(self, host_array) -> None:
+        """host_array: contiguous float32 numpy array in the reference's checkpoint order."""
+        self._check(self._lib.gptb200_model_load_weights(self._m, host_array.ctypes.data, host_array.size))
+
+    def read_weights(self, out) -> None:
+        self._check(self._lib.gptb200_model_read(self._m, out.ctypes.data, out.size, 0))
+
+    def read_grads(self, out) -> None:
+        self._check(self._lib.gptb200_model_read(self._m, out.ctypes.data, out.size, 1))
+
+    def load_checkpoint(self, filename: str) -> None:
+        self._check(self._lib.gptb200_model_load_checkpoint(self._m, filename.encode()))
+
+    def save_checkpoint(self, filename: str) -> None:
+        self._check(self._lib.gptb200_model_save_checkpoint(self._m, filename.encode()))
+
+    def set_size(self, batch_size: int, seq_len: int) -> None:
+        self._check(self._lib.gptb200_model_set_size(self._m, batch_size, seq_len))
+
+    def zero_grad(self) -> None:
+        self._check(self._lib.gptb200_model_zero_grad(self._m))
+
+    def forward(self, input_tokens) -> None:
+        self._check(self._lib.gptb200_model_forward(self._m, _ptr(input_tokens)))
+
+    def backward(self, input_tokens, label_tokens, layer_done=None) -> None:
+        """layer_done(l): host callback fired when layer l's weight gradients have been enqueued
+        (l = num_layers: un-embedding + final LayerNorm; l = -1: embeddings, i.e. everything)."""
+        if layer_done is None:
+            cb = ctypes.cast(None, _LAYER_DONE)
+        else:
+            cb = _LAYER_DONE(lambda l, _u: layer_done(l))
+        self._cb_keepalive = cb
+        self._check(self._lib.gptb200_model_backward(self._m, _ptr(input_tokens), _ptr(label_tokens), cb, None))
+
+    def loss(self, label_tokens) -> float:
+        out = ctypes.c_float()
+        self._check(self._lib.gptb200_model_loss(self._m, _ptr(label_tokens), ctypes.byref(out)))
+        return float(out.value)
+
+    def unscale_and_clip_grads(self, max_norm: float, accum_steps: int) -> None:
+        self._check(self._lib.gptb200_model_clip(self._m, max_norm, accum_steps))
+
+    def optimizer_step(self, learning_rate: float, beta1: float, beta2: float, decay: float) -> None:
+        self._check(self._lib.gptb200_model_optimizer_step(self._m, learning_rate, beta1, beta2, decay))

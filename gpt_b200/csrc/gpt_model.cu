@@ -1,0 +1,425 @@
+// GptModel: host-side driver of one GPT-2 training / inference step over an IGPTBackend.
+//
+// It issues the operator sequence of the reference's model class (src/model/gpt.cpp:426-642: embedding,
+// per layer LN1 -> QKV -> attention -> projection -> LN2 -> FFN up (GELU) -> FFN down, final LN, un-embedding,
+// softmax; and the mirror image for the backward pass) and keeps the reference's parameter packing
+// (src/model/gpt.cpp:46-62: sixteen tensors, kind-major, all layers of a kind contiguous, no padding), so raw
+// fp32 checkpoints of the reference load unchanged and gradient buffers compare element for element.
+//
+// What is added for data-parallel training: the backward pass can report, layer by layer, that the weight
+// gradients of a layer are complete (a host callback fired right after that layer's operators were enqueued),
+// so that the caller can start all-reducing finished slices on another stream while the remaining layers run.
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+
+#include "backend_interface.h"
+#include "b200_backend.h"
+#include "../../include/gptb200.h"
+
+namespace {
+
+struct Config {
+    int max_seq_len, vocab, vocab_padded, layers, heads, d_model, d_ffn;
+};
+
+// Offsets (in floats) of the sixteen parameter tensors inside one packed buffer.
+struct ParamLayout {
+    size_t wte, wpe, ln1_w, ln1_b, qkv_w, qkv_b, proj_w, proj_b, ln2_w, ln2_b, up_w, up_b, down_w, down_b, lnf_w, lnf_b, total;
+    explicit ParamLayout(const Config &c)
+    {
+        const size_t L = c.layers, D = c.d_model, F = c.d_ffn;
+        size_t o = 0;
+        auto take = [&](size_t n) { const size_t at = o; o += n; return at; };
+        wte = take(size_t(c.vocab_padded) * D);
+        wpe = take(size_t(c.max_seq_len) * D);
+        ln1_w = take(L * D);
+        ln1_b = take(L * D);
+        qkv_w = take(L * D * 3 * D);
+        qkv_b = take(L * 3 * D);
+        proj_w = take(L * D * D);
+        proj_b = take(L * D);
+        ln2_w = take(L * D);
+        ln2_b = take(L * D);
+        up_w = take(L * D * F);
+        up_b = take(L * F);
+        down_w = take(L * F * D);
+        down_b = take(L * D);
+        lnf_w = take(D);
+        lnf_b = take(D);
+        total = o;
+    }
+};
+
+size_t pad4(size_t n) { return (n + 3) & ~size_t(3); }
+
+class GptModel
+{
+public:
+    GptModel(IGPTBackend *be, const Config &c, bool use_grad) : be_(be), c_(c), lay_(c), use_grad_(use_grad)
+    {
+        const int nbuf = use_grad ? 4 : 1;  // weights, gradients, Adam first and second moments
+        for (int i = 0; i < nbuf; ++i) {
+            void *p = nullptr;
+            be_->device_malloc(&p, lay_.total * sizeof(float));
+            be_->device_memset(p, 0, lay_.total * sizeof(float));
+            bufs_[i] = static_cast<float *>(p);
+        }
+        void *l = nullptr;
+        be_->device_malloc(&l, sizeof(float));
+        loss_dev_ = static_cast<float *>(l);
+    }
+
+    ~GptModel()
+    {
+        release_activations();
+        for (float *b : bufs_)
+            if (b) be_->device_free(b);
+        if (loss_dev_) be_->device_free(loss_dev_);
+    }
+
+    float *weights() { return bufs_[0]; }
+    float *grads() { return bufs_[1]; }
+    size_t num_params() const { return lay_.total; }
+    const ParamLayout &layout() const { return lay_; }
+
+    // Same initialisation as the reference (src/model/gpt.cpp:297-325) plus zeroed padding rows of wte.
+    void init(float mean, float stddev)
+    {
+        float *w = weights();
+        const size_t L = c_.layers, D = c_.d_model, F = c_.d_ffn;
+        be_->device_fill_normal(w, mean, stddev, lay_.total);
+        const float resid = stddev / sqrtf(2.0f * c_.layers);
+        be_->device_fill_normal(w + lay_.proj_w, mean, resid, L * D * D);
+        be_->device_fill_normal(w + lay_.down_w, mean, resid, L * F * D);
+        for (size_t off : {lay_.ln1_w, lay_.ln2_w}) be_->device_fill_const(w + off, 1.0f, L * D);
+        be_->device_fill_const(w + lay_.lnf_w, 1.0f, D);
+        for (size_t off : {lay_.ln1_b, lay_.proj_b, lay_.ln2_b, lay_.down_b}) be_->device_fill_const(w + off, 0.0f, L * D);
+        be_->device_fill_const(w + lay_.qkv_b, 0.0f, L * 3 * D);
+        be_->device_fill_const(w + lay_.up_b, 0.0f, L * F);
+        be_->device_fill_const(w + lay_.lnf_b, 0.0f, D);
+        be_->device_fill_const(w + lay_.wte + size_t(c_.vocab) * D, 0.0f, size_t(c_.vocab_padded - c_.vocab) * D);
+    }
+
+    void set_size(int batch, int seq)
+    {
+        release_activations();
+        B_ = batch;
+        T_ = seq;
+        const size_t M = size_t(batch) * seq, L = c_.layers, D = c_.d_model, F = c_.d_ffn, H = c_.heads, Vp = c_.vocab_padded;
+        size_t o = 0;
+        auto take = [&](size_t n) { const size_t at = o; o += pad4(n); return at; };
+        a_.x_emb = take(M * D);
+        a_.ln1 = take(L * M * D); a_.ln1_mean = take(L * M); a_.ln1_var = take(L * M);
+        a_.qkv = take(L * M * 3 * D); a_.lse = take(L * M * H); a_.attn = take(L * M * D); a_.proj = take(L * M * D);
+        a_.ln2 = take(L * M * D); a_.ln2_mean = take(L * M); a_.ln2_var = take(L * M);
+        a_.up = take(L * M * F); a_.act = take(L * M * F); a_.down = take(L * M * D);
+        a_.lnf = take(M * D); a_.lnf_mean = take(M); a_.lnf_var = take(M);
+        a_.logits = take(M * Vp); a_.probs = take(M * Vp);
+        a_.total = o;
+        void *p = nullptr;
+        be_->device_malloc(&p, a_.total * sizeof(float));
+        acts_ = static_cast<float *>(p);
+        if (use_grad_) {
+            // activation gradients are consumed right after they are produced: one set of buffers serves all layers
+            o = 0;
+            g_.d_ln = take(M * D); g_.d_res = take(M * D); g_.d_x = take(M * D); g_.d_qkv = take(M * 3 * D); g_.d_helper = take(M * H);
+            g_.d_f1 = take(M * F); g_.d_f2 = take(M * F); g_.d_logits = take(M * Vp);
+            g_.total = o;
+            be_->device_malloc(&p, g_.total * sizeof(float));
+            be_->device_memset(p, 0, g_.total * sizeof(float));
+            agrads_ = static_cast<float *>(p);
+        }
+    }
+
+    void zero_grad()
+    {
+        if (use_grad_) be_->device_memset(grads(), 0, lay_.total * sizeof(float));
+    }
+
+    void forward(const int *tokens)
+    {
+        const size_t M = size_t(B_) * T_, D = c_.d_model, F = c_.d_ffn, H = c_.heads;
+        float *w = weights(), *A = acts_;
+        be_->device_embedding_forward(A + a_.x_emb, w + lay_.wte, w + lay_.wpe, tokens, B_, T_, c_.d_model);
+        float *stream = A + a_.x_emb;  // residual stream entering the next LayerNorm
+        float *resid = nullptr;        // pending residual, added inside the next LayerNorm
+        for (int l = 0; l < c_.layers; ++l) {
+            float *ln1 = A + a_.ln1 + l * M * D, *qkv = A + a_.qkv + l * M * 3 * D, *attn = A + a_.attn + l * M * D;
+            float *proj = A + a_.proj + l * M * D, *ln2 = A + a_.ln2 + l * M * D, *up = A + a_.up + l * M * F;
+            float *act = A + a_.act + l * M * F, *down = A + a_.down + l * M * D;
+            be_->device_layernorm_residual_fused_forward(ln1, A + a_.ln1_mean + l * M, A + a_.ln1_var + l * M, stream, resid, w + lay_.ln1_w + l * D,
+                                                         w + lay_.ln1_b + l * D, B_, T_, c_.d_model);
+            resid = stream;
+            be_->device_linear_activation_fused_forward(qkv, nullptr, ln1, w + lay_.qkv_w + l * D * 3 * D, w + lay_.qkv_b + l * 3 * D, false, B_, T_,
+                                                        c_.d_model, 3 * c_.d_model);
+            be_->device_flash_attention_forward(attn, A + a_.lse + l * M * H, qkv, B_, T_, c_.d_model, c_.heads);
+            be_->device_linear_activation_fused_forward(proj, nullptr, attn, w + lay_.proj_w + l * D * D, w + lay_.proj_b + l * D, false, B_, T_,
+                                                        c_.d_model, c_.d_model);
+            be_->device_layernorm_residual_fused_forward(ln2, A + a_.ln2_mean + l * M, A + a_.ln2_var + l * M, proj, resid, w + lay_.ln2_w + l * D,
+                                                         w + lay_.ln2_b + l * D, B_, T_, c_.d_model);
+            resid = proj;
+            be_->device_linear_activation_fused_forward(up, act, ln2, w + lay_.up_w + l * D * F, w + lay_.up_b + l * F, true, B_, T_, c_.d_model,
+                                                        c_.d_ffn);
+            be_->device_linear_activation_fused_forward(down, nullptr, act, w + lay_.down_w + l * F * D, w + lay_.down_b + l * D, false, B_, T_,
+                                                        c_.d_ffn, c_.d_model);
+            stream = down;
+        }
+        be_->device_layernorm_residual_fused_forward(A + a_.lnf, A + a_.lnf_mean, A + a_.lnf_var, stream, resid, w + lay_.lnf_w, w + lay_.lnf_b, B_, T_,
+                                                     c_.d_model);
+        be_->device_unembedding_forward(A + a_.logits, A + a_.lnf, w + lay_.wte, B_, T_, c_.d_model, c_.vocab_padded);
+        if (use_grad_) be_->device_softmax_forward(A + a_.probs, A + a_.logits, B_, T_, c_.vocab, c_.vocab_padded);
+    }
+
+    // layer_done(l, user): gradients of layer l's twelve parameter tensors are complete (enqueued);
+    // l == layers means "un-embedding and final LayerNorm done (wte still open)", l == -1 means "everything done".
+    void backward(const int *tokens, const int *labels, void (*layer_done)(int, void *), void *user)
+    {
+        const size_t M = size_t(B_) * T_, D = c_.d_model, F = c_.d_ffn, H = c_.heads;
+        float *w = weights(), *gw = grads(), *A = acts_, *G = agrads_;
+        float *d_ln = G + g_.d_ln, *d_res = G + g_.d_res, *d_x = G + g_.d_x;
+        // the padding columns of d_logits are never written by the cross-entropy backward: they stay zero from set_size
+        be_->device_cross_entropy_softmax_fused_backward(G + g_.d_logits, A + a_.probs, labels, B_, T_, c_.vocab, c_.vocab_padded);
+        be_->device_unembedding_backward(d_x, gw + lay_.wte, G + g_.d_logits, A + a_.lnf, w + lay_.wte, B_, T_, c_.d_model, c_.vocab_padded);
+        be_->device_layernorm_residual_fused_backward(d_res, gw + lay_.lnf_w, gw + lay_.lnf_b, d_x, nullptr, A + a_.down + (c_.layers - 1) * M * D,
+                                                      A + a_.lnf_mean, A + a_.lnf_var, w + lay_.lnf_w, B_, T_, c_.d_model);
+        if (layer_done) layer_done(c_.layers, user);
+        // d_res holds the gradient of the residual stream at the output of layer l
+        for (int l = c_.layers - 1; l >= 0; --l) {
+            be_->device_linear_backward(G + g_.d_f1, gw + lay_.down_w + l * F * D, gw + lay_.down_b + l * D, d_res, A + a_.act + l * M * F,
+                                        w + lay_.down_w + l * F * D, B_, T_, c_.d_ffn, c_.d_model);
+            be_->device_activation_backward(G + g_.d_f2, G + g_.d_f1, A + a_.up + l * M * F, B_, T_, c_.d_ffn);
+            be_->device_linear_backward(d_x, gw + lay_.up_w + l * D * F, gw + lay_.up_b + l * F, G + g_.d_f2, A + a_.ln2 + l * M * D,
+                                        w + lay_.up_w + l * D * F, B_, T_, c_.d_model, c_.d_ffn);
+            be_->device_layernorm_residual_fused_backward(d_ln, gw + lay_.ln2_w + l * D, gw + lay_.ln2_b + l * D, d_x, d_res, A + a_.proj + l * M * D,
+                                                          A + a_.ln2_mean + l * M, A + a_.ln2_var + l * M, w + lay_.ln2_w + l * D, B_, T_, c_.d_model);
+            // d_ln: gradient of the stream after the attention projection (+ residual)
+            be_->device_linear_backward(d_x, gw + lay_.proj_w + l * D * D, gw + lay_.proj_b + l * D, d_ln, A + a_.attn + l * M * D,
+                                        w + lay_.proj_w + l * D * D, B_, T_, c_.d_model, c_.d_model);
+            be_->device_flash_attention_backward(G + g_.d_qkv, G + g_.d_helper, A + a_.lse + l * M * H, d_x, A + a_.attn + l * M * D,
+                                                 A + a_.qkv + l * M * 3 * D, B_, T_, c_.d_model, c_.heads);
+            be_->device_linear_backward(d_x, gw + lay_.qkv_w + l * D * 3 * D, gw + lay_.qkv_b + l * 3 * D, G + g_.d_qkv, A + a_.ln1 + l * M * D,
+                                        w + lay_.qkv_w + l * D * 3 * D, B_, T_, c_.d_model, 3 * c_.d_model);
+            const float *ln1_in = l == 0 ? A + a_.x_emb : A + a_.down + (l - 1) * M * D;
+            be_->device_layernorm_residual_fused_backward(d_res, gw + lay_.ln1_w + l * D, gw + lay_.ln1_b + l * D, d_x, d_ln, ln1_in,
+                                                          A + a_.ln1_mean + l * M, A + a_.ln1_var + l * M, w + lay_.ln1_w + l * D, B_, T_, c_.d_model);
+            if (layer_done) layer_done(l, user);
+        }
+        be_->device_embedding_backward(gw + lay_.wte, gw + lay_.wpe, d_res, tokens, B_, T_, c_.d_model);
+        if (layer_done) layer_done(-1, user);
+    }
+
+    float loss(const int *labels)
+    {
+        be_->device_cross_entropy_loss(loss_dev_, acts_ + a_.probs, labels, B_, T_, c_.vocab_padded);
+        float v = 0.0f;
+        be_->device_memcpy_d2h(&v, loss_dev_, sizeof(float));
+        return v;
+    }
+
+    void clip(float max_norm, int accum_steps) { be_->device_scale_and_clip_grad(grads(), static_cast<int>(lay_.total), max_norm, accum_steps); }
+
+    // AdamW over the sixteen tensors; weight decay only on the matrices and embeddings (src/model/gpt.cpp:649-677).
+    void optimizer_step(float lr, float beta1, float beta2, float decay)
+    {
+        ++step_;
+        const size_t L = c_.layers, D = c_.d_model, F = c_.d_ffn;
+        struct Slice { size_t off, n; bool decay; };
+        const Slice slices[] = {
+            {lay_.wte, size_t(c_.vocab_padded) * D, true}, {lay_.wpe, size_t(c_.max_seq_len) * D, true}, {lay_.ln1_w, L * D, false},
+            {lay_.ln1_b, L * D, false}, {lay_.qkv_w, L * D * 3 * D, true}, {lay_.qkv_b, L * 3 * D, false}, {lay_.proj_w, L * D * D, true},
+            {lay_.proj_b, L * D, false}, {lay_.ln2_w, L * D, false}, {lay_.ln2_b, L * D, false}, {lay_.up_w, L * D * F, true},
+            {lay_.up_b, L * F, false}, {lay_.down_w, L * F * D, true}, {lay_.down_b, L * D, false}, {lay_.lnf_w, D, false}, {lay_.lnf_b, D, false}};
+        for (const Slice &s : slices)
+            be_->device_adamw_step(bufs_[0] + s.off, bufs_[1] + s.off, bufs_[2] + s.off, bufs_[3] + s.off, static_cast<int>(s.n), lr, beta1, beta2,
+                                   1e-8f, s.decay ? decay : 0.0f, step_);
+    }
+
+    float *logits() { return acts_ ? acts_ + a_.logits : nullptr; }
+    int batch() const { return B_; }
+    int seq() const { return T_; }
+    const Config &config() const { return c_; }
+
+private:
+    void release_activations()
+    {
+        if (acts_) be_->device_free(acts_);
+        if (agrads_) be_->device_free(agrads_);
+        acts_ = agrads_ = nullptr;
+    }
+
+    struct ActLayout {
+        size_t x_emb, ln1, ln1_mean, ln1_var, qkv, lse, attn, proj, ln2, ln2_mean, ln2_var, up, act, down, lnf, lnf_mean, lnf_var, logits, probs, total;
+    } a_{};
+    struct GradLayout {
+        size_t d_ln, d_res, d_x, d_qkv, d_helper, d_f1, d_f2, d_logits, total;
+    } g_{};
+
+    IGPTBackend *be_;
+    Config c_;
+    ParamLayout lay_;
+    bool use_grad_;
+    float *bufs_[4] = {nullptr, nullptr, nullptr, nullptr};
+    float *acts_ = nullptr, *agrads_ = nullptr, *loss_dev_ = nullptr;
+    int B_ = 0, T_ = 0, step_ = 0;
+};
+
+struct ModelHandle {
+    B200Backend *backend;
+    GptModel *model;
+};
+
+}  // namespace
+
+// ---- C entry points (declared in include/gptb200.h) ------------------------------------------------------
+
+struct gptb200_model {
+    ModelHandle h;
+};
+
+extern "C" {
+
+int gptb200_model_create(gptb200_model **out, const int *cfg, int device, void *stream, int mode, unsigned long seed, int use_grad)
+{
+    if (!out || !cfg) return GPTB200_ERR_INVALID_ARG;
+    for (int i = 0; i < 7; ++i)
+        if (cfg[i] <= 0) return GPTB200_ERR_INVALID_ARG;
+    Config c{cfg[0], cfg[1], cfg[2], cfg[3], cfg[4], cfg[5], cfg[6]};
+    if (c.vocab_padded < c.vocab || c.d_model % c.heads != 0) return GPTB200_ERR_INVALID_ARG;
+    gptb200_ctx *probe = nullptr;
+    const int rc = gptb200_ctx_create(&probe, device, stream, mode);  // report a missing device as a status, not an abort
+    if (rc != GPTB200_OK) return rc;
+    gptb200_ctx_destroy(probe);
+    auto *m = new gptb200_model();
+    m->h.backend = new B200Backend(seed, device, stream, mode);
+    m->h.model = new GptModel(m->h.backend, c, use_grad != 0);
+    *out = m;
+    return GPTB200_OK;
+}
+
+int gptb200_model_destroy(gptb200_model *m)
+{
+    if (!m) return GPTB200_ERR_INVALID_ARG;
+    delete m->h.model;
+    delete m->h.backend;
+    delete m;
+    return GPTB200_OK;
+}
+
+gptb200_ctx *gptb200_model_context(gptb200_model *m) { return m ? m->h.backend->context() : nullptr; }
+long long gptb200_model_num_params(gptb200_model *m) { return m ? static_cast<long long>(m->h.model->num_params()) : -1; }
+float *gptb200_model_weights(gptb200_model *m) { return m ? m->h.model->weights() : nullptr; }
+float *gptb200_model_grads(gptb200_model *m) { return m ? m->h.model->grads() : nullptr; }
+float *gptb200_model_logits(gptb200_model *m) { return m ? m->h.model->logits() : nullptr; }
+
+// offsets[16] (floats) of wte, wpe, ln_1_w, ln_1_b, qkv_proj_w, qkv_proj_b, attn_proj_w, attn_proj_b, ln_2_w, ln_2_b,
+// ffn_up_w, ffn_up_b, ffn_down_w, ffn_down_b, ln_f_w, ln_f_b inside the packed parameter / gradient buffers
+int gptb200_model_param_offsets(gptb200_model *m, long long *offsets16)
+{
+    if (!m || !offsets16) return GPTB200_ERR_INVALID_ARG;
+    const ParamLayout &l = m->h.model->layout();
+    const size_t v[16] = {l.wte, l.wpe, l.ln1_w, l.ln1_b, l.qkv_w, l.qkv_b, l.proj_w, l.proj_b, l.ln2_w, l.ln2_b, l.up_w, l.up_b, l.down_w, l.down_b,
+                          l.lnf_w, l.lnf_b};
+    for (int i = 0; i < 16; ++i) offsets16[i] = static_cast<long long>(v[i]);
+    return GPTB200_OK;
+}
+
+int gptb200_model_init(gptb200_model *m, float mean, float stddev)
+{
+    if (!m) return GPTB200_ERR_INVALID_ARG;
+    m->h.model->init(mean, stddev);
+    return GPTB200_OK;
+}
+
+// Raw fp32 parameter image in the reference's checkpoint layout (src/model/gpt.cpp:327-397), from / to host memory.
+int gptb200_model_load_weights(gptb200_model *m, const float *host, long long count)
+{
+    if (!m || !host || count != static_cast<long long>(m->h.model->num_params())) return GPTB200_ERR_INVALID_ARG;
+    m->h.backend->device_memcpy_h2d(m->h.model->weights(), host, size_t(count) * sizeof(float));
+    return GPTB200_OK;
+}
+
+int gptb200_model_read(gptb200_model *m, float *host, long long count, int which)
+{
+    if (!m || !host || count != static_cast<long long>(m->h.model->num_params()) || which < 0 || which > 1) return GPTB200_ERR_INVALID_ARG;
+    m->h.backend->device_memcpy_d2h(host, which == 0 ? m->h.model->weights() : m->h.model->grads(), size_t(count) * sizeof(float));
+    return GPTB200_OK;
+}
+
+int gptb200_model_load_checkpoint(gptb200_model *m, const char *path)
+{
+    if (!m || !path) return GPTB200_ERR_INVALID_ARG;
+    FILE *fp = fopen(path, "rb");
+    if (!fp) return GPTB200_ERR_INVALID_ARG;
+    std::vector<float> data(m->h.model->num_params());
+    const size_t got = fread(data.data(), sizeof(float), data.size(), fp);
+    fclose(fp);
+    if (got != data.size()) return GPTB200_ERR_INVALID_ARG;
+    return gptb200_model_load_weights(m, data.data(), static_cast<long long>(data.size()));
+}
+
+int gptb200_model_save_checkpoint(gptb200_model *m, const char *path)
+{
+    if (!m || !path) return GPTB200_ERR_INVALID_ARG;
+    std::vector<float> data(m->h.model->num_params());
+    int rc = gptb200_model_read(m, data.data(), static_cast<long long>(data.size()), 0);
+    if (rc) return rc;
+    FILE *fp = fopen(path, "wb");
+    if (!fp) return GPTB200_ERR_INVALID_ARG;
+    const size_t put = fwrite(data.data(), sizeof(float), data.size(), fp);
+    fclose(fp);
+    return put == data.size() ? GPTB200_OK : GPTB200_ERR_INVALID_ARG;
+}
+
+int gptb200_model_set_size(gptb200_model *m, int batch, int seq)
+{
+    if (!m || batch <= 0 || seq <= 0 || seq > m->h.model->config().max_seq_len) return GPTB200_ERR_INVALID_ARG;
+    m->h.model->set_size(batch, seq);
+    return GPTB200_OK;
+}
+
+int gptb200_model_zero_grad(gptb200_model *m)
+{
+    if (!m) return GPTB200_ERR_INVALID_ARG;
+    m->h.model->zero_grad();
+    return GPTB200_OK;
+}
+
+int gptb200_model_forward(gptb200_model *m, const int *tokens_dev)
+{
+    if (!m || !tokens_dev || m->h.model->batch() == 0) return GPTB200_ERR_INVALID_ARG;
+    m->h.model->forward(tokens_dev);
+    return GPTB200_OK;
+}
+
+int gptb200_model_backward(gptb200_model *m, const int *tokens_dev, const int *labels_dev, void (*layer_done)(int, void *), void *user)
+{
+    if (!m || !tokens_dev || !labels_dev || m->h.model->batch() == 0) return GPTB200_ERR_INVALID_ARG;
+    m->h.model->backward(tokens_dev, labels_dev, layer_done, user);
+    return GPTB200_OK;
+}
+
+int gptb200_model_loss(gptb200_model *m, const int *labels_dev, float *loss_out)
+{
+    if (!m || !labels_dev || !loss_out) return GPTB200_ERR_INVALID_ARG;
+    *loss_out = m->h.model->loss(labels_dev);
+    return GPTB200_OK;
+}
+
+int gptb200_model_clip(gptb200_model *m, float max_norm, int accum_steps)
+{
+    if (!m || accum_steps <= 0) return GPTB200_ERR_INVALID_ARG;
+    m->h.model->clip(max_norm, accum_steps);
+    return GPTB200_OK;
+}
+
+int gptb200_model_optimizer_step(gptb200_model *m, float lr, float beta1, float beta2, float weight_decay)
+{
+    if (!m) return GPTB200_ERR_INVALID_ARG;
+    m->h.model->optimizer_step(lr, beta1, beta2, weight_decay);
+    return GPTB200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,101 @@
+"""Data-parallel training step: one process per GPU, the batch (whole sequences) sharded over ranks, weight
+gradients summed with NCCL over NVLink / NVSwitch while the rest of the backward pass still runs.
+
+The reference has no multi-GPU path (single process, single stream).  The only place where tokens interact in
+the linear path is the reduction over tokens in grad_w / grad_b / grad_wte, so data parallelism needs exactly
+one exchange step: an all-reduce of the packed gradient buffer (src/model/gpt.cpp:46-62 packs sixteen tensors
+kind-major, every kind holding all layers contiguously).
+
+GradientBuckets turns "layer l is done" events of the backward pass into contiguous slices of that buffer that
+are ready to be reduced: layers are grouped (default 3 per group), and when the lowest layer of a group
+completes, each of the twelve per-layer kinds contributes one contiguous slice covering the group.  wte, wpe and
+the final LayerNorm go last (wte also receives the embedding backward at the very end).  The plan is pure
+index arithmetic and is tested on CPU with the gloo backend.
+"""
+from __future__ import annotations
+
+from typing import Callable
+
+LAYER_KINDS = ["ln_1_w", "ln_1_b", "qkv_proj_w", "qkv_proj_b", "attn_proj_w", "attn_proj_b", "ln_2_w", "ln_2_b",
+               "ffn_up_w", "ffn_up_b", "ffn_down_w", "ffn_down_b"]
+
+
+def per_layer_sizes(cfg: dict) -> dict:
+    D, F = cfg["d_model"], cfg["d_ffn"]
+    return {"ln_1_w": D, "ln_1_b": D, "qkv_proj_w": D * 3 * D, "qkv_proj_b": 3 * D, "attn_proj_w": D * D, "attn_proj_b": D,
+            "ln_2_w": D, "ln_2_b": D, "ffn_up_w": D * F, "ffn_up_b": F, "ffn_down_w": F * D, "ffn_down_b": D}
+
+
+class GradientBuckets:
+    """Maps backward-pass events to (offset, count) slices of the packed gradient buffer that became final."""
+
+    def __init__(self, cfg: dict, param_offsets: dict, num_params: int, layers_per_group: int = 3):
+        self.cfg = cfg
+        self.off = param_offsets
+        self.num_params = num_params
+        self.L = cfg["num_layers"]
+        self.group = max(1, min(layers_per_group, self.L))
+        self.sizes = per_layer_sizes(cfg)
+
+    def ready_after(self, event: int) -> list[tuple[int, int]]:
+        """event: the layer index reported by the backward pass (L, L-1, ..., 0, -1)."""
+        L, D = self.L, self.cfg["d_model"]
+        if event == L:      # un-embedding + final LayerNorm done: ln_f_w, ln_f_b are adjacent at the end of the buffer
+            return [(self.off["ln_f_w"], 2 * D)]
+        if event == -1:     # embedding backward done: wte and wpe are adjacent at the start of the buffer
+            return [(self.off["wte"], self.off["ln_1_w"] - self.off["wte"])]
+        if event % self.group != 0:
+            return []
+        hi = min(event + self.group, L)  # layers [event, hi) are complete
+        return [(self.off[k] + event * self.sizes[k], (hi - event) * self.sizes[k]) for k in LAYER_KINDS]
+
+    def all_slices(self) -> list[tuple[int, int]]:
+        out = []
+        for ev in [self.L] + list(range(self.L - 1, -2, -1)):
+            out += self.ready_after(ev)
+        return out
+
+
+class DataParallelStep:
+    """Runs zero_grad / forward / backward on the local shard and all-reduces gradients bucket by bucket.
+
+    `model` is a gpt_b200.Model whose context uses `compute_stream`; `grad_tensor` is a torch view of its packed
+    gradient buffer.  Collectives are issued on `comm_stream` behind events recorded on the compute stream, so
+    they overlap the remaining backward kernels.  Gradients are averaged over ranks: every rank's cross-entropy
+    backward divides by its local token count, so the mean over ranks equals the single-GPU gradient of the
+    global batch.
+    """
+
+    def __init__(self, model, grad_tensor, world_size: int, layers_per_group: int = 3, all_reduce: Callable | None = None):
+        import torch
+        import torch.distributed as dist
+        self.torch = torch
+        self.dist = dist
+        self.model = model
+        self.grads = grad_tensor
+        self.world = world_size
+        self.buckets = GradientBuckets(model.config, model.param_offsets, model.num_params, layers_per_group)
+        self.compute_stream = torch.cuda.current_stream()
+        self.comm_stream = torch.cuda.Stream() if world_size > 1 else None
+        self._all_reduce = all_reduce or (lambda t: dist.all_reduce(t, op=dist.ReduceOp.AVG))
+        self.collectives = 0
+
+    def _on_layer_done(self, layer: int) -> None:
+        slices = self.buckets.ready_after(layer)
+        if not slices or self.world == 1:
+            return
+        ev = self.torch.cuda.Event()
+        ev.record(self.compute_stream)
+        with self.torch.cuda.stream(self.comm_stream):
+            self.comm_stream.wait_event(ev)
+            for off, n in slices:
+                self._all_reduce(self.grads[off:off + n])
+                self.collectives += 1
+
+    def step(self, tokens, labels) -> None:
+        m = self.model
+        m.zero_grad()
+        m.forward(tokens)
+        m.backward(tokens, labels, self._on_layer_done)
+        if self.world > 1:
+            self.compute_stream.wait_stream(self.comm_stream)

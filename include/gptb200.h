@@ -124,6 +124,36 @@ int gptb200_adamw_step(gptb200_ctx *ctx, float *params, const float *g, float *m
 int gptb200_scale_and_clip_grad(gptb200_ctx *ctx, float *g, size_t count, float max_norm, int accum_steps);
 int gptb200_memory_info(gptb200_ctx *ctx, float *free_mb, float *total_mb);
 
+/* ---- model driver: one GPT-2 forward / backward / optimiser step issued as the reference's operator
+ *      sequence (src/model/gpt.cpp:426-690) over the operators above, with the reference's parameter packing
+ *      (src/model/gpt.cpp:46-62) so that its raw fp32 checkpoints load unchanged.
+ *      cfg = {max_seq_len, vocab_size, vocab_size_padded, num_layers, num_heads, d_model, d_ffn}.
+ *      Token / label arrays are int32 in device memory, [batch x seq]. */
+typedef struct gptb200_model gptb200_model;
+int gptb200_model_create(gptb200_model **out, const int *cfg, int device, void *cuda_stream, int mode, unsigned long seed, int use_grad);
+int gptb200_model_destroy(gptb200_model *m);
+gptb200_ctx *gptb200_model_context(gptb200_model *m);
+long long gptb200_model_num_params(gptb200_model *m);
+float *gptb200_model_weights(gptb200_model *m);   /* device pointer, packed */
+float *gptb200_model_grads(gptb200_model *m);     /* device pointer, packed like the weights */
+float *gptb200_model_logits(gptb200_model *m);    /* device pointer, [batch*seq x vocab_size_padded], after forward */
+int gptb200_model_param_offsets(gptb200_model *m, long long *offsets16);
+int gptb200_model_init(gptb200_model *m, float mean, float stddev);
+int gptb200_model_load_weights(gptb200_model *m, const float *host, long long count);
+int gptb200_model_read(gptb200_model *m, float *host, long long count, int which /* 0 weights, 1 gradients */);
+int gptb200_model_load_checkpoint(gptb200_model *m, const char *path);
+int gptb200_model_save_checkpoint(gptb200_model *m, const char *path);
+int gptb200_model_set_size(gptb200_model *m, int batch, int seq);
+int gptb200_model_zero_grad(gptb200_model *m);
+int gptb200_model_forward(gptb200_model *m, const int *tokens_dev);
+/* layer_done(l, user) is called on the host right after the operators that complete layer l's weight gradients
+ * have been enqueued: l = num_layers after the un-embedding and final LayerNorm, l = num_layers-1 .. 0 after each
+ * transformer layer, l = -1 after the embedding backward (wte, wpe complete).  May be NULL. */
+int gptb200_model_backward(gptb200_model *m, const int *tokens_dev, const int *labels_dev, void (*layer_done)(int, void *), void *user);
+int gptb200_model_loss(gptb200_model *m, const int *labels_dev, float *loss_out);
+int gptb200_model_clip(gptb200_model *m, float max_norm, int accum_steps);
+int gptb200_model_optimizer_step(gptb200_model *m, float lr, float beta1, float beta2, float weight_decay);
+
 #ifdef __cplusplus
 }
 #endif

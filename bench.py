@@ -261,6 +261,118 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_train(args):
+    """--workload train: one full GPT-2 124M training step (BASELINE.json configs[3]) -- zero_grad, forward, backward
+    with bucketed NCCL all-reduce of every weight gradient overlapped with the backward pass, gradient clipping and
+    AdamW -- global batch 64 x 256 tokens sharded over the ranks (strong scaling).  Seeded random-init weights and
+    uniform random token ids.  Reports tokens/s."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import gpt_b200
+    from gpt_b200.data_parallel import DataParallelStep
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = gpt_b200.GPT2_124M
+    GB, T = args.global_batch, 256
+    assert GB % world == 0
+    B = GB // world
+    mode = gpt_b200.MODE_TF32 if args.mode == "tf32" else gpt_b200.MODE_3XTF32
+    stream = torch.cuda.current_stream()
+    model = gpt_b200.Model(cfg, local_rank, stream.cuda_stream, mode, seed=42)
+    model.init(0.0, 0.02)           # same seed on every rank: identical replicas
+    model.set_size(B, T)
+    # torch view of the packed gradient buffer (no copy) for the collectives
+    class _Raw:
+        __cuda_array_interface__ = dict(shape=(model.num_params,), typestr="<f4", data=(model.grads_ptr, False), version=3, strides=None)
+    grads = torch.as_tensor(_Raw(), device=dev)
+    dp = DataParallelStep(model, grads, world, layers_per_group=3)
+    rng = np.random.default_rng(1000)
+    seqs = rng.integers(0, cfg["vocab_size"], size=(GB, T + 1)).astype(np.int32)[rank * B:(rank + 1) * B]
+    h_in = torch.from_numpy(np.ascontiguousarray(seqs[:, :T])).pin_memory()
+    h_lbl = torch.from_numpy(np.ascontiguousarray(seqs[:, 1:])).pin_memory()
+    d_in, d_lbl = h_in.to(dev), h_lbl.to(dev)
+
+    def step(e2e=False):
+        if e2e:  # the step as a host program sees it: tokens from pinned host memory in, loss back out
+            d_in.copy_(h_in, non_blocking=True)
+            d_lbl.copy_(h_lbl, non_blocking=True)
+        dp.step(d_in, d_lbl)
+        model.unscale_and_clip_grads(1.0, 1)
+        model.optimizer_step(6e-4, 0.9, 0.95, 0.1)
+        return model.loss(d_lbl) if e2e else None
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    for _ in range(args.warmup):
+        step()
+    model.synchronize()
+    barrier()
+    t_begin = time.time()
+    l0 = model.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = model.launch_count() - l0
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    n_e2e = max(2, min(args.steps, 5))
+    loss = step(True)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(n_e2e):
+        loss = step(True)
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    clocks = sampler.stop(t_begin, time.time()) if sampler else None
+    model.synchronize()
+    if rank == 0:
+        ms_step = ms / args.steps
+        tokens = GB * T
+        lin_flops = 3 * 247.1e6 * tokens  # forward + backward of all linear layers: 741.4 MFLOP per token
+        peaks = measured_peaks()
+        out = dict(metric="train_tokens_per_s", value=tokens / (ms_step * 1e-3), unit="tokens/s", n_gpus=world, steps=args.steps,
+                   warmup=args.warmup, ms_per_step=ms_step, higher_is_better=True, scaling="strong", vs_baseline=None,
+                   dtype="tf32x3 (fp32-accurate split)" if mode == gpt_b200.MODE_3XTF32 else "tf32", data="synthetic", impl="ours",
+                   config=dict(workload="GPT-2 124M full training step (forward, backward, grad all-reduce, clip, AdamW)", global_batch=GB,
+                               seq_len=T, per_gpu_batch=B, mode=args.mode, parallelism=f"dp{world}",
+                               l2="activations and weights (>10 GB per step) exceed the 126 MB L2"),
+                   linear_path_tflops=lin_flops / (ms_step * 1e-3) / 1e12,
+                   roofline=dict(bound="tensor", achieved=lin_flops / world / (ms_step * 1e-3) / 1e12, peak=peaks["tf32_tflops"], unit="TFLOP/s",
+                                 frac=lin_flops / world / (ms_step * 1e-3) / 1e12 / peaks["tf32_tflops"], traffic=None,
+                                 note="linear-path algorithmic flops per GPU over the WHOLE step time (attention, LayerNorm, softmax, "
+                                      "optimizer included in the time)", peak_source=peaks["source"]),
+                   gpu_launches=int(launches), collectives_per_step=dp.collectives // max(1, args.warmup + args.steps + n_e2e + 1),
+                   e2e=dict(value=tokens / (e2e_s / n_e2e), unit="tokens/s", h2d_bytes_per_step=int(2 * B * T * 4), d2h_bytes_per_step=4,
+                            ms_per_step=e2e_s / n_e2e * 1e3, loss=loss),
+                   clocks=clocks)
+        print(json.dumps(out), flush=True)
+    model.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def cpu_reference_sample(rows: int):
     """The reference CPU backend (unmodified sources behind oracle/_ref, one thread -- it has no threading) on
     `rows` rows of the workload; falls back to the oracle port when the reference library was not prebuilt."""
@@ -319,11 +431,15 @@ def main():
     ap.add_argument("--cpu-rows", type=int, default=256, help="rows of the workload the cpu_baseline leg runs")
     ap.add_argument("--ref-rows", type=int, default=32, help="rows per step of the --impl reference arm")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", choices=["ffn", "train"], default="ffn", help="ffn: BASELINE configs[1] (default); train: configs[3]")
+    ap.add_argument("--global-batch", type=int, default=64, help="sequences per step over all GPUs (train workload)")
     ap.add_argument("--m-per-gpu", type=int, default=M_PER_GPU, help="tokens per GPU (smaller for profiler captures)")
     ap.add_argument("--profile", action="store_true", help="only the timed steps: no end-to-end, clock-load or CPU legs")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "train":
+        run_train(args)
     else:
         run_ours(args)
 

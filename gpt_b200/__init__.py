@@ -34,6 +34,7 @@ EXPORTED_SYMBOLS = [
     "gptb200_layernorm_forward", "gptb200_layernorm_backward", "gptb200_attention_forward", "gptb200_attention_backward",
     "gptb200_softmax_forward", "gptb200_cross_entropy_softmax_backward", "gptb200_cross_entropy_loss",
     "gptb200_adamw_step", "gptb200_scale_and_clip_grad", "gptb200_memory_info",
+    "gptb200_bias_grad_noalloc",
 ]
 
 
@@ -95,6 +96,7 @@ def load_library(path: str | None = None) -> ctypes.CDLL:
         "gptb200_scale_and_clip_grad": (i, [vp, fp, sz, f32, i]),
         "gptb200_memory_info": (i, [vp, ctypes.POINTER(f32), ctypes.POINTER(f32)]),
         # C++ object factory: an IGPTBackend* for host programs written against the reference's interface
+        "gptb200_bias_grad_noalloc": (i, [fp, fp, i, i, vp]),
         "gptb200_backend_create": (vp, [ctypes.c_ulong, i, vp, i]),
         "gptb200_backend_destroy": (None, [vp]),
         "gptb200_backend_context": (vp, [vp]),

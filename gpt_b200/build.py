@@ -42,7 +42,7 @@ def _stale(target: str, deps: list[str]) -> bool:
 def build(verbose: bool = False, force: bool = False) -> str:
     os.makedirs(LIBDIR, exist_ok=True)
     deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(HERE, "..", "include", "gptb200.h")]
-    cu = _sources("capi.cu", "backend_capi.cu", "b200_backend.cu", "gpt_model.cu")
+    cu = _sources("capi.cu", "backend_capi.cu", "b200_backend.cu", "gpt_model.cu", "noalloc.cu")
     cu = [f for f in cu if os.path.exists(f)]
     if force or _stale(LIB, deps):
         cmd = [_nvcc(), "-std=c++17", "-O3", *ARCH_FLAGS, "-lineinfo", "-Xcompiler", "-fPIC", "-shared",

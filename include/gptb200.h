@@ -154,6 +154,15 @@ int gptb200_model_loss(gptb200_model *m, const int *labels_dev, float *loss_out)
 int gptb200_model_clip(gptb200_model *m, float max_norm, int accum_steps);
 int gptb200_model_optimizer_step(gptb200_model *m, float lr, float beta1, float beta2, float weight_decay);
 
+/* ---- no counterpart in the reference: bias-gradient column sums without any allocation.
+ *   grad_b[n] += column sums of grad_y[m x n], the same result as the grad_b part of gptb200_linear_backward,
+ *   for callers that cannot allocate device memory (the GPU's memory belongs to the host program's own pool, or
+ *   the call happens where the runtime forbids allocation).  The partial sums live in a fixed 1 MiB array inside
+ *   the library instead of the context's growable scratch buffer; no context is needed.  n <= 8192, otherwise
+ *   GPTB200_ERR_TOO_LARGE.  Runs on `cuda_stream` of the current device.  The first call on a device looks up the
+ *   array's address; make it before any stream capture.  Calls share the array: calls that overlap on the GPU race. */
+int gptb200_bias_grad_noalloc(float *grad_b, const float *grad_y, int m, int n, void *cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -13,6 +13,7 @@
 
 #include "ctx_internal.h"
 #include "gemm_sm100.cuh"
+#include "gemm_sm100_pair.cuh"
 #include "kernels_misc.cuh"
 
 using namespace gptb200;
@@ -98,6 +99,32 @@ cudaError_t launch_majors(gptb200_ctx *ctx, bool a_mn, bool b_mn, const CUtensor
     return cudaErrorInvalidValue;  // (MN, K) does not occur on this path
 }
 
+template <bool A_MN, bool B_MN, bool X3>
+cudaError_t launch_pair_instance(gptb200_ctx *ctx, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &to, const CUtensorMap &tact,
+                                 const GemmParams &p, int grid)
+{
+    using C = PairCfg<X3>;
+    auto kernel = gemm_tcgen05_pair_kernel<A_MN, B_MN, X3>;
+    const void *key = reinterpret_cast<const void *>(kernel);
+    if (!ctx->configured.count(key)) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        if (e != cudaSuccess) return e;
+        ctx->configured.insert(key);
+    }
+    kernel<<<grid, C::kThreads, C::kSmemBytes, ctx->stream>>>(ta, tb, to, tact, p);  // cluster shape (2,1,1) is a kernel attribute
+    return cudaGetLastError();
+}
+
+template <bool X3>
+cudaError_t launch_pair(gptb200_ctx *ctx, bool a_mn, bool b_mn, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &to,
+                        const CUtensorMap &tact, const GemmParams &p, int grid)
+{
+    if (!a_mn && b_mn) return launch_pair_instance<false, true, X3>(ctx, ta, tb, to, tact, p, grid);
+    if (!a_mn && !b_mn) return launch_pair_instance<false, false, X3>(ctx, ta, tb, to, tact, p, grid);
+    if (a_mn && b_mn) return launch_pair_instance<true, true, X3>(ctx, ta, tb, to, tact, p, grid);
+    return cudaErrorInvalidValue;
+}
+
 // Output tensor [depth][rows][cols] (depth > 1 only for split-K partial tiles), written in
 // [32 x 32] pieces from 128-byte-swizzled staging tiles.
 int make_out_tmap(gptb200_ctx *ctx, CUtensorMap *map, float *base, long long depth, long long rows, long long cols)
@@ -113,10 +140,11 @@ int make_out_tmap(gptb200_ctx *ctx, CUtensorMap *map, float *base, long long dep
     return GPTB200_OK;
 }
 
-int pick_splits(const gptb200_ctx *ctx, long long tiles, int num_kb, bool allowed, size_t bytes_per_split)
+// `units`: number of CTAs (or CTA pairs) that run concurrently
+int pick_splits(const gptb200_ctx *ctx, long long tiles, int num_kb, bool allowed, size_t bytes_per_split, int units)
 {
     if (!allowed) return 1;
-    const int sms = ctx->num_sms;
+    const int sms = units;
     int cap = ctx->max_splits > 0 ? ctx->max_splits : 16;
     cap = std::min(cap, std::max(1, num_kb / 8));  // at least 8 k-blocks per split
     if (bytes_per_split > 0) cap = static_cast<int>(std::min<size_t>(cap, std::max<size_t>(1, (ctx->ws_limit / 2) / bytes_per_split)));
@@ -156,7 +184,17 @@ int run_gemm(gptb200_ctx *ctx, const GemmCall &c)
     }
 
     const bool x3 = ctx->mode == GPTB200_MODE_3XTF32;
-    int bn = ctx->tile_n;
+    // CTA pairs (256 x 256 tiles, cta_group::2): measured faster than one CTA per tile on every GPT-2 124M shape
+    // as long as there are enough 256 x 256 tiles to occupy most SM pairs; with fewer tiles the one-CTA kernel with
+    // 128-wide tiles fills the machine better.  Option "pair": 1 = always, 0 = this heuristic, -1 = never.
+    const long long pair_tiles = 1LL * ((c.M + 255) / 256) * ((c.N + 255) / 256);
+    const bool split_allowed = !c.bias && !c.act;
+    const size_t bytes_per_split = size_t(c.M) * size_t(c.N) * sizeof(float);
+    const int num_kb = (c.K + kBK - 1) / kBK;
+    const int pair_splits = pick_splits(ctx, pair_tiles, num_kb, split_allowed, bytes_per_split, ctx->num_sms / 2);
+    const bool pair = ctx->pair > 0 ||
+                      (ctx->pair == 0 && ctx->tile_n == 0 && c.M > kBM && c.N > 128 && pair_tiles * pair_splits * 20 >= 9LL * ctx->num_sms);
+    int bn = pair ? 256 : ctx->tile_n;
     if (bn != 128 && bn != 256) {
         const long long tiles256 = 1LL * ((c.M + kBM - 1) / kBM) * ((c.N + 255) / 256);
         bn = (c.N <= 128 || tiles256 < ctx->num_sms / 2) ? 128 : 256;
@@ -170,10 +208,9 @@ int run_gemm(gptb200_ctx *ctx, const GemmCall &c)
     p.tiles_n = (c.N + bn - 1) / bn;
     p.num_kb = (c.K + kBK - 1) / kBK;
     p.status = ctx->d_status;
-    const long long tiles = 1LL * p.tiles_m * p.tiles_n;
-    const bool split_allowed = !c.bias && !c.act;
-    const size_t bytes_per_split = size_t(c.M) * size_t(c.N) * sizeof(float);
-    int splits = pick_splits(ctx, tiles, p.num_kb, split_allowed, bytes_per_split);
+    p.debug = ctx->debug;
+    const long long tiles = pair ? 1LL * ((p.tiles_m + 1) / 2) * p.tiles_n : 1LL * p.tiles_m * p.tiles_n;
+    int splits = pair ? pair_splits : pick_splits(ctx, tiles, p.num_kb, split_allowed, bytes_per_split, ctx->num_sms);
     p.kb_per_split = (p.num_kb + splits - 1) / splits;
     splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
     p.splits = splits;
@@ -209,13 +246,16 @@ int run_gemm(gptb200_ctx *ctx, const GemmCall &c)
     if (c.b_mn)
         rc = make_tmap(ctx, &tb, c.b, c.K, c.N, 32, kBK, true);
     else
-        rc = make_tmap(ctx, &tb, c.b, c.N, c.K, kBK, bn, false);
+        rc = make_tmap(ctx, &tb, c.b, c.N, c.K, kBK, pair ? bn / 2 : bn, false);
     if (rc != GPTB200_OK) return rc;
 
     const long long items = tiles * splits;
-    const int grid = static_cast<int>(std::min<long long>(items, ctx->num_sms));
+    const int grid = pair ? 2 * static_cast<int>(std::min<long long>(items, ctx->num_sms / 2))
+                          : static_cast<int>(std::min<long long>(items, ctx->num_sms));
     cudaError_t e;
-    if (bn == 256)
+    if (pair)
+        e = x3 ? launch_pair<true>(ctx, c.a_mn, c.b_mn, ta, tb, to, tact, p, grid) : launch_pair<false>(ctx, c.a_mn, c.b_mn, ta, tb, to, tact, p, grid);
+    else if (bn == 256)
         e = x3 ? launch_majors<256, true>(ctx, c.a_mn, c.b_mn, ta, tb, to, tact, p, grid)
                : launch_majors<256, false>(ctx, c.a_mn, c.b_mn, ta, tb, to, tact, p, grid);
     else
@@ -350,6 +390,15 @@ int gptb200_ctx_set_option(gptb200_ctx *ctx, const char *key, int value)
     if (!strcmp(key, "tile_n")) {
         if (value != 0 && value != 128 && value != 256) return fail(ctx, GPTB200_ERR_INVALID_ARG, "tile_n must be 0, 128 or 256");
         ctx->tile_n = value;
+        return GPTB200_OK;
+    }
+    if (!strcmp(key, "pair")) {
+        if (value < -1 || value > 1) return fail(ctx, GPTB200_ERR_INVALID_ARG, "pair must be -1, 0 or 1");
+        ctx->pair = value;
+        return GPTB200_OK;
+    }
+    if (!strcmp(key, "debug")) {
+        ctx->debug = value;
         return GPTB200_OK;
     }
     if (!strcmp(key, "max_splits")) {

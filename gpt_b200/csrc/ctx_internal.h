@@ -22,6 +22,8 @@ struct gptb200_ctx {
     int num_sms = 0;
     int tile_n = 0;      // 0 = automatic
     int max_splits = 0;  // 0 = automatic
+    int debug = 0;       // timing experiments (see GemmParams::debug)
+    int pair = 0;        // CTA-pair (cta_group::2) kernel: 1 = always, 0 = heuristic, -1 = never
     int *d_status = nullptr;
     float *ws = nullptr;  // scratch: split-K partial tiles, partial rows of column reductions
     size_t ws_bytes = 0;

@@ -1,0 +1,454 @@
+// CTA-pair form of the tcgen05 GEMM (cta_group::2): two CTAs on neighbouring SMs compute one
+// 256 x 256 output tile.  Each CTA loads the 128 rows of A that it owns and HALF of the B tile
+// (128 of the 256 output columns); the tensor cores of both SMs read both halves of B.  Compared with the
+// one-CTA kernel (gemm_sm100.cuh) an SM receives 32 KiB instead of 48 KiB of operands per k-block for the
+// same number of MMAs, and the operand ring is half as wide, so it is deeper (6 stages, 3 in 3xTF32 mode).
+//
+// Division of work inside the pair (rank 0 = leader):
+//   both CTAs   TMA producer (own A rows, own half of B) -> local full[s]
+//   both CTAs   3xTF32 converters (own tiles)
+//   leader      one thread issues every tcgen05.mma.cta_group::2 and the commits
+//   both CTAs   epilogue warps drain their own 128 TMEM lanes (the rows they own) and store them
+// Cross-CTA signalling (no multicast copy anywhere):
+//   TF32:    the peer's TMA loads report their bytes straight to the leader's full[s] (cta_group::2 load form),
+//            which the leader arms with the byte count of both CTAs;
+//   3xTF32:  loads report to the local full[s]; the peer's converter warps, once the low parts are written,
+//            arrive on leader.peer_ready[s] (one remote arrive per warp);
+//   leader -> both   "stage s is free" / "accumulator b is full": one tcgen05.commit that signals the barrier at
+//            the same offset in both CTAs;
+//   peer -> leader   "accumulator b is drained": remote mbarrier.arrive on leader.tmem_empty[b].
+// All waits are bounded exactly as in the one-CTA kernel; both CTAs always reach the closing cluster barrier.
+#pragma once
+
+#include "gemm_sm100.cuh"
+
+namespace gptb200 {
+
+template <bool X3>
+struct PairCfg {
+    static constexpr int BN = 256;                     // tile columns (both CTAs together)
+    static constexpr int kBRows = BN / 2;              // rows of the B tile held by one CTA
+    static constexpr bool kChunked = X3;
+    static constexpr int kEpiWarps = X3 ? 8 : 4;
+    static constexpr int kColsPerEpiWarp = BN / (kEpiWarps / 4);
+    static constexpr int kStageBufsPerWarp = kEpiWarps == 8 ? 1 : 2;
+    static constexpr int kStagingBytes = kEpiWarps * kStageBufsPerWarp * kStageTileBytes;
+    static constexpr int kConvWarps = X3 ? 4 : 0;
+    static constexpr int kThreads = (4 + kEpiWarps + kConvWarps) * 32;
+    static constexpr int kBTileBytes = kBRows * kBK * 4;             // 16 KiB
+    static constexpr int kHiBytes = kATileBytes + kBTileBytes;       // 32 KiB per CTA and stage
+    static constexpr int kStageBytes = kHiBytes;       // one stage of the raw-operand ring
+    // 3xTF32: raw tiles and low-order tiles have rings of their own (a low-part buffer is only busy from its
+    // conversion to the MMAs that read it).  Measured on the FFN shapes: 3 + 3 stages (1246 ns per k-block) beat
+    // 4 + 2 (1628 ns): with two low-part buffers the convert -> MMA -> release chain of a buffer becomes the
+    // critical path.
+    static constexpr int kStages = X3 ? 3 : 6;
+    static constexpr int kLoStages = X3 ? 3 : 0;
+    static constexpr int kNumBarriers = 2 * kStages + 3 * (X3 ? kLoStages : 1) + 5;
+    static constexpr int kSmemBytes = (kStages + kLoStages) * kHiBytes + kStagingBytes + 1024 + 256;
+    static_assert(8 * kNumBarriers + 8 <= 256, "barrier block overflows its slot");
+    static_assert(kSmemBytes <= 232448, "exceeds 227 KiB of shared memory");
+};
+
+__device__ __forceinline__ bool bounded_wait_cluster(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, int *status, int code)
+{
+    if (ptx::mbar_try_wait_cluster(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (true) {
+        if (ptx::mbar_try_wait_cluster(bar, parity)) return true;
+        if ((++spins & 31u) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > kWaitTimeoutCycles) {
+                *abort_flag = 1u;
+                atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+template <bool A_MN, bool B_MN, bool X3>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<X3>::kThreads, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                         const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_act, const GemmParams p)
+{
+    using C = PairCfg<X3>;
+    constexpr int BN = C::BN;
+    constexpr int STAGES = C::kStages;
+    constexpr int kTmemCols = 2 * BN;
+    constexpr int kBoxesA = A_MN ? kBM / 32 : 1;
+    constexpr int kBoxesB = B_MN ? C::kBRows / 32 : 1;
+    constexpr uint32_t kIdesc = ptx::make_idesc_tf32(2 * kBM, BN, A_MN, B_MN);  // M = 256 over the pair
+    constexpr int kFirstEpiWarp = 4;
+    constexpr int kFirstConvWarp = 4 + C::kEpiWarps;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+
+    constexpr int NL = X3 ? C::kLoStages : 1;   // low-part buffers (3xTF32)
+    const uint32_t lo_base = smem_base + STAGES * C::kHiBytes;
+    const uint32_t staging_base = lo_base + C::kLoStages * C::kHiBytes;
+    const uint32_t bar_base = staging_base + C::kStagingBytes;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto conv_bar = [&](int j) { return bar_base + 8u * (2 * STAGES + j); };              // low parts of buffer j written (own CTA)
+    auto peer_bar = [&](int j) { return bar_base + 8u * (2 * STAGES + NL + j); };         // same, reported by the peer (leader only)
+    auto lo_empty_bar = [&](int j) { return bar_base + 8u * (2 * STAGES + 2 * NL + j); }; // low-part buffer j read by its MMAs
+    auto tmem_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 3 * NL + b); };
+    auto tmem_empty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 3 * NL + 2 + b); };  // used in the leader only
+    const uint32_t drain_bar = bar_base + 8u * (2 * STAGES + 3 * NL + 4);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_gen + (bar_base - smem_base) + 8 * C::kNumBarriers);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = ptx::cluster_ctarank();   // 0 = leader
+    const bool leader = rank == 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(full_bar(s), 1);
+            ptx::mbar_init(empty_bar(s), 1);
+        }
+        for (int j = 0; j < NL; ++j) {
+            ptx::mbar_init(conv_bar(j), 3);   // one arrival per converter warp of the group that owns the buffer
+            ptx::mbar_init(peer_bar(j), 3);
+            ptx::mbar_init(lo_empty_bar(j), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(tmem_full_bar(b), 1);
+            ptx::mbar_init(tmem_empty_bar(b), 2 * C::kEpiWarps * 32);
+        }
+        ptx::mbar_init(drain_bar, 1);
+        *abort_flag = 0u;
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&tmap_a);
+        ptx::prefetch_tensormap(&tmap_b);
+        ptx::prefetch_tensormap(&tmap_out);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), kTmemCols);
+        ptx::tmem_relinquish_pair();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::cluster_sync();   // the peer's barriers exist before anything is signalled across CTAs
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int tiles_m2 = (p.tiles_m + 1) / 2;   // pairs of 128-row tiles
+    const long long num_items = 1LL * tiles_m2 * p.tiles_n * p.splits;
+    const long long first_item = blockIdx.x >> 1;
+    const long long item_stride = gridDim.x >> 1;
+
+    auto decode = [&](long long w, int &tm2, int &tn, int &kb0, int &kb1, int &split) {
+        tm2 = static_cast<int>(w % tiles_m2);
+        const long long r = w / tiles_m2;
+        tn = static_cast<int>(r % p.tiles_n);
+        split = static_cast<int>(r / p.tiles_n);
+        kb0 = split * p.kb_per_split;
+        kb1 = min(kb0 + p.kb_per_split, p.num_kb);
+    };
+
+    // 3xTF32 converters: six warps (warps 2, 3 and the last four) in two groups of three; group g handles the
+    // k-blocks with (iteration & 1) == g, so that waking up, converting and signalling one stage overlaps with
+    // the other group's stage.  lo = a - trunc_tf32(a), written at the same swizzled offset as the raw tile.
+    auto convert_loop = [&](int group, int ctid) {
+        uint32_t it = 0;
+        bool ok = true;
+        for (long long w = first_item; ok && w < num_items; w += item_stride) {
+            int tm2, tn, kb0, kb1, split;
+            decode(w, tm2, tn, kb0, kb1, split);
+            for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                if (static_cast<int>(it & 1u) != group) continue;
+                const int s = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1u;
+                const int j = it % NL;
+                const uint32_t lph = (it / NL) & 1u;
+                // the low-part buffer must have been read by the MMAs of its previous use, the raw tile must have landed
+                if (!bounded_wait_cluster(lo_empty_bar(j), lph ^ 1u, abort_flag, p.status, DEV_TIMEOUT_CONVERT) ||
+                    !bounded_wait(full_bar(s), ph, abort_flag, p.status, DEV_TIMEOUT_CONVERT)) {
+                    ok = false;
+                    break;
+                }
+                const float4 *hi = reinterpret_cast<const float4 *>(smem_gen + s * C::kHiBytes);
+                float4 *lo = reinterpret_cast<float4 *>(smem_gen + (lo_base - smem_base) + j * C::kHiBytes);
+                constexpr int kVec = C::kHiBytes / 16;
+#pragma unroll 8
+                for (int i = ctid; i < kVec; i += 96) {
+                    const float4 h = hi[i];
+                    float4 l;
+                    l.x = h.x - __uint_as_float(__float_as_uint(h.x) & 0xFFFFE000u);
+                    l.y = h.y - __uint_as_float(__float_as_uint(h.y) & 0xFFFFE000u);
+                    l.z = h.z - __uint_as_float(__float_as_uint(h.z) & 0xFFFFE000u);
+                    l.w = h.w - __uint_as_float(__float_as_uint(h.w) & 0xFFFFE000u);
+                    lo[i] = l;
+                }
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    if (leader)
+                        ptx::mbar_arrive(conv_bar(j));
+                    else
+                        ptx::mbar_arrive_cluster(ptx::map_to_cta(peer_bar(j), 0u));
+                }
+            }
+        }
+    };
+
+    if (warp < 4) {
+        if (C::kChunked) ptx::reg_dec<56>();
+        if (warp == 0) {
+            // ------------------------------------------------------------ TMA producer (both CTAs)
+            uint32_t it = 0;
+            bool ok = true;
+            for (long long w = first_item; ok && w < num_items; w += item_stride) {
+                int tm2, tn, kb0, kb1, split;
+                decode(w, tm2, tn, kb0, kb1, split);
+                const int m0 = tm2 * 2 * kBM + static_cast<int>(rank) * kBM;          // the rows this CTA owns
+                const int n0 = tn * BN + static_cast<int>(rank) * C::kBRows;          // the half of B this CTA loads
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    if (!bounded_wait_cluster(empty_bar(s), ph ^ 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) {
+                        ok = false;
+                        break;
+                    }
+                    if (p.debug & 1) {
+                        if (lane == 0 && (X3 || leader)) ptx::mbar_arrive(full_bar(s));
+                        __syncwarp();
+                        continue;
+                    }
+                    // TF32: every load of the pair reports to the leader's barrier, armed by the leader for both CTAs.
+                    // 3xTF32: each CTA's loads report to its own barrier (its converter warps wait on it).
+                    const uint32_t bar = X3 ? full_bar(s) : ptx::map_to_cta(full_bar(s), 0u);
+                    if (lane == 0 && (X3 || leader)) ptx::mbar_arrive_expect_tx(full_bar(s), X3 ? C::kHiBytes : 2 * C::kHiBytes);
+                    __syncwarp();
+                    const uint32_t a_dst = smem_base + s * C::kHiBytes;
+                    const uint32_t b_dst = a_dst + kATileBytes;
+                    const int k0 = kb * kBK;
+                    if (lane < kBoxesA) {
+                        if (A_MN)
+                            ptx::tma_load_2d_pair(a_dst + lane * kBoxBytesMN, &tmap_a, m0 + 32 * lane, k0, bar);
+                        else
+                            ptx::tma_load_2d_pair(a_dst, &tmap_a, k0, m0, bar);
+                    } else if (lane < kBoxesA + kBoxesB) {
+                        const int j = lane - kBoxesA;
+                        if (B_MN)
+                            ptx::tma_load_2d_pair(b_dst + j * kBoxBytesMN, &tmap_b, n0 + 32 * j, k0, bar);
+                        else
+                            ptx::tma_load_2d_pair(b_dst, &tmap_b, k0, n0, bar);
+                    }
+                    __syncwarp();
+                }
+            }
+        } else if (warp == 1) {
+            // ------------------------------------------------------------ MMA issuer (leader CTA, one thread)
+            if (leader && lane == 0) {
+                uint32_t it = 0, g = 0;
+                bool ok = true;
+                for (long long w = first_item; ok && w < num_items; w += item_stride) {
+                    int tm2, tn, kb0, kb1, split;
+                    decode(w, tm2, tn, kb0, kb1, split);
+                    int kb = kb0;
+                    while (ok && kb < kb1) {
+                        const int kend = C::kChunked ? min(kb + kChunkKB, kb1) : kb1;
+                        const uint32_t buf = g & 1u;
+                        const uint32_t use = (g >> 1) & 1u;
+                        if (!bounded_wait_cluster(tmem_empty_bar(buf), use ^ 1u, abort_flag, p.status, DEV_TIMEOUT_MMA_TMEM)) {
+                            ok = false;
+                            break;
+                        }
+                        ptx::tc_fence_after();
+                        const uint32_t d_tmem = tmem_base + buf * BN;
+                        uint32_t accumulate = 0;
+                        for (; kb < kend; ++kb, ++it) {
+                            const int s = it % STAGES;
+                            const uint32_t ph = (it / STAGES) & 1u;
+                            if (!bounded_wait_cluster(full_bar(s), ph, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL)) { ok = false; break; }
+                            const int j = it % NL;
+                            const uint32_t lph = (it / NL) & 1u;
+                            if (X3 && !bounded_wait(conv_bar(j), lph, abort_flag, p.status, DEV_TIMEOUT_MMA_CONV)) { ok = false; break; }
+                            if (X3 && !bounded_wait_cluster(peer_bar(j), lph, abort_flag, p.status, DEV_TIMEOUT_MMA_CONV)) { ok = false; break; }
+                            ptx::tc_fence_after();
+                            const uint32_t a_hi = smem_base + s * C::kHiBytes;
+                            const uint32_t b_hi = a_hi + kATileBytes;
+                            const uint32_t a_lo = lo_base + j * C::kHiBytes;
+                            const uint32_t b_lo = a_lo + kATileBytes;
+#pragma unroll
+                            for (int k = 0; k < ((p.debug & 2) ? 0 : kBK / kUmmaK); ++k) {
+                                const uint32_t a_off = A_MN ? k * 1024 : k * 32;
+                                const uint32_t b_off = B_MN ? k * 1024 : k * 32;
+                                constexpr uint32_t a_lbo = A_MN ? kBoxBytesMN : 16, a_sbo = A_MN ? 512 : 1024;
+                                constexpr uint32_t b_lbo = B_MN ? kBoxBytesMN : 16, b_sbo = B_MN ? 512 : 1024;
+                                constexpr uint32_t a_lay = A_MN ? ptx::kLayoutSw128Base32B : ptx::kLayoutSw128;
+                                constexpr uint32_t b_lay = B_MN ? ptx::kLayoutSw128Base32B : ptx::kLayoutSw128;
+                                const uint64_t da_hi = ptx::make_smem_desc(a_hi + a_off, a_lbo, a_sbo, a_lay);
+                                const uint64_t db_hi = ptx::make_smem_desc(b_hi + b_off, b_lbo, b_sbo, b_lay);
+                                if (X3) {
+                                    const uint64_t da_lo = ptx::make_smem_desc(a_lo + a_off, a_lbo, a_sbo, a_lay);
+                                    const uint64_t db_lo = ptx::make_smem_desc(b_lo + b_off, b_lbo, b_sbo, b_lay);
+                                    ptx::mma_tf32_ss_pair(d_tmem, da_lo, db_hi, kIdesc, accumulate);
+                                    ptx::mma_tf32_ss_pair(d_tmem, da_hi, db_lo, kIdesc, 1u);
+                                    ptx::mma_tf32_ss_pair(d_tmem, da_hi, db_hi, kIdesc, 1u);
+                                } else {
+                                    ptx::mma_tf32_ss_pair(d_tmem, da_hi, db_hi, kIdesc, accumulate);
+                                }
+                                accumulate = 1u;
+                            }
+                            // the stage is free in both CTAs once these MMAs have read it
+                            ptx::mma_commit_pair_both(empty_bar(s), 3);
+                            if (X3) ptx::mma_commit_pair_both(lo_empty_bar(j), 3);
+                        }
+                        if (ok) {
+                            ptx::mma_commit_pair_both(tmem_full_bar(buf), 3);
+                            ++g;
+                        }
+                    }
+                }
+                ptx::mma_commit_pair(drain_bar);
+                bounded_wait(drain_bar, 0u, abort_flag, p.status, DEV_TIMEOUT_DRAIN);
+            }
+            __syncwarp();
+        } else if (X3) {
+            convert_loop(warp - 2, lane);   // warps 2 and 3: first warp of converter group 0 and 1
+        }
+    } else if (warp < kFirstConvWarp) {
+        // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
+        if (C::kChunked) ptx::reg_inc<184>();
+        const int e = warp - kFirstEpiWarp;
+        const int q = warp & 3;
+        const int col_base = (e >> 2) * C::kColsPerEpiWarp;
+        const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
+        StageRing<C::kStageBufsPerWarp> ring;
+        ring.base = staging_base + e * C::kStageBufsPerWarp * kStageTileBytes;
+        ring.count = 0;
+        uint32_t g = 0;
+        bool ok = true;
+        const uint32_t leader_tmem_empty[2] = {ptx::map_to_cta(tmem_empty_bar(0), 0u), ptx::map_to_cta(tmem_empty_bar(1), 0u)};
+
+        auto emit = [&](float (&v)[32], int row0, int col0, int split) {
+            if (p.bias && p.epi_mode == EPI_STORE) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] += (col0 + j < p.N) ? __ldg(p.bias + col0 + j) : 0.0f;
+            }
+            const bool in_range = row0 < p.M && col0 < p.N;
+            {
+                const uint32_t buf = ring.acquire(lane);
+                stage_row(buf, lane, v);
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    if (in_range) {
+                        if (p.epi_mode == EPI_ACCUM)
+                            ptx::tma_reduce_add_3d(&tmap_out, col0, row0, 0, buf);
+                        else
+                            ptx::tma_store_3d(&tmap_out, col0, row0, split, buf);
+                    }
+                    ptx::tma_store_commit();
+                }
+                ring.count++;
+            }
+            if (p.has_act) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+                const uint32_t buf = ring.acquire(lane);
+                stage_row(buf, lane, v);
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    if (in_range) ptx::tma_store_3d(&tmap_act, col0, row0, 0, buf);
+                    ptx::tma_store_commit();
+                }
+                ring.count++;
+            }
+        };
+
+        for (long long w = first_item; ok && w < num_items; w += item_stride) {
+            int tm2, tn, kb0, kb1, split;
+            decode(w, tm2, tn, kb0, kb1, split);
+            const int row0 = tm2 * 2 * kBM + static_cast<int>(rank) * kBM + q * 32;
+            const int n0 = tn * BN + col_base;
+            if (C::kChunked) {
+                float acc[128];
+#pragma unroll
+                for (int j = 0; j < 128; ++j) acc[j] = 0.0f;
+                for (int kb = kb0; ok && kb < kb1; kb += kChunkKB, ++g) {
+                    const uint32_t buf = g & 1u;
+                    const uint32_t use = (g >> 1) & 1u;
+                    if (!bounded_wait_cluster(tmem_full_bar(buf), use, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t v[32];
+                        ptx::tmem_ld_32x32(tmem_base + lane_base + buf * BN + col_base + c * 32, v);
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) acc[c * 32 + j] += __uint_as_float(v[j]);
+                    }
+                    ptx::tc_fence_before();
+                    ptx::mbar_arrive_cluster(leader_tmem_empty[buf]);
+                }
+                if (ok) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = acc[c * 32 + j];
+                        emit(v, row0, n0 + c * 32, split);
+                    }
+                }
+            } else {
+                const uint32_t buf = g & 1u;
+                const uint32_t use = (g >> 1) & 1u;
+                ++g;
+                if (!bounded_wait_cluster(tmem_full_bar(buf), use, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE)) {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after();
+#pragma unroll 1
+                for (int c = 0; c < C::kColsPerEpiWarp / 32; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32(tmem_base + lane_base + buf * BN + col_base + c * 32, r);
+                    ptx::tmem_ld_wait();
+                    if (c == C::kColsPerEpiWarp / 32 - 1) {
+                        ptx::tc_fence_before();
+                        ptx::mbar_arrive_cluster(leader_tmem_empty[buf]);
+                    }
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                    emit(v, row0, n0 + c * 32, split);
+                }
+            }
+        }
+        if (lane == 0) ptx::tma_store_wait_all<0>();
+        __syncwarp();
+    } else if (X3) {
+        // ------------------------------------------------------------ 3xTF32 converters (last four warps)
+        ptx::reg_dec<72>();
+        const int j = warp - kFirstConvWarp;
+        convert_loop(j >> 1, (1 + (j & 1)) * 32 + lane);
+    }
+
+    // ---------------------------------------------------------------- teardown
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    // Neither CTA may leave while the other can still signal its barriers or read its shared memory.
+    ptx::cluster_sync();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+    }
+}
+
+}  // namespace gptb200

@@ -26,11 +26,16 @@ def torch():
     return t
 
 
-@pytest.fixture(scope="module", params=[0, 1], ids=["3xTF32", "TF32"])
+# (precision mode, kernel choice): automatic choice in both modes, plus the CTA-pair (cta_group::2) kernel and the
+# one-CTA kernel forced, so that every shape below runs through both GEMM kernels.
+@pytest.fixture(scope="module", params=[(0, 0), (1, 0), (0, 1), (1, 1), (0, -1)],
+                ids=["3xTF32", "TF32", "3xTF32-pair", "TF32-pair", "3xTF32-single"])
 def be(request, torch, built_library):
     import gpt_b200
-    b = gpt_b200.Backend(0, None, request.param)
-    b.mode = request.param
+    mode, pair = request.param
+    b = gpt_b200.Backend(0, None, mode)
+    b.set_option("pair", pair)
+    b.mode = mode
     yield b
     b.close()
 

@@ -29,7 +29,7 @@ struct PairCfg {
     static constexpr int BN = 256;                     // tile columns (both CTAs together)
     static constexpr int kBRows = BN / 2;              // rows of the B tile held by one CTA
     static constexpr bool kChunked = X3;
-    static constexpr int kEpiWarps = X3 ? 8 : 4;
+    static constexpr int kEpiWarps = 8;                // two warps per TMEM lane quarter, 128 columns each
     static constexpr int kColsPerEpiWarp = BN / (kEpiWarps / 4);
     static constexpr int kStageBufsPerWarp = kEpiWarps == 8 ? 1 : 2;
     static constexpr int kStagingBytes = kEpiWarps * kStageBufsPerWarp * kStageTileBytes;

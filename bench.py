@@ -373,6 +373,87 @@ def run_train(args):
         dist.destroy_process_group()
 
 
+def run_decode(args):
+    """--workload decode: the linear layers of one GPT-2 124M decode step (BASELINE.json configs[4]) for batch 1, 8, 64:
+    per layer QKV, attention projection, FFN up (GELU), FFN down, then the 50304-wide LM head, with m = batch rows.
+    HBM-bound: 494.27 MB of fp32 weights are read once per step.  Reports GB/s (weights bytes / time) per batch; the
+    JSON `value` is the batch-8 figure.  The reference has no KV-cached decode (src/infer/infer.cpp:121 recomputes the
+    whole prefix), so this measures the GEMM shapes of such a step, not end-to-end generation."""
+    import torch
+    import gpt_b200
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    cfg = gpt_b200.GPT2_124M
+    L, D, F, Vp = cfg["num_layers"], cfg["d_model"], cfg["d_ffn"], cfg["vocab_size_padded"]
+    mode = gpt_b200.MODE_TF32 if args.mode == "tf32" else gpt_b200.MODE_3XTF32
+    be = gpt_b200.Backend(0, torch.cuda.current_stream().cuda_stream, mode)
+    g = torch.Generator(device=dev).manual_seed(5)
+    W = dict(qkv=[torch.randn(D, 3 * D, device=dev, generator=g) * 0.02 for _ in range(L)],
+             proj=[torch.randn(D, D, device=dev, generator=g) * 0.02 for _ in range(L)],
+             up=[torch.randn(D, F, device=dev, generator=g) * 0.02 for _ in range(L)],
+             down=[torch.randn(F, D, device=dev, generator=g) * 0.02 for _ in range(L)])
+    wte = torch.randn(Vp, D, device=dev, generator=g) * 0.02
+    bias = dict(qkv=torch.zeros(3 * D, device=dev), proj=torch.zeros(D, device=dev), up=torch.zeros(F, device=dev), down=torch.zeros(D, device=dev))
+    weight_bytes = 4.0 * (L * (D * 3 * D + D * D + 2 * D * F) + Vp * D)
+    peaks = measured_peaks()
+    results = {}
+    sampler = ClockSampler(0)
+    t_begin = time.time()
+    launches = 0
+    for batch in (1, 8, 64):
+        x = torch.randn(batch, D, device=dev, generator=g)
+        q, a, u, ua, dn, lg = (torch.empty(batch, n, device=dev) for n in (3 * D, D, F, F, D, Vp))
+
+        def step():
+            for l in range(L):
+                be.device_linear_activation_fused_forward(q, None, x, W["qkv"][l], bias["qkv"], False, 1, batch, D, 3 * D)
+                be.device_linear_activation_fused_forward(a, None, x, W["proj"][l], bias["proj"], False, 1, batch, D, D)
+                be.device_linear_activation_fused_forward(u, ua, x, W["up"][l], bias["up"], True, 1, batch, D, F)
+                be.device_linear_activation_fused_forward(dn, None, ua, W["down"][l], bias["down"], False, 1, batch, F, D)
+            be.device_unembedding_forward(lg, x, wte, 1, batch, D, Vp)
+
+        # a decode step is 49 small GEMMs (about 100 launches): replay it as one CUDA graph so that the time is the
+        # kernels', not the host's launch loop
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            be.set_stream(side.cuda_stream)
+            for _ in range(max(args.warmup, 3)):   # sizes the scratch buffer and sets kernel attributes before capture
+                step()
+            side.synchronize()
+            l0 = be.launch_count()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                step()
+            per_step = be.launch_count() - l0
+            graph.replay()
+            side.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(side)
+            for _ in range(args.steps):
+                graph.replay()
+            e1.record(side)
+            side.synchronize()
+        launches += per_step * args.steps
+        ms = e0.elapsed_time(e1) / args.steps
+        results[f"batch{batch}"] = dict(ms_per_step=ms, gbs=weight_bytes / (ms * 1e-3) / 1e9, tokens_per_s=batch / (ms * 1e-3),
+                                         hbm_frac=weight_bytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"])
+    be.synchronize()
+    clocks = sampler.stop(t_begin, time.time())
+    r8 = results["batch8"]
+    out = dict(metric="decode_linear_weight_stream_gbs", value=r8["gbs"], unit="GB/s", n_gpus=1, steps=args.steps, warmup=args.warmup,
+               ms_per_step=r8["ms_per_step"], higher_is_better=True, scaling="weak", vs_baseline=None,
+               dtype="f32" if True else "tf32", data="synthetic", impl="ours",
+               config=dict(workload="GPT-2 124M decode step, linear layers only (49 GEMMs with m = batch)", mode=args.mode,
+                           weight_bytes=weight_bytes, l2="494 MB of weights per step exceed the 126 MB L2"),
+               per_batch=results,
+               roofline=dict(bound="hbm", achieved=r8["gbs"], peak=peaks["hbm_gbs"], unit="GB/s", frac=r8["hbm_frac"], traffic=None,
+                             note="algorithmic bytes = fp32 weights read once per step (494.27 MB); batch 8", peak_source="of measured (MEASURED_PEAKS.json copy bandwidth)"),
+               gpu_launches=int(launches), clocks=clocks)
+    print(json.dumps(out), flush=True)
+    be.close()
+
+
 def cpu_reference_sample(rows: int):
     """The reference CPU backend (unmodified sources behind oracle/_ref, one thread -- it has no threading) on
     `rows` rows of the workload; falls back to the oracle port when the reference library was not prebuilt."""
@@ -431,7 +512,8 @@ def main():
     ap.add_argument("--cpu-rows", type=int, default=256, help="rows of the workload the cpu_baseline leg runs")
     ap.add_argument("--ref-rows", type=int, default=32, help="rows per step of the --impl reference arm")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", choices=["ffn", "train"], default="ffn", help="ffn: BASELINE configs[1] (default); train: configs[3]")
+    ap.add_argument("--workload", choices=["ffn", "train", "decode"], default="ffn",
+                    help="ffn: BASELINE configs[1] (default); train: configs[3]; decode: configs[4] (linear layers)")
     ap.add_argument("--global-batch", type=int, default=64, help="sequences per step over all GPUs (train workload)")
     ap.add_argument("--m-per-gpu", type=int, default=M_PER_GPU, help="tokens per GPU (smaller for profiler captures)")
     ap.add_argument("--profile", action="store_true", help="only the timed steps: no end-to-end, clock-load or CPU legs")
@@ -440,6 +522,8 @@ def main():
         run_reference(args)
     elif args.workload == "train":
         run_train(args)
+    elif args.workload == "decode":
+        run_decode(args)
     else:
         run_ours(args)
 

@@ -14,6 +14,7 @@
 #include "ctx_internal.h"
 #include "gemm_sm100.cuh"
 #include "gemm_sm100_pair.cuh"
+#include "skinny_sm100.cuh"
 #include "kernels_misc.cuh"
 
 using namespace gptb200;
@@ -163,9 +164,52 @@ int pick_splits(const gptb200_ctx *ctx, long long tiles, int num_kb, bool allowe
     return best;
 }
 
+template <bool W_KN>
+int launch_skinny(gptb200_ctx *ctx, int mr, dim3 grid, float *partial, const GemmCall &c, int k_per_split)
+{
+    switch (mr) {
+        case 1: skinny_gemm_kernel<1, W_KN><<<grid, kSkinnyThreads, 0, ctx->stream>>>(partial, c.a, c.b, c.M, c.N, c.K, k_per_split); break;
+        case 2: skinny_gemm_kernel<2, W_KN><<<grid, kSkinnyThreads, 0, ctx->stream>>>(partial, c.a, c.b, c.M, c.N, c.K, k_per_split); break;
+        case 4: skinny_gemm_kernel<4, W_KN><<<grid, kSkinnyThreads, 0, ctx->stream>>>(partial, c.a, c.b, c.M, c.N, c.K, k_per_split); break;
+        case 8: skinny_gemm_kernel<8, W_KN><<<grid, kSkinnyThreads, 0, ctx->stream>>>(partial, c.a, c.b, c.M, c.N, c.K, k_per_split); break;
+        default: skinny_gemm_kernel<16, W_KN><<<grid, kSkinnyThreads, 0, ctx->stream>>>(partial, c.a, c.b, c.M, c.N, c.K, k_per_split); break;
+    }
+    ctx->launches++;
+    CUDA_TRY(ctx, cudaGetLastError());
+    return GPTB200_OK;
+}
+
+// Decode-shaped forward GEMMs (m <= 16, x K-major): stream the weights once, split k over CTAs, finish in a
+// second small kernel.  HBM-bound: 4*k*n bytes per call.
+int run_skinny(gptb200_ctx *ctx, const GemmCall &c)
+{
+    int mr = 1;
+    while (mr < c.M) mr *= 2;
+    const bool w_kn = c.b_mn;  // W stored [k][n]
+    const int cols_per_block = kSkinnyThreads * (w_kn ? 4 : 1);
+    const int col_blocks = (c.N + cols_per_block - 1) / cols_per_block;
+    int splits = std::max(1, std::min((ctx->num_sms * 4 + col_blocks - 1) / col_blocks, c.K / 32));
+    int k_per_split = (((c.K + splits - 1) / splits) + 3) & ~3;
+    splits = (c.K + k_per_split - 1) / k_per_split;
+    const int rc = ensure_workspace(ctx, size_t(splits) * c.M * c.N * sizeof(float));
+    if (rc != GPTB200_OK) return rc;
+    const dim3 grid(col_blocks, splits);
+    const int rc2 = w_kn ? launch_skinny<true>(ctx, mr, grid, ctx->ws, c, k_per_split) : launch_skinny<false>(ctx, mr, grid, ctx->ws, c, k_per_split);
+    if (rc2 != GPTB200_OK) return rc2;
+    const long long total = 1LL * c.M * c.N;
+    skinny_finish_kernel<<<static_cast<int>(std::min<long long>((total + 255) / 256, 1LL * ctx->num_sms * 4)), 256, 0, ctx->stream>>>(
+        c.out, c.act, ctx->ws, c.bias, c.M, c.N, splits);
+    ctx->launches++;
+    CUDA_TRY(ctx, cudaGetLastError());
+    return GPTB200_OK;
+}
+
 int run_gemm(gptb200_ctx *ctx, const GemmCall &c)
 {
     if (c.M == 0 || c.N == 0) return GPTB200_OK;
+    if (ctx->skinny && c.M <= 16 && !c.a_mn && !c.accumulate && c.K >= 32 && c.K % 4 == 0 && c.N % 4 == 0 && aligned16(c.a) && aligned16(c.b) &&
+        aligned16(c.out) && (!c.act || aligned16(c.act)))
+        return run_skinny(ctx, c);
     const long long lda = c.a_mn ? c.M : c.K;
     const long long ldb = c.b_mn ? c.N : c.K;
     const bool tma_ok = c.K > 0 && aligned16(c.a) && aligned16(c.b) && aligned16(c.out) && (!c.act || aligned16(c.act)) &&
@@ -395,6 +439,10 @@ int gptb200_ctx_set_option(gptb200_ctx *ctx, const char *key, int value)
     if (!strcmp(key, "pair")) {
         if (value < -1 || value > 1) return fail(ctx, GPTB200_ERR_INVALID_ARG, "pair must be -1, 0 or 1");
         ctx->pair = value;
+        return GPTB200_OK;
+    }
+    if (!strcmp(key, "skinny")) {
+        ctx->skinny = value != 0;
         return GPTB200_OK;
     }
     if (!strcmp(key, "debug")) {

@@ -22,6 +22,7 @@ struct gptb200_ctx {
     int num_sms = 0;
     int tile_n = 0;      // 0 = automatic
     int max_splits = 0;  // 0 = automatic
+    bool skinny = true;  // weight-streaming kernel for forward calls with m <= 16
     int debug = 0;       // timing experiments (see GemmParams::debug)
     int pair = 0;        // CTA-pair (cta_group::2) kernel: 1 = always, 0 = heuristic, -1 = never
     int *d_status = nullptr;

@@ -51,7 +51,8 @@ int gptb200_ctx_set_mode(gptb200_ctx *ctx, int mode);
 int gptb200_ctx_get_mode(const gptb200_ctx *ctx);
 int gptb200_ctx_set_stream(gptb200_ctx *ctx, void *cuda_stream);
 /* Tuning knobs, for benchmarking: key "tile_n" (0 = automatic, 128, 256), "max_splits" (0 = automatic),
- * "pair" (CTA-pair kernel with 256 x 256 tiles: 1 = always, 0 = heuristic, -1 = never). */
+ * "pair" (CTA-pair kernel with 256 x 256 tiles: 1 = always, 0 = heuristic, -1 = never),
+ * "skinny" (weight-streaming kernel for forward calls with m <= 16: 1 = on (default), 0 = off). */
 int gptb200_ctx_set_option(gptb200_ctx *ctx, const char *key, int value);
 /* Waits for the context's stream and reports a device-side timeout recorded by any earlier kernel. */
 int gptb200_ctx_synchronize(gptb200_ctx *ctx);

@@ -136,7 +136,8 @@ def test_unembed_ops_against_reference_golden_vectors(be, torch, path):
 
 # (m, k, n): GPT-2 124M layer shapes at a reduced token count, ragged and unaligned shapes, tile-boundary cases
 SEEDED_LINEAR = [(256, 768, 2304), (256, 768, 768), (384, 768, 3072), (256, 3072, 768), (1, 768, 3072), (8, 768, 768),
-                 (127, 36, 260), (129, 260, 36), (300, 100, 420), (77, 30, 50), (5, 7, 9), (1024, 64, 128)]
+                 (127, 36, 260), (129, 260, 36), (300, 100, 420), (77, 30, 50), (5, 7, 9), (1024, 64, 128),
+                 (16, 3072, 768), (3, 768, 2304), (64, 768, 3072)]  # decode-shaped calls: m = batch
 
 
 @pytest.mark.parametrize("m,k,n", SEEDED_LINEAR, ids=lambda v: str(v))
@@ -155,7 +156,8 @@ def test_linear_ops_against_oracle_seeded(be, torch, oracle, m, k, n):
         check(f"{name} {m}x{k}x{n}", out[name], ref, be.mode)
 
 
-@pytest.mark.parametrize("m,d,vp,v", [(128, 768, 50304, 50257), (64, 32, 512, 507), (33, 40, 132, 130), (4, 768, 1024, 1000)],
+@pytest.mark.parametrize("m,d,vp,v", [(128, 768, 50304, 50257), (64, 32, 512, 507), (33, 40, 132, 130), (4, 768, 1024, 1000),
+                                      (8, 768, 50304, 50257)],
                          ids=lambda v: str(v))
 def test_unembed_ops_against_oracle_seeded(be, torch, oracle, m, d, vp, v):
     rng = np.random.default_rng(m + d + vp)

@@ -238,7 +238,9 @@ def run_ours(args):
         x3 = mode == gpt_b200.MODE_3XTF32
         fwd = kern["forward_gemm_bias_gelu"]
         roof = dict(bound="tensor", achieved=fwd["tflops"], peak=peaks["tf32_tflops"], unit="TFLOP/s", frac=fwd["tflops"] / peaks["tf32_tflops"],
-                    traffic=None, kernel="gemm_tcgen05_kernel (forward: x.w + bias, GELU)", peak_source=peaks["source"],
+                    traffic=214.6e6 if (M == M_PER_GPU and x3) else None,
+                    traffic_note="dram read+write bytes per launch from ncu (profiles/ffn_fc_step_M8192_launch_list.md); algorithmic 235.9e6",
+                    kernel="gemm_tcgen05_pair_kernel<A=K-major, B=MN-major> (forward: x.w + bias, GELU)", peak_source=peaks["source"],
                     issued_tflops=fwd["tflops"] * (3 if x3 else 1),
                     issued_frac=fwd["tflops"] * (3 if x3 else 1) / peaks["tf32_tflops"],
                     note="achieved = 2*M*K*N algorithmic flops per launch / CUDA-event launch time; in 3xTF32 mode the tensor pipe "
@@ -479,6 +481,34 @@ def cpu_reference_sample(rows: int):
                 sample=f"{rows} of {M_PER_GPU} rows of the same step (cost is linear in rows), forward+backward")
 
 
+def run_reference_cuda(args):
+    """--impl reference_cuda (information only, not the contract's reference arm): the reference's own CUDA backend --
+    cuBLAS TF32 sgemm plus its separate bias/GELU and bias-gradient kernels -- compiled unmodified into
+    oracle/_ref/libref_cuda.so, timed on the same GPU for the same workload."""
+    import ctypes
+    path = os.path.join(ROOT, "oracle", "_ref", "libref_cuda.so")
+    if not os.path.exists(path):
+        print(json.dumps(dict(impl="reference_cuda", unavailable="oracle/_ref/libref_cuda.so was not prebuilt")))
+        return
+    lib = ctypes.CDLL(path)
+    lib.refcuda_ffn_step_ms.restype = ctypes.c_float
+    lib.refcuda_ffn_step_ms.argtypes = [ctypes.c_int] * 6
+    lib.refcuda_gpt_step_ms.restype = ctypes.c_float
+    lib.refcuda_gpt_step_ms.argtypes = [ctypes.POINTER(ctypes.c_int)] + [ctypes.c_int] * 4
+    if args.workload == "train":
+        cfg = (ctypes.c_int * 7)(256, 50257, 50304, 12, 12, 768, 3072)
+        ms = float(lib.refcuda_gpt_step_ms(cfg, args.global_batch, 256, args.steps, args.warmup))
+        out = dict(metric="train_tokens_per_s", value=args.global_batch * 256 / (ms * 1e-3), unit="tokens/s", n_gpus=1, steps=args.steps,
+                   warmup=args.warmup, ms_per_step=ms, higher_is_better=True, dtype="tf32 (cuBLAS)", data="synthetic", impl="reference_cuda",
+                   config=dict(workload="GPT-2 124M full training step, reference CUDA backend", global_batch=args.global_batch, seq_len=256))
+    else:
+        ms = float(lib.refcuda_ffn_step_ms(args.m_per_gpu, K_IN, N_OUT, args.steps, args.warmup, 4))
+        out = dict(metric=METRIC, value=6.0 * args.m_per_gpu * K_IN * N_OUT / (ms * 1e-3) / 1e12, unit=UNIT, n_gpus=1, steps=args.steps,
+                   warmup=args.warmup, ms_per_step=ms, higher_is_better=True, dtype="tf32 (cuBLAS)", data="synthetic", impl="reference_cuda",
+                   config=dict(workload=WORKLOAD + ", reference CUDA backend (cuBLAS + unfused kernels)", m_per_gpu=args.m_per_gpu, k=K_IN, n=N_OUT))
+    print(json.dumps(out), flush=True)
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -508,7 +538,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--mode", choices=["3xtf32", "tf32"], default="3xtf32")
-    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--impl", choices=["ours", "reference", "reference_cuda"], default="ours")
     ap.add_argument("--cpu-rows", type=int, default=256, help="rows of the workload the cpu_baseline leg runs")
     ap.add_argument("--ref-rows", type=int, default=32, help="rows per step of the --impl reference arm")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -520,6 +550,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.impl == "reference_cuda":
+        run_reference_cuda(args)
     elif args.workload == "train":
         run_train(args)
     elif args.workload == "decode":

@@ -136,13 +136,24 @@ def run_ours(args):
     gw = torch.zeros(K, N, device=dev)
     gb = torch.zeros(N, device=dev)
 
+    comm = torch.cuda.Stream() if world > 1 else None
+
     def step(i):
         s = sets[i % NSETS]
         be.device_linear_activation_fused_forward(s["y"], s["act"], s["x"], w, b, True, 1, M, K, N)
-        be.device_linear_backward(s["gx"], gw, gb, s["gy"], s["x"], w, 1, M, K, N)
-        if world > 1:
-            dist.all_reduce(gw)
-            dist.all_reduce(gb)
+        if world == 1:
+            be.device_linear_backward(s["gx"], gw, gb, s["gy"], s["x"], w, 1, M, K, N)
+            return
+        # data parallel: weight gradients first, their all-reduce runs on a second stream while grad_x is computed
+        be.linear_backward_weights(gw, gb, s["gy"], s["x"], M, K, N)
+        ready = torch.cuda.Event()
+        ready.record(stream)
+        with torch.cuda.stream(comm):
+            comm.wait_event(ready)
+            dist.all_reduce(gw, op=dist.ReduceOp.AVG)   # average: the accumulated gradient keeps its magnitude over many steps
+            dist.all_reduce(gb, op=dist.ReduceOp.AVG)
+        be.linear_backward_input(s["gx"], s["gy"], w, M, K, N)
+        stream.wait_stream(comm)
 
     def barrier():
         if world > 1:
@@ -204,8 +215,9 @@ def run_ours(args):
         be.device_linear_activation_fused_forward(s0["y"], s0["act"], s0["x"], w, b, True, 1, M, K, N)
         be.device_linear_backward(s0["gx"], gw, gb, s0["gy"], s0["x"], w, 1, M, K, N)
         if world > 1:
-            dist.all_reduce(gw)
-            dist.all_reduce(gb)
+            dist.all_reduce(gw, op=dist.ReduceOp.AVG)
+            dist.all_reduce(gb, op=dist.ReduceOp.AVG)
+            torch.cuda.current_stream().synchronize()
         be.device_memcpy_d2h(hact.data_ptr(), s0["act"].data_ptr(), hact.numel() * 4)
         be.device_memcpy_d2h(hgx.data_ptr(), s0["gx"].data_ptr(), hgx.numel() * 4)
         be.device_memcpy_d2h(hgw.data_ptr(), gw.data_ptr(), hgw.numel() * 4)

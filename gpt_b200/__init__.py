@@ -27,7 +27,8 @@ EXPORTED_SYMBOLS = [
     "gptb200_ctx_create", "gptb200_ctx_destroy", "gptb200_ctx_set_mode", "gptb200_ctx_get_mode",
     "gptb200_ctx_set_stream", "gptb200_ctx_set_option", "gptb200_ctx_synchronize", "gptb200_ctx_launch_count",
     "gptb200_status_string", "gptb200_last_error",
-    "gptb200_linear_forward", "gptb200_linear_backward", "gptb200_gelu_backward",
+    "gptb200_linear_forward", "gptb200_linear_backward", "gptb200_linear_backward_weights", "gptb200_linear_backward_input",
+    "gptb200_gelu_backward",
     "gptb200_unembed_forward", "gptb200_unembed_backward",
     "gptb200_malloc", "gptb200_free", "gptb200_memset", "gptb200_memcpy_h2d", "gptb200_memcpy_d2h",
     "gptb200_fill_normal", "gptb200_fill_const", "gptb200_embedding_forward", "gptb200_embedding_backward",
@@ -70,6 +71,8 @@ def load_library(path: str | None = None) -> ctypes.CDLL:
         "gptb200_last_error": (ctypes.c_char_p, [vp]),
         "gptb200_linear_forward": (i, [vp, fp, fp, fp, fp, fp, i, i, i, i]),
         "gptb200_linear_backward": (i, [vp, fp, fp, fp, fp, fp, fp, i, i, i]),
+        "gptb200_linear_backward_weights": (i, [vp, fp, fp, fp, fp, i, i, i]),
+        "gptb200_linear_backward_input": (i, [vp, fp, fp, fp, i, i, i]),
         "gptb200_gelu_backward": (i, [vp, fp, fp, fp, i, i]),
         "gptb200_unembed_forward": (i, [vp, fp, fp, fp, i, i, i]),
         "gptb200_unembed_backward": (i, [vp, fp, fp, fp, fp, fp, i, i, i]),
@@ -183,6 +186,16 @@ class Backend:
         self._check(self._lib.gptb200_linear_backward(self._ctx, _ptr(grad_x), _ptr(grad_w), _ptr(grad_b), _ptr(grad_y),
                                                       _ptr(x), _ptr(w), batch_size * seq_len, input_size, output_size),
                     "gptb200_linear_backward")
+
+    def linear_backward_weights(self, grad_w, grad_b, grad_y, x, m: int, k: int, n: int) -> None:
+        """Weight half of device_linear_backward: grad_w += x^T . grad_y, grad_b += column sums (for data-parallel overlap)."""
+        self._check(self._lib.gptb200_linear_backward_weights(self._ctx, _ptr(grad_w), _ptr(grad_b), _ptr(grad_y), _ptr(x), m, k, n),
+                    "gptb200_linear_backward_weights")
+
+    def linear_backward_input(self, grad_x, grad_y, w, m: int, k: int, n: int) -> None:
+        """Input half of device_linear_backward: grad_x = grad_y . w^T."""
+        self._check(self._lib.gptb200_linear_backward_input(self._ctx, _ptr(grad_x), _ptr(grad_y), _ptr(w), m, k, n),
+                    "gptb200_linear_backward_input")
 
     def device_activation_backward(self, grad_x, grad_y, x, batch_size: int, seq_len: int, output_size: int) -> None:
         self._check(self._lib.gptb200_gelu_backward(self._ctx, _ptr(grad_x), _ptr(grad_y), _ptr(x), batch_size * seq_len,

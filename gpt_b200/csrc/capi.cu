@@ -484,23 +484,27 @@ int gptb200_linear_forward(gptb200_ctx *ctx, float *y, float *act, const float *
     return run_gemm(ctx, c);
 }
 
-int gptb200_linear_backward(gptb200_ctx *ctx, float *grad_x, float *grad_w, float *grad_b, const float *grad_y, const float *x,
-                            const float *w, int m, int k, int n)
+int gptb200_linear_backward_input(gptb200_ctx *ctx, float *grad_x, const float *grad_y, const float *w, int m, int k, int n)
 {
     int rc = check_dims(ctx, m, k, n);
     if (rc) return rc;
-    if ((1LL * m * k > 0 && (!grad_x || !x)) || (1LL * k * n > 0 && (!grad_w || !w)) || (n > 0 && !grad_b) || (1LL * m * n > 0 && !grad_y))
-        return fail(ctx, GPTB200_ERR_INVALID_ARG, "null tensor pointer");
-    // grad_x[m x k] = grad_y[m x n] . w^T : A = grad_y (K-major), B = w stored [k x n] = [N' x K'] (K-major)
-    if (m > 0 && k > 0) {
-        if (n == 0) {
-            CUDA_TRY(ctx, cudaMemsetAsync(grad_x, 0, size_t(m) * k * sizeof(float), ctx->stream));
-        } else {
-            GemmCall dx{m, k, n, grad_y, false, w, false, grad_x, nullptr, nullptr, false};
-            rc = run_gemm(ctx, dx);
-            if (rc) return rc;
-        }
+    if (1LL * m * k == 0) return GPTB200_OK;
+    if (!grad_x || (n > 0 && (!grad_y || !w))) return fail(ctx, GPTB200_ERR_INVALID_ARG, "null tensor pointer");
+    if (n == 0) {
+        CUDA_TRY(ctx, cudaMemsetAsync(grad_x, 0, size_t(m) * k * sizeof(float), ctx->stream));
+        return GPTB200_OK;
     }
+    // grad_x[m x k] = grad_y[m x n] . w^T : A = grad_y (K-major), B = w stored [k x n] = [N' x K'] (K-major)
+    GemmCall dx{m, k, n, grad_y, false, w, false, grad_x, nullptr, nullptr, false};
+    return run_gemm(ctx, dx);
+}
+
+int gptb200_linear_backward_weights(gptb200_ctx *ctx, float *grad_w, float *grad_b, const float *grad_y, const float *x, int m, int k, int n)
+{
+    int rc = check_dims(ctx, m, k, n);
+    if (rc) return rc;
+    if ((1LL * k * n > 0 && !grad_w) || (n > 0 && !grad_b) || (1LL * m * n > 0 && !grad_y) || (1LL * m * k > 0 && !x))
+        return fail(ctx, GPTB200_ERR_INVALID_ARG, "null tensor pointer");
     // grad_w[k x n] += x^T . grad_y : A = x stored [m x k] = [K' x M'] (MN-major), B = grad_y [m x n] = [K' x N'] (MN-major)
     if (m > 0 && k > 0 && n > 0) {
         GemmCall dw{k, n, m, x, true, grad_y, true, grad_w, nullptr, nullptr, true};
@@ -508,6 +512,18 @@ int gptb200_linear_backward(gptb200_ctx *ctx, float *grad_x, float *grad_w, floa
         if (rc) return rc;
     }
     return run_bias_grad(ctx, grad_b, grad_y, m, n);
+}
+
+int gptb200_linear_backward(gptb200_ctx *ctx, float *grad_x, float *grad_w, float *grad_b, const float *grad_y, const float *x,
+                            const float *w, int m, int k, int n)
+{
+    int rc = check_dims(ctx, m, k, n);
+    if (rc) return rc;
+    if ((1LL * m * k > 0 && (!grad_x || !x)) || (1LL * k * n > 0 && (!grad_w || !w)) || (n > 0 && !grad_b) || (1LL * m * n > 0 && !grad_y))
+        return fail(ctx, GPTB200_ERR_INVALID_ARG, "null tensor pointer");
+    rc = gptb200_linear_backward_input(ctx, grad_x, grad_y, w, m, k, n);
+    if (rc) return rc;
+    return gptb200_linear_backward_weights(ctx, grad_w, grad_b, grad_y, x, m, k, n);
 }
 
 int gptb200_gelu_backward(gptb200_ctx *ctx, float *grad_x, const float *grad_y, const float *x, int m, int n)

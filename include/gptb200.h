@@ -74,6 +74,12 @@ int gptb200_linear_forward(gptb200_ctx *ctx, float *y, float *act, const float *
 int gptb200_linear_backward(gptb200_ctx *ctx, float *grad_x, float *grad_w, float *grad_b, const float *grad_y,
                             const float *x, const float *w, int m, int k, int n);
 
+/* The two halves of gptb200_linear_backward as separate calls (same kernels, same results): a data-parallel caller
+ * issues the weight half first and all-reduces grad_w / grad_b on another stream while the input half still runs.
+ * The reference has no multi-GPU path; both halves together are device_linear_backward (linear.cu:116-159). */
+int gptb200_linear_backward_weights(gptb200_ctx *ctx, float *grad_w, float *grad_b, const float *grad_y, const float *x, int m, int k, int n);
+int gptb200_linear_backward_input(gptb200_ctx *ctx, float *grad_x, const float *grad_y, const float *w, int m, int k, int n);
+
 /* ---- IGPTBackend::device_activation_backward
  *      (backend_interface.h:150-159, cuda/kernels/linear.cu:162-203, cpu/cpu_backend.cpp:268-287)
  *   grad_x = grad_y * gelu_tanh'(x), all [m x n]. */

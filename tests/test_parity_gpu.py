@@ -243,6 +243,24 @@ def test_accumulate_semantics_two_micro_batches(be, torch, oracle):
     check("grad_b", gb.cpu().numpy(), rgb, be.mode)
 
 
+def test_backward_halves_equal_the_whole(be, torch):
+    """gptb200_linear_backward_weights + gptb200_linear_backward_input give the bits of gptb200_linear_backward."""
+    rng = np.random.default_rng(21)
+    m, k, n = 700, 96, 260
+    d = Dev(torch)
+    x, gy, w = d.put(rng.standard_normal((m, k), dtype=np.float32)), d.put(rng.standard_normal((m, n), dtype=np.float32)), d.put(
+        (0.02 * rng.standard_normal((k, n))).astype(np.float32))
+    gw0, gb0 = rng.standard_normal((k, n), dtype=np.float32), rng.standard_normal(n, dtype=np.float32)
+    gx1, gw1, gb1 = d.nan(m, k), d.put(gw0), d.put(gb0)
+    be.device_linear_backward(gx1, gw1, gb1, gy, x, w, 1, m, k, n)
+    gx2, gw2, gb2 = d.nan(m, k), d.put(gw0), d.put(gb0)
+    be.linear_backward_weights(gw2, gb2, gy, x, m, k, n)
+    be.linear_backward_input(gx2, gy, w, m, k, n)
+    be.synchronize()
+    d.check_canaries()
+    assert torch.equal(gx1, gx2) and torch.equal(gw1, gw2) and torch.equal(gb1, gb2)
+
+
 def test_run_to_run_bitwise_repeatability(be, torch):
     """Split-K partial sums are reduced in a fixed order: identical inputs give identical bits."""
     rng = np.random.default_rng(11)

@@ -26,7 +26,7 @@ MODE_TF32 = 1
 EXPORTED_SYMBOLS = [
     "gptb200_ctx_create", "gptb200_ctx_destroy", "gptb200_ctx_set_mode", "gptb200_ctx_get_mode",
     "gptb200_ctx_set_stream", "gptb200_ctx_set_option", "gptb200_ctx_synchronize", "gptb200_ctx_launch_count",
-    "gptb200_status_string", "gptb200_last_error",
+    "gptb200_status_string", "gptb200_last_error", "gptb200_plan_gemm", "gptb200_selftest_wait_timeout",
     "gptb200_linear_forward", "gptb200_linear_backward", "gptb200_linear_backward_weights", "gptb200_linear_backward_input",
     "gptb200_gelu_backward",
     "gptb200_unembed_forward", "gptb200_unembed_backward",
@@ -67,6 +67,8 @@ def load_library(path: str | None = None) -> ctypes.CDLL:
         "gptb200_ctx_set_option": (i, [vp, ctypes.c_char_p, i]),
         "gptb200_ctx_synchronize": (i, [vp]),
         "gptb200_ctx_launch_count": (ctypes.c_longlong, [vp]),
+        "gptb200_selftest_wait_timeout": (i, [vp, i]),
+        "gptb200_plan_gemm": (i, [i, i, i, i, i, i, i, i, ctypes.POINTER(i)]),
         "gptb200_status_string": (ctypes.c_char_p, [i]),
         "gptb200_last_error": (ctypes.c_char_p, [vp]),
         "gptb200_linear_forward": (i, [vp, fp, fp, fp, fp, fp, i, i, i, i]),
@@ -111,6 +113,22 @@ def load_library(path: str | None = None) -> ctypes.CDLL:
     if path is None:
         _lib = lib
     return lib
+
+
+PLAN_KERNELS = {0: "none", 1: "pair", 2: "single", 3: "skinny", 4: "simt"}
+
+
+def plan_gemm(num_sms: int, m: int, n: int, k: int, a_mn: bool, b_mn: bool, has_epilogue: bool = False, accumulate: bool = False) -> dict:
+    """Launch plan of one GEMM (host logic only, no GPU needed); see gptb200_plan_gemm in include/gptb200.h."""
+    lib = load_library()
+    out = (ctypes.c_int * 8)()
+    rc = lib.gptb200_plan_gemm(num_sms, m, n, k, int(a_mn), int(b_mn), int(has_epilogue), int(accumulate), out)
+    if rc != 0:
+        raise GptB200Error(rc, "gptb200_plan_gemm")
+    keys = ["kernel", "tile_n", "tiles_m", "tiles_n", "splits", "k_per_split", "grid", "scratch_kib"]
+    d = dict(zip(keys, list(out)))
+    d["kernel"] = PLAN_KERNELS[d["kernel"]]
+    return d
 
 
 def _ptr(t: Any) -> int | None:

@@ -12,6 +12,7 @@
 #include <cuda_runtime.h>
 
 #include "ctx_internal.h"
+#include "gemm_plan.h"
 #include "gemm_sm100.cuh"
 #include "gemm_sm100_pair.cuh"
 #include "skinny_sm100.cuh"
@@ -141,29 +142,6 @@ int make_out_tmap(gptb200_ctx *ctx, CUtensorMap *map, float *base, long long dep
     return GPTB200_OK;
 }
 
-// `units`: number of CTAs (or CTA pairs) that run concurrently
-int pick_splits(const gptb200_ctx *ctx, long long tiles, int num_kb, bool allowed, size_t bytes_per_split, int units)
-{
-    if (!allowed) return 1;
-    const int sms = units;
-    int cap = ctx->max_splits > 0 ? ctx->max_splits : 16;
-    cap = std::min(cap, std::max(1, num_kb / 8));  // at least 8 k-blocks per split
-    if (bytes_per_split > 0) cap = static_cast<int>(std::min<size_t>(cap, std::max<size_t>(1, (ctx->ws_limit / 2) / bytes_per_split)));
-    if (ctx->max_splits > 0) return std::max(1, cap);
-    int best = 1;
-    double best_eff = 0.0;
-    for (int s = 1; s <= cap; ++s) {
-        const long long items = tiles * s;
-        const long long waves = (items + sms - 1) / sms;
-        const double eff = double(items) / double(waves * sms);
-        if (eff > best_eff + 0.04) {  // take a larger split only for a real gain in SM occupancy
-            best_eff = eff;
-            best = s;
-        }
-    }
-    return best;
-}
-
 template <bool W_KN>
 int launch_skinny(gptb200_ctx *ctx, int mr, dim3 grid, float *partial, const GemmCall &c, int k_per_split)
 {
@@ -181,45 +159,49 @@ int launch_skinny(gptb200_ctx *ctx, int mr, dim3 grid, float *partial, const Gem
 
 // Decode-shaped forward GEMMs (m <= 16, x K-major): stream the weights once, split k over CTAs, finish in a
 // second small kernel.  HBM-bound: 4*k*n bytes per call.
-int run_skinny(gptb200_ctx *ctx, const GemmCall &c)
+int run_skinny(gptb200_ctx *ctx, const GemmCall &c, const GemmPlan &pl)
 {
     int mr = 1;
     while (mr < c.M) mr *= 2;
     const bool w_kn = c.b_mn;  // W stored [k][n]
-    const int cols_per_block = kSkinnyThreads * (w_kn ? 4 : 1);
-    const int col_blocks = (c.N + cols_per_block - 1) / cols_per_block;
-    int splits = std::max(1, std::min((ctx->num_sms * 4 + col_blocks - 1) / col_blocks, c.K / 32));
-    int k_per_split = (((c.K + splits - 1) / splits) + 3) & ~3;
-    splits = (c.K + k_per_split - 1) / k_per_split;
-    const int rc = ensure_workspace(ctx, size_t(splits) * c.M * c.N * sizeof(float));
+    const int rc = ensure_workspace(ctx, pl.workspace_bytes);
     if (rc != GPTB200_OK) return rc;
-    const dim3 grid(col_blocks, splits);
-    const int rc2 = w_kn ? launch_skinny<true>(ctx, mr, grid, ctx->ws, c, k_per_split) : launch_skinny<false>(ctx, mr, grid, ctx->ws, c, k_per_split);
+    const dim3 grid(pl.tiles_n, pl.splits);
+    const int rc2 = w_kn ? launch_skinny<true>(ctx, mr, grid, ctx->ws, c, pl.kb_per_split) : launch_skinny<false>(ctx, mr, grid, ctx->ws, c, pl.kb_per_split);
     if (rc2 != GPTB200_OK) return rc2;
     const long long total = 1LL * c.M * c.N;
     skinny_finish_kernel<<<static_cast<int>(std::min<long long>((total + 255) / 256, 1LL * ctx->num_sms * 4)), 256, 0, ctx->stream>>>(
-        c.out, c.act, ctx->ws, c.bias, c.M, c.N, splits);
+        c.out, c.act, ctx->ws, c.bias, c.M, c.N, pl.splits);
     ctx->launches++;
     CUDA_TRY(ctx, cudaGetLastError());
     return GPTB200_OK;
 }
 
+GemmPlanInput plan_input(const gptb200_ctx *ctx, const GemmCall &c)
+{
+    GemmPlanInput in{};
+    in.M = c.M; in.N = c.N; in.K = c.K;
+    in.a_mn = c.a_mn; in.b_mn = c.b_mn;
+    in.has_epilogue = c.bias != nullptr || c.act != nullptr;
+    in.accumulate = c.accumulate;
+    in.aligned = aligned16(c.a) && aligned16(c.b) && aligned16(c.out) && (!c.act || aligned16(c.act));
+    in.num_sms = ctx->num_sms;
+    in.opt_tile_n = ctx->tile_n; in.opt_max_splits = ctx->max_splits; in.opt_pair = ctx->pair; in.opt_skinny = ctx->skinny;
+    in.ws_limit = ctx->ws_limit;
+    return in;
+}
+
 int run_gemm(gptb200_ctx *ctx, const GemmCall &c)
 {
-    if (c.M == 0 || c.N == 0) return GPTB200_OK;
-    if (ctx->skinny && c.M <= 16 && !c.a_mn && !c.accumulate && c.K >= 32 && c.K % 4 == 0 && c.N % 4 == 0 && aligned16(c.a) && aligned16(c.b) &&
-        aligned16(c.out) && (!c.act || aligned16(c.act)))
-        return run_skinny(ctx, c);
-    const long long lda = c.a_mn ? c.M : c.K;
-    const long long ldb = c.b_mn ? c.N : c.K;
-    const bool tma_ok = c.K > 0 && aligned16(c.a) && aligned16(c.b) && aligned16(c.out) && (!c.act || aligned16(c.act)) &&
-                        (lda % 4 == 0) && (ldb % 4 == 0) && (c.N % 4 == 0) && !(c.a_mn && !c.b_mn);
-    if (!tma_ok) {
+    const GemmPlan pl = plan_gemm(plan_input(ctx, c));
+    if (pl.kernel == KERNEL_NONE) return GPTB200_OK;
+    if (pl.kernel == KERNEL_SKINNY) return run_skinny(ctx, c, pl);
+    if (pl.kernel == KERNEL_SIMT) {
         // Plain SIMT kernel for the shapes TMA cannot address.
         const long long a_rs = c.a_mn ? 1 : c.K, a_cs = c.a_mn ? c.M : 1;
         const long long b_rs = c.b_mn ? c.N : 1, b_cs = c.b_mn ? 1 : c.K;
         dim3 block(32, 8);
-        dim3 grid((c.N + 31) / 32, (c.M + 31) / 32);
+        dim3 grid(pl.tiles_n, pl.tiles_m);
         simt_gemm_kernel<<<grid, block, 0, ctx->stream>>>(c.M, c.N, c.K, c.a, a_rs, a_cs, c.b, b_rs, b_cs, c.out, c.act, c.bias, c.N,
                                                           c.accumulate ? EPI_ACCUM : EPI_STORE);
         ctx->launches++;
@@ -228,36 +210,21 @@ int run_gemm(gptb200_ctx *ctx, const GemmCall &c)
     }
 
     const bool x3 = ctx->mode == GPTB200_MODE_3XTF32;
-    // CTA pairs (256 x 256 tiles, cta_group::2): measured faster than one CTA per tile on every GPT-2 124M shape
-    // as long as there are enough 256 x 256 tiles to occupy most SM pairs; with fewer tiles the one-CTA kernel with
-    // 128-wide tiles fills the machine better.  Option "pair": 1 = always, 0 = this heuristic, -1 = never.
-    const long long pair_tiles = 1LL * ((c.M + 255) / 256) * ((c.N + 255) / 256);
-    const bool split_allowed = !c.bias && !c.act;
+    const bool pair = pl.kernel == KERNEL_PAIR;
+    const int bn = pl.tile_n;
+    const int splits = pl.splits;
     const size_t bytes_per_split = size_t(c.M) * size_t(c.N) * sizeof(float);
-    const int num_kb = (c.K + kBK - 1) / kBK;
-    const int pair_splits = pick_splits(ctx, pair_tiles, num_kb, split_allowed, bytes_per_split, ctx->num_sms / 2);
-    const bool pair = ctx->pair > 0 ||
-                      (ctx->pair == 0 && ctx->tile_n == 0 && c.M > kBM && c.N > 128 && pair_tiles * pair_splits * 20 >= 9LL * ctx->num_sms);
-    int bn = pair ? 256 : ctx->tile_n;
-    if (bn != 128 && bn != 256) {
-        const long long tiles256 = 1LL * ((c.M + kBM - 1) / kBM) * ((c.N + 255) / 256);
-        bn = (c.N <= 128 || tiles256 < ctx->num_sms / 2) ? 128 : 256;
-    }
-
     GemmParams p{};
     p.M = c.M;
     p.N = c.N;
     p.K = c.K;
-    p.tiles_m = (c.M + kBM - 1) / kBM;
-    p.tiles_n = (c.N + bn - 1) / bn;
-    p.num_kb = (c.K + kBK - 1) / kBK;
+    p.tiles_m = pl.tiles_m;
+    p.tiles_n = pl.tiles_n;
+    p.num_kb = pl.num_kb;
+    p.kb_per_split = pl.kb_per_split;
+    p.splits = splits;
     p.status = ctx->d_status;
     p.debug = ctx->debug;
-    const long long tiles = pair ? 1LL * ((p.tiles_m + 1) / 2) * p.tiles_n : 1LL * p.tiles_m * p.tiles_n;
-    int splits = pair ? pair_splits : pick_splits(ctx, tiles, p.num_kb, split_allowed, bytes_per_split, ctx->num_sms);
-    p.kb_per_split = (p.num_kb + splits - 1) / splits;
-    splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
-    p.splits = splits;
 
     float *out_base = c.out;
     if (splits > 1) {
@@ -293,9 +260,7 @@ int run_gemm(gptb200_ctx *ctx, const GemmCall &c)
         rc = make_tmap(ctx, &tb, c.b, c.N, c.K, kBK, pair ? bn / 2 : bn, false);
     if (rc != GPTB200_OK) return rc;
 
-    const long long items = tiles * splits;
-    const int grid = pair ? 2 * static_cast<int>(std::min<long long>(items, ctx->num_sms / 2))
-                          : static_cast<int>(std::min<long long>(items, ctx->num_sms));
+    const int grid = pl.grid;
     cudaError_t e;
     if (pair)
         e = x3 ? launch_pair<true>(ctx, c.a_mn, c.b_mn, ta, tb, to, tact, p, grid) : launch_pair<false>(ctx, c.a_mn, c.b_mn, ta, tb, to, tact, p, grid);
@@ -471,6 +436,33 @@ int gptb200_ctx_synchronize(gptb200_ctx *ctx)
 }
 
 long long gptb200_ctx_launch_count(const gptb200_ctx *ctx) { return ctx ? ctx->launches : -1; }
+
+int gptb200_selftest_wait_timeout(gptb200_ctx *ctx, int limit_us)
+{
+    if (!ctx || limit_us <= 0 || limit_us > 100000) return GPTB200_ERR_INVALID_ARG;
+    int khz = 0;
+    CUDA_TRY(ctx, cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, ctx->device));
+    const long long cycles = static_cast<long long>(limit_us) * std::max(khz, 1000) / 1000;
+    wait_timeout_selftest_kernel<<<1, 32, 0, ctx->stream>>>(ctx->d_status, cycles);
+    ctx->launches++;
+    CUDA_TRY(ctx, cudaGetLastError());
+    return GPTB200_OK;
+}
+
+int gptb200_plan_gemm(int num_sms, int m, int n, int k, int a_mn_major, int b_mn_major, int has_epilogue, int accumulate, int *plan8)
+{
+    if (!plan8 || num_sms <= 0 || m < 0 || n < 0 || k < 0) return GPTB200_ERR_INVALID_ARG;
+    GemmPlanInput in{};
+    in.M = m; in.N = n; in.K = k;
+    in.a_mn = a_mn_major != 0; in.b_mn = b_mn_major != 0;
+    in.has_epilogue = has_epilogue != 0; in.accumulate = accumulate != 0; in.aligned = true;
+    in.num_sms = num_sms; in.opt_skinny = true; in.ws_limit = size_t(1) << 30;
+    const GemmPlan p = plan_gemm(in);
+    const long long ws = static_cast<long long>(p.workspace_bytes);
+    const int out[8] = {p.kernel, p.tile_n, p.tiles_m, p.tiles_n, p.splits, p.kb_per_split, p.grid, static_cast<int>(std::min<long long>(ws >> 10, 0x7fffffff))};
+    for (int i = 0; i < 8; ++i) plan8[i] = out[i];
+    return GPTB200_OK;
+}
 
 int gptb200_linear_forward(gptb200_ctx *ctx, float *y, float *act, const float *x, const float *w, const float *b, int activation,
                            int m, int k, int n)

@@ -1,0 +1,124 @@
+// Host-side planning of one GEMM call: which kernel, which tile, how many split-K parts, how many CTAs and how much
+// scratch.  Plain C++ without CUDA so that the same code is used by the launcher (capi.cu) and exercised by CPU
+// tests through gptb200_plan_gemm.
+#pragma once
+
+#include <algorithm>
+#include <cstddef>
+
+namespace gptb200 {
+
+enum GemmKernelKind : int {
+    KERNEL_NONE = 0,    // empty output: nothing to launch
+    KERNEL_PAIR = 1,    // gemm_tcgen05_pair_kernel: CTA pairs, 256 x 256 tiles
+    KERNEL_SINGLE = 2,  // gemm_tcgen05_kernel: one CTA per 128 x tile_n tile
+    KERNEL_SKINNY = 3,  // skinny_gemm_kernel: weight streaming for m <= 16
+    KERNEL_SIMT = 4,    // simt_gemm_kernel: shapes TMA cannot address
+};
+
+struct GemmPlanInput {
+    int M, N, K;             // D[M x N] = A[M x K] . B[K x N]
+    bool a_mn, b_mn;         // operand stored with the free index contiguous
+    bool has_epilogue;       // bias and / or GELU output: split-K is not possible
+    bool accumulate;         // out += result
+    bool aligned;            // base pointers 16-byte aligned
+    int num_sms;
+    int opt_tile_n;          // 0 automatic, 128, 256
+    int opt_max_splits;      // 0 automatic
+    int opt_pair;            // 1 always, 0 heuristic, -1 never
+    bool opt_skinny;
+    size_t ws_limit;         // scratch limit in bytes
+};
+
+struct GemmPlan {
+    int kernel;
+    int tile_n;
+    int tiles_m, tiles_n;    // 128-row tiles, tile_n-column tiles
+    int splits, kb_per_split, num_kb;
+    int grid;                // CTAs
+    size_t workspace_bytes;  // split-K partial tiles (or skinny partial sums)
+};
+
+constexpr int kPlanBM = 128;
+constexpr int kPlanBK = 32;
+
+// `units`: number of CTAs (or CTA pairs) that run concurrently
+inline int plan_splits(const GemmPlanInput &in, long long tiles, int num_kb, bool allowed, size_t bytes_per_split, int units)
+{
+    if (!allowed) return 1;
+    int cap = in.opt_max_splits > 0 ? in.opt_max_splits : 16;
+    cap = std::min(cap, std::max(1, num_kb / 8));  // at least 8 k-blocks per split
+    if (bytes_per_split > 0) cap = static_cast<int>(std::min<size_t>(cap, std::max<size_t>(1, (in.ws_limit / 2) / bytes_per_split)));
+    if (in.opt_max_splits > 0) return std::max(1, cap);
+    int best = 1;
+    double best_eff = 0.0;
+    for (int s = 1; s <= cap; ++s) {
+        const long long items = tiles * s;
+        const long long waves = (items + units - 1) / units;
+        const double eff = double(items) / double(waves * units);
+        if (eff > best_eff + 0.04) {  // take a larger split only for a real gain in SM occupancy
+            best_eff = eff;
+            best = s;
+        }
+    }
+    return best;
+}
+
+inline GemmPlan plan_gemm(const GemmPlanInput &in)
+{
+    GemmPlan p{};
+    if (in.M <= 0 || in.N <= 0) return p;
+    const bool fours = in.K % 4 == 0 && in.N % 4 == 0;
+    if (in.opt_skinny && in.M <= 16 && !in.a_mn && !in.accumulate && in.K >= 32 && fours && in.aligned) {
+        p.kernel = KERNEL_SKINNY;
+        const int cols_per_block = 128 * (in.b_mn ? 4 : 1);
+        p.tiles_n = (in.N + cols_per_block - 1) / cols_per_block;
+        p.tiles_m = 1;
+        int splits = std::max(1, std::min((in.num_sms * 4 + p.tiles_n - 1) / p.tiles_n, in.K / 32));
+        p.kb_per_split = (((in.K + splits - 1) / splits) + 3) & ~3;   // here: k ELEMENTS per split, a multiple of 4
+        p.splits = (in.K + p.kb_per_split - 1) / p.kb_per_split;
+        p.grid = p.tiles_n * p.splits;
+        p.workspace_bytes = size_t(p.splits) * in.M * in.N * sizeof(float);
+        return p;
+    }
+    const long long lda = in.a_mn ? in.M : in.K;
+    const long long ldb = in.b_mn ? in.N : in.K;
+    const bool tma_ok = in.K > 0 && in.aligned && lda % 4 == 0 && ldb % 4 == 0 && in.N % 4 == 0 && !(in.a_mn && !in.b_mn);
+    if (!tma_ok) {
+        p.kernel = KERNEL_SIMT;
+        p.tiles_m = (in.M + 31) / 32;
+        p.tiles_n = (in.N + 31) / 32;
+        p.splits = 1;
+        p.grid = p.tiles_m * p.tiles_n;
+        return p;
+    }
+    // CTA pairs (256 x 256 tiles, cta_group::2): measured faster than one CTA per tile on every GPT-2 124M shape as long
+    // as there are enough 256 x 256 work items to occupy most SM pairs; with fewer, 128-wide one-CTA tiles fill the
+    // machine better.
+    const long long pair_tiles = 1LL * ((in.M + 255) / 256) * ((in.N + 255) / 256);
+    const bool split_allowed = !in.has_epilogue;
+    const size_t bytes_per_split = size_t(in.M) * size_t(in.N) * sizeof(float);
+    p.num_kb = (in.K + kPlanBK - 1) / kPlanBK;
+    const int pair_splits = plan_splits(in, pair_tiles, p.num_kb, split_allowed, bytes_per_split, in.num_sms / 2);
+    const bool pair = in.opt_pair > 0 || (in.opt_pair == 0 && in.opt_tile_n == 0 && in.M > kPlanBM && in.N > 128 &&
+                                          pair_tiles * pair_splits * 20 >= 9LL * in.num_sms);
+    int bn = pair ? 256 : in.opt_tile_n;
+    if (bn != 128 && bn != 256) {
+        const long long tiles256 = 1LL * ((in.M + kPlanBM - 1) / kPlanBM) * ((in.N + 255) / 256);
+        bn = (in.N <= 128 || tiles256 < in.num_sms / 2) ? 128 : 256;
+    }
+    p.kernel = pair ? KERNEL_PAIR : KERNEL_SINGLE;
+    p.tile_n = bn;
+    p.tiles_m = (in.M + kPlanBM - 1) / kPlanBM;
+    p.tiles_n = (in.N + bn - 1) / bn;
+    const long long tiles = pair ? 1LL * ((p.tiles_m + 1) / 2) * p.tiles_n : 1LL * p.tiles_m * p.tiles_n;
+    int splits = pair ? pair_splits : plan_splits(in, tiles, p.num_kb, split_allowed, bytes_per_split, in.num_sms);
+    p.kb_per_split = (p.num_kb + splits - 1) / splits;
+    p.splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
+    const long long items = tiles * p.splits;
+    p.grid = pair ? 2 * static_cast<int>(std::min<long long>(items, in.num_sms / 2)) : static_cast<int>(std::min<long long>(items, in.num_sms));
+    p.workspace_bytes = p.splits > 1 ? bytes_per_split * p.splits : 0;
+    return p;
+}
+
+}  // namespace gptb200

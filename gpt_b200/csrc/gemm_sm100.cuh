@@ -44,6 +44,7 @@ enum DeviceStatus : int {
     DEV_TIMEOUT_EPILOGUE = 105,   // epilogue gave up waiting for a finished accumulator
     DEV_TIMEOUT_CONVERT = 106,    // converter gave up waiting for a landed stage
     DEV_TIMEOUT_DRAIN = 107,      // teardown gave up waiting for outstanding MMAs
+    DEV_TIMEOUT_SELFTEST = 108,   // the self-test's wait on a barrier that nothing signals ran out, as intended
 };
 
 enum EpilogueMode : int {
@@ -94,7 +95,8 @@ struct GemmCfg {
     static_assert(!kChunked || kColsPerEpiWarp == 128, "chunked epilogue keeps 128 running sums per thread");
 };
 
-__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, int *status, int code)
+__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, int *status, int code,
+                                             long long limit_cycles = kWaitTimeoutCycles)
 {
     if (ptx::mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
@@ -103,7 +105,7 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, vola
         if (ptx::mbar_try_wait(bar, parity)) return true;
         if ((++spins & 31u) == 0) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitTimeoutCycles) {
+            if (clock64() - t0 > limit_cycles) {
                 *abort_flag = 1u;
                 atomicCAS(status, 0, code);
                 return false;
@@ -509,6 +511,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         ptx::tc_fence_after();
         ptx::tmem_dealloc(tmem_base, kTmemCols);
     }
+}
+
+// Self-test of the bounded wait: one thread waits, with a short limit, on a barrier that nothing will ever signal.
+// The wait runs out, the status word receives DEV_TIMEOUT_SELFTEST and the kernel returns normally: exactly the path
+// a real kernel takes when an expected signal never comes.
+__global__ void wait_timeout_selftest_kernel(int *status, long long limit_cycles)
+{
+    __shared__ __align__(8) unsigned long long bar_storage;
+    __shared__ uint32_t abort_flag;
+    const uint32_t bar = ptx::smem_u32(&bar_storage);
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(bar, 1);
+        abort_flag = 0u;
+        ptx::fence_mbar_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) bounded_wait(bar, 0u, &abort_flag, status, DEV_TIMEOUT_SELFTEST, limit_cycles);
+    __syncthreads();
 }
 
 // out[i] (+)= sum_s ws[s][i], fixed order s = 0..splits-1 (deterministic split-K reduction).

@@ -58,6 +58,14 @@ int gptb200_ctx_set_option(gptb200_ctx *ctx, const char *key, int value);
 int gptb200_ctx_synchronize(gptb200_ctx *ctx);
 /* Number of kernels this context has launched so far. */
 long long gptb200_ctx_launch_count(const gptb200_ctx *ctx);
+/* Failure-detection self-test: launches a one-CTA kernel whose bounded wait (limit_us microseconds, at most 100 ms) is on a
+ * barrier that nothing signals.  The wait runs out, the kernel returns normally, and the next gptb200_ctx_synchronize reports
+ * GPTB200_ERR_DEVICE_TIMEOUT (and clears the device status); the context stays usable. */
+int gptb200_selftest_wait_timeout(gptb200_ctx *ctx, int limit_us);
+/* The launch plan for D[m x n] = A[m x k] . B[k x n] on a GPU with num_sms SMs, without touching a GPU (host logic only,
+ * default options).  plan8 = {kernel (0 none, 1 CTA-pair tcgen05, 2 one-CTA tcgen05, 3 weight streaming, 4 SIMT), tile_n,
+ * tiles_m, tiles_n, split_k, k-blocks (or k elements for kernel 3) per split, CTAs, scratch KiB}. */
+int gptb200_plan_gemm(int num_sms, int m, int n, int k, int a_mn_major, int b_mn_major, int has_epilogue, int accumulate, int *plan8);
 const char *gptb200_status_string(int status);
 const char *gptb200_last_error(const gptb200_ctx *ctx);
 

@@ -313,3 +313,24 @@ def test_full_size_ffn_properties(be, torch):
     assert float((gw[:, cols].double() - refw).abs().max() / refw.abs().max()) <= tol
     refx = gy[rows].double() @ w.double().t()
     assert float((gx[rows].double() - refx).abs().max() / refx.abs().max()) <= tol
+
+
+def test_bounded_wait_runs_out_and_is_reported(torch, built_library):
+    """Failure detection: a wait on a barrier that nothing signals ends after its limit, the kernel returns, the host reads
+    the status as GPTB200_ERR_DEVICE_TIMEOUT, and the context keeps working (no trap, no hang, no lost context)."""
+    import gpt_b200
+    b = gpt_b200.Backend(0)
+    assert b.lib.gptb200_selftest_wait_timeout(b.handle, 2000) == 0    # 2 ms limit
+    with pytest.raises(gpt_b200.GptB200Error) as e:
+        b.synchronize()
+    assert e.value.status == 4 and "108" in str(e.value)
+    b.synchronize()                                                   # status was cleared
+    x = torch.randn(256, 64, device="cuda")
+    w = torch.randn(64, 128, device="cuda") * 0.02
+    bias = torch.zeros(128, device="cuda")
+    y = torch.empty(256, 128, device="cuda")
+    b.device_linear_activation_fused_forward(y, None, x, w, bias, False, 1, 256, 64, 128)
+    b.synchronize()
+    ref = x.double() @ w.double()
+    assert float((y.double() - ref).abs().max() / ref.abs().max()) <= 1e-5
+    b.close()

@@ -1,0 +1,69 @@
+"""CPU tests of the host-side launch planning (gpt_b200/csrc/gemm_plan.h through gptb200_plan_gemm): no GPU involved."""
+import itertools
+
+import pytest
+
+SMS = 148
+
+
+@pytest.fixture(scope="module")
+def plan(built_library):
+    import gpt_b200
+    return gpt_b200.plan_gemm
+
+
+def test_gpt2_124m_shapes_use_the_cta_pair_kernel_at_m_8192(plan):
+    D, F, V = 768, 3072, 50304
+    for k, n in ((D, 3 * D), (D, D), (D, F), (F, D)):
+        fwd = plan(SMS, 8192, n, k, False, True, has_epilogue=True)
+        assert fwd["kernel"] == "pair" and fwd["splits"] == 1 and fwd["grid"] == 148
+        dx = plan(SMS, 8192, k, n, False, False)
+        assert dx["kernel"] == "pair"
+        dw = plan(SMS, k, n, 8192, True, True, accumulate=True)
+        assert dw["kernel"] in ("pair", "single")
+    assert plan(SMS, 8192, V, D, False, False)["kernel"] == "pair"           # LM head forward
+    assert plan(SMS, V, D, 8192, True, True, accumulate=True)["splits"] == 1   # 1179 tiles need no split-K
+
+
+def test_small_and_odd_shapes(plan):
+    assert plan(SMS, 64, 96, 32, False, True, True)["kernel"] == "single"      # the reference's test shapes: ragged tiles
+    assert plan(SMS, 64, 32, 256, False, True, True)["grid"] == 1
+    assert plan(SMS, 8, 3072, 768, False, True, True)["kernel"] == "skinny"    # decode-shaped
+    assert plan(SMS, 1, 50304, 768, False, False)["kernel"] == "skinny"
+    assert plan(SMS, 16, 768, 768, True, True, False, True)["kernel"] != "skinny"   # weight gradients never stream
+    assert plan(SMS, 77, 50, 30, False, True, True)["kernel"] == "simt"        # row pitch not a multiple of 16 bytes
+    assert plan(SMS, 5, 9, 7, False, True, True)["kernel"] == "simt"
+    assert plan(SMS, 0, 128, 64, False, True, True)["kernel"] == "none"
+    assert plan(SMS, 128, 128, 0, False, True, True)["kernel"] == "simt"       # k == 0: y = bias
+
+
+@pytest.mark.parametrize("sms", [148, 132, 16])
+def test_plan_invariants_over_a_sweep(plan, sms):
+    dims_m = [1, 17, 128, 129, 256, 1000, 2048, 8192, 32768]
+    dims_nk = [32, 96, 128, 260, 768, 2304, 3072, 50304]
+    for m, n, k in itertools.product(dims_m, dims_nk, dims_nk):
+        if m * n >= 2 ** 31 or m * k >= 2 ** 31:
+            continue
+        for a_mn, b_mn, epi, acc in ((False, True, True, False), (False, False, False, False), (True, True, False, True)):
+            p = plan(sms, m, n, k, a_mn, b_mn, epi, acc)
+            assert p["grid"] >= 1
+            if p["kernel"] in ("pair", "single"):
+                assert p["grid"] <= sms
+                num_kb = (k + 31) // 32
+                assert p["splits"] >= 1 and p["k_per_split"] >= 1
+                assert p["splits"] * p["k_per_split"] >= num_kb                  # the splits cover all of k
+                assert (p["splits"] - 1) * p["k_per_split"] < num_kb             # and none of them is empty
+                if epi:
+                    assert p["splits"] == 1                                     # bias / GELU epilogues cannot be split
+                if p["splits"] > 1:
+                    assert p["scratch_kib"] * 1024 >= p["splits"] * m * n * 4 - 1023
+                    assert p["scratch_kib"] <= 1 << 20                          # scratch limit of 1 GiB
+                    assert p["k_per_split"] >= 8                                # at least eight k-blocks per split
+                else:
+                    assert p["scratch_kib"] == 0
+                if p["kernel"] == "pair":
+                    assert p["grid"] % 2 == 0 and p["tile_n"] == 256 and m > 128
+                else:
+                    assert p["tile_n"] in (128, 256)
+            if p["kernel"] == "skinny":
+                assert m <= 16 and not acc and p["splits"] * p["k_per_split"] >= k and p["k_per_split"] % 4 == 0

@@ -468,6 +468,64 @@ def run_decode(args):
     be.close()
 
 
+def run_generate(args):
+    """--workload generate: autoregressive generation with GPT-2 124M random-init weights (BASELINE.json configs[4]): for batch
+    1, 8, 64 a random-id prompt of 64 tokens is extended to 256 tokens at temperature 1.0.  As in the reference
+    (src/infer/infer.cpp:112-148) there is no KV cache: every new token recomputes the whole prefix, so the linear layers see
+    m = batch * prefix rows (64 ... 255 per sequence).  Sampling (softmax at temperature 1 + multinomial over the 50257 real
+    tokens) runs on the GPU with torch; everything else goes through the model driver of this library."""
+    import numpy as np
+    import torch
+    import gpt_b200
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    cfg = gpt_b200.GPT2_124M
+    V, Vp = cfg["vocab_size"], cfg["vocab_size_padded"]
+    mode = gpt_b200.MODE_TF32 if args.mode == "tf32" else gpt_b200.MODE_3XTF32
+    model = gpt_b200.Model(cfg, 0, torch.cuda.current_stream().cuda_stream, mode, seed=42, use_grad=False)
+    model.init(0.0, 0.02)
+    results = {}
+    launches = 0
+    PROMPT, TOTAL = 64, 256
+    for batch in (1, 8, 64):
+        torch.manual_seed(batch)
+        tokens = torch.zeros(batch, TOTAL, dtype=torch.int32, device=dev)
+        tokens[:, :PROMPT] = torch.randint(0, V, (batch, PROMPT), dtype=torch.int32, device=dev)
+        model.set_size(batch, TOTAL)          # allocate once at the largest shape; later calls reuse the buffers
+
+        class _Raw:
+            pass
+
+        def generate():
+            for t in range(PROMPT, TOTAL):
+                model.set_size(batch, t)
+                prefix = tokens[:, :t].contiguous()
+                model.forward(prefix)
+                raw = _Raw()
+                raw.__cuda_array_interface__ = dict(shape=(batch, t, Vp), typestr="<f4", data=(model.logits_ptr, False), version=3, strides=None)
+                logits = torch.as_tensor(raw, device=dev)[:, t - 1, :V]
+                probs = torch.softmax(logits.float(), dim=-1)            # temperature 1.0
+                tokens[:, t] = torch.multinomial(probs, 1).squeeze(1).to(torch.int32)
+
+        generate()                            # warm-up pass (also sizes scratch buffers)
+        torch.cuda.synchronize()
+        l0 = model.launch_count()
+        t0 = time.perf_counter()
+        generate()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        launches += model.launch_count() - l0
+        new_tokens = batch * (TOTAL - PROMPT)
+        results[f"batch{batch}"] = dict(seconds=dt, tokens_per_s=new_tokens / dt, ms_per_token_step=dt / (TOTAL - PROMPT) * 1e3)
+    out = dict(metric="generate_tokens_per_s", value=results["batch8"]["tokens_per_s"], unit="tokens/s", n_gpus=1, steps=1, warmup=1,
+               ms_per_step=results["batch8"]["ms_per_token_step"], higher_is_better=True, scaling="weak", vs_baseline=None,
+               dtype="tf32x3 (fp32-accurate split)" if mode == gpt_b200.MODE_3XTF32 else "tf32", data="synthetic", impl="ours",
+               config=dict(workload="GPT-2 124M generation, prompt 64 -> 256 tokens, temperature 1.0, full-prefix recompute (no KV cache, as the reference)",
+                           mode=args.mode), per_batch=results, gpu_launches=int(launches))
+    print(json.dumps(out), flush=True)
+    model.close()
+
+
 def cpu_reference_sample(rows: int):
     """The reference CPU backend (unmodified sources behind oracle/_ref, one thread -- it has no threading) on
     `rows` rows of the workload; falls back to the oracle port when the reference library was not prebuilt."""
@@ -554,8 +612,8 @@ def main():
     ap.add_argument("--cpu-rows", type=int, default=256, help="rows of the workload the cpu_baseline leg runs")
     ap.add_argument("--ref-rows", type=int, default=32, help="rows per step of the --impl reference arm")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", choices=["ffn", "train", "decode"], default="ffn",
-                    help="ffn: BASELINE configs[1] (default); train: configs[3]; decode: configs[4] (linear layers)")
+    ap.add_argument("--workload", choices=["ffn", "train", "decode", "generate"], default="ffn",
+                    help="ffn: BASELINE configs[1] (default); train: configs[3]; decode: configs[4] (linear layers of a decode step); generate: configs[4] end to end")
     ap.add_argument("--global-batch", type=int, default=64, help="sequences per step over all GPUs (train workload)")
     ap.add_argument("--m-per-gpu", type=int, default=M_PER_GPU, help="tokens per GPU (smaller for profiler captures)")
     ap.add_argument("--profile", action="store_true", help="only the timed steps: no end-to-end, clock-load or CPU legs")
@@ -568,6 +626,8 @@ def main():
         run_train(args)
     elif args.workload == "decode":
         run_decode(args)
+    elif args.workload == "generate":
+        run_generate(args)
     else:
         run_ours(args)
 

@@ -103,9 +103,10 @@ public:
         be_->device_fill_const(w + lay_.wte + size_t(c_.vocab) * D, 0.0f, size_t(c_.vocab_padded - c_.vocab) * D);
     }
 
+    // Unlike the reference (src/model/gpt.cpp:399-424 frees and reallocates on every call, i.e. once per generated
+    // token in its inference loop), buffers are kept when the new shape fits into what is already allocated.
     void set_size(int batch, int seq)
     {
-        release_activations();
         B_ = batch;
         T_ = seq;
         const size_t M = size_t(batch) * seq, L = c_.layers, D = c_.d_model, F = c_.d_ffn, H = c_.heads, Vp = c_.vocab_padded;
@@ -120,17 +121,25 @@ public:
         a_.logits = take(M * Vp); a_.probs = take(M * Vp);
         a_.total = o;
         void *p = nullptr;
-        be_->device_malloc(&p, a_.total * sizeof(float));
-        acts_ = static_cast<float *>(p);
+        if (a_.total > acts_capacity_) {
+            if (acts_) be_->device_free(acts_);
+            be_->device_malloc(&p, a_.total * sizeof(float));
+            acts_ = static_cast<float *>(p);
+            acts_capacity_ = a_.total;
+        }
         if (use_grad_) {
             // activation gradients are consumed right after they are produced: one set of buffers serves all layers
             o = 0;
             g_.d_ln = take(M * D); g_.d_res = take(M * D); g_.d_x = take(M * D); g_.d_qkv = take(M * 3 * D); g_.d_helper = take(M * H);
             g_.d_f1 = take(M * F); g_.d_f2 = take(M * F); g_.d_logits = take(M * Vp);
             g_.total = o;
-            be_->device_malloc(&p, g_.total * sizeof(float));
-            be_->device_memset(p, 0, g_.total * sizeof(float));
-            agrads_ = static_cast<float *>(p);
+            if (g_.total > agrads_capacity_) {
+                if (agrads_) be_->device_free(agrads_);
+                be_->device_malloc(&p, g_.total * sizeof(float));
+                agrads_ = static_cast<float *>(p);
+                agrads_capacity_ = g_.total;
+            }
+            be_->device_memset(agrads_, 0, g_.total * sizeof(float));  // the padding columns of d_logits must be zero
         }
     }
 
@@ -248,6 +257,7 @@ private:
         if (acts_) be_->device_free(acts_);
         if (agrads_) be_->device_free(agrads_);
         acts_ = agrads_ = nullptr;
+        acts_capacity_ = agrads_capacity_ = 0;
     }
 
     struct ActLayout {
@@ -263,6 +273,7 @@ private:
     bool use_grad_;
     float *bufs_[4] = {nullptr, nullptr, nullptr, nullptr};
     float *acts_ = nullptr, *agrads_ = nullptr, *loss_dev_ = nullptr;
+    size_t acts_capacity_ = 0, agrads_capacity_ = 0;
     int B_ = 0, T_ = 0, step_ = 0;
 };
 

@@ -236,6 +236,22 @@ __global__ void layernorm_backward_params_final_kernel(float *__restrict__ grad_
 constexpr int kAttnTile = 32;
 constexpr int kAttnRowsPerBlock = 64;  // rows (queries or keys) per block
 
+// Dot product of a register array with a shared-memory row slice, with four independent partial sums so that the
+// FMAs do not form one long dependency chain (the compiler may not reassociate fp32 adds on its own).
+template <int DPT>
+__device__ __forceinline__ float dot_partial(const float (&a)[DPT], const float *__restrict__ b)
+{
+    float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < DPT; i += 4) {
+        s0 += a[i] * b[i];
+        if (i + 1 < DPT) s1 += a[i + 1] * b[i + 1];
+        if (i + 2 < DPT) s2 += a[i + 2] * b[i + 2];
+        if (i + 3 < DPT) s3 += a[i + 3] * b[i + 3];
+    }
+    return (s0 + s1) + (s2 + s3);
+}
+
 template <int TPR>
 __device__ __forceinline__ float row_sum(float v)
 {
@@ -281,9 +297,7 @@ attention_forward_kernel(float *__restrict__ y, float *__restrict__ logsumexp, c
         const int tend = row - t0 + 1;                               // this row uses keys s2 <= row
         const int tmax = min(kAttnTile, last_row - t0 + 1);          // block-uniform bound: shuffles stay convergent
         for (int r = 0; r < tmax; ++r) {
-            float sc = 0.0f;
-#pragma unroll
-            for (int i = 0; i < DPT; ++i) sc += q[i] * ks[r][part * DPT + i];
+            float sc = dot_partial<DPT>(q, &ks[r][part * DPT]);
             sc = row_sum<TPR>(sc) * scale;
             if (r >= tend) continue;
             const float m_new = fmaxf(m, sc);
@@ -354,12 +368,8 @@ attention_backward_dq_kernel(float *__restrict__ grad_qkv, const float *__restri
         const int tend = row - t0 + 1;
         const int tmax = min(kAttnTile, last_row - t0 + 1);
         for (int r = 0; r < tmax; ++r) {
-            float sc = 0.0f, dp = 0.0f;
-#pragma unroll
-            for (int i = 0; i < DPT; ++i) {
-                sc += q[i] * ks[r][part * DPT + i];
-                dp += go[i] * vs[r][part * DPT + i];
-            }
+            float sc = dot_partial<DPT>(q, &ks[r][part * DPT]);
+            float dp = dot_partial<DPT>(go, &vs[r][part * DPT]);
             sc = row_sum<TPR>(sc);
             dp = row_sum<TPR>(dp);
             if (r >= tend) continue;
@@ -418,12 +428,8 @@ attention_backward_dkv_kernel(float *__restrict__ grad_qkv, const float *__restr
         const int rbeg = max(0, first_row - t0);              // block-uniform bounds: shuffles stay convergent
         const int rend = min(kAttnTile, seq_len - t0);
         for (int r = rbeg; r < rend; ++r) {
-            float sc = 0.0f, dp = 0.0f;
-#pragma unroll
-            for (int i = 0; i < DPT; ++i) {
-                sc += qs[r][part * DPT + i] * k[i];
-                dp += gs[r][part * DPT + i] * v[i];
-            }
+            float sc = dot_partial<DPT>(k, &qs[r][part * DPT]);
+            float dp = dot_partial<DPT>(v, &gs[r][part * DPT]);
             sc = row_sum<TPR>(sc);
             dp = row_sum<TPR>(dp);
             if (t0 + r < row) continue;                       // this key only sees queries s1 >= row

@@ -154,6 +154,51 @@ void ref_cross_entropy_softmax_backward(float *grad_x, const float *probs, const
     be.device_cross_entropy_softmax_fused_backward(grad_x, probs, labels, 1, m, v, vp);
 }
 
+// ---- the remaining operators of the reference CPU backend, one by one (for the op-level tests of the plain kernels)
+void ref_embedding_forward(float *y, const float *wte, const float *wpe, const int *tokens, int batch, int seq, int d)
+{
+    CPUBackend be;
+    be.device_embedding_forward(y, wte, wpe, tokens, batch, seq, d);
+}
+
+void ref_embedding_backward(float *grad_wte, float *grad_wpe, const float *grad_y, const int *tokens, int batch, int seq, int d)
+{
+    CPUBackend be;
+    be.device_embedding_backward(grad_wte, grad_wpe, grad_y, tokens, batch, seq, d);
+}
+
+void ref_layernorm_forward(float *y, float *means, float *vars, float *x, const float *residual, const float *gamma, const float *beta, int rows, int d)
+{
+    CPUBackend be;
+    be.device_layernorm_residual_fused_forward(y, means, vars, x, residual, gamma, beta, 1, rows, d);
+}
+
+void ref_layernorm_backward(float *grad_x, float *grad_gamma, float *grad_beta, const float *grad_y, const float *grad_residual, const float *x,
+                            const float *means, const float *vars, const float *gamma, int rows, int d)
+{
+    CPUBackend be;
+    be.device_layernorm_residual_fused_backward(grad_x, grad_gamma, grad_beta, grad_y, grad_residual, x, means, vars, gamma, 1, rows, d);
+}
+
+void ref_attention_forward(float *y, float *logsumexp, const float *qkv, int batch, int seq, int d, int heads)
+{
+    CPUBackend be;
+    be.device_flash_attention_forward(y, logsumexp, qkv, batch, seq, d, heads);
+}
+
+void ref_attention_backward(float *grad_qkv, float *d_cache, const float *logsumexp, const float *grad_y, const float *y, const float *qkv, int batch,
+                            int seq, int d, int heads)
+{
+    CPUBackend be;
+    be.device_flash_attention_backward(grad_qkv, d_cache, logsumexp, grad_y, y, qkv, batch, seq, d, heads);
+}
+
+void ref_cross_entropy_loss(float *loss, const float *probs, const int *labels, int rows, int vp)
+{
+    CPUBackend be;
+    be.device_cross_entropy_loss(loss, probs, labels, 1, rows, vp);
+}
+
 // cfg = {max_seq_len, vocab_size, vocab_size_padded, num_layers, num_heads, d_model, d_ffn}
 int ref_gpt_forward_backward(const int *cfg, const float *weights, long long n_weights, const int *inputs, const int *labels, int batch,
                              int seq, int use_restated_ops, float *grads_out, float *loss_out, float *logits_out)

@@ -186,7 +186,7 @@ GemmPlanInput plan_input(const gptb200_ctx *ctx, const GemmCall &c)
     in.accumulate = c.accumulate;
     in.aligned = aligned16(c.a) && aligned16(c.b) && aligned16(c.out) && (!c.act || aligned16(c.act));
     in.num_sms = ctx->num_sms;
-    in.opt_tile_n = ctx->tile_n; in.opt_max_splits = ctx->max_splits; in.opt_pair = ctx->pair; in.opt_skinny = ctx->skinny;
+    in.opt_tile_n = ctx->tile_n; in.opt_max_splits = ctx->max_splits; in.opt_pair = ctx->pair; in.opt_stream_k = ctx->stream_k; in.opt_skinny = ctx->skinny;
     in.ws_limit = ctx->ws_limit;
     return in;
 }
@@ -227,6 +227,18 @@ int run_gemm(gptb200_ctx *ctx, const GemmCall &c)
     p.debug = ctx->debug;
 
     float *out_base = c.out;
+    if (pair) {
+        p.sk_total = pl.sk_total;
+        p.sk_unit = pl.sk_unit;
+        if (pl.sk_max_share > 1) {
+            const int rc = ensure_workspace(ctx, pl.workspace_bytes);
+            if (rc != GPTB200_OK) return rc;
+            p.sk_slots = ctx->ws;
+            p.sk_flags = ctx->d_pair_flags;
+            if (++ctx->pair_epoch == 0) ++ctx->pair_epoch;   // 0 is the value of a flag that was never written
+            p.sk_epoch = ctx->pair_epoch;
+        }
+    }
     if (splits > 1) {
         const int rc = ensure_workspace(ctx, bytes_per_split * splits);
         if (rc != GPTB200_OK) return rc;
@@ -358,7 +370,10 @@ int gptb200_ctx_create(gptb200_ctx **out, int device, void *cuda_stream, int mod
         return GPTB200_ERR_CUDA;
     }
     ctx->encode = reinterpret_cast<EncodeTiledFn>(fn);
-    if (cudaMalloc(&ctx->d_status, sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_status, 0, sizeof(int)) != cudaSuccess) {
+    const size_t flag_bytes = size_t(ctx->num_sms) * 8 * sizeof(unsigned int);   // [pair][CTA][epilogue warp]
+    if (cudaMalloc(&ctx->d_status, sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_status, 0, sizeof(int)) != cudaSuccess ||
+        cudaMalloc(&ctx->d_pair_flags, flag_bytes) != cudaSuccess || cudaMemset(ctx->d_pair_flags, 0, flag_bytes) != cudaSuccess) {
+        if (ctx->d_status) cudaFree(ctx->d_status);
         delete ctx;
         return GPTB200_ERR_CUDA;
     }
@@ -373,6 +388,7 @@ int gptb200_ctx_destroy(gptb200_ctx *ctx)
     cudaStreamSynchronize(ctx->stream);
     if (ctx->ws) cudaFree(ctx->ws);
     if (ctx->d_status) cudaFree(ctx->d_status);
+    if (ctx->d_pair_flags) cudaFree(ctx->d_pair_flags);
     delete ctx;
     return GPTB200_OK;
 }
@@ -404,6 +420,11 @@ int gptb200_ctx_set_option(gptb200_ctx *ctx, const char *key, int value)
     if (!strcmp(key, "pair")) {
         if (value < -1 || value > 1) return fail(ctx, GPTB200_ERR_INVALID_ARG, "pair must be -1, 0 or 1");
         ctx->pair = value;
+        return GPTB200_OK;
+    }
+    if (!strcmp(key, "stream_k")) {
+        if (value < -1 || value > 1) return fail(ctx, GPTB200_ERR_INVALID_ARG, "stream_k must be -1, 0 or 1");
+        ctx->stream_k = value;
         return GPTB200_OK;
     }
     if (!strcmp(key, "skinny")) {
@@ -459,7 +480,9 @@ int gptb200_plan_gemm(int num_sms, int m, int n, int k, int a_mn_major, int b_mn
     in.num_sms = num_sms; in.opt_skinny = true; in.ws_limit = size_t(1) << 30;
     const GemmPlan p = plan_gemm(in);
     const long long ws = static_cast<long long>(p.workspace_bytes);
-    const int out[8] = {p.kernel, p.tile_n, p.tiles_m, p.tiles_n, p.splits, p.kb_per_split, p.grid, static_cast<int>(std::min<long long>(ws >> 10, 0x7fffffff))};
+    const int pairs = p.kernel == KERNEL_PAIR ? p.grid / 2 : 1;
+    const int kb_each = p.kernel == KERNEL_PAIR ? static_cast<int>((p.sk_total + pairs - 1) / pairs) : p.kb_per_split;
+    const int out[8] = {p.kernel, p.tile_n, p.tiles_m, p.tiles_n, p.kernel == KERNEL_PAIR ? p.sk_max_share : p.splits, kb_each, p.grid, static_cast<int>(std::min<long long>(ws >> 10, 0x7fffffff))};
     for (int i = 0; i < 8; ++i) plan8[i] = out[i];
     return GPTB200_OK;
 }

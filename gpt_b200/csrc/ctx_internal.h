@@ -25,7 +25,10 @@ struct gptb200_ctx {
     bool skinny = true;  // weight-streaming kernel for forward calls with m <= 16
     int debug = 0;       // timing experiments (see GemmParams::debug)
     int pair = 0;        // CTA-pair (cta_group::2) kernel: 1 = always, 0 = heuristic, -1 = never
+    int stream_k = 0;    // CTA-pair kernel, ranges cut inside tiles: 1 = always, 0 = heuristic, -1 = never
     int *d_status = nullptr;
+    unsigned int *d_pair_flags = nullptr;  // per CTA pair, CTA and epilogue warp: number of the launch whose partial tile is complete
+    unsigned int pair_epoch = 0;           // number of the latest CTA-pair launch that used the flags
     float *ws = nullptr;  // scratch: split-K partial tiles, partial rows of column reductions
     size_t ws_bytes = 0;
     size_t ws_limit = size_t(1) << 30;

@@ -26,6 +26,7 @@ struct GemmPlanInput {
     int opt_tile_n;          // 0 automatic, 128, 256
     int opt_max_splits;      // 0 automatic
     int opt_pair;            // 1 always, 0 heuristic, -1 never
+    int opt_stream_k;        // CTA-pair kernel: 1 always cut ranges inside tiles, 0 heuristic, -1 whole tiles only
     bool opt_skinny;
     size_t ws_limit;         // scratch limit in bytes
 };
@@ -36,8 +37,15 @@ struct GemmPlan {
     int tiles_m, tiles_n;    // 128-row tiles, tile_n-column tiles
     int splits, kb_per_split, num_kb;
     int grid;                // CTAs
-    size_t workspace_bytes;  // split-K partial tiles (or skinny partial sums)
+    size_t workspace_bytes;  // split-K partial tiles, skinny partial sums, or one partial tile per CTA pair
+    // CTA-pair kernel: the k-blocks of all tiles, tile after tile, are cut into `grid / 2` contiguous ranges at multiples
+    // of sk_unit k-blocks (num_kb: whole tiles; 1: anywhere, tiles cut by a range boundary are summed through scratch).
+    long long sk_total;
+    int sk_unit;
+    int sk_max_share;        // largest number of pairs that work on one tile
 };
+
+constexpr size_t kPairSlotBytes = 256 * 256 * sizeof(float);
 
 constexpr int kPlanBM = 128;
 constexpr int kPlanBK = 32;
@@ -99,24 +107,66 @@ inline GemmPlan plan_gemm(const GemmPlanInput &in)
     const bool split_allowed = !in.has_epilogue;
     const size_t bytes_per_split = size_t(in.M) * size_t(in.N) * sizeof(float);
     p.num_kb = (in.K + kPlanBK - 1) / kPlanBK;
-    const int pair_splits = plan_splits(in, pair_tiles, p.num_kb, split_allowed, bytes_per_split, in.num_sms / 2);
-    const bool pair = in.opt_pair > 0 || (in.opt_pair == 0 && in.opt_tile_n == 0 && in.M > kPlanBM && in.N > 128 &&
-                                          pair_tiles * pair_splits * 20 >= 9LL * in.num_sms);
-    int bn = pair ? 256 : in.opt_tile_n;
+    const int max_pairs = std::max(1, in.num_sms / 2);
+    const long long pair_kb = pair_tiles * p.num_kb;
+    // pairs that can be given at least eight k-blocks each
+    const long long pairs_busy = std::min<long long>(max_pairs, std::max<long long>(pair_tiles, pair_kb / 8));
+    const bool pair = in.opt_pair > 0 || (in.opt_pair == 0 && in.opt_tile_n == 0 && in.M > kPlanBM && in.N > 128 && pairs_busy * 20 >= 9LL * in.num_sms);
+    if (pair) {
+        p.kernel = KERNEL_PAIR;
+        p.tile_n = 256;
+        p.tiles_m = (in.M + kPlanBM - 1) / kPlanBM;
+        p.tiles_n = (in.N + 255) / 256;
+        p.splits = 1;
+        p.kb_per_split = p.num_kb;
+        p.sk_total = pair_kb;
+        const long long whole_pairs = std::min<long long>(max_pairs, pair_tiles);
+        const long long rounds = (pair_tiles + whole_pairs - 1) / whole_pairs;
+        const double whole_eff = double(pair_tiles) / double(rounds * pairs_busy);   // share of the usable pairs kept busy by whole tiles
+        long long pairs;
+        if (in.opt_stream_k < 0 || (in.opt_stream_k == 0 && whole_eff >= 0.97)) {
+            p.sk_unit = p.num_kb;   // whole tiles, as evenly as they go
+            pairs = whole_pairs;
+            p.sk_max_share = 1;
+        } else {
+            p.sk_unit = 1;
+            pairs = in.opt_stream_k > 0 ? std::min<long long>(max_pairs, pair_kb) : pairs_busy;
+            p.workspace_bytes = size_t(pairs) * kPairSlotBytes;
+            p.sk_max_share = 1;
+            long long cur_tile = -1;
+            int cur = 0;
+            for (long long q = 0; q < pairs; ++q) {   // ranges are in tile order: count those that meet the same tile
+                const long long g0 = q * pair_kb / pairs, g1 = (q + 1) * pair_kb / pairs;
+                if (g0 >= g1) continue;
+                const long long t_first = g0 / p.num_kb, t_last = (g1 - 1) / p.num_kb;
+                cur = t_first == cur_tile ? cur + 1 : 1;
+                cur_tile = t_first;
+                p.sk_max_share = std::max(p.sk_max_share, cur);
+                if (t_last != t_first) {
+                    cur_tile = t_last;
+                    cur = 1;
+                }
+            }
+            if (p.sk_max_share == 1) p.workspace_bytes = 0;   // every boundary fell between tiles
+        }
+        p.grid = 2 * static_cast<int>(pairs);
+        return p;
+    }
+    int bn = in.opt_tile_n;
     if (bn != 128 && bn != 256) {
         const long long tiles256 = 1LL * ((in.M + kPlanBM - 1) / kPlanBM) * ((in.N + 255) / 256);
         bn = (in.N <= 128 || tiles256 < in.num_sms / 2) ? 128 : 256;
     }
-    p.kernel = pair ? KERNEL_PAIR : KERNEL_SINGLE;
+    p.kernel = KERNEL_SINGLE;
     p.tile_n = bn;
     p.tiles_m = (in.M + kPlanBM - 1) / kPlanBM;
     p.tiles_n = (in.N + bn - 1) / bn;
-    const long long tiles = pair ? 1LL * ((p.tiles_m + 1) / 2) * p.tiles_n : 1LL * p.tiles_m * p.tiles_n;
-    int splits = pair ? pair_splits : plan_splits(in, tiles, p.num_kb, split_allowed, bytes_per_split, in.num_sms);
+    const long long tiles = 1LL * p.tiles_m * p.tiles_n;
+    const int splits = plan_splits(in, tiles, p.num_kb, split_allowed, bytes_per_split, in.num_sms);
     p.kb_per_split = (p.num_kb + splits - 1) / splits;
     p.splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
     const long long items = tiles * p.splits;
-    p.grid = pair ? 2 * static_cast<int>(std::min<long long>(items, in.num_sms / 2)) : static_cast<int>(std::min<long long>(items, in.num_sms));
+    p.grid = static_cast<int>(std::min<long long>(items, in.num_sms));
     p.workspace_bytes = p.splits > 1 ? bytes_per_split * p.splits : 0;
     return p;
 }

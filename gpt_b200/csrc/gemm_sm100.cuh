@@ -44,6 +44,7 @@ enum DeviceStatus : int {
     DEV_TIMEOUT_EPILOGUE = 105,   // epilogue gave up waiting for a finished accumulator
     DEV_TIMEOUT_CONVERT = 106,    // converter gave up waiting for a landed stage
     DEV_TIMEOUT_DRAIN = 107,      // teardown gave up waiting for outstanding MMAs
+    DEV_TIMEOUT_PARTIAL = 109,    // epilogue gave up waiting for another CTA pair's partial tile
     DEV_TIMEOUT_SELFTEST = 108,   // the self-test's wait on a barrier that nothing signals ran out, as intended
 };
 
@@ -64,6 +65,13 @@ struct GemmParams {
     int epi_mode;
     int *status;         // device status word
     int debug;           // timing experiments only: bit 0 = no TMA loads, bit 1 = no MMAs (results are garbage)
+    // CTA-pair kernel only: the tiles' k-blocks form one line of sk_total = tiles * num_kb entries that is cut into
+    // one range per pair, at multiples of sk_unit (1: anywhere, num_kb: whole tiles only).
+    long long sk_total;
+    int sk_unit;
+    float *sk_slots;         // one partial 256 x 256 tile per pair
+    unsigned int *sk_flags;  // one word per pair, CTA and epilogue warp: the launch number whose partial tile is complete
+    unsigned int sk_epoch;   // this launch's number
 };
 
 constexpr int kBM = 128;

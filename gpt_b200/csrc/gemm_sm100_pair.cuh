@@ -17,6 +17,14 @@
 //   leader -> both   "stage s is free" / "accumulator b is full": one tcgen05.commit that signals the barrier at
 //            the same offset in both CTAs;
 //   peer -> leader   "accumulator b is drained": remote mbarrier.arrive on leader.tmem_empty[b].
+// Work distribution: the k-blocks of all tiles form one line (tile after tile) that is cut into one contiguous range
+// per CTA pair, so that every pair executes the same number of k-blocks whatever the tile count.  A range may begin
+// and end inside a tile.  The pair whose range holds a tile's FIRST k-block owns the tile: it writes the output
+// (bias, GELU, accumulate).  A pair whose range begins inside a tile computes that remainder first, stores the raw
+// sums in its slot of a scratch buffer and publishes one flag per epilogue warp (release); the owner, which reaches
+// the tile at the END of its own range, waits for the flags of the pairs that follow it (acquire, bounded) and
+// adds their slots in pair order, so results do not depend on timing.  Pairs that publish never wait, hence the
+// scheme cannot deadlock even when not all CTAs are resident at once.
 // All waits are bounded exactly as in the one-CTA kernel; both CTAs always reach the closing cluster barrier.
 #pragma once
 
@@ -66,6 +74,66 @@ __device__ __forceinline__ bool bounded_wait_cluster(uint32_t bar, uint32_t pari
             }
         }
     }
+}
+
+// First k-block (on the line of all tiles' k-blocks) of pair q out of P.
+__device__ __forceinline__ long long pair_range_start(const GemmParams &p, long long q, long long P)
+{
+    const long long units = p.sk_total / p.sk_unit;
+    return (q * units / P) * p.sk_unit;
+}
+
+// Walk of one pair over the (tile, k-block range) segments of its range.
+struct PairWork {
+    long long g, g_end;
+    int num_kb, tiles_m2;
+    __device__ __forceinline__ bool next(int &tm2, int &tn, int &kb0, int &kb1)
+    {
+        if (g >= g_end) return false;
+        const long long tile = g / num_kb;
+        kb0 = static_cast<int>(g - tile * num_kb);
+        kb1 = static_cast<int>(min(static_cast<long long>(num_kb), kb0 + (g_end - g)));
+        tm2 = static_cast<int>(tile % tiles_m2);
+        tn = static_cast<int>(tile / tiles_m2);
+        g += kb1 - kb0;
+        return true;
+    }
+};
+
+__device__ __forceinline__ void flag_release(unsigned int *flag, unsigned int value)
+{
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(value) : "memory");
+}
+
+__device__ __forceinline__ unsigned int flag_acquire(const unsigned int *flag)
+{
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    return v;
+}
+
+// One lane polls, the warp learns the outcome.  False: gave up (time limit or abort flag).
+__device__ __forceinline__ bool bounded_flag_wait(const unsigned int *flag, unsigned int value, int lane, volatile uint32_t *abort_flag, int *status)
+{
+    int ok = 1;
+    if (lane == 0 && flag_acquire(flag) != value) {
+        const long long t0 = clock64();
+        uint32_t spins = 0;
+        while (flag_acquire(flag) != value) {
+            if ((++spins & 15u) == 0) {
+                if (*abort_flag) { ok = 0; break; }
+                if (clock64() - t0 > kWaitTimeoutCycles) {
+                    *abort_flag = 1u;
+                    atomicCAS(status, 0, DEV_TIMEOUT_PARTIAL);
+                    ok = 0;
+                    break;
+                }
+            }
+            __nanosleep(64);
+        }
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    return ok != 0;
 }
 
 template <bool A_MN, bool B_MN, bool X3>
@@ -139,17 +207,15 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     const uint32_t tmem_base = *tmem_slot;
 
     const int tiles_m2 = (p.tiles_m + 1) / 2;   // pairs of 128-row tiles
-    const long long num_items = 1LL * tiles_m2 * p.tiles_n * p.splits;
-    const long long first_item = blockIdx.x >> 1;
-    const long long item_stride = gridDim.x >> 1;
-
-    auto decode = [&](long long w, int &tm2, int &tn, int &kb0, int &kb1, int &split) {
-        tm2 = static_cast<int>(w % tiles_m2);
-        const long long r = w / tiles_m2;
-        tn = static_cast<int>(r % p.tiles_n);
-        split = static_cast<int>(r / p.tiles_n);
-        kb0 = split * p.kb_per_split;
-        kb1 = min(kb0 + p.kb_per_split, p.num_kb);
+    const long long num_pairs = gridDim.x >> 1;
+    const long long pair_id = blockIdx.x >> 1;
+    auto my_work = [&]() {
+        PairWork w;
+        w.g = pair_range_start(p, pair_id, num_pairs);
+        w.g_end = pair_range_start(p, pair_id + 1, num_pairs);
+        w.num_kb = p.num_kb;
+        w.tiles_m2 = tiles_m2;
+        return w;
     };
 
     // 3xTF32 converters: six warps (warps 2, 3 and the last four) in two groups of three; group g handles the
@@ -158,9 +224,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     auto convert_loop = [&](int group, int ctid) {
         uint32_t it = 0;
         bool ok = true;
-        for (long long w = first_item; ok && w < num_items; w += item_stride) {
-            int tm2, tn, kb0, kb1, split;
-            decode(w, tm2, tn, kb0, kb1, split);
+        PairWork work = my_work();
+        int tm2, tn, kb0, kb1;
+        while (ok && work.next(tm2, tn, kb0, kb1)) {
             for (int kb = kb0; kb < kb1; ++kb, ++it) {
                 if (static_cast<int>(it & 1u) != group) continue;
                 const int s = it % STAGES;
@@ -204,9 +270,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             // ------------------------------------------------------------ TMA producer (both CTAs)
             uint32_t it = 0;
             bool ok = true;
-            for (long long w = first_item; ok && w < num_items; w += item_stride) {
-                int tm2, tn, kb0, kb1, split;
-                decode(w, tm2, tn, kb0, kb1, split);
+            PairWork work = my_work();
+            int tm2, tn, kb0, kb1;
+            while (ok && work.next(tm2, tn, kb0, kb1)) {
                 const int m0 = tm2 * 2 * kBM + static_cast<int>(rank) * kBM;          // the rows this CTA owns
                 const int n0 = tn * BN + static_cast<int>(rank) * C::kBRows;          // the half of B this CTA loads
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
@@ -249,9 +315,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             if (leader && lane == 0) {
                 uint32_t it = 0, g = 0;
                 bool ok = true;
-                for (long long w = first_item; ok && w < num_items; w += item_stride) {
-                    int tm2, tn, kb0, kb1, split;
-                    decode(w, tm2, tn, kb0, kb1, split);
+                PairWork work = my_work();
+                int tm2, tn, kb0, kb1;
+                while (ok && work.next(tm2, tn, kb0, kb1)) {
                     int kb = kb0;
                     while (ok && kb < kb1) {
                         const int kend = C::kChunked ? min(kb + kChunkKB, kb1) : kb1;
@@ -329,7 +395,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         bool ok = true;
         const uint32_t leader_tmem_empty[2] = {ptx::map_to_cta(tmem_empty_bar(0), 0u), ptx::map_to_cta(tmem_empty_bar(1), 0u)};
 
-        auto emit = [&](float (&v)[32], int row0, int col0, int split) {
+        auto emit = [&](float (&v)[32], int row0, int col0) {
             if (p.bias && p.epi_mode == EPI_STORE) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] += (col0 + j < p.N) ? __ldg(p.bias + col0 + j) : 0.0f;
@@ -345,7 +411,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                         if (p.epi_mode == EPI_ACCUM)
                             ptx::tma_reduce_add_3d(&tmap_out, col0, row0, 0, buf);
                         else
-                            ptx::tma_store_3d(&tmap_out, col0, row0, split, buf);
+                            ptx::tma_store_3d(&tmap_out, col0, row0, 0, buf);
                     }
                     ptx::tma_store_commit();
                 }
@@ -366,11 +432,17 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             }
         };
 
-        for (long long w = first_item; ok && w < num_items; w += item_stride) {
-            int tm2, tn, kb0, kb1, split;
-            decode(w, tm2, tn, kb0, kb1, split);
+        PairWork work = my_work();
+        int tm2, tn, kb0, kb1;
+        while (ok && work.next(tm2, tn, kb0, kb1)) {
             const int row0 = tm2 * 2 * kBM + static_cast<int>(rank) * kBM + q * 32;
             const int n0 = tn * BN + col_base;
+            const bool owner = kb0 == 0;              // this pair writes the tile's output
+            const bool complete = kb1 == p.num_kb;    // ... and nobody else holds a part of it
+            const long long tile_end = (1LL * tn * tiles_m2 + tm2 + 1) * p.num_kb;
+            // slot of pair r: [CTA][epilogue warp][128 values][lane]
+            auto slot_of = [&](long long r) { return p.sk_slots + ((r * 2 + rank) * C::kEpiWarps + e) * 4096 + lane; };
+            auto flag_of = [&](long long r) { return p.sk_flags + (r * 2 + rank) * C::kEpiWarps + e; };
             if (C::kChunked) {
                 float acc[128];
 #pragma unroll
@@ -394,13 +466,31 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     ptx::tc_fence_before();
                     ptx::mbar_arrive_cluster(leader_tmem_empty[buf]);
                 }
-                if (ok) {
+                if (ok && !owner) {
+                    float *slot = slot_of(pair_id);
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        float v[32];
+                    for (int j = 0; j < 128; ++j) __stcg(slot + j * 32, acc[j]);
+                    __threadfence();
+                    __syncwarp();
+                    if (lane == 0) flag_release(flag_of(pair_id), p.sk_epoch);
+                } else if (ok) {
+                    if (!complete) {
+                        for (long long r = pair_id + 1; ok && r < num_pairs && pair_range_start(p, r, num_pairs) < tile_end; ++r) {
+                            ok = bounded_flag_wait(flag_of(r), p.sk_epoch, lane, abort_flag, p.status);
+                            if (!ok) break;
+                            const float *slot = slot_of(r);
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] = acc[c * 32 + j];
-                        emit(v, row0, n0 + c * 32, split);
+                            for (int j = 0; j < 128; ++j) acc[j] += __ldcg(slot + j * 32);
+                        }
+                    }
+                    if (ok) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            float v[32];
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = acc[c * 32 + j];
+                            emit(v, row0, n0 + c * 32);
+                        }
                     }
                 }
             } else {
@@ -412,6 +502,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     break;
                 }
                 ptx::tc_fence_after();
+                long long r_end = pair_id + 1;   // pairs [pair_id + 1, r_end) hold the rest of this tile
+                if (owner && !complete) {
+                    while (r_end < num_pairs && pair_range_start(p, r_end, num_pairs) < tile_end) ++r_end;
+                    for (long long r = pair_id + 1; ok && r < r_end; ++r) ok = bounded_flag_wait(flag_of(r), p.sk_epoch, lane, abort_flag, p.status);
+                }
 #pragma unroll 1
                 for (int c = 0; c < C::kColsPerEpiWarp / 32; ++c) {
                     uint32_t r[32];
@@ -424,7 +519,24 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     float v[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-                    emit(v, row0, n0 + c * 32, split);
+                    if (!ok) continue;   // the accumulator is still released so that the MMA thread can finish
+                    if (!owner) {
+                        float *slot = slot_of(pair_id) + c * 32 * 32;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) __stcg(slot + j * 32, v[j]);
+                    } else {
+                        for (long long rr = pair_id + 1; rr < r_end; ++rr) {
+                            const float *slot = slot_of(rr) + c * 32 * 32;
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] += __ldcg(slot + j * 32);
+                        }
+                        emit(v, row0, n0 + c * 32);
+                    }
+                }
+                if (ok && !owner) {
+                    __threadfence();
+                    __syncwarp();
+                    if (lane == 0) flag_release(flag_of(pair_id), p.sk_epoch);
                 }
             }
         }

@@ -52,6 +52,8 @@ int gptb200_ctx_get_mode(const gptb200_ctx *ctx);
 int gptb200_ctx_set_stream(gptb200_ctx *ctx, void *cuda_stream);
 /* Tuning knobs, for benchmarking: key "tile_n" (0 = automatic, 128, 256), "max_splits" (0 = automatic),
  * "pair" (CTA-pair kernel with 256 x 256 tiles: 1 = always, 0 = heuristic, -1 = never),
+ * "stream_k" (CTA-pair kernel: give every pair the same number of k-blocks by letting a pair's range begin and end inside a
+ * tile, partial tiles summed through scratch: 1 = always, 0 = when whole tiles would leave SMs idle, -1 = never),
  * "skinny" (weight-streaming kernel for forward calls with m <= 16: 1 = on (default), 0 = off). */
 int gptb200_ctx_set_option(gptb200_ctx *ctx, const char *key, int value);
 /* Waits for the context's stream and reports a device-side timeout recorded by any earlier kernel. */
@@ -64,7 +66,9 @@ long long gptb200_ctx_launch_count(const gptb200_ctx *ctx);
 int gptb200_selftest_wait_timeout(gptb200_ctx *ctx, int limit_us);
 /* The launch plan for D[m x n] = A[m x k] . B[k x n] on a GPU with num_sms SMs, without touching a GPU (host logic only,
  * default options).  plan8 = {kernel (0 none, 1 CTA-pair tcgen05, 2 one-CTA tcgen05, 3 weight streaming, 4 SIMT), tile_n,
- * tiles_m, tiles_n, split_k, k-blocks (or k elements for kernel 3) per split, CTAs, scratch KiB}. */
+ * tiles_m, tiles_n, split_k, k-blocks (or k elements for kernel 3) per split, CTAs, scratch KiB}.  For kernel 1 split_k is the
+ * largest number of CTA pairs that work on one 256 x 256 tile (1: every pair computes whole tiles) and the next field the
+ * k-blocks per CTA pair. */
 int gptb200_plan_gemm(int num_sms, int m, int n, int k, int a_mn_major, int b_mn_major, int has_epilogue, int accumulate, int *plan8);
 const char *gptb200_status_string(int status);
 const char *gptb200_last_error(const gptb200_ctx *ctx);

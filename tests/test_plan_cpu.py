@@ -16,13 +16,19 @@ def test_gpt2_124m_shapes_use_the_cta_pair_kernel_at_m_8192(plan):
     D, F, V = 768, 3072, 50304
     for k, n in ((D, 3 * D), (D, D), (D, F), (F, D)):
         fwd = plan(SMS, 8192, n, k, False, True, has_epilogue=True)
-        assert fwd["kernel"] == "pair" and fwd["splits"] == 1 and fwd["grid"] == 148
+        assert fwd["kernel"] == "pair" and fwd["grid"] == 148
+        tiles = 32 * ((n + 255) // 256)
+        assert fwd["k_per_split"] == -(-tiles * (k // 32) // 74)               # every pair gets its share of all k-blocks
         dx = plan(SMS, 8192, k, n, False, False)
         assert dx["kernel"] == "pair"
         dw = plan(SMS, k, n, 8192, True, True, accumulate=True)
         assert dw["kernel"] in ("pair", "single")
     assert plan(SMS, 8192, V, D, False, False)["kernel"] == "pair"           # LM head forward
-    assert plan(SMS, V, D, 8192, True, True, accumulate=True)["splits"] == 1   # 1179 tiles need no split-K
+    assert plan(SMS, V, D, 8192, True, True, accumulate=True)["splits"] == 1   # 1179 tiles: whole tiles keep the pairs busy
+    fc = plan(SMS, 8192, F, D, False, True, has_epilogue=True)                 # 384 tiles on 74 pairs: 5.19 rounds of whole tiles
+    assert fc["splits"] == 2 and fc["scratch_kib"] == 74 * 256                 # ... so ranges are cut inside tiles
+    dw = plan(SMS, D, F, 8192, True, True, accumulate=True)                    # 36 tiles of 256 k-blocks
+    assert dw["kernel"] == "pair" and dw["grid"] == 148 and dw["splits"] == 3
 
 
 def test_small_and_odd_shapes(plan):
@@ -47,7 +53,19 @@ def test_plan_invariants_over_a_sweep(plan, sms):
         for a_mn, b_mn, epi, acc in ((False, True, True, False), (False, False, False, False), (True, True, False, True)):
             p = plan(sms, m, n, k, a_mn, b_mn, epi, acc)
             assert p["grid"] >= 1
-            if p["kernel"] in ("pair", "single"):
+            if p["kernel"] == "pair":
+                pairs = p["grid"] // 2
+                tiles = ((m + 255) // 256) * ((n + 255) // 256)
+                num_kb = (k + 31) // 32
+                assert p["grid"] % 2 == 0 and p["grid"] <= sms and p["tile_n"] == 256 and m > 128
+                assert pairs * p["k_per_split"] >= tiles * num_kb               # the ranges cover every k-block of every tile
+                assert tiles * num_kb >= pairs                                  # and no pair is left without work
+                if p["splits"] == 1:
+                    assert p["scratch_kib"] == 0
+                else:
+                    assert p["scratch_kib"] == pairs * 256                      # one 256 x 256 partial tile per pair
+                    assert tiles * num_kb // pairs >= 8 or pairs <= tiles       # pairs beyond one per tile get eight k-blocks or more
+            if p["kernel"] == "single":
                 assert p["grid"] <= sms
                 num_kb = (k + 31) // 32
                 assert p["splits"] >= 1 and p["k_per_split"] >= 1
@@ -61,9 +79,6 @@ def test_plan_invariants_over_a_sweep(plan, sms):
                     assert p["k_per_split"] >= 8                                # at least eight k-blocks per split
                 else:
                     assert p["scratch_kib"] == 0
-                if p["kernel"] == "pair":
-                    assert p["grid"] % 2 == 0 and p["tile_n"] == 256 and m > 128
-                else:
-                    assert p["tile_n"] in (128, 256)
+                assert p["tile_n"] in (128, 256)
             if p["kernel"] == "skinny":
                 assert m <= 16 and not acc and p["splits"] * p["k_per_split"] >= k and p["k_per_split"] % 4 == 0

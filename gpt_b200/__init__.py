@@ -25,7 +25,7 @@ MODE_TF32 = 1
 # Every symbol include/gptb200.h declares (checked by the CPU test-suite against the built library).
 EXPORTED_SYMBOLS = [
     "gptb200_ctx_create", "gptb200_ctx_destroy", "gptb200_ctx_set_mode", "gptb200_ctx_get_mode",
-    "gptb200_ctx_set_stream", "gptb200_ctx_set_option", "gptb200_ctx_synchronize", "gptb200_ctx_launch_count",
+    "gptb200_ctx_set_stream", "gptb200_ctx_set_option", "gptb200_ctx_synchronize", "gptb200_ctx_launch_count", "gptb200_ctx_read_trace",
     "gptb200_status_string", "gptb200_last_error", "gptb200_plan_gemm", "gptb200_selftest_wait_timeout",
     "gptb200_linear_forward", "gptb200_linear_backward", "gptb200_linear_backward_weights", "gptb200_linear_backward_input",
     "gptb200_gelu_backward",
@@ -65,6 +65,7 @@ def load_library(path: str | None = None) -> ctypes.CDLL:
         "gptb200_ctx_get_mode": (i, [vp]),
         "gptb200_ctx_set_stream": (i, [vp, vp]),
         "gptb200_ctx_set_option": (i, [vp, ctypes.c_char_p, i]),
+        "gptb200_ctx_read_trace": (i, [vp, vp, i]),
         "gptb200_ctx_synchronize": (i, [vp]),
         "gptb200_ctx_launch_count": (ctypes.c_longlong, [vp]),
         "gptb200_selftest_wait_timeout": (i, [vp, i]),
@@ -182,6 +183,12 @@ class Backend:
 
     def set_stream(self, stream: int) -> None:
         self._check(self._lib.gptb200_ctx_set_stream(self._ctx, ctypes.c_void_p(stream)), "gptb200_ctx_set_stream")
+
+    def read_trace(self):
+        """[11 events][128 k-blocks] SM clock samples of the latest CTA-pair GEMM launch (option "trace" must be on)."""
+        buf = (ctypes.c_longlong * (11 * 128))()
+        self._check(self._lib.gptb200_ctx_read_trace(self._ctx, buf, 11 * 128), "gptb200_ctx_read_trace")
+        return [list(buf[e * 128:(e + 1) * 128]) for e in range(11)]
 
     def set_option(self, key: str, value: int) -> None:
         self._check(self._lib.gptb200_ctx_set_option(self._ctx, key.encode(), value), "gptb200_ctx_set_option")

@@ -227,6 +227,10 @@ int run_gemm(gptb200_ctx *ctx, const GemmCall &c)
     p.debug = ctx->debug;
 
     float *out_base = c.out;
+    if (pair && ctx->d_trace) {
+        CUDA_TRY(ctx, cudaMemsetAsync(ctx->d_trace, 0, sizeof(long long) * kTraceEvents * kTraceSlots, ctx->stream));
+        p.trace = ctx->d_trace;
+    }
     if (pair) {
         p.sk_total = pl.sk_total;
         p.sk_unit = pl.sk_unit;
@@ -389,6 +393,7 @@ int gptb200_ctx_destroy(gptb200_ctx *ctx)
     if (ctx->ws) cudaFree(ctx->ws);
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->d_pair_flags) cudaFree(ctx->d_pair_flags);
+    if (ctx->d_trace) cudaFree(ctx->d_trace);
     delete ctx;
     return GPTB200_OK;
 }
@@ -422,6 +427,15 @@ int gptb200_ctx_set_option(gptb200_ctx *ctx, const char *key, int value)
         ctx->pair = value;
         return GPTB200_OK;
     }
+    if (!strcmp(key, "trace")) {
+        if (value && !ctx->d_trace) CUDA_TRY(ctx, cudaMalloc(&ctx->d_trace, sizeof(long long) * kTraceEvents * kTraceSlots));
+        if (!value && ctx->d_trace) {
+            CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+            cudaFree(ctx->d_trace);
+            ctx->d_trace = nullptr;
+        }
+        return GPTB200_OK;
+    }
     if (!strcmp(key, "stream_k")) {
         if (value < -1 || value > 1) return fail(ctx, GPTB200_ERR_INVALID_ARG, "stream_k must be -1, 0 or 1");
         ctx->stream_k = value;
@@ -441,6 +455,16 @@ int gptb200_ctx_set_option(gptb200_ctx *ctx, const char *key, int value)
         return GPTB200_OK;
     }
     return fail(ctx, GPTB200_ERR_INVALID_ARG, "unknown option '%s'", key);
+}
+
+int gptb200_ctx_read_trace(gptb200_ctx *ctx, long long *samples, int capacity)
+{
+    if (!ctx || !samples || capacity < 0) return GPTB200_ERR_INVALID_ARG;
+    if (!ctx->d_trace) return fail(ctx, GPTB200_ERR_INVALID_ARG, "tracing is off (option \"trace\")");
+    const int n = std::min(capacity, int(kTraceEvents) * kTraceSlots);
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpy(samples, ctx->d_trace, sizeof(long long) * n, cudaMemcpyDeviceToHost));
+    return GPTB200_OK;
 }
 
 int gptb200_ctx_synchronize(gptb200_ctx *ctx)

@@ -26,6 +26,7 @@ struct gptb200_ctx {
     int debug = 0;       // timing experiments (see GemmParams::debug)
     int pair = 0;        // CTA-pair (cta_group::2) kernel: 1 = always, 0 = heuristic, -1 = never
     int stream_k = 0;    // CTA-pair kernel, ranges cut inside tiles: 1 = always, 0 = heuristic, -1 = never
+    long long *d_trace = nullptr;  // clock samples of the CTA-pair kernel (option "trace")
     int *d_status = nullptr;
     unsigned int *d_pair_flags = nullptr;  // per CTA pair, CTA and epilogue warp: number of the launch whose partial tile is complete
     unsigned int pair_epoch = 0;           // number of the latest CTA-pair launch that used the flags

@@ -72,6 +72,23 @@ struct GemmParams {
     float *sk_slots;         // one partial 256 x 256 tile per pair
     unsigned int *sk_flags;  // one word per pair, CTA and epilogue warp: the launch number whose partial tile is complete
     unsigned int sk_epoch;   // this launch's number
+    long long *trace;        // optional [kTraceEvents][kTraceSlots] clock64 samples of the first k-blocks of CTA 0
+};
+
+constexpr int kTraceSlots = 128;
+enum TraceEvent : int {
+    TRACE_LOAD_ISSUE = 0,   // producer: stage free, loads about to be issued
+    TRACE_CONV_BEGIN = 1,   // converter (first warp of the group): raw tile landed, low-part buffer free
+    TRACE_CONV_END = 2,     // converter: tiles written and published
+    TRACE_MMA_FULL = 3,     // MMA thread: raw tile landed
+    TRACE_MMA_READY = 4,    // MMA thread: converted tiles of both CTAs ready
+    TRACE_MMA_ISSUED = 5,   // MMA thread: MMAs and commits issued
+    TRACE_EPI_BEGIN = 6,    // epilogue warp 0: accumulator chunk complete (slot = chunk number)
+    TRACE_EPI_END = 7,      // epilogue warp 0: chunk drained
+    TRACE_PEER_LOAD_ISSUE = 8,   // the same three events in the second CTA of the pair
+    TRACE_PEER_CONV_BEGIN = 9,
+    TRACE_PEER_CONV_END = 10,
+    kTraceEvents = 11,
 };
 
 constexpr int kBM = 128;

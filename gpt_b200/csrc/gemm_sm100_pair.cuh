@@ -76,6 +76,69 @@ __device__ __forceinline__ bool bounded_wait_cluster(uint32_t bar, uint32_t pari
     }
 }
 
+// 3xTF32 on CTA pairs computes a.b as  a_hi.b_hi (tf32 MMAs on the raw fp32 tiles: the tensor core drops the low 13
+// mantissa bits)  +  a_lo.b + a.b_lo (bf16 MMAs), with a_lo = a - a_hi.  The converter warps write, per operand tile, a
+// bf16 tile with 64 k-positions per 32 k of the raw tile:  A: [a_lo | a]   B: [b | b_lo]  (groups of 8 values of each kind
+// alternate), so that ONE bf16 MMA chain over the 64 positions yields both correction terms.  Rounding a_lo, b_lo, a
+// and b to bf16 leaves an error of about 1.5e-6 of the result's scale (the products that matter are 2^-11 small).
+//
+// Offsets (source | destination << 16) of unit u (0..511, 8 floats of one operand tile) inside a stage.
+template <bool MN>
+__device__ __forceinline__ uint32_t conv_offsets(int u, uint32_t tile)
+{
+    uint32_t src, dst;
+    if (MN) {
+        // raw: [32 k-rows x 32 floats] boxes, 32-byte chunks XOR-ed with (k-row & 3).  The eight lanes of a quarter warp
+        // take one k-row of two neighbouring boxes, the second box's lanes load their two halves in the other order:
+        // every 16-byte load and store phase then covers all 32 banks.
+        // bf16 tile: [8 k-positions x 64 rows] atoms of 1 KiB (16-byte chunks XOR-ed with the k-position), the 8 atoms of a
+        // 64-row half one after the other, 8 KiB to the other half.
+        const int p32 = u & 3, bpar = (u >> 2) & 1, kr = (u >> 3) & 31, bpair = u >> 8;
+        src = tile + (2 * bpair + bpar) * kBoxBytesMN + kr * 128 + p32 * 32 + 16 * bpar;
+        const int row = kr & 7;
+        const int chunk = (4 * bpar + (p32 ^ (kr & 3))) ^ row;
+        dst = tile + bpair * 8192 + 2 * (kr >> 3) * 1024 + row * 128 + chunk * 16;
+    } else {
+        // raw: 128-byte rows (32 k), 16-byte chunks XOR-ed with (row & 7); the bf16 tile has the same geometry and swizzle.
+        // Odd rows start with the odd chunk, which is also the logically first one of the pair.
+        const int r = u >> 2, c = u & 3;
+        src = tile + r * 128 + (2 * c + (r & 1)) * 16;
+        dst = src;
+    }
+    return src | (dst << 16);
+}
+
+template <bool MN, bool IS_B>
+__device__ __forceinline__ void convert_unit(uint32_t raw, uint32_t cor, uint32_t offsets, int lane)
+{
+    const uint32_t src = raw + (offsets & 0xFFFFu);
+    const uint32_t dst = cor + (offsets >> 16);
+    float4 f1 = ptx::lds128(src);
+    float4 f2 = ptx::lds128(src ^ 16u);
+    if (MN && (lane & 4)) {   // second box of the pair: halves were loaded in the other order
+        const float4 t = f1;
+        f1 = f2;
+        f2 = t;
+    }
+    const float v[8] = {f1.x, f1.y, f1.z, f1.w, f2.x, f2.y, f2.z, f2.w};
+    uint32_t lo[4], whole[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float l0 = v[2 * e] - __uint_as_float(__float_as_uint(v[2 * e]) & 0xFFFFE000u);
+        const float l1 = v[2 * e + 1] - __uint_as_float(__float_as_uint(v[2 * e + 1]) & 0xFFFFE000u);
+        lo[e] = ptx::pack_bf16x2(l0, l1);
+        whole[e] = ptx::pack_bf16x2(v[2 * e], v[2 * e + 1]);
+    }
+    const uint32_t dst2 = MN ? dst + 1024u : dst ^ 16u;
+    if (IS_B) {
+        ptx::sts128(dst, whole[0], whole[1], whole[2], whole[3]);
+        ptx::sts128(dst2, lo[0], lo[1], lo[2], lo[3]);
+    } else {
+        ptx::sts128(dst, lo[0], lo[1], lo[2], lo[3]);
+        ptx::sts128(dst2, whole[0], whole[1], whole[2], whole[3]);
+    }
+}
+
 // First k-block (on the line of all tiles' k-blocks) of pair q out of P.
 __device__ __forceinline__ long long pair_range_start(const GemmParams &p, long long q, long long P)
 {
@@ -148,6 +211,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     constexpr int kBoxesA = A_MN ? kBM / 32 : 1;
     constexpr int kBoxesB = B_MN ? C::kBRows / 32 : 1;
     constexpr uint32_t kIdesc = ptx::make_idesc_tf32(2 * kBM, BN, A_MN, B_MN);  // M = 256 over the pair
+    constexpr uint32_t kIdescCorr = ptx::make_idesc_bf16(2 * kBM, BN, A_MN, B_MN);
     constexpr int kFirstEpiWarp = 4;
     constexpr int kFirstConvWarp = 4 + C::kEpiWarps;
 
@@ -181,13 +245,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             ptx::mbar_init(empty_bar(s), 1);
         }
         for (int j = 0; j < NL; ++j) {
-            ptx::mbar_init(conv_bar(j), 3);   // one arrival per converter warp of the group that owns the buffer
-            ptx::mbar_init(peer_bar(j), 3);
+            ptx::mbar_init(conv_bar(j), 6);   // leader: one arrival per converter warp (three of each CTA) of the group that owns the buffer
+            ptx::mbar_init(peer_bar(j), 3);   // unused
             ptx::mbar_init(lo_empty_bar(j), 1);
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(tmem_full_bar(b), 1);
-            ptx::mbar_init(tmem_empty_bar(b), 2 * C::kEpiWarps * 32);
+            ptx::mbar_init(tmem_empty_bar(b), 2 * C::kEpiWarps);   // one arrival per epilogue warp of either CTA
         }
         ptx::mbar_init(drain_bar, 1);
         *abort_flag = 0u;
@@ -209,6 +273,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     const int tiles_m2 = (p.tiles_m + 1) / 2;   // pairs of 128-row tiles
     const long long num_pairs = gridDim.x >> 1;
     const long long pair_id = blockIdx.x >> 1;
+    auto trace = [&](int event, uint32_t slot) {
+        if (p.trace == nullptr || blockIdx.x > 1 || slot >= kTraceSlots) return;
+        if (blockIdx.x == 1) {   // the peer CTA records its producer and converter events only
+            if (event > TRACE_CONV_END) return;
+            event += TRACE_PEER_LOAD_ISSUE;
+        }
+        p.trace[event * kTraceSlots + slot] = clock64();
+    };
     auto my_work = [&]() {
         PairWork w;
         w.g = pair_range_start(p, pair_id, num_pairs);
@@ -221,7 +293,16 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     // 3xTF32 converters: six warps (warps 2, 3 and the last four) in two groups of three; group g handles the
     // k-blocks with (iteration & 1) == g, so that waking up, converting and signalling one stage overlaps with
     // the other group's stage.  lo = a - trunc_tf32(a), written at the same swizzled offset as the raw tile.
-    auto convert_loop = [&](int group, int ctid) {
+    auto convert_loop = [&](int group, int wgrp) {
+        // A stage is 32 warp-sized pieces (32 units of 8 floats): 16 of the A tile, 16 of the B tile.  The three warps of a
+        // group take every third piece of A and, starting one warp later, every third piece of B (11, 11 and 10 pieces).
+        const int wgrp_b = (wgrp + 2) % 3;
+        uint32_t tab_a[6], tab_b[6];
+#pragma unroll
+        for (int t = 0; t < 6; ++t) {
+            tab_a[t] = conv_offsets<A_MN>(((wgrp + 3 * t) & 15) * 32 + lane, 0u);
+            tab_b[t] = conv_offsets<B_MN>(((wgrp_b + 3 * t) & 15) * 32 + lane, kATileBytes);
+        }
         uint32_t it = 0;
         bool ok = true;
         PairWork work = my_work();
@@ -239,18 +320,16 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     ok = false;
                     break;
                 }
-                const float4 *hi = reinterpret_cast<const float4 *>(smem_gen + s * C::kHiBytes);
-                float4 *lo = reinterpret_cast<float4 *>(smem_gen + (lo_base - smem_base) + j * C::kHiBytes);
-                constexpr int kVec = C::kHiBytes / 16;
-#pragma unroll 8
-                for (int i = ctid; i < kVec; i += 96) {
-                    const float4 h = hi[i];
-                    float4 l;
-                    l.x = h.x - __uint_as_float(__float_as_uint(h.x) & 0xFFFFE000u);
-                    l.y = h.y - __uint_as_float(__float_as_uint(h.y) & 0xFFFFE000u);
-                    l.z = h.z - __uint_as_float(__float_as_uint(h.z) & 0xFFFFE000u);
-                    l.w = h.w - __uint_as_float(__float_as_uint(h.w) & 0xFFFFE000u);
-                    lo[i] = l;
+                if (wgrp == 0 && lane == 0) trace(TRACE_CONV_BEGIN, it);
+                const uint32_t raw = smem_base + s * C::kHiBytes;
+                const uint32_t cor = lo_base + j * C::kHiBytes;
+#pragma unroll
+                for (int t = 0; t < 6; ++t) {
+                    if (wgrp + 3 * t < 16) convert_unit<A_MN, false>(raw, cor, tab_a[t], lane);
+                }
+#pragma unroll
+                for (int t = 0; t < 6; ++t) {
+                    if (wgrp_b + 3 * t < 16) convert_unit<B_MN, true>(raw, cor, tab_b[t], lane);
                 }
                 ptx::fence_proxy_async_smem();
                 __syncwarp();
@@ -258,14 +337,15 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     if (leader)
                         ptx::mbar_arrive(conv_bar(j));
                     else
-                        ptx::mbar_arrive_cluster(ptx::map_to_cta(peer_bar(j), 0u));
+                        ptx::mbar_arrive_remote(ptx::map_to_cta(conv_bar(j), 0u));
+                    if (wgrp == 0) trace(TRACE_CONV_END, it);
                 }
             }
         }
     };
 
     if (warp < 4) {
-        if (C::kChunked) ptx::reg_dec<56>();
+        if (C::kChunked) ptx::reg_dec<64>();
         if (warp == 0) {
             // ------------------------------------------------------------ TMA producer (both CTAs)
             uint32_t it = 0;
@@ -282,6 +362,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                         ok = false;
                         break;
                     }
+                    if (lane == 0) trace(TRACE_LOAD_ISSUE, it);
                     if (p.debug & 1) {
                         if (lane == 0 && (X3 || leader)) ptx::mbar_arrive(full_bar(s));
                         __syncwarp();
@@ -333,40 +414,48 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                         for (; kb < kend; ++kb, ++it) {
                             const int s = it % STAGES;
                             const uint32_t ph = (it / STAGES) & 1u;
-                            if (!bounded_wait_cluster(full_bar(s), ph, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL)) { ok = false; break; }
+                            // 3xTF32: the converters of both CTAs report to one barrier of the leader; they have seen their raw
+                            // tiles land, so that barrier stands for the loads as well
+                            if (!X3 && !bounded_wait_cluster(full_bar(s), ph, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL)) { ok = false; break; }
+                            trace(TRACE_MMA_FULL, it);
                             const int j = it % NL;
                             const uint32_t lph = (it / NL) & 1u;
-                            if (X3 && !bounded_wait(conv_bar(j), lph, abort_flag, p.status, DEV_TIMEOUT_MMA_CONV)) { ok = false; break; }
-                            if (X3 && !bounded_wait_cluster(peer_bar(j), lph, abort_flag, p.status, DEV_TIMEOUT_MMA_CONV)) { ok = false; break; }
+                            if (X3 && !bounded_wait_cluster(conv_bar(j), lph, abort_flag, p.status, DEV_TIMEOUT_MMA_CONV)) { ok = false; break; }
                             ptx::tc_fence_after();
+                            trace(TRACE_MMA_READY, it);
                             const uint32_t a_hi = smem_base + s * C::kHiBytes;
                             const uint32_t b_hi = a_hi + kATileBytes;
                             const uint32_t a_lo = lo_base + j * C::kHiBytes;
                             const uint32_t b_lo = a_lo + kATileBytes;
+                            constexpr uint32_t a_lbo = A_MN ? kBoxBytesMN : 16, a_sbo = A_MN ? 512 : 1024;
+                            constexpr uint32_t b_lbo = B_MN ? kBoxBytesMN : 16, b_sbo = B_MN ? 512 : 1024;
+                            constexpr uint32_t a_lay = A_MN ? ptx::kLayoutSw128Base32B : ptx::kLayoutSw128;
+                            constexpr uint32_t b_lay = B_MN ? ptx::kLayoutSw128Base32B : ptx::kLayoutSw128;
+                            if (X3 && !(p.debug & 2)) {
+                                // correction terms a_lo.b + a.b_lo: bf16 tiles with 64 k-positions (low parts and whole values
+                                // side by side), 16 of them per instruction.  K-major: 128-byte rows, +32 bytes per step;
+                                // MN-major: [8 k x 64 m] atoms, 1 KiB per group of 8 k, 8 KiB to the next 64 rows.
+#pragma unroll
+                                for (int k = 0; k < 4; ++k) {
+                                    const uint64_t da = ptx::make_smem_desc(a_lo + (A_MN ? k * 2048 : k * 32), A_MN ? 8192 : 16, 1024, ptx::kLayoutSw128);
+                                    const uint64_t db = ptx::make_smem_desc(b_lo + (B_MN ? k * 2048 : k * 32), B_MN ? 8192 : 16, 1024, ptx::kLayoutSw128);
+                                    ptx::mma_f16_ss_pair(d_tmem, da, db, kIdescCorr, accumulate);
+                                    accumulate = 1u;
+                                }
+                            }
 #pragma unroll
                             for (int k = 0; k < ((p.debug & 2) ? 0 : kBK / kUmmaK); ++k) {
                                 const uint32_t a_off = A_MN ? k * 1024 : k * 32;
                                 const uint32_t b_off = B_MN ? k * 1024 : k * 32;
-                                constexpr uint32_t a_lbo = A_MN ? kBoxBytesMN : 16, a_sbo = A_MN ? 512 : 1024;
-                                constexpr uint32_t b_lbo = B_MN ? kBoxBytesMN : 16, b_sbo = B_MN ? 512 : 1024;
-                                constexpr uint32_t a_lay = A_MN ? ptx::kLayoutSw128Base32B : ptx::kLayoutSw128;
-                                constexpr uint32_t b_lay = B_MN ? ptx::kLayoutSw128Base32B : ptx::kLayoutSw128;
                                 const uint64_t da_hi = ptx::make_smem_desc(a_hi + a_off, a_lbo, a_sbo, a_lay);
                                 const uint64_t db_hi = ptx::make_smem_desc(b_hi + b_off, b_lbo, b_sbo, b_lay);
-                                if (X3) {
-                                    const uint64_t da_lo = ptx::make_smem_desc(a_lo + a_off, a_lbo, a_sbo, a_lay);
-                                    const uint64_t db_lo = ptx::make_smem_desc(b_lo + b_off, b_lbo, b_sbo, b_lay);
-                                    ptx::mma_tf32_ss_pair(d_tmem, da_lo, db_hi, kIdesc, accumulate);
-                                    ptx::mma_tf32_ss_pair(d_tmem, da_hi, db_lo, kIdesc, 1u);
-                                    ptx::mma_tf32_ss_pair(d_tmem, da_hi, db_hi, kIdesc, 1u);
-                                } else {
-                                    ptx::mma_tf32_ss_pair(d_tmem, da_hi, db_hi, kIdesc, accumulate);
-                                }
+                                ptx::mma_tf32_ss_pair(d_tmem, da_hi, db_hi, kIdesc, accumulate);
                                 accumulate = 1u;
                             }
                             // the stage is free in both CTAs once these MMAs have read it
                             ptx::mma_commit_pair_both(empty_bar(s), 3);
                             if (X3) ptx::mma_commit_pair_both(lo_empty_bar(j), 3);
+                            trace(TRACE_MMA_ISSUED, it);
                         }
                         if (ok) {
                             ptx::mma_commit_pair_both(tmem_full_bar(buf), 3);
@@ -379,11 +468,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             }
             __syncwarp();
         } else if (X3) {
-            convert_loop(warp - 2, lane);   // warps 2 and 3: first warp of converter group 0 and 1
+            convert_loop(warp - 2, 0);   // warps 2 and 3: first warp of converter group 0 and 1
         }
     } else if (warp < kFirstConvWarp) {
         // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
-        if (C::kChunked) ptx::reg_inc<184>();
+        if (C::kChunked) ptx::reg_inc<192>();
         const int e = warp - kFirstEpiWarp;
         const int q = warp & 3;
         const int col_base = (e >> 2) * C::kColsPerEpiWarp;
@@ -455,6 +544,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                         break;
                     }
                     ptx::tc_fence_after();
+                    if (e == 0 && lane == 0) trace(TRACE_EPI_BEGIN, g);
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         uint32_t v[32];
@@ -464,7 +554,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                         for (int j = 0; j < 32; ++j) acc[c * 32 + j] += __uint_as_float(v[j]);
                     }
                     ptx::tc_fence_before();
-                    ptx::mbar_arrive_cluster(leader_tmem_empty[buf]);
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive_cluster(leader_tmem_empty[buf]);
+                    if (e == 0 && lane == 0) trace(TRACE_EPI_END, g);
                 }
                 if (ok && !owner) {
                     float *slot = slot_of(pair_id);
@@ -514,7 +606,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     ptx::tmem_ld_wait();
                     if (c == C::kColsPerEpiWarp / 32 - 1) {
                         ptx::tc_fence_before();
-                        ptx::mbar_arrive_cluster(leader_tmem_empty[buf]);
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive_cluster(leader_tmem_empty[buf]);
                     }
                     float v[32];
 #pragma unroll
@@ -544,9 +637,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         __syncwarp();
     } else if (X3) {
         // ------------------------------------------------------------ 3xTF32 converters (last four warps)
-        ptx::reg_dec<72>();
+        ptx::reg_dec<64>();
         const int j = warp - kFirstConvWarp;
-        convert_loop(j >> 1, (1 + (j & 1)) * 32 + lane);
+        convert_loop(j >> 1, 1 + (j & 1));
     }
 
     // ---------------------------------------------------------------- teardown

@@ -54,8 +54,14 @@ int gptb200_ctx_set_stream(gptb200_ctx *ctx, void *cuda_stream);
  * "pair" (CTA-pair kernel with 256 x 256 tiles: 1 = always, 0 = heuristic, -1 = never),
  * "stream_k" (CTA-pair kernel: give every pair the same number of k-blocks by letting a pair's range begin and end inside a
  * tile, partial tiles summed through scratch: 1 = always, 0 = when whole tiles would leave SMs idle, -1 = never),
- * "skinny" (weight-streaming kernel for forward calls with m <= 16: 1 = on (default), 0 = off). */
+ * "skinny" (weight-streaming kernel for forward calls with m <= 16: 1 = on (default), 0 = off),
+ * "trace" (record a kernel-phase trace of each CTA-pair GEMM launch: 1 = on, 0 = off (default)). */
 int gptb200_ctx_set_option(gptb200_ctx *ctx, const char *key, int value);
+/* Kernel-phase trace (option "trace" = 1): the most recent CTA-pair GEMM launch recorded, in its first CTA and for its first 128
+ * k-blocks, the SM clock at 8 events: [event][k-block], events 0 loads issued, 1 conversion begins, 2 conversion published,
+ * 3 MMA thread sees the raw tile, 4 ... and the converted tiles, 5 MMAs issued, 6 / 7 accumulator chunk complete / drained (index
+ * = chunk).  Copies up to `capacity` samples (8 * 128 in all; 0 = not recorded) after waiting for the stream. */
+int gptb200_ctx_read_trace(gptb200_ctx *ctx, long long *samples, int capacity);
 /* Waits for the context's stream and reports a device-side timeout recorded by any earlier kernel. */
 int gptb200_ctx_synchronize(gptb200_ctx *ctx);
 /* Number of kernels this context has launched so far. */

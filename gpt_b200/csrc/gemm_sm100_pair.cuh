@@ -28,6 +28,8 @@
 // All waits are bounded exactly as in the one-CTA kernel; both CTAs always reach the closing cluster barrier.
 #pragma once
 
+#include <type_traits>
+
 #include "gemm_sm100.cuh"
 
 namespace gptb200 {
@@ -480,21 +482,32 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         StageRing<C::kStageBufsPerWarp> ring;
         ring.base = staging_base + e * C::kStageBufsPerWarp * kStageTileBytes;
         ring.count = 0;
-        uint32_t g = 0;
+        uint32_t g = 0, tile_count = 0;
+        long long acq_clks = 0;
         bool ok = true;
         const uint32_t leader_tmem_empty[2] = {ptx::map_to_cta(tmem_empty_bar(0), 0u), ptx::map_to_cta(tmem_empty_bar(1), 0u)};
 
-        auto emit = [&](float (&v)[32], int row0, int col0) {
+        // bias_lane: bias[col0 + lane], fetched when the tile was started
+        auto emit = [&](float (&v)[32], int row0, int col0, float bias_lane) {
+            const bool tr_on = p.trace && blockIdx.x == 0 && e == 0 && lane == 0 && tile_count == 1 && (col0 & 127) == 0;
+            auto mark = [&](int k) { if (tr_on) p.trace[TRACE_EPI_END * kTraceSlots + 80 + k] = clock64(); };
+            mark(0);
             if (p.bias && p.epi_mode == EPI_STORE) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] += (col0 + j < p.N) ? __ldg(p.bias + col0 + j) : 0.0f;
+                for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, bias_lane, j);
             }
             const bool in_range = row0 < p.M && col0 < p.N;
+            mark(1);
             {
+                const long long tq0 = clock64();
                 const uint32_t buf = ring.acquire(lane);
+                acq_clks += clock64() - tq0;
+                mark(2);
                 stage_row(buf, lane, v);
+                mark(3);
                 ptx::fence_proxy_async_smem();
                 __syncwarp();
+                mark(4);
                 if (lane == 0) {
                     if (in_range) {
                         if (p.epi_mode == EPI_ACCUM)
@@ -506,10 +519,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 }
                 ring.count++;
             }
+            mark(5);
             if (p.has_act) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+                mark(6);
+                const long long tq0 = clock64();
                 const uint32_t buf = ring.acquire(lane);
+                acq_clks += clock64() - tq0;
                 stage_row(buf, lane, v);
                 ptx::fence_proxy_async_smem();
                 __syncwarp();
@@ -518,6 +535,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     ptx::tma_store_commit();
                 }
                 ring.count++;
+                mark(7);
             }
         };
 
@@ -532,6 +550,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             // slot of pair r: [CTA][epilogue warp][128 values][lane]
             auto slot_of = [&](long long r) { return p.sk_slots + ((r * 2 + rank) * C::kEpiWarps + e) * 4096 + lane; };
             auto flag_of = [&](long long r) { return p.sk_flags + (r * 2 + rank) * C::kEpiWarps + e; };
+            float bias_pre[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (owner && p.bias && p.epi_mode == EPI_STORE) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) bias_pre[c] = (n0 + c * 32 + lane < p.N) ? __ldg(p.bias + n0 + c * 32 + lane) : 0.0f;
+            }
             if (C::kChunked) {
                 float acc[128];
 #pragma unroll
@@ -544,7 +567,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                         break;
                     }
                     ptx::tc_fence_after();
-                    if (e == 0 && lane == 0) trace(TRACE_EPI_BEGIN, g);
+
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         uint32_t v[32];
@@ -556,7 +579,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     ptx::tc_fence_before();
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive_cluster(leader_tmem_empty[buf]);
-                    if (e == 0 && lane == 0) trace(TRACE_EPI_END, g);
+
                 }
                 if (ok && !owner) {
                     float *slot = slot_of(pair_id);
@@ -576,13 +599,18 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                         }
                     }
                     if (ok) {
+                        if (e == 0 && lane == 0) trace(TRACE_EPI_BEGIN, tile_count);
 #pragma unroll
                         for (int c = 0; c < 4; ++c) {
                             float v[32];
 #pragma unroll
                             for (int j = 0; j < 32; ++j) v[j] = acc[c * 32 + j];
-                            emit(v, row0, n0 + c * 32);
+                            emit(v, row0, n0 + c * 32, bias_pre[c]);
                         }
+                        if (e == 0 && lane == 0) trace(TRACE_EPI_END, tile_count);
+                        if (e == 0 && lane == 0 && p.trace && blockIdx.x == 0 && tile_count < 8) p.trace[TRACE_EPI_END * kTraceSlots + 64 + tile_count] = acq_clks;
+                        acq_clks = 0;
+                        ++tile_count;
                     }
                 }
             } else {
@@ -623,7 +651,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 #pragma unroll
                             for (int j = 0; j < 32; ++j) v[j] += __ldcg(slot + j * 32);
                         }
-                        emit(v, row0, n0 + c * 32);
+                        emit(v, row0, n0 + c * 32, c == 0 ? bias_pre[0] : c == 1 ? bias_pre[1] : c == 2 ? bias_pre[2] : bias_pre[3]);
                     }
                 }
                 if (ok && !owner) {

@@ -83,8 +83,8 @@ enum TraceEvent : int {
     TRACE_MMA_FULL = 3,     // MMA thread: raw tile landed
     TRACE_MMA_READY = 4,    // MMA thread: converted tiles of both CTAs ready
     TRACE_MMA_ISSUED = 5,   // MMA thread: MMAs and commits issued
-    TRACE_EPI_BEGIN = 6,    // epilogue warp 0: accumulator chunk complete (slot = chunk number)
-    TRACE_EPI_END = 7,      // epilogue warp 0: chunk drained
+    TRACE_EPI_BEGIN = 6,    // epilogue warp 0 (3xTF32): a tile's sums are complete, output begins (slot = tile number)
+    TRACE_EPI_END = 7,      // epilogue warp 0: the tile's output stores are issued
     TRACE_PEER_LOAD_ISSUE = 8,   // the same three events in the second CTA of the pair
     TRACE_PEER_CONV_BEGIN = 9,
     TRACE_PEER_CONV_END = 10,

@@ -6,14 +6,15 @@
 //
 // Division of work inside the pair (rank 0 = leader):
 //   both CTAs   TMA producer (own A rows, own half of B) -> local full[s]
-//   both CTAs   3xTF32 converters (own tiles)
+//   both CTAs   3xTF32 converters (own tiles): bf16 correction tiles for a_lo.b + a.b_lo
 //   leader      one thread issues every tcgen05.mma.cta_group::2 and the commits
 //   both CTAs   epilogue warps drain their own 128 TMEM lanes (the rows they own) and store them
 // Cross-CTA signalling (no multicast copy anywhere):
 //   TF32:    the peer's TMA loads report their bytes straight to the leader's full[s] (cta_group::2 load form),
 //            which the leader arms with the byte count of both CTAs;
-//   3xTF32:  loads report to the local full[s]; the peer's converter warps, once the low parts are written,
-//            arrive on leader.peer_ready[s] (one remote arrive per warp);
+//   3xTF32:  loads report to the local full[s]; the converter warps of BOTH CTAs, once the correction tiles are
+//            written, arrive on the leader's conv[j] (the peer's with one remote arrive per warp), the only
+//            barrier the MMA thread waits on per k-block;
 //   leader -> both   "stage s is free" / "accumulator b is full": one tcgen05.commit that signals the barrier at
 //            the same offset in both CTAs;
 //   peer -> leader   "accumulator b is drained": remote mbarrier.arrive on leader.tmem_empty[b].
@@ -54,7 +55,7 @@ struct PairCfg {
     // critical path.
     static constexpr int kStages = X3 ? 3 : 6;
     static constexpr int kLoStages = X3 ? 3 : 0;
-    static constexpr int kNumBarriers = 2 * kStages + 3 * (X3 ? kLoStages : 1) + 5;
+    static constexpr int kNumBarriers = 2 * kStages + 2 * (X3 ? kLoStages : 1) + 5;
     static constexpr int kSmemBytes = (kStages + kLoStages) * kHiBytes + kStagingBytes + 1024 + 256;
     static_assert(8 * kNumBarriers + 8 <= 256, "barrier block overflows its slot");
     static_assert(kSmemBytes <= 232448, "exceeds 227 KiB of shared memory");
@@ -84,39 +85,55 @@ __device__ __forceinline__ bool bounded_wait_cluster(uint32_t bar, uint32_t pari
 // alternate), so that ONE bf16 MMA chain over the 64 positions yields both correction terms.  Rounding a_lo, b_lo, a
 // and b to bf16 leaves an error of about 1.5e-6 of the result's scale (the products that matter are 2^-11 small).
 //
-// Offsets (source | destination << 16) of unit u (0..511, 8 floats of one operand tile) inside a stage.
+// A tile is converted in 16 warp-sized pieces of 32 units (8 floats each).  Per-lane constants of the addressing:
+// source offset and destination offsets (for even and odd pieces) of the lane's unit in piece 0.
+//   MN-major raw tile: [32 k-rows x 32 floats] boxes, 32-byte chunks XOR-ed with (k-row & 3).  Piece p holds k-rows
+//   4 (p & 7) .. + 3 of the boxes 2 (p >> 3) and 2 (p >> 3) + 1; the eight lanes of a quarter warp take one k-row of the
+//   two boxes, the second box's lanes load their two halves in the other order, so that every 16-byte load and store
+//   phase covers all 32 banks.  bf16 tile: [8 k-positions x 64 rows] atoms of 1 KiB (16-byte chunks XOR-ed with the
+//   k-position), the 8 atoms of a 64-row half one after the other, 8 KiB to the other half.
+//   K-major raw tile: 128-byte rows (32 k), 16-byte chunks XOR-ed with (row & 7); piece p holds rows 8 p .. 8 p + 7.  The
+//   bf16 tile has the same geometry and swizzle.  Odd rows start with the odd chunk, which is also the logically first.
+struct ConvLane {
+    uint32_t src, dst_even, dst_odd;
+};
+
 template <bool MN>
-__device__ __forceinline__ uint32_t conv_offsets(int u, uint32_t tile)
+__device__ __forceinline__ ConvLane conv_lane(int lane, uint32_t tile)
 {
-    uint32_t src, dst;
+    ConvLane c;
     if (MN) {
-        // raw: [32 k-rows x 32 floats] boxes, 32-byte chunks XOR-ed with (k-row & 3).  The eight lanes of a quarter warp
-        // take one k-row of two neighbouring boxes, the second box's lanes load their two halves in the other order:
-        // every 16-byte load and store phase then covers all 32 banks.
-        // bf16 tile: [8 k-positions x 64 rows] atoms of 1 KiB (16-byte chunks XOR-ed with the k-position), the 8 atoms of a
-        // 64-row half one after the other, 8 KiB to the other half.
-        const int p32 = u & 3, bpar = (u >> 2) & 1, kr = (u >> 3) & 31, bpair = u >> 8;
-        src = tile + (2 * bpair + bpar) * kBoxBytesMN + kr * 128 + p32 * 32 + 16 * bpar;
-        const int row = kr & 7;
-        const int chunk = (4 * bpar + (p32 ^ (kr & 3))) ^ row;
-        dst = tile + bpair * 8192 + 2 * (kr >> 3) * 1024 + row * 128 + chunk * 16;
+        const int p32 = lane & 3, bpar = (lane >> 2) & 1, krl = lane >> 3;
+        c.src = tile + bpar * kBoxBytesMN + krl * 128 + p32 * 32 + 16 * bpar;
+        const int chunk = 4 * bpar + (p32 ^ krl);
+        c.dst_even = tile + krl * 128 + ((chunk ^ krl) << 4);
+        c.dst_odd = tile + (4 + krl) * 128 + ((chunk ^ (4 + krl)) << 4);
     } else {
-        // raw: 128-byte rows (32 k), 16-byte chunks XOR-ed with (row & 7); the bf16 tile has the same geometry and swizzle.
-        // Odd rows start with the odd chunk, which is also the logically first one of the pair.
-        const int r = u >> 2, c = u & 3;
-        src = tile + r * 128 + (2 * c + (r & 1)) * 16;
-        dst = src;
+        const int r = lane >> 2, q = lane & 3;
+        c.src = tile + r * 128 + (2 * q + (r & 1)) * 16;
+        c.dst_even = c.src;
+        c.dst_odd = c.src;
     }
-    return src | (dst << 16);
+    return c;
 }
 
-template <bool MN, bool IS_B>
-__device__ __forceinline__ void convert_unit(uint32_t raw, uint32_t cor, uint32_t offsets, int lane)
+template <bool MN>
+__device__ __forceinline__ constexpr uint32_t conv_src_offset(int piece)
 {
-    const uint32_t src = raw + (offsets & 0xFFFFu);
-    const uint32_t dst = cor + (offsets >> 16);
-    float4 f1 = ptx::lds128(src);
-    float4 f2 = ptx::lds128(src ^ 16u);
+    return MN ? (piece >> 3) * 8192 + (piece & 7) * 512 : piece * 1024;
+}
+
+template <bool MN>
+__device__ __forceinline__ constexpr uint32_t conv_dst_offset(int piece)
+{
+    return MN ? (piece >> 3) * 8192 + ((piece & 7) >> 1) * 2048 : piece * 1024;
+}
+
+// The arithmetic of one unit: 8 raw floats -> 8 low parts and 8 whole values in bf16, stored as A: [low | whole],
+// B: [whole | low] so that one bf16 MMA chain over the doubled k gives a_lo.b + a.b_lo.
+template <bool MN, bool IS_B>
+__device__ __forceinline__ void convert_store(float4 f1, float4 f2, uint32_t dst, int lane)
+{
     if (MN && (lane & 4)) {   // second box of the pair: halves were loaded in the other order
         const float4 t = f1;
         f1 = f2;
@@ -138,6 +155,20 @@ __device__ __forceinline__ void convert_unit(uint32_t raw, uint32_t cor, uint32_
     } else {
         ptx::sts128(dst, lo[0], lo[1], lo[2], lo[3]);
         ptx::sts128(dst2, whole[0], whole[1], whole[2], whole[3]);
+    }
+}
+
+// The pieces first, first + 3, ... (< 16) of one operand tile.  Deliberately a rolled loop: the kernel's code is large
+// (the unrolled epilogue above all) and the converter warps were measured to run faster with a compact body than with
+// unrolled or load-batched ones.
+template <bool MN, bool IS_B>
+__device__ __forceinline__ void convert_tile(uint32_t raw, uint32_t cor, const ConvLane &c, int first, int lane)
+{
+#pragma unroll 1
+    for (int p = first; p < 16; p += 3) {
+        const uint32_t src = raw + c.src + conv_src_offset<MN>(p);
+        const float4 f1 = ptx::lds128(src), f2 = ptx::lds128(src ^ 16u);
+        convert_store<MN, IS_B>(f1, f2, cor + ((p & 1) ? c.dst_odd : c.dst_even) + conv_dst_offset<MN>(p), lane);
     }
 }
 
@@ -227,12 +258,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     const uint32_t bar_base = staging_base + C::kStagingBytes;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
-    auto conv_bar = [&](int j) { return bar_base + 8u * (2 * STAGES + j); };              // low parts of buffer j written (own CTA)
-    auto peer_bar = [&](int j) { return bar_base + 8u * (2 * STAGES + NL + j); };         // same, reported by the peer (leader only)
-    auto lo_empty_bar = [&](int j) { return bar_base + 8u * (2 * STAGES + 2 * NL + j); }; // low-part buffer j read by its MMAs
-    auto tmem_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 3 * NL + b); };
-    auto tmem_empty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 3 * NL + 2 + b); };  // used in the leader only
-    const uint32_t drain_bar = bar_base + 8u * (2 * STAGES + 3 * NL + 4);
+    auto conv_bar = [&](int j) { return bar_base + 8u * (2 * STAGES + j); };          // correction tiles of buffer j written, both CTAs (leader only)
+    auto lo_empty_bar = [&](int j) { return bar_base + 8u * (2 * STAGES + NL + j); }; // correction buffer j read by its MMAs
+    auto tmem_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 * NL + b); };
+    auto tmem_empty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 * NL + 2 + b); };  // used in the leader only
+    const uint32_t drain_bar = bar_base + 8u * (2 * STAGES + 2 * NL + 4);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_gen + (bar_base - smem_base) + 8 * C::kNumBarriers);
     volatile uint32_t *abort_flag = tmem_slot + 1;
 
@@ -248,7 +278,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         }
         for (int j = 0; j < NL; ++j) {
             ptx::mbar_init(conv_bar(j), 6);   // leader: one arrival per converter warp (three of each CTA) of the group that owns the buffer
-            ptx::mbar_init(peer_bar(j), 3);   // unused
             ptx::mbar_init(lo_empty_bar(j), 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -294,17 +323,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 
     // 3xTF32 converters: six warps (warps 2, 3 and the last four) in two groups of three; group g handles the
     // k-blocks with (iteration & 1) == g, so that waking up, converting and signalling one stage overlaps with
-    // the other group's stage.  lo = a - trunc_tf32(a), written at the same swizzled offset as the raw tile.
+    // the other group's stage.
     auto convert_loop = [&](int group, int wgrp) {
         // A stage is 32 warp-sized pieces (32 units of 8 floats): 16 of the A tile, 16 of the B tile.  The three warps of a
         // group take every third piece of A and, starting one warp later, every third piece of B (11, 11 and 10 pieces).
         const int wgrp_b = (wgrp + 2) % 3;
-        uint32_t tab_a[6], tab_b[6];
-#pragma unroll
-        for (int t = 0; t < 6; ++t) {
-            tab_a[t] = conv_offsets<A_MN>(((wgrp + 3 * t) & 15) * 32 + lane, 0u);
-            tab_b[t] = conv_offsets<B_MN>(((wgrp_b + 3 * t) & 15) * 32 + lane, kATileBytes);
-        }
+        const ConvLane lane_a = conv_lane<A_MN>(lane, 0u);
+        const ConvLane lane_b = conv_lane<B_MN>(lane, kATileBytes);
         uint32_t it = 0;
         bool ok = true;
         PairWork work = my_work();
@@ -325,14 +350,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 if (wgrp == 0 && lane == 0) trace(TRACE_CONV_BEGIN, it);
                 const uint32_t raw = smem_base + s * C::kHiBytes;
                 const uint32_t cor = lo_base + j * C::kHiBytes;
-#pragma unroll
-                for (int t = 0; t < 6; ++t) {
-                    if (wgrp + 3 * t < 16) convert_unit<A_MN, false>(raw, cor, tab_a[t], lane);
-                }
-#pragma unroll
-                for (int t = 0; t < 6; ++t) {
-                    if (wgrp_b + 3 * t < 16) convert_unit<B_MN, true>(raw, cor, tab_b[t], lane);
-                }
+                convert_tile<A_MN, false>(raw, cor, lane_a, wgrp, lane);
+                convert_tile<B_MN, true>(raw, cor, lane_b, wgrp_b, lane);
                 ptx::fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
@@ -483,32 +502,22 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         ring.base = staging_base + e * C::kStageBufsPerWarp * kStageTileBytes;
         ring.count = 0;
         uint32_t g = 0, tile_count = 0;
-        long long acq_clks = 0;
         bool ok = true;
         const uint32_t leader_tmem_empty[2] = {ptx::map_to_cta(tmem_empty_bar(0), 0u), ptx::map_to_cta(tmem_empty_bar(1), 0u)};
 
         // bias_lane: bias[col0 + lane], fetched when the tile was started
         auto emit = [&](float (&v)[32], int row0, int col0, float bias_lane) {
-            const bool tr_on = p.trace && blockIdx.x == 0 && e == 0 && lane == 0 && tile_count == 1 && (col0 & 127) == 0;
-            auto mark = [&](int k) { if (tr_on) p.trace[TRACE_EPI_END * kTraceSlots + 80 + k] = clock64(); };
-            mark(0);
             if (p.bias && p.epi_mode == EPI_STORE) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, bias_lane, j);
             }
             const bool in_range = row0 < p.M && col0 < p.N;
-            mark(1);
             {
-                const long long tq0 = clock64();
                 const uint32_t buf = ring.acquire(lane);
-                acq_clks += clock64() - tq0;
-                mark(2);
-                stage_row(buf, lane, v);
-                mark(3);
-                ptx::fence_proxy_async_smem();
+                    stage_row(buf, lane, v);
+                    ptx::fence_proxy_async_smem();
                 __syncwarp();
-                mark(4);
-                if (lane == 0) {
+                    if (lane == 0) {
                     if (in_range) {
                         if (p.epi_mode == EPI_ACCUM)
                             ptx::tma_reduce_add_3d(&tmap_out, col0, row0, 0, buf);
@@ -519,14 +528,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 }
                 ring.count++;
             }
-            mark(5);
             if (p.has_act) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
-                mark(6);
-                const long long tq0 = clock64();
-                const uint32_t buf = ring.acquire(lane);
-                acq_clks += clock64() - tq0;
+                    const uint32_t buf = ring.acquire(lane);
                 stage_row(buf, lane, v);
                 ptx::fence_proxy_async_smem();
                 __syncwarp();
@@ -535,8 +540,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     ptx::tma_store_commit();
                 }
                 ring.count++;
-                mark(7);
-            }
+                }
         };
 
         PairWork work = my_work();
@@ -608,8 +612,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                             emit(v, row0, n0 + c * 32, bias_pre[c]);
                         }
                         if (e == 0 && lane == 0) trace(TRACE_EPI_END, tile_count);
-                        if (e == 0 && lane == 0 && p.trace && blockIdx.x == 0 && tile_count < 8) p.trace[TRACE_EPI_END * kTraceSlots + 64 + tile_count] = acq_clks;
-                        acq_clks = 0;
                         ++tile_count;
                     }
                 }

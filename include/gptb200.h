@@ -57,10 +57,13 @@ int gptb200_ctx_set_stream(gptb200_ctx *ctx, void *cuda_stream);
  * "skinny" (weight-streaming kernel for forward calls with m <= 16: 1 = on (default), 0 = off),
  * "trace" (record a kernel-phase trace of each CTA-pair GEMM launch: 1 = on, 0 = off (default)). */
 int gptb200_ctx_set_option(gptb200_ctx *ctx, const char *key, int value);
-/* Kernel-phase trace (option "trace" = 1): the most recent CTA-pair GEMM launch recorded, in its first CTA and for its first 128
- * k-blocks, the SM clock at 8 events: [event][k-block], events 0 loads issued, 1 conversion begins, 2 conversion published,
- * 3 MMA thread sees the raw tile, 4 ... and the converted tiles, 5 MMAs issued, 6 / 7 accumulator chunk complete / drained (index
- * = chunk).  Copies up to `capacity` samples (8 * 128 in all; 0 = not recorded) after waiting for the stream. */
+/* Kernel-phase trace (option "trace" = 1): the most recent CTA-pair GEMM launch recorded the SM clock at 11 events,
+ * [event][slot] with 128 slots per event.  Events 0-5 are taken in the launch's first CTA, slot = k-block (the first 128):
+ * 0 loads issued, 1 conversion begins (first converter warp of the group, 3xTF32), 2 conversion published, 3 MMA thread at the
+ * k-block, 4 MMA thread has the operands, 5 MMAs and commits issued.  Events 6 / 7: a tile's output begins / its stores are
+ * issued (slot = tile, 3xTF32).  Events 8-10: events 0-2 in the pair's second CTA (another SM: its clock is a different
+ * counter, compare durations only).  Copies up to `capacity` samples (11 * 128 in all; 0 = not recorded) after waiting for
+ * the stream. */
 int gptb200_ctx_read_trace(gptb200_ctx *ctx, long long *samples, int capacity);
 /* Waits for the context's stream and reports a device-side timeout recorded by any earlier kernel. */
 int gptb200_ctx_synchronize(gptb200_ctx *ctx);

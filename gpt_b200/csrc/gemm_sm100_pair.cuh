@@ -172,6 +172,13 @@ __device__ __forceinline__ void convert_tile(uint32_t raw, uint32_t cor, const C
     }
 }
 
+// k-blocks per accumulator hand-off (3xTF32).  The first chunk of a tile is twice as long as the others: while the
+// epilogue warps write the previous tile's output (about 13 thousand cycles with GELU) they cannot drain the new tile's
+// chunks, and the MMA thread can run only two chunks ahead of them; with 8 + 4 k-blocks of head start it no longer
+// stalls at tile boundaries.  The truncation error of the accumulator grows with the square root of the chunk length,
+// one long chunk in six raises the total by about a seventh.
+__device__ __forceinline__ constexpr int pair_chunk_kb(bool first_of_tile) { return first_of_tile ? 2 * kChunkKB : kChunkKB; }
+
 // First k-block (on the line of all tiles' k-blocks) of pair q out of P.
 __device__ __forceinline__ long long pair_range_start(const GemmParams &p, long long q, long long P)
 {
@@ -422,7 +429,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 while (ok && work.next(tm2, tn, kb0, kb1)) {
                     int kb = kb0;
                     while (ok && kb < kb1) {
-                        const int kend = C::kChunked ? min(kb + kChunkKB, kb1) : kb1;
+                        const int kend = C::kChunked ? min(kb + pair_chunk_kb(kb == kb0), kb1) : kb1;
                         const uint32_t buf = g & 1u;
                         const uint32_t use = (g >> 1) & 1u;
                         if (!bounded_wait_cluster(tmem_empty_bar(buf), use ^ 1u, abort_flag, p.status, DEV_TIMEOUT_MMA_TMEM)) {
@@ -563,7 +570,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 float acc[128];
 #pragma unroll
                 for (int j = 0; j < 128; ++j) acc[j] = 0.0f;
-                for (int kb = kb0; ok && kb < kb1; kb += kChunkKB, ++g) {
+                for (int kb = kb0; ok && kb < kb1; kb += pair_chunk_kb(kb == kb0), ++g) {
                     const uint32_t buf = g & 1u;
                     const uint32_t use = (g >> 1) & 1u;
                     if (!bounded_wait_cluster(tmem_full_bar(buf), use, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE)) {

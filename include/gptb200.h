@@ -40,7 +40,7 @@ typedef enum gptb200_status {
 /* Precision of the tensor-core path.  Replaces cublasSetMathMode(CUBLAS_TF32_TENSOR_OP_MATH)
  * (src/backend/cuda/core/cuda_backend.cu:7). */
 typedef enum gptb200_mode {
-    GPTB200_MODE_3XTF32 = 0,  /* default: split operands, three MMAs per step, fp32-level accuracy */
+    GPTB200_MODE_3XTF32 = 0,  /* default: split operands (main term + two correction terms), fp32-level accuracy */
     GPTB200_MODE_TF32 = 1     /* single-pass TF32 */
 } gptb200_mode;
 

@@ -336,3 +336,46 @@ def test_bounded_wait_runs_out_and_is_reported(torch, built_library):
     ref = x.double() @ w.double()
     assert float((y.double() - ref).abs().max() / ref.abs().max()) <= 1e-5
     b.close()
+
+
+def test_kernel_phase_trace_and_cut_ranges_at_full_width(torch, built_library):
+    """The CTA-pair kernel with every pair's k-block range cut inside tiles (36 tiles of 64 k-blocks on 74 pairs: most tiles are
+    summed from three pairs' parts) gives the same result as with whole tiles, bit for bit on repeated runs; the kernel-phase
+    trace of the launch holds increasing clock samples in pipeline order."""
+    import gpt_b200
+    m, k, n = 1536, 2048, 1536
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(m, k, device="cuda", generator=g)
+    w = torch.randn(k, n, device="cuda", generator=g) * 0.02
+    bias = torch.randn(n, device="cuda", generator=g)
+    ref = x.double() @ w.double() + bias.double()
+    out = {}
+    for cut in (-1, 1):
+        b = gpt_b200.Backend(0)
+        b.set_option("pair", 1)
+        b.set_option("stream_k", cut)
+        b.set_option("trace", 1)
+        ys = []
+        for _ in range(2):
+            y = torch.full((m, n), float("nan"), device="cuda")
+            act = torch.full((m, n), float("nan"), device="cuda")
+            b.device_linear_activation_fused_forward(y, act, x, w, bias, True, 1, m, k, n)
+            b.synchronize()
+            ys.append((y, act))
+        assert torch.equal(ys[0][0], ys[1][0]) and torch.equal(ys[0][1], ys[1][1])       # no dependence on timing
+        assert float((ys[0][0].double() - ref).abs().max() / ref.abs().max()) <= 1e-5
+        gelu = torch.nn.functional.gelu(ref, approximate="tanh")
+        assert float((ys[0][1].double() - gelu).abs().max() / gelu.abs().max()) <= 1e-5
+        tr = np.array(b.read_trace(), dtype=np.int64)
+        assert tr.shape == (11, 128)
+        kb = 8                                                                             # every pair runs at least 8 k-blocks here
+        for event in (0, 1, 2, 4, 5):
+            assert (tr[event, :kb] > 0).all(), event
+        assert (np.diff(tr[5, :kb]) > 0).all()                                             # k-blocks are issued in order
+        assert (tr[0, :kb] < tr[1, :kb]).all() and (tr[1, :kb] < tr[2, :kb]).all()         # load -> conversion begins -> published
+        assert (tr[2, :kb] < tr[5, :kb]).all()                                             # ... -> MMAs issued
+        b.set_option("trace", 0)
+        out[cut] = ys[0][0]
+        b.close()
+    diff = float((out[1].double() - out[-1].double()).abs().max() / ref.abs().max())
+    assert diff <= 4e-6                                                                    # same sums, other grouping of the k range

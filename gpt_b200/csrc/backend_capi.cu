@@ -1,9 +1,12 @@
 // extern "C" entry points of the operators that are not on the linear-layer hot path (see backend_ops.cuh).
 #include <algorithm>
 #include <cmath>
+#include <cstdint>
+#include <initializer_list>
 
 #include "ctx_internal.h"
 #include "backend_ops.cuh"
+#include "attention_tiled.cuh"
 
 using namespace gptb200;
 
@@ -38,6 +41,46 @@ int attention_backward_t(gptb200_ctx *ctx, float *gqkv, float *dcache, const flo
     ops::attention_backward_dq_kernel<HD, TPR><<<grid, ops::kAttnRowsPerBlock * TPR, 0, ctx->stream>>>(gqkv, dcache, lse, gy, qkv, seq_len, d, heads);
     ops::attention_backward_dkv_kernel<HD, TPR><<<grid, ops::kAttnRowsPerBlock * TPR, 0, ctx->stream>>>(gqkv, dcache, lse, gy, qkv, seq_len, d, heads);
     return launched(ctx, 2);
+}
+
+bool aligned16_all(std::initializer_list<const void *> ptrs)
+{
+    for (const void *p : ptrs)
+        if (reinterpret_cast<uintptr_t>(p) & 15u) return false;
+    return true;
+}
+
+// Raises the dynamic shared-memory limit of a kernel once per context (the attribute is per device).
+template <typename Kernel>
+cudaError_t allow_smem(gptb200_ctx *ctx, Kernel kernel, int bytes)
+{
+    const void *key = reinterpret_cast<const void *>(kernel);
+    if (ctx->configured.count(key)) return cudaSuccess;
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) ctx->configured.insert(key);
+    return e;
+}
+
+// Head size 64 with 16-byte aligned tensors: the register-tiled kernels of attention_tiled.cuh.
+int attention64_forward(gptb200_ctx *ctx, float *y, float *lse, const float *qkv, int batch, int seq_len, int d, int heads)
+{
+    CUDA_TRY(ctx, allow_smem(ctx, ops::attention64_forward_kernel, ops::kFaForwardSmem));
+    dim3 grid((seq_len + ops::kFaBlock - 1) / ops::kFaBlock, heads, batch);
+    ops::attention64_forward_kernel<<<grid, ops::kFaThreads, ops::kFaForwardSmem, ctx->stream>>>(y, lse, qkv, seq_len, d, heads);
+    return launched(ctx);
+}
+
+int attention64_backward(gptb200_ctx *ctx, float *gqkv, float *dcache, const float *lse, const float *gy, const float *y, const float *qkv,
+                         int batch, int seq_len, int d, int heads)
+{
+    CUDA_TRY(ctx, allow_smem(ctx, ops::attention64_backward_dq_kernel, ops::kFaDqSmem));
+    CUDA_TRY(ctx, allow_smem(ctx, ops::attention64_backward_dkv_kernel, ops::kFaDkvSmem));
+    const long long rows = 1LL * batch * seq_len;
+    ops::attention64_rowsum_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, ctx->stream>>>(dcache, gy, y, rows, d, heads);
+    dim3 grid((seq_len + ops::kFaBlock - 1) / ops::kFaBlock, heads, batch);
+    ops::attention64_backward_dq_kernel<<<grid, ops::kFaThreads, ops::kFaDqSmem, ctx->stream>>>(gqkv, dcache, lse, gy, qkv, seq_len, d, heads);
+    ops::attention64_backward_dkv_kernel<<<grid, ops::kFaThreads, ops::kFaDkvSmem, ctx->stream>>>(gqkv, dcache, lse, gy, qkv, seq_len, d, heads);
+    return launched(ctx, 3);
 }
 
 }  // namespace
@@ -130,7 +173,9 @@ int gptb200_attention_forward(gptb200_ctx *ctx, float *y, float *logsumexp, cons
         case 8: return attention_forward_t<8, 1>(ctx, y, logsumexp, qkv, batch, seq_len, d, heads);
         case 16: return attention_forward_t<16, 1>(ctx, y, logsumexp, qkv, batch, seq_len, d, heads);
         case 32: return attention_forward_t<32, 1>(ctx, y, logsumexp, qkv, batch, seq_len, d, heads);
-        case 64: return attention_forward_t<64, 2>(ctx, y, logsumexp, qkv, batch, seq_len, d, heads);
+        case 64:
+            if (ctx->attention_tiled && d % 4 == 0 && aligned16_all({y, qkv})) return attention64_forward(ctx, y, logsumexp, qkv, batch, seq_len, d, heads);
+            return attention_forward_t<64, 2>(ctx, y, logsumexp, qkv, batch, seq_len, d, heads);
         case 128: return attention_forward_t<128, 4>(ctx, y, logsumexp, qkv, batch, seq_len, d, heads);
         default: return fail(ctx, GPTB200_ERR_INVALID_ARG, "attention: head size %d not in {8,16,32,64,128}", d / heads);
     }
@@ -142,6 +187,8 @@ int gptb200_attention_backward(gptb200_ctx *ctx, float *grad_qkv, float *d_cache
     NEED(ctx, batch >= 0 && seq_len >= 0 && d >= 0 && heads > 0 && d % heads == 0);
     if (1LL * batch * seq_len * d == 0) return GPTB200_OK;
     NEED(ctx, grad_qkv && d_cache && logsumexp && grad_y && y && qkv && batch <= 65535 && heads <= 65535);
+    if (d / heads == 64 && ctx->attention_tiled && d % 4 == 0 && aligned16_all({grad_qkv, grad_y, y, qkv}))
+        return attention64_backward(ctx, grad_qkv, d_cache, logsumexp, grad_y, y, qkv, batch, seq_len, d, heads);
     const long long rh = 1LL * batch * seq_len * heads;
     ops::attention_rowsum_kernel<<<static_cast<unsigned>((rh + 255) / 256), 256, 0, ctx->stream>>>(d_cache, grad_y, y, batch * seq_len, d, heads);
     ctx->launches++;

@@ -428,6 +428,10 @@ int gptb200_ctx_set_option(gptb200_ctx *ctx, const char *key, int value)
         ctx->pair = value;
         return GPTB200_OK;
     }
+    if (!strcmp(key, "attention_tiled")) {
+        ctx->attention_tiled = value != 0;
+        return GPTB200_OK;
+    }
     if (!strcmp(key, "trace")) {
         if (value && !ctx->d_trace) CUDA_TRY(ctx, cudaMalloc(&ctx->d_trace, sizeof(long long) * kTraceEvents * kTraceSlots));
         if (!value && ctx->d_trace) {

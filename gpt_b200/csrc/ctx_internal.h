@@ -24,6 +24,7 @@ struct gptb200_ctx {
     int max_splits = 0;  // 0 = automatic
     bool skinny = true;  // weight-streaming kernel for forward calls with m <= 16
     int debug = 0;       // timing experiments (see GemmParams::debug)
+    bool attention_tiled = true;  // head size 64: register-tiled attention kernels (false: the one-row-per-thread-group kernels)
     int pair = 0;        // CTA-pair (cta_group::2) kernel: 1 = always, 0 = heuristic, -1 = never
     int stream_k = 0;    // CTA-pair kernel, ranges cut inside tiles: 1 = always, 0 = heuristic, -1 = never
     long long *d_trace = nullptr;  // clock samples of the CTA-pair kernel (option "trace")

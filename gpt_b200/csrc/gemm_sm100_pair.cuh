@@ -177,7 +177,8 @@ __device__ __forceinline__ void convert_tile(uint32_t raw, uint32_t cor, const C
 // chunks, and the MMA thread can run only two chunks ahead of them; with 8 + 4 k-blocks of head start it no longer
 // stalls at tile boundaries.  The truncation error of the accumulator grows with the square root of the chunk length,
 // one long chunk in six raises the total by about a seventh.
-__device__ __forceinline__ constexpr int pair_chunk_kb(bool first_of_tile) { return first_of_tile ? 2 * kChunkKB : kChunkKB; }
+constexpr int kFirstChunkKB = 4;
+__device__ __forceinline__ constexpr int pair_chunk_kb(bool first_of_tile) { return first_of_tile ? kFirstChunkKB : kChunkKB; }
 
 // First k-block (on the line of all tiles' k-blocks) of pair q out of P.
 __device__ __forceinline__ long long pair_range_start(const GemmParams &p, long long q, long long P)

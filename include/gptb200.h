@@ -55,7 +55,8 @@ int gptb200_ctx_set_stream(gptb200_ctx *ctx, void *cuda_stream);
  * "stream_k" (CTA-pair kernel: give every pair the same number of k-blocks by letting a pair's range begin and end inside a
  * tile, partial tiles summed through scratch: 1 = always, 0 = when whole tiles would leave SMs idle, -1 = never),
  * "skinny" (weight-streaming kernel for forward calls with m <= 16: 1 = on (default), 0 = off),
- * "trace" (record a kernel-phase trace of each CTA-pair GEMM launch: 1 = on, 0 = off (default)). */
+ * "trace" (record a kernel-phase trace of each CTA-pair GEMM launch: 1 = on, 0 = off (default)),
+ * "attention_tiled" (attention with head size 64: register-tiled kernels, 1 = on (default), 0 = one row per thread group). */
 int gptb200_ctx_set_option(gptb200_ctx *ctx, const char *key, int value);
 /* Kernel-phase trace (option "trace" = 1): the most recent CTA-pair GEMM launch recorded the SM clock at 11 events,
  * [event][slot] with 128 slots per event.  Events 0-5 are taken in the launch's first CTA, slot = k-block (the first 128):

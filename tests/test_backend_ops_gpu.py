@@ -95,9 +95,11 @@ def test_layernorm(env, rows, d, with_residual):
     close("grad_beta", gb, gb_ref)
 
 
-@pytest.mark.parametrize("batch,seq,d,heads", [(1, 64, 32, 4), (2, 100, 128, 2), (2, 256, 768, 12), (1, 37, 64, 4)])
-def test_attention(env, batch, seq, d, heads):
+@pytest.mark.parametrize("tiled", [1, 0])
+@pytest.mark.parametrize("batch,seq,d,heads", [(1, 64, 32, 4), (2, 100, 128, 2), (2, 256, 768, 12), (1, 37, 64, 4), (3, 130, 192, 3), (1, 1, 64, 1)])
+def test_attention(env, batch, seq, d, heads, tiled):
     torch, be, lib, ref = env
+    be.set_option("attention_tiled", tiled)       # head size 64 has two sets of kernels
     rng = np.random.default_rng(3)
     qkv = rng.standard_normal((batch, seq, 3 * d), dtype=np.float32)
     y_ref, lse_ref = np.empty((batch, seq, d), np.float32), np.empty((batch, seq, heads), np.float32)

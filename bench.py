@@ -137,6 +137,8 @@ def run_ours(args):
     gb = torch.zeros(N, device=dev)
 
     comm = torch.cuda.Stream() if world > 1 else None
+    num_sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    sms_beside_nccl = max(2, num_sms - args.comm_sms) if args.comm_sms > 0 else 0
 
     def step(i):
         s = sets[i % NSETS]
@@ -152,7 +154,9 @@ def run_ours(args):
             comm.wait_event(ready)
             dist.all_reduce(gw, op=dist.ReduceOp.AVG)   # average: the accumulated gradient keeps its magnitude over many steps
             dist.all_reduce(gb, op=dist.ReduceOp.AVG)
+        be.set_option("max_sms", sms_beside_nccl)                # NCCL's CTAs need SMs of their own next to the persistent GEMM
         be.linear_backward_input(s["gx"], s["gy"], w, M, K, N)
+        be.set_option("max_sms", 0)
         stream.wait_stream(comm)
 
     def barrier():
@@ -617,6 +621,7 @@ def main():
                     help="ffn: BASELINE configs[1] (default); train: configs[3]; decode: configs[4] (linear layers of a decode step); generate: configs[4] end to end")
     ap.add_argument("--global-batch", type=int, default=64, help="sequences per step over all GPUs (train workload)")
     ap.add_argument("--m-per-gpu", type=int, default=M_PER_GPU, help="tokens per GPU (smaller for profiler captures)")
+    ap.add_argument("--comm-sms", type=int, default=16, help="SMs left to NCCL while a GEMM overlaps a collective (N > 1)")
     ap.add_argument("--profile", action="store_true", help="only the timed steps: no end-to-end, clock-load or CPU legs")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -338,6 +338,10 @@ class Model:
     def context(self) -> int:
         return int(self._lib.gptb200_model_context(self._m))
 
+    def set_option(self, key: str, value: int) -> None:
+        """Tuning option of the model's context (gptb200_ctx_set_option)."""
+        self._check(self._lib.gptb200_ctx_set_option(ctypes.c_void_p(self.context), key.encode(), value))
+
     @property
     def weights_ptr(self) -> int:
         return int(self._lib.gptb200_model_weights(self._m))

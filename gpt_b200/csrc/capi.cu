@@ -185,7 +185,7 @@ GemmPlanInput plan_input(const gptb200_ctx *ctx, const GemmCall &c)
     in.has_epilogue = c.bias != nullptr || c.act != nullptr;
     in.accumulate = c.accumulate;
     in.aligned = aligned16(c.a) && aligned16(c.b) && aligned16(c.out) && (!c.act || aligned16(c.act));
-    in.num_sms = ctx->num_sms;
+    in.num_sms = ctx->max_sms > 0 ? std::min(ctx->max_sms, ctx->num_sms) : ctx->num_sms;
     in.tf32 = ctx->mode == GPTB200_MODE_TF32;
     in.opt_tile_n = ctx->tile_n; in.opt_max_splits = ctx->max_splits; in.opt_pair = ctx->pair; in.opt_stream_k = ctx->stream_k; in.opt_skinny = ctx->skinny;
     in.ws_limit = ctx->ws_limit;
@@ -426,6 +426,11 @@ int gptb200_ctx_set_option(gptb200_ctx *ctx, const char *key, int value)
     if (!strcmp(key, "pair")) {
         if (value < -1 || value > 1) return fail(ctx, GPTB200_ERR_INVALID_ARG, "pair must be -1, 0 or 1");
         ctx->pair = value;
+        return GPTB200_OK;
+    }
+    if (!strcmp(key, "max_sms")) {
+        if (value < 0) return fail(ctx, GPTB200_ERR_INVALID_ARG, "max_sms must be >= 0");
+        ctx->max_sms = value;
         return GPTB200_OK;
     }
     if (!strcmp(key, "attention_tiled")) {

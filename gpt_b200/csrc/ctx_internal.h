@@ -20,6 +20,7 @@ struct gptb200_ctx {
     cudaStream_t stream = nullptr;
     int mode = GPTB200_MODE_3XTF32;
     int num_sms = 0;
+    int max_sms = 0;     // 0 = all; otherwise the GEMM planner uses at most this many SMs (leaves room for a concurrent collective)
     int tile_n = 0;      // 0 = automatic
     int max_splits = 0;  // 0 = automatic
     bool skinny = true;  // weight-streaming kernel for forward calls with m <= 16

@@ -55,6 +55,8 @@ int gptb200_ctx_set_stream(gptb200_ctx *ctx, void *cuda_stream);
  * "stream_k" (CTA-pair kernel: give every pair the same number of k-blocks by letting a pair's range begin and end inside a
  * tile, partial tiles summed through scratch: 1 = always, 0 = when whole tiles would leave SMs idle, -1 = never),
  * "skinny" (weight-streaming kernel for forward calls with m <= 16: 1 = on (default), 0 = off),
+ * "max_sms" (0 = all SMs; otherwise the GEMM kernels occupy at most this many, which leaves SMs to a collective that runs
+ * at the same time on another stream),
  * "trace" (record a kernel-phase trace of each CTA-pair GEMM launch: 1 = on, 0 = off (default)),
  * "attention_tiled" (attention with head size 64: register-tiled kernels, 1 = on (default), 0 = one row per thread group). */
 int gptb200_ctx_set_option(gptb200_ctx *ctx, const char *key, int value);

@@ -7,6 +7,7 @@
 #include "ctx_internal.h"
 #include "backend_ops.cuh"
 #include "attention_tiled.cuh"
+#include "layernorm_warp.cuh"
 
 using namespace gptb200;
 
@@ -69,6 +70,24 @@ int attention64_forward(gptb200_ctx *ctx, float *y, float *lse, const float *qkv
     ops::attention64_forward_kernel<<<grid, ops::kFaThreads, ops::kFaForwardSmem, ctx->stream>>>(y, lse, qkv, seq_len, d, heads);
     return launched(ctx);
 }
+
+template <int VEC>
+void layernorm_forward_warp(gptb200_ctx *ctx, float *y, float *means, float *vars, float *x, const float *residual, const float *gamma,
+                            const float *beta, int rows)
+{
+    const int blocks = (rows + ops::kLnWarpsPerBlock - 1) / ops::kLnWarpsPerBlock;
+    ops::layernorm_forward_warp_kernel<VEC><<<blocks, ops::kLnWarpsPerBlock * 32, 0, ctx->stream>>>(y, means, vars, x, residual, gamma, beta, rows);
+}
+
+template <int VEC>
+void layernorm_backward_warp(gptb200_ctx *ctx, int blocks, float *gx, float *wg, float *wb, const float *gy, const float *gres, const float *x,
+                             const float *means, const float *vars, const float *gamma, int rows)
+{
+    ops::layernorm_backward_warp_kernel<VEC><<<blocks, ops::kLnWarpsPerBlock * 32, 0, ctx->stream>>>(gx, wg, wb, gy, gres, x, means, vars, gamma, rows);
+}
+
+// Row lengths the one-warp-per-row LayerNorm kernels cover.
+bool layernorm_warp_ok(int d) { return d % 128 == 0 && d >= 128 && d <= 1024; }
 
 int attention64_backward(gptb200_ctx *ctx, float *gqkv, float *dcache, const float *lse, const float *gy, const float *y, const float *qkv,
                          int batch, int seq_len, int d, int heads)
@@ -137,6 +156,19 @@ int gptb200_layernorm_forward(gptb200_ctx *ctx, float *y, float *means, float *v
     NEED(ctx, rows >= 0 && d >= 0);
     if (rows == 0 || d == 0) return GPTB200_OK;
     NEED(ctx, y && means && vars && x && gamma && beta);
+    if (layernorm_warp_ok(d) && aligned16_all({y, x, residual, gamma, beta})) {
+        switch (d / 128) {
+            case 1: layernorm_forward_warp<1>(ctx, y, means, vars, x, residual, gamma, beta, rows); break;
+            case 2: layernorm_forward_warp<2>(ctx, y, means, vars, x, residual, gamma, beta, rows); break;
+            case 3: layernorm_forward_warp<3>(ctx, y, means, vars, x, residual, gamma, beta, rows); break;
+            case 4: layernorm_forward_warp<4>(ctx, y, means, vars, x, residual, gamma, beta, rows); break;
+            case 5: layernorm_forward_warp<5>(ctx, y, means, vars, x, residual, gamma, beta, rows); break;
+            case 6: layernorm_forward_warp<6>(ctx, y, means, vars, x, residual, gamma, beta, rows); break;
+            case 7: layernorm_forward_warp<7>(ctx, y, means, vars, x, residual, gamma, beta, rows); break;
+            default: layernorm_forward_warp<8>(ctx, y, means, vars, x, residual, gamma, beta, rows); break;
+        }
+        return launched(ctx);
+    }
     const int threads = std::min(1024, std::max(32, ((d + 31) / 32) * 32));
     ops::layernorm_forward_kernel<<<rows, threads, 0, ctx->stream>>>(y, means, vars, x, residual, gamma, beta, d);
     return launched(ctx);
@@ -149,6 +181,24 @@ int gptb200_layernorm_backward(gptb200_ctx *ctx, float *grad_x, float *grad_gamm
     NEED(ctx, rows >= 0 && d >= 0);
     if (rows == 0 || d == 0) return GPTB200_OK;
     NEED(ctx, grad_x && grad_gamma && grad_beta && grad_y && x && means && vars && gamma);
+    if (layernorm_warp_ok(d) && aligned16_all({grad_x, grad_y, grad_residual, x, gamma})) {
+        const int blocks = std::max(1, std::min((rows + ops::kLnWarpsPerBlock - 1) / ops::kLnWarpsPerBlock, ctx->num_sms * 4));
+        const int rc = ensure_workspace(ctx, size_t(2) * blocks * d * sizeof(float));
+        if (rc) return rc;
+        float *wg = ctx->ws, *wb = ctx->ws + size_t(blocks) * d;
+        switch (d / 128) {
+            case 1: layernorm_backward_warp<1>(ctx, blocks, grad_x, wg, wb, grad_y, grad_residual, x, means, vars, gamma, rows); break;
+            case 2: layernorm_backward_warp<2>(ctx, blocks, grad_x, wg, wb, grad_y, grad_residual, x, means, vars, gamma, rows); break;
+            case 3: layernorm_backward_warp<3>(ctx, blocks, grad_x, wg, wb, grad_y, grad_residual, x, means, vars, gamma, rows); break;
+            case 4: layernorm_backward_warp<4>(ctx, blocks, grad_x, wg, wb, grad_y, grad_residual, x, means, vars, gamma, rows); break;
+            case 5: layernorm_backward_warp<5>(ctx, blocks, grad_x, wg, wb, grad_y, grad_residual, x, means, vars, gamma, rows); break;
+            case 6: layernorm_backward_warp<6>(ctx, blocks, grad_x, wg, wb, grad_y, grad_residual, x, means, vars, gamma, rows); break;
+            case 7: layernorm_backward_warp<7>(ctx, blocks, grad_x, wg, wb, grad_y, grad_residual, x, means, vars, gamma, rows); break;
+            default: layernorm_backward_warp<8>(ctx, blocks, grad_x, wg, wb, grad_y, grad_residual, x, means, vars, gamma, rows); break;
+        }
+        ops::layernorm_backward_params_final_kernel<<<(d + 127) / 128, 128, 0, ctx->stream>>>(grad_gamma, grad_beta, wg, wb, d, blocks);
+        return launched(ctx, 2);
+    }
     const int threads = std::min(1024, std::max(32, ((d + 31) / 32) * 32));
     ops::layernorm_backward_dx_kernel<<<rows, threads, 0, ctx->stream>>>(grad_x, grad_y, grad_residual, x, means, vars, gamma, d);
     const int col_groups = (d + 31) / 32;
@@ -207,7 +257,12 @@ int gptb200_softmax_forward(gptb200_ctx *ctx, float *y, const float *x, int rows
     NEED(ctx, rows >= 0 && vocab >= 0 && vocab_padded >= vocab);
     if (rows == 0 || vocab_padded == 0) return GPTB200_OK;
     NEED(ctx, y && x);
-    ops::softmax_forward_kernel<<<rows, 1024, 0, ctx->stream>>>(y, x, vocab, vocab_padded);
+    if (vocab_padded % 4 == 0 && vocab_padded <= 512 * 4 * 25 && vocab_padded > 1024 * 4 * 4 && aligned16_all({y, x}))
+        ops::softmax_forward_rowreg_kernel<512, 25><<<rows, 512, 0, ctx->stream>>>(y, x, vocab, vocab_padded);
+    else if (vocab_padded % 4 == 0 && vocab_padded <= 1024 * 4 * 4 && aligned16_all({y, x}))
+        ops::softmax_forward_rowreg_kernel<1024, 4><<<rows, 1024, 0, ctx->stream>>>(y, x, vocab, vocab_padded);
+    else
+        ops::softmax_forward_kernel<<<rows, 1024, 0, ctx->stream>>>(y, x, vocab, vocab_padded);
     return launched(ctx);
 }
 
@@ -217,7 +272,10 @@ int gptb200_cross_entropy_softmax_backward(gptb200_ctx *ctx, float *grad_x, cons
     NEED(ctx, rows >= 0 && vocab >= 0 && vocab_padded >= vocab);
     if (rows == 0 || vocab == 0) return GPTB200_OK;
     NEED(ctx, grad_x && probs && labels);
-    ops::cross_entropy_softmax_backward_kernel<<<rows, 1024, 0, ctx->stream>>>(grad_x, probs, labels, rows, vocab, vocab_padded);
+    if (vocab_padded % 4 == 0 && aligned16_all({grad_x, probs}))
+        ops::cross_entropy_softmax_backward_vec_kernel<<<rows, 1024, 0, ctx->stream>>>(grad_x, probs, labels, rows, vocab, vocab_padded);
+    else
+        ops::cross_entropy_softmax_backward_kernel<<<rows, 1024, 0, ctx->stream>>>(grad_x, probs, labels, rows, vocab, vocab_padded);
     return launched(ctx);
 }
 

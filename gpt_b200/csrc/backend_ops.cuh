@@ -474,6 +474,50 @@ __global__ void softmax_forward_kernel(float *__restrict__ y, const float *__res
     for (int i = v + threadIdx.x; i < vp; i += blockDim.x) yr[i] = 0.0f;
 }
 
+// The same for rows of up to THREADS * 4 * NV floats whose pitch is a multiple of 4 (16-byte aligned rows): a thread keeps its
+// NV float4 of the row in registers, so the logits are read once and the probabilities written once.
+template <int THREADS, int NV>
+__global__ void __launch_bounds__(THREADS) softmax_forward_rowreg_kernel(float *__restrict__ y, const float *__restrict__ x, int v, int vp)
+{
+    __shared__ float red[32];
+    const size_t r = blockIdx.x;
+    const float4 *xr = reinterpret_cast<const float4 *>(x + r * vp);
+    float4 *yr = reinterpret_cast<float4 *>(y + r * vp);
+    const int nvec = vp >> 2;
+    float4 e[NV];
+    float m = -FLT_MAX;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int c = threadIdx.x + THREADS * k;
+        e[k] = make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
+        if (c < nvec) {
+            const float4 t = __ldg(xr + c);
+            const int i = 4 * c;
+            e[k].x = i < v ? t.x : -FLT_MAX;
+            e[k].y = i + 1 < v ? t.y : -FLT_MAX;
+            e[k].z = i + 2 < v ? t.z : -FLT_MAX;
+            e[k].w = i + 3 < v ? t.w : -FLT_MAX;
+        }
+        m = fmaxf(m, fmaxf(fmaxf(e[k].x, e[k].y), fmaxf(e[k].z, e[k].w)));
+    }
+    m = block_max(m, red);
+    float s = 0.0f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        e[k].x = e[k].x == -FLT_MAX ? 0.0f : expf(e[k].x - m);
+        e[k].y = e[k].y == -FLT_MAX ? 0.0f : expf(e[k].y - m);
+        e[k].z = e[k].z == -FLT_MAX ? 0.0f : expf(e[k].z - m);
+        e[k].w = e[k].w == -FLT_MAX ? 0.0f : expf(e[k].w - m);
+        s += (e[k].x + e[k].y) + (e[k].z + e[k].w);
+    }
+    s = block_sum(s, red);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int c = threadIdx.x + THREADS * k;
+        if (c < nvec) yr[c] = make_float4(e[k].x / s, e[k].y / s, e[k].z / s, e[k].w / s);   // masked and padding columns: 0 / s = 0
+    }
+}
+
 // grad_x[r, :V] = (p - onehot(label)) / rows; padding columns are left as they are   (cpu_backend.cpp:474-491)
 __global__ void cross_entropy_softmax_backward_kernel(float *__restrict__ grad_x, const float *__restrict__ probs,
                                                       const int *__restrict__ labels, int rows, int v, int vp)
@@ -482,6 +526,26 @@ __global__ void cross_entropy_softmax_backward_kernel(float *__restrict__ grad_x
     const int label = labels[r];
     const float inv = static_cast<float>(rows);
     for (int i = threadIdx.x; i < v; i += blockDim.x) grad_x[r * vp + i] = (probs[r * vp + i] - (i == label ? 1.0f : 0.0f)) / inv;
+}
+
+// The same with 16-byte accesses (row pitch a multiple of 4); the last vector of a row is written element by element so that
+// the padding columns stay untouched.
+__global__ void cross_entropy_softmax_backward_vec_kernel(float *__restrict__ grad_x, const float *__restrict__ probs,
+                                                          const int *__restrict__ labels, int rows, int v, int vp)
+{
+    const size_t r = blockIdx.x;
+    const int label = labels[r];
+    const float inv = static_cast<float>(rows);
+    const float4 *p = reinterpret_cast<const float4 *>(probs + r * vp);
+    float4 *g = reinterpret_cast<float4 *>(grad_x + r * vp);
+    const int full = v >> 2;
+    for (int c = threadIdx.x; c < full; c += blockDim.x) {
+        const float4 t = __ldg(p + c);
+        const int i = 4 * c;
+        g[c] = make_float4((t.x - (i == label ? 1.0f : 0.0f)) / inv, (t.y - (i + 1 == label ? 1.0f : 0.0f)) / inv,
+                           (t.z - (i + 2 == label ? 1.0f : 0.0f)) / inv, (t.w - (i + 3 == label ? 1.0f : 0.0f)) / inv);
+    }
+    for (int i = 4 * full + threadIdx.x; i < v; i += blockDim.x) grad_x[r * vp + i] = (probs[r * vp + i] - (i == label ? 1.0f : 0.0f)) / inv;
 }
 
 // loss = -(1/rows) sum_r log(p[r, label[r]] + 1e-8)   (cpu_backend.cpp:493-509).  Single block, fixed order per thread.

@@ -58,7 +58,8 @@ def test_embedding(env, batch, seq, d, vp):
     close("grad_wpe", gwpe, gwpe_ref)
 
 
-@pytest.mark.parametrize("rows,d,with_residual", [(64, 32, True), (200, 768, True), (33, 100, False)])
+@pytest.mark.parametrize("rows,d,with_residual", [(64, 32, True), (200, 768, True), (33, 100, False), (100, 128, False), (1000, 1024, True),
+                                                   (5, 768, True), (4100, 768, False), (64, 1152, True)])
 def test_layernorm(env, rows, d, with_residual):
     torch, be, lib, ref = env
     rng = np.random.default_rng(2)

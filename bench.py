@@ -123,6 +123,8 @@ def run_ours(args):
     mode = gpt_b200.MODE_TF32 if args.mode == "tf32" else gpt_b200.MODE_3XTF32
     stream = torch.cuda.current_stream()
     be = gpt_b200.Backend(local_rank, stream.cuda_stream, mode)
+    if args.max_sms:
+        be.set_option("max_sms", args.max_sms)
     M, K, N = args.m_per_gpu, K_IN, N_OUT
     flops_per_step = 6.0 * M * K * N
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
@@ -621,6 +623,7 @@ def main():
                     help="ffn: BASELINE configs[1] (default); train: configs[3]; decode: configs[4] (linear layers of a decode step); generate: configs[4] end to end")
     ap.add_argument("--global-batch", type=int, default=64, help="sequences per step over all GPUs (train workload)")
     ap.add_argument("--m-per-gpu", type=int, default=M_PER_GPU, help="tokens per GPU (smaller for profiler captures)")
+    ap.add_argument("--max-sms", type=int, default=0, help="SMs the GEMM kernels may occupy (0 = all; experiments)")
     ap.add_argument("--comm-sms", type=int, default=16, help="SMs left to NCCL while a GEMM overlaps a collective (N > 1)")
     ap.add_argument("--profile", action="store_true", help="only the timed steps: no end-to-end, clock-load or CPU legs")
     args = ap.parse_args()

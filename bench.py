@@ -256,7 +256,7 @@ def run_ours(args):
         x3 = mode == gpt_b200.MODE_3XTF32
         fwd = kern["forward_gemm_bias_gelu"]
         roof = dict(bound="tensor", achieved=fwd["tflops"], peak=peaks["tf32_tflops"], unit="TFLOP/s", frac=fwd["tflops"] / peaks["tf32_tflops"],
-                    traffic=256.7e6 if (M == M_PER_GPU and x3) else None,
+                    traffic=204.4e6 if (M == M_PER_GPU and x3) else None,
                     traffic_note="dram read+write bytes per launch from ncu (profiles/ffn_fc_step_M8192_launch_list.md); algorithmic 235.9e6",
                     kernel="gemm_tcgen05_pair_kernel<A=K-major, B=MN-major> (forward: x.w + bias, GELU)", peak_source=peaks["source"],
                     issued_tflops=fwd["tflops"] * (2 if x3 else 1),

@@ -182,7 +182,7 @@ int gptb200_layernorm_backward(gptb200_ctx *ctx, float *grad_x, float *grad_gamm
     if (rows == 0 || d == 0) return GPTB200_OK;
     NEED(ctx, grad_x && grad_gamma && grad_beta && grad_y && x && means && vars && gamma);
     if (layernorm_warp_ok(d) && aligned16_all({grad_x, grad_y, grad_residual, x, gamma})) {
-        const int blocks = std::max(1, std::min((rows + ops::kLnWarpsPerBlock - 1) / ops::kLnWarpsPerBlock, ctx->num_sms * 4));
+        const int blocks = std::max(1, std::min((rows + ops::kLnWarpsPerBlock - 1) / ops::kLnWarpsPerBlock, ctx->num_sms * 2));
         const int rc = ensure_workspace(ctx, size_t(2) * blocks * d * sizeof(float));
         if (rc) return rc;
         float *wg = ctx->ws, *wb = ctx->ws + size_t(blocks) * d;
@@ -196,7 +196,7 @@ int gptb200_layernorm_backward(gptb200_ctx *ctx, float *grad_x, float *grad_gamm
             case 7: layernorm_backward_warp<7>(ctx, blocks, grad_x, wg, wb, grad_y, grad_residual, x, means, vars, gamma, rows); break;
             default: layernorm_backward_warp<8>(ctx, blocks, grad_x, wg, wb, grad_y, grad_residual, x, means, vars, gamma, rows); break;
         }
-        ops::layernorm_backward_params_final_kernel<<<(d + 127) / 128, 128, 0, ctx->stream>>>(grad_gamma, grad_beta, wg, wb, d, blocks);
+        ops::layernorm_backward_params_final_kernel<<<(d + 31) / 32, dim3(32, 8), 0, ctx->stream>>>(grad_gamma, grad_beta, wg, wb, d, blocks);
         return launched(ctx, 2);
     }
     const int threads = std::min(1024, std::max(32, ((d + 31) / 32) * 32));
@@ -210,7 +210,7 @@ int gptb200_layernorm_backward(gptb200_ctx *ctx, float *grad_x, float *grad_gamm
     float *wg = ctx->ws, *wb = ctx->ws + size_t(chunks) * d;
     ops::layernorm_backward_params_partial_kernel<<<dim3(col_groups, chunks), dim3(32, 8), 0, ctx->stream>>>(wg, wb, grad_y, x, means, vars,
                                                                                                              rows, d, rows_per_chunk);
-    ops::layernorm_backward_params_final_kernel<<<(d + 127) / 128, 128, 0, ctx->stream>>>(grad_gamma, grad_beta, wg, wb, d, chunks);
+    ops::layernorm_backward_params_final_kernel<<<(d + 31) / 32, dim3(32, 8), 0, ctx->stream>>>(grad_gamma, grad_beta, wg, wb, d, chunks);
     return launched(ctx, 3);
 }
 

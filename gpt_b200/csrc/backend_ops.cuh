@@ -212,18 +212,32 @@ __global__ void layernorm_backward_params_partial_kernel(float *__restrict__ ws_
     }
 }
 
+// Stage 2: block (32, 8) covers 32 columns; the eight thread rows take every eighth partial row, then add up in a fixed order.
 __global__ void layernorm_backward_params_final_kernel(float *__restrict__ grad_gamma, float *__restrict__ grad_beta,
                                                        const float *__restrict__ ws_gamma, const float *__restrict__ ws_beta, int d, int chunks)
 {
-    const int col = blockIdx.x * blockDim.x + threadIdx.x;
-    if (col >= d) return;
+    __shared__ float rg[8][33], rb[8][33];
+    const int col = blockIdx.x * 32 + threadIdx.x;
     float sg = 0.0f, sb = 0.0f;
-    for (int c = 0; c < chunks; ++c) {
-        sg += ws_gamma[size_t(c) * d + col];
-        sb += ws_beta[size_t(c) * d + col];
+    if (col < d) {
+        for (int c = threadIdx.y; c < chunks; c += 8) {
+            sg += ws_gamma[size_t(c) * d + col];
+            sb += ws_beta[size_t(c) * d + col];
+        }
     }
-    grad_gamma[col] += sg;
-    grad_beta[col] += sb;
+    rg[threadIdx.y][threadIdx.x] = sg;
+    rb[threadIdx.y][threadIdx.x] = sb;
+    __syncthreads();
+    if (threadIdx.y == 0 && col < d) {
+        float tg = 0.0f, tb = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            tg += rg[i][threadIdx.x];
+            tb += rb[i][threadIdx.x];
+        }
+        grad_gamma[col] += tg;
+        grad_beta[col] += tb;
+    }
 }
 
 // ------------------------------------------------------------------------------------------------ attention

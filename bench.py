@@ -354,6 +354,29 @@ def run_train(args):
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
+    # where the step's time goes (rank 0's view, three steps): the same calls as dp.step with events in between
+    phase_names = ("zero_grad+forward", "backward", "wait_for_allreduce", "clip", "adamw")
+    phases = dict.fromkeys(phase_names, 0.0)
+    for _ in range(3):
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+        ev[0].record()
+        model.zero_grad()
+        model.forward(d_in)
+        ev[1].record()
+        model.backward(d_in, d_lbl, dp._on_layer_done)
+        dp._limit_sms(False)
+        ev[2].record()
+        if world > 1:
+            dp.compute_stream.wait_stream(dp.comm_stream)
+        ev[3].record()
+        model.unscale_and_clip_grads(1.0, 1)
+        ev[4].record()
+        model.optimizer_step(6e-4, 0.9, 0.95, 0.1)
+        ev[5].record()
+        torch.cuda.synchronize()
+        for i, name in enumerate(phase_names):
+            phases[name] += ev[i].elapsed_time(ev[i + 1]) / 3.0
+    barrier()
     n_e2e = max(2, min(args.steps, 5))
     loss = step(True)
     barrier()
@@ -384,7 +407,7 @@ def run_train(args):
                                  frac=lin_flops / world / (ms_step * 1e-3) / 1e12 / peaks["tf32_tflops"], traffic=None,
                                  note="linear-path algorithmic flops per GPU over the WHOLE step time (attention, LayerNorm, softmax, "
                                       "optimizer included in the time)", peak_source=peaks["source"]),
-                   gpu_launches=int(launches), collectives_per_step=dp.collectives // max(1, args.warmup + args.steps + n_e2e + 1),
+                   phases_ms=phases, gpu_launches=int(launches), collectives_per_step=dp.collectives // max(1, args.warmup + args.steps + n_e2e + 4),
                    e2e=dict(value=tokens / (e2e_s / n_e2e), unit="tokens/s", h2d_bytes_per_step=int(2 * B * T * 4), d2h_bytes_per_step=4,
                             ms_per_step=e2e_s / n_e2e * 1e3, loss=loss),
                    clocks=clocks)

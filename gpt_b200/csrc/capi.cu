@@ -240,8 +240,7 @@ int run_gemm(gptb200_ctx *ctx, const GemmCall &c)
             if (rc != GPTB200_OK) return rc;
             p.sk_slots = ctx->ws;
             p.sk_flags = ctx->d_pair_flags;
-            if (++ctx->pair_epoch == 0) ++ctx->pair_epoch;   // 0 is the value of a flag that was never written
-            p.sk_epoch = ctx->pair_epoch;
+            p.sk_state = ctx->d_pair_flags + size_t(ctx->num_sms) * 8;   // two words behind the flags
         }
     }
     if (splits > 1) {
@@ -375,7 +374,7 @@ int gptb200_ctx_create(gptb200_ctx **out, int device, void *cuda_stream, int mod
         return GPTB200_ERR_CUDA;
     }
     ctx->encode = reinterpret_cast<EncodeTiledFn>(fn);
-    const size_t flag_bytes = size_t(ctx->num_sms) * 8 * sizeof(unsigned int);   // [pair][CTA][epilogue warp]
+    const size_t flag_bytes = (size_t(ctx->num_sms) * 8 + 2) * sizeof(unsigned int);   // [pair][CTA][epilogue warp] + launch number, CTA count
     if (cudaMalloc(&ctx->d_status, sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_status, 0, sizeof(int)) != cudaSuccess ||
         cudaMalloc(&ctx->d_pair_flags, flag_bytes) != cudaSuccess || cudaMemset(ctx->d_pair_flags, 0, flag_bytes) != cudaSuccess) {
         if (ctx->d_status) cudaFree(ctx->d_status);

@@ -30,8 +30,8 @@ struct gptb200_ctx {
     int stream_k = 0;    // CTA-pair kernel, ranges cut inside tiles: 1 = always, 0 = heuristic, -1 = never
     long long *d_trace = nullptr;  // clock samples of the CTA-pair kernel (option "trace")
     int *d_status = nullptr;
-    unsigned int *d_pair_flags = nullptr;  // per CTA pair, CTA and epilogue warp: number of the launch whose partial tile is complete
-    unsigned int pair_epoch = 0;           // number of the latest CTA-pair launch that used the flags
+    unsigned int *d_pair_flags = nullptr;  // per CTA pair, CTA and epilogue warp: number of the launch whose partial tile is complete;
+                                           // then the number of completed launches and a CTA counter (both kept by the kernel)
     float *ws = nullptr;  // scratch: split-K partial tiles, partial rows of column reductions
     size_t ws_bytes = 0;
     size_t ws_limit = size_t(1) << 30;

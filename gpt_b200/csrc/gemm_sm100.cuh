@@ -70,8 +70,8 @@ struct GemmParams {
     long long sk_total;
     int sk_unit;
     float *sk_slots;         // one partial 256 x 256 tile per pair
-    unsigned int *sk_flags;  // one word per pair, CTA and epilogue warp: the launch number whose partial tile is complete
-    unsigned int sk_epoch;   // this launch's number
+    unsigned int *sk_flags;  // one word per pair, CTA and epilogue warp: the number of the launch whose partial tile is complete
+    unsigned int *sk_state;  // [0] number of completed launches that used the flags, [1] CTAs of this launch that have finished
     long long *trace;        // optional [kTraceEvents][kTraceSlots] clock64 samples of the first k-blocks of CTA 0
 };
 

@@ -512,6 +512,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         ring.count = 0;
         uint32_t g = 0, tile_count = 0;
         bool ok = true;
+        // This launch's number: kept in device memory and advanced by the launch's last CTA (see the teardown), so that it is
+        // right also when the launch is replayed from a CUDA graph with unchanged parameters.  0 never occurs as a number.
+        const unsigned int sk_epoch = p.sk_flags ? __ldcg(p.sk_state) + 1u : 0u;
         const uint32_t leader_tmem_empty[2] = {ptx::map_to_cta(tmem_empty_bar(0), 0u), ptx::map_to_cta(tmem_empty_bar(1), 0u)};
 
         // bias_lane: bias[col0 + lane], fetched when the tile was started
@@ -600,11 +603,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     for (int j = 0; j < 128; ++j) __stcg(slot + j * 32, acc[j]);
                     __threadfence();
                     __syncwarp();
-                    if (lane == 0) flag_release(flag_of(pair_id), p.sk_epoch);
+                    if (lane == 0) flag_release(flag_of(pair_id), sk_epoch);
                 } else if (ok) {
                     if (!complete) {
                         for (long long r = pair_id + 1; ok && r < num_pairs && pair_range_start(p, r, num_pairs) < tile_end; ++r) {
-                            ok = bounded_flag_wait(flag_of(r), p.sk_epoch, lane, abort_flag, p.status);
+                            ok = bounded_flag_wait(flag_of(r), sk_epoch, lane, abort_flag, p.status);
                             if (!ok) break;
                             const float *slot = slot_of(r);
 #pragma unroll
@@ -636,7 +639,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 long long r_end = pair_id + 1;   // pairs [pair_id + 1, r_end) hold the rest of this tile
                 if (owner && !complete) {
                     while (r_end < num_pairs && pair_range_start(p, r_end, num_pairs) < tile_end) ++r_end;
-                    for (long long r = pair_id + 1; ok && r < r_end; ++r) ok = bounded_flag_wait(flag_of(r), p.sk_epoch, lane, abort_flag, p.status);
+                    for (long long r = pair_id + 1; ok && r < r_end; ++r) ok = bounded_flag_wait(flag_of(r), sk_epoch, lane, abort_flag, p.status);
                 }
 #pragma unroll 1
                 for (int c = 0; c < C::kColsPerEpiWarp / 32; ++c) {
@@ -668,7 +671,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 if (ok && !owner) {
                     __threadfence();
                     __syncwarp();
-                    if (lane == 0) flag_release(flag_of(pair_id), p.sk_epoch);
+                    if (lane == 0) flag_release(flag_of(pair_id), sk_epoch);
                 }
             }
         }
@@ -692,6 +695,16 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     if (warp == 1) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+    }
+    if (threadIdx.x == 0 && p.sk_flags) {
+        // the last CTA to get here closes the launch: the next one (same stream, hence after this kernel) sees a new number
+        __threadfence();
+        if (atomicAdd(p.sk_state + 1, 1u) == gridDim.x - 1) {
+            p.sk_state[1] = 0u;
+            const unsigned int next = p.sk_state[0] + 1u;
+            p.sk_state[0] = next == 0xFFFFFFFFu ? 0u : next;   // the number used is state + 1: skip the wrap to 0
+            __threadfence();
+        }
     }
 }
 

@@ -379,3 +379,35 @@ def test_kernel_phase_trace_and_cut_ranges_at_full_width(torch, built_library):
         b.close()
     diff = float((out[1].double() - out[-1].double()).abs().max() / ref.abs().max())
     assert diff <= 4e-6                                                                    # same sums, other grouping of the k range
+
+
+def test_cut_ranges_replayed_from_a_cuda_graph(torch, built_library):
+    """A GEMM whose tiles are summed from several CTA pairs' parts numbers its launches in device memory, so a launch captured
+    in a CUDA graph and replayed with unchanged parameters still pairs partial tiles with the right launch."""
+    import gpt_b200
+    m, k, n = 1024, 4096, 1024
+    g = torch.Generator(device="cuda").manual_seed(6)
+    w = torch.randn(k, n, device="cuda", generator=g) * 0.02
+    bias = torch.zeros(n, device="cuda")
+    x = torch.randn(m, k, device="cuda", generator=g)
+    y = torch.empty(m, n, device="cuda")
+    side = torch.cuda.Stream()
+    b = gpt_b200.Backend(0, side.cuda_stream)
+    b.set_option("pair", 1)
+    b.set_option("stream_k", 1)
+    with torch.cuda.stream(side):
+        b.device_linear_activation_fused_forward(y, None, x, w, bias, False, 1, m, k, n)    # warm-up: scratch is allocated here
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            b.device_linear_activation_fused_forward(y, None, x, w, bias, False, 1, m, k, n)
+    for _ in range(3):
+        x.normal_(generator=g)
+        y.fill_(float("nan"))
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        ref = x.double() @ w.double()
+        assert float((y.double() - ref).abs().max() / ref.abs().max()) <= 1e-5
+    b.synchronize()
+    b.close()

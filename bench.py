@@ -135,10 +135,10 @@ def run_ours(args):
                          y=torch.empty(M, N, device=dev), act=torch.empty(M, N, device=dev), gx=torch.empty(M, K, device=dev)))
     w = torch.randn(K, N, device=dev, generator=torch.Generator(device=dev).manual_seed(7)) * 0.02
     b = torch.randn(N, device=dev, generator=torch.Generator(device=dev).manual_seed(8)) * 0.02
-    gw = torch.zeros(K, N, device=dev)
-    gb = torch.zeros(N, device=dev)
+    grads = torch.zeros(K * N + N, device=dev)          # weight and bias gradients side by side: one collective per step
+    gw, gb = grads[:K * N].view(K, N), grads[K * N:]
 
-    comm = torch.cuda.Stream() if world > 1 else None
+    comm = torch.cuda.Stream(priority=-1) if world > 1 else None   # NCCL's CTAs go before pending compute CTAs
     num_sms = torch.cuda.get_device_properties(dev).multi_processor_count
     sms_beside_nccl = max(2, num_sms - args.comm_sms) if args.comm_sms > 0 else 0
 
@@ -154,8 +154,7 @@ def run_ours(args):
         ready.record(stream)
         with torch.cuda.stream(comm):
             comm.wait_event(ready)
-            dist.all_reduce(gw, op=dist.ReduceOp.AVG)   # average: the accumulated gradient keeps its magnitude over many steps
-            dist.all_reduce(gb, op=dist.ReduceOp.AVG)
+            dist.all_reduce(grads, op=dist.ReduceOp.AVG)   # average: the accumulated gradient keeps its magnitude over many steps
         be.set_option("max_sms", sms_beside_nccl)                # NCCL's CTAs need SMs of their own next to the persistent GEMM
         be.linear_backward_input(s["gx"], s["gy"], w, M, K, N)
         be.set_option("max_sms", 0)

@@ -77,7 +77,8 @@ class DataParallelStep:
         self.world = world_size
         self.buckets = GradientBuckets(model.config, model.param_offsets, model.num_params, layers_per_group)
         self.compute_stream = torch.cuda.current_stream()
-        self.comm_stream = torch.cuda.Stream() if world_size > 1 else None
+        # high priority: the collective's CTAs are placed before the pending CTAs of the compute kernels
+        self.comm_stream = torch.cuda.Stream(priority=-1) if world_size > 1 else None
         self._all_reduce = all_reduce or (lambda t: dist.all_reduce(t, op=dist.ReduceOp.AVG))
         self.collectives = 0
         # While collectives are in flight the persistent GEMM kernels leave `comm_sms` SMs free: NCCL's CTAs otherwise wait for

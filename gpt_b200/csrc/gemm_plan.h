@@ -128,7 +128,7 @@ inline GemmPlan plan_gemm(const GemmPlanInput &in)
         // Cutting ranges inside tiles costs two more (partial) tile epilogues per pair.  In 3xTF32 mode the epilogue warps have
         // time to spare; in TF32 mode with GELU they are nearly as busy as the tensor pipe, so whole tiles win until a
         // fifth of the pairs would idle.
-        const double enough = in.tf32 ? 0.80 : 0.97;
+        const double enough = in.tf32 ? 0.97 : 0.97;
         if (in.opt_stream_k < 0 || (in.opt_stream_k == 0 && whole_eff >= enough)) {
             p.sk_unit = p.num_kb;   // whole tiles, as evenly as they go
             pairs = whole_pairs;

@@ -186,7 +186,6 @@ GemmPlanInput plan_input(const gptb200_ctx *ctx, const GemmCall &c)
     in.accumulate = c.accumulate;
     in.aligned = aligned16(c.a) && aligned16(c.b) && aligned16(c.out) && (!c.act || aligned16(c.act));
     in.num_sms = ctx->max_sms > 0 ? std::min(ctx->max_sms, ctx->num_sms) : ctx->num_sms;
-    in.tf32 = ctx->mode == GPTB200_MODE_TF32;
     in.opt_tile_n = ctx->tile_n; in.opt_max_splits = ctx->max_splits; in.opt_pair = ctx->pair; in.opt_stream_k = ctx->stream_k; in.opt_skinny = ctx->skinny;
     in.ws_limit = ctx->ws_limit;
     return in;

@@ -28,7 +28,6 @@ struct GemmPlanInput {
     int opt_pair;            // 1 always, 0 heuristic, -1 never
     int opt_stream_k;        // CTA-pair kernel: 1 always cut ranges inside tiles, 0 heuristic, -1 whole tiles only
     bool opt_skinny;
-    bool tf32;               // single-pass TF32 mode (default: 3xTF32)
     size_t ws_limit;         // scratch limit in bytes
 };
 
@@ -125,11 +124,8 @@ inline GemmPlan plan_gemm(const GemmPlanInput &in)
         const long long rounds = (pair_tiles + whole_pairs - 1) / whole_pairs;
         const double whole_eff = double(pair_tiles) / double(rounds * pairs_busy);   // share of the usable pairs kept busy by whole tiles
         long long pairs;
-        // Cutting ranges inside tiles costs two more (partial) tile epilogues per pair.  In 3xTF32 mode the epilogue warps have
-        // time to spare; in TF32 mode with GELU they are nearly as busy as the tensor pipe, so whole tiles win until a
-        // fifth of the pairs would idle.
-        const double enough = in.tf32 ? 0.97 : 0.97;
-        if (in.opt_stream_k < 0 || (in.opt_stream_k == 0 && whole_eff >= enough)) {
+        // Whole tiles per pair only when they keep at least 97 % of the usable pairs busy.
+        if (in.opt_stream_k < 0 || (in.opt_stream_k == 0 && whole_eff >= 0.97)) {
             p.sk_unit = p.num_kb;   // whole tiles, as evenly as they go
             pairs = whole_pairs;
             p.sk_max_share = 1;

@@ -148,16 +148,17 @@ def run_ours(args):
         if world == 1:
             be.device_linear_backward(s["gx"], gw, gb, s["gy"], s["x"], w, 1, M, K, N)
             return
-        # data parallel: weight gradients first, their all-reduce runs on a second stream while grad_x is computed
+        # data parallel: weight gradients first; their all-reduce runs on a second stream while grad_x is computed.  grad_x is
+        # launched before the collective is enqueued so that the GPU has work while the host is inside NCCL.
         be.linear_backward_weights(gw, gb, s["gy"], s["x"], M, K, N)
         ready = torch.cuda.Event()
         ready.record(stream)
-        with torch.cuda.stream(comm):
-            comm.wait_event(ready)
-            dist.all_reduce(grads, op=dist.ReduceOp.AVG)   # average: the accumulated gradient keeps its magnitude over many steps
         be.set_option("max_sms", sms_beside_nccl)                # NCCL's CTAs need SMs of their own next to the persistent GEMM
         be.linear_backward_input(s["gx"], s["gy"], w, M, K, N)
         be.set_option("max_sms", 0)
+        with torch.cuda.stream(comm):
+            comm.wait_event(ready)
+            dist.all_reduce(grads, op=dist.ReduceOp.AVG)   # average: the accumulated gradient keeps its magnitude over many steps
         stream.wait_stream(comm)
 
     def barrier():

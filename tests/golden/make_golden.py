@@ -1,4 +1,4 @@
-"""Regenerates the committed golden fixtures.  Needs the reference tree (REF, default /root/reference) and
+"""Regenerates the committed golden fixtures.  Needs the reference tree (environment variable REF) and
 oracle/_ref/libref_cpu.so (make -C oracle).  Run from the repository root:
 
     python tests/golden/make_golden.py

@@ -140,7 +140,8 @@ def run_ours(args):
 
     comm = torch.cuda.Stream(priority=-1) if world > 1 else None   # NCCL's CTAs go before pending compute CTAs
     num_sms = torch.cuda.get_device_properties(dev).multi_processor_count
-    sms_beside_nccl = max(2, num_sms - args.comm_sms) if args.comm_sms > 0 else 0
+    comm_sms = args.comm_sms if args.comm_sms >= 0 else (16 if world <= 2 else 32)
+    sms_beside_nccl = max(2, num_sms - comm_sms) if comm_sms > 0 else 0
 
     def step(i):
         s = sets[i % NSETS]
@@ -215,28 +216,49 @@ def run_ours(args):
     h2d = (hx.numel() + hgy.numel()) * 4
     d2h = (hact.numel() + hgx.numel() + hgw.numel() + hgb.numel()) * 4
 
-    def e2e_step():
-        be.device_memcpy_h2d(s0["x"].data_ptr(), hx.data_ptr(), hx.numel() * 4)
-        be.device_memcpy_h2d(s0["gy"].data_ptr(), hgy.data_ptr(), hgy.numel() * 4)
-        be.device_linear_activation_fused_forward(s0["y"], s0["act"], s0["x"], w, b, True, 1, M, K, N)
-        be.device_linear_backward(s0["gx"], gw, gb, s0["gy"], s0["x"], w, 1, M, K, N)
-        if world > 1:
-            dist.all_reduce(gw, op=dist.ReduceOp.AVG)
-            dist.all_reduce(gb, op=dist.ReduceOp.AVG)
-            torch.cuda.current_stream().synchronize()
-        be.device_memcpy_d2h(hact.data_ptr(), s0["act"].data_ptr(), hact.numel() * 4)
-        be.device_memcpy_d2h(hgx.data_ptr(), s0["gx"].data_ptr(), hgx.numel() * 4)
-        be.device_memcpy_d2h(hgw.data_ptr(), gw.data_ptr(), hgw.numel() * 4)
-        be.device_memcpy_d2h(hgb.data_ptr(), gb.data_ptr(), hgb.numel() * 4)
+    # Pipelined over three streams (copy-in, compute, copy-out) and two device buffer sets, the way a host program that
+    # wants throughput drives the C ABI: step i's inputs arrive while step i-1 computes and step i-2's results leave, so the
+    # two directions of the host link work at the same time.  Every step's copies are inside the timed region.
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    snaps = [(torch.empty_like(gw), torch.empty_like(gb)) for _ in range(2)]
+    ev_out = [None, None]
 
-    e2e_steps = 0 if args.profile else max(3, min(args.steps, 10))
-    for _ in range(0 if args.profile else 2):
-        e2e_step()
+    def e2e_step(i):
+        st = sets[i % 2]
+        with torch.cuda.stream(s_in):
+            if ev_out[i % 2] is not None:
+                s_in.wait_event(ev_out[i % 2])         # this set's previous results have left (which implies its compute is done)
+            st["x"].copy_(hx, non_blocking=True)
+            st["gy"].copy_(hgy, non_blocking=True)
+            ev_in = torch.cuda.Event()
+            ev_in.record(s_in)
+        stream.wait_event(ev_in)                       # also orders this step after the copy-out of step i - 2 (same buffers)
+        gw_snap, gb_snap = snaps[i % 2]
+        be.device_linear_activation_fused_forward(st["y"], st["act"], st["x"], w, b, True, 1, M, K, N)
+        be.device_linear_backward(st["gx"], gw, gb, st["gy"], st["x"], w, 1, M, K, N)
+        if world > 1:
+            dist.all_reduce(grads, op=dist.ReduceOp.AVG)
+        gw_snap.copy_(gw, non_blocking=True)           # grad_w / grad_b keep accumulating: the host gets this step's state
+        gb_snap.copy_(gb, non_blocking=True)
+        ev_comp = torch.cuda.Event()
+        ev_comp.record(stream)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_comp)
+            hact.copy_(st["act"], non_blocking=True)
+            hgx.copy_(st["gx"], non_blocking=True)
+            hgw.copy_(gw_snap, non_blocking=True)
+            hgb.copy_(gb_snap, non_blocking=True)
+            ev_out[i % 2] = torch.cuda.Event()
+            ev_out[i % 2].record(s_out)
+
+    e2e_steps = 0 if args.profile else max(4, min(args.steps, 10))
+    for i in range(0 if args.profile else 2):
+        e2e_step(i)
     barrier()
     t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_step()
-    barrier()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    barrier()                                          # torch.cuda.synchronize(): all three streams have drained
     e2e_s = time.perf_counter() - t0
     if world > 1:
         t = torch.tensor([e2e_s], device=dev)
@@ -647,7 +669,8 @@ def main():
     ap.add_argument("--global-batch", type=int, default=64, help="sequences per step over all GPUs (train workload)")
     ap.add_argument("--m-per-gpu", type=int, default=M_PER_GPU, help="tokens per GPU (smaller for profiler captures)")
     ap.add_argument("--max-sms", type=int, default=0, help="SMs the GEMM kernels may occupy (0 = all; experiments)")
-    ap.add_argument("--comm-sms", type=int, default=16, help="SMs left to NCCL while a GEMM overlaps a collective (N > 1)")
+    ap.add_argument("--comm-sms", type=int, default=-1,
+                    help="SMs left to NCCL while a GEMM overlaps a collective (N > 1); -1: 16 at two GPUs, 32 beyond (measured best)")
     ap.add_argument("--profile", action="store_true", help="only the timed steps: no end-to-end, clock-load or CPU legs")
     args = ap.parse_args()
     if args.impl == "reference":

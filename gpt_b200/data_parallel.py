@@ -67,7 +67,7 @@ class DataParallelStep:
     """
 
     def __init__(self, model, grad_tensor, world_size: int, layers_per_group: int = 3, all_reduce: Callable | None = None,
-                 comm_sms: int = 16):
+                 comm_sms: int | None = None):
         import torch
         import torch.distributed as dist
         self.torch = torch
@@ -84,6 +84,8 @@ class DataParallelStep:
         # While collectives are in flight the persistent GEMM kernels leave `comm_sms` SMs free: NCCL's CTAs otherwise wait for
         # a GEMM CTA to finish, and the GEMM's equal k-block ranges assume that all of its CTAs run at once (measured on the
         # FFN step at 2 GPUs: 0.55 ms per step with all SMs claimed, 0.50 ms with 16 left free, 0.48 ms without any collective).
+        if comm_sms is None:
+            comm_sms = 16 if world_size <= 2 else 32   # NCCL uses more channels with more ranks (measured: FFN step at 2 and 8 GPUs)
         self.comm_sms = comm_sms if world_size > 1 else 0
         self._sms_limited = False
 

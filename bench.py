@@ -15,7 +15,8 @@ timed region, as in a data-parallel training step.
 
 `value` is timed with CUDA events on the launching stream, inputs resident in HBM, max over ranks.  `e2e` is
 the same step through the C ABI starting from pinned HOST buffers: x and the upstream gradient are copied to
-the device, and act / grad_x / grad_w / grad_b are copied back, inside the timed region.
+the device, and act / grad_x / grad_w / grad_b are copied back, inside the timed region; consecutive steps are
+pipelined over a copy-in, a compute and a copy-out stream with two buffer sets.
 
 --impl reference times the reference's own CPU implementation (unmodified sources, oracle/_ref) of the same
 step on the host, on a bounded row sample per step (its cost is exactly linear in M).

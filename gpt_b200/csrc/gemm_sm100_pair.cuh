@@ -238,6 +238,7 @@ __device__ __forceinline__ bool bounded_flag_wait(const unsigned int *flag, unsi
         }
     }
     ok = __shfl_sync(0xffffffffu, ok, 0);
+    __syncwarp();   // orders the other lanes' loads of the partial tile behind lane 0's acquire
     return ok != 0;
 }
 

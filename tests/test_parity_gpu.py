@@ -280,12 +280,14 @@ def test_run_to_run_bitwise_repeatability(be, torch):
         assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
 
 
-def test_full_size_ffn_properties(be, torch):
-    """BASELINE config 1 at M = 8192 (x [8192 x 768], w [768 x 3072]): size-independent properties on the GPU
-    output, with an fp64 torch matmul on sampled rows as the yardstick (the oracle is covered at smaller m)."""
+@pytest.mark.parametrize("m", [8192, 32768])
+def test_full_size_ffn_properties(be, torch, m):
+    """BASELINE config 1 at M = 8192 and at its largest M = 32768 (x [M x 768], w [768 x 3072]): size-independent
+    properties on the GPU output, with an fp64 torch matmul on sampled rows as the yardstick (the oracle is covered at
+    smaller m)."""
     t = torch
     g = t.Generator(device="cuda").manual_seed(1)
-    m, k, n = 8192, 768, 3072
+    k, n = 768, 3072
     x = t.randn(m, k, device="cuda", generator=g)
     w = t.randn(k, n, device="cuda", generator=g) * 0.02
     b = t.randn(n, device="cuda", generator=g) * 0.02
@@ -315,6 +317,36 @@ def test_full_size_ffn_properties(be, torch):
     assert float((gw[:, cols].double() - refw).abs().max() / refw.abs().max()) <= tol
     refx = gy[rows].double() @ w.double().t()
     assert float((gx[rows].double() - refx).abs().max() / refx.abs().max()) <= tol
+
+
+def test_full_size_lm_head_properties(be, torch):
+    """BASELINE config 2 (x [8192 x 768], wte [50304 x 768], 50257 real rows): logits, grad_x (a 50304-term reduction) and
+    grad_wte against fp64 on sampled rows / columns; padding rows of wte give zero logits and receive zero gradient."""
+    t = torch
+    g = t.Generator(device="cuda").manual_seed(2)
+    m, d, vp, v = 8192, 768, 50304, 50257
+    x = t.randn(m, d, device="cuda", generator=g)
+    wte = t.randn(vp, d, device="cuda", generator=g) * 0.02
+    wte[v:] = 0.0
+    logits = t.empty(m, vp, device="cuda")
+    be.device_unembedding_forward(logits, x, wte, 1, m, d, vp)
+    be.synchronize()
+    tol = TOL[be.mode]
+    rows = t.arange(0, m, 257, device="cuda")
+    ref = x[rows].double() @ wte.double().t()
+    assert float((logits[rows].double() - ref).abs().max() / ref.abs().max()) <= tol
+    assert bool((logits[:, v:] == 0).all())
+    gy = t.randn(m, vp, device="cuda", generator=g) / m
+    gy[:, v:] = 0.0                                       # as the cross-entropy backward leaves the padding columns
+    gx, gw = t.empty(m, d, device="cuda"), t.zeros(vp, d, device="cuda")
+    be.device_unembedding_backward(gx, gw, gy, x, wte, 1, m, d, vp)
+    be.synchronize()
+    refx = gy[rows].double() @ wte.double()
+    assert float((gx[rows].double() - refx).abs().max() / refx.abs().max()) <= tol
+    vrows = t.arange(0, vp, 499, device="cuda")
+    refw = gy[:, vrows].double().t() @ x.double()
+    assert float((gw[vrows].double() - refw).abs().max() / refw.abs().max()) <= tol
+    assert bool((gw[v:] == 0).all())
 
 
 def test_bounded_wait_runs_out_and_is_reported(torch, built_library):

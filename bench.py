@@ -454,6 +454,9 @@ def run_decode(args):
     L, D, F, Vp = cfg["num_layers"], cfg["d_model"], cfg["d_ffn"], cfg["vocab_size_padded"]
     mode = gpt_b200.MODE_TF32 if args.mode == "tf32" else gpt_b200.MODE_3XTF32
     be = gpt_b200.Backend(0, torch.cuda.current_stream().cuda_stream, mode)
+    for kv in args.ctx_option:
+        key, _, val = kv.partition("=")
+        be.set_option(key, int(val))
     g = torch.Generator(device=dev).manual_seed(5)
     W = dict(qkv=[torch.randn(D, 3 * D, device=dev, generator=g) * 0.02 for _ in range(L)],
              proj=[torch.randn(D, D, device=dev, generator=g) * 0.02 for _ in range(L)],
@@ -467,7 +470,7 @@ def run_decode(args):
     sampler = ClockSampler(0)
     t_begin = time.time()
     launches = 0
-    for batch in (1, 8, 64):
+    for batch in [int(b) for b in args.decode_batches.split(",")]:
         x = torch.randn(batch, D, device=dev, generator=g)
         q, a, u, ua, dn, lg = (torch.empty(batch, n, device=dev) for n in (3 * D, D, F, F, D, Vp))
 
@@ -507,11 +510,11 @@ def run_decode(args):
                                          hbm_frac=weight_bytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"])
     be.synchronize()
     clocks = sampler.stop(t_begin, time.time())
-    r8 = results["batch8"]
+    r8 = results.get("batch8") or next(iter(results.values()))
     out = dict(metric="decode_linear_weight_stream_gbs", value=r8["gbs"], unit="GB/s", n_gpus=1, steps=args.steps, warmup=args.warmup,
                ms_per_step=r8["ms_per_step"], higher_is_better=True, scaling="weak", vs_baseline=None,
                dtype="f32" if True else "tf32", data="synthetic", impl="ours",
-               config=dict(workload="GPT-2 124M decode step, linear layers only (49 GEMMs with m = batch)", mode=args.mode,
+               config=dict(workload="GPT-2 124M decode step, linear layers only (49 GEMMs with m = batch)", mode=args.mode, options=args.ctx_option,
                            weight_bytes=weight_bytes, l2="494 MB of weights per step exceed the 126 MB L2"),
                per_batch=results,
                roofline=dict(bound="hbm", achieved=r8["gbs"], peak=peaks["hbm_gbs"], unit="GB/s", frac=r8["hbm_frac"], traffic=None,
@@ -672,6 +675,9 @@ def main():
     ap.add_argument("--max-sms", type=int, default=0, help="SMs the GEMM kernels may occupy (0 = all; experiments)")
     ap.add_argument("--comm-sms", type=int, default=-1,
                     help="SMs left to NCCL while a GEMM overlaps a collective (N > 1); -1: 16 at two GPUs, 32 beyond (measured best)")
+    ap.add_argument("--decode-batches", default="1,8,64", help="decode workload: batch sizes (the JSON value is the batch-8 figure)")
+    ap.add_argument("--ctx-option", action="append", default=[], metavar="KEY=VALUE",
+                    help="gptb200_ctx_set_option before the run (decode workload; experiments)")
     ap.add_argument("--profile", action="store_true", help="only the timed steps: no end-to-end, clock-load or CPU legs")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -143,32 +143,85 @@ int make_out_tmap(gptb200_ctx *ctx, CUtensorMap *map, float *base, long long dep
 }
 
 template <bool W_KN>
-int launch_skinny(gptb200_ctx *ctx, int mr, dim3 grid, float *partial, const GemmCall &c, int k_per_split)
+int launch_skinny(gptb200_ctx *ctx, int mr, dim3 grid, float *partial, const GemmCall &c, int k_per_split, unsigned int *tickets)
 {
     switch (mr) {
-        case 1: skinny_gemm_kernel<1, W_KN><<<grid, kSkinnyThreads, 0, ctx->stream>>>(partial, c.a, c.b, c.M, c.N, c.K, k_per_split); break;
-        case 2: skinny_gemm_kernel<2, W_KN><<<grid, kSkinnyThreads, 0, ctx->stream>>>(partial, c.a, c.b, c.M, c.N, c.K, k_per_split); break;
-        case 4: skinny_gemm_kernel<4, W_KN><<<grid, kSkinnyThreads, 0, ctx->stream>>>(partial, c.a, c.b, c.M, c.N, c.K, k_per_split); break;
-        case 8: skinny_gemm_kernel<8, W_KN><<<grid, kSkinnyThreads, 0, ctx->stream>>>(partial, c.a, c.b, c.M, c.N, c.K, k_per_split); break;
-        default: skinny_gemm_kernel<16, W_KN><<<grid, kSkinnyThreads, 0, ctx->stream>>>(partial, c.a, c.b, c.M, c.N, c.K, k_per_split); break;
+        case 1: skinny_gemm_kernel<1, W_KN><<<grid, kSkinnyThreads, 0, ctx->stream>>>(partial, c.a, c.b, c.M, c.N, c.K, k_per_split, c.out, c.act, c.bias, tickets); break;
+        case 2: skinny_gemm_kernel<2, W_KN><<<grid, kSkinnyThreads, 0, ctx->stream>>>(partial, c.a, c.b, c.M, c.N, c.K, k_per_split, c.out, c.act, c.bias, tickets); break;
+        case 4: skinny_gemm_kernel<4, W_KN><<<grid, kSkinnyThreads, 0, ctx->stream>>>(partial, c.a, c.b, c.M, c.N, c.K, k_per_split, c.out, c.act, c.bias, tickets); break;
+        case 8: skinny_gemm_kernel<8, W_KN><<<grid, kSkinnyThreads, 0, ctx->stream>>>(partial, c.a, c.b, c.M, c.N, c.K, k_per_split, c.out, c.act, c.bias, tickets); break;
+        default: skinny_gemm_kernel<16, W_KN><<<grid, kSkinnyThreads, 0, ctx->stream>>>(partial, c.a, c.b, c.M, c.N, c.K, k_per_split, c.out, c.act, c.bias, tickets); break;
     }
     ctx->launches++;
     CUDA_TRY(ctx, cudaGetLastError());
     return GPTB200_OK;
 }
 
-// Decode-shaped forward GEMMs (m <= 16, x K-major): stream the weights once, split k over CTAs, finish in a
-// second small kernel.  HBM-bound: 4*k*n bytes per call.
+// One-launch cluster kernel for decode-shaped linear layers with W stored [k][n] (see decode_gemm_cluster_kernel).
+template <int MR>
+int launch_decode_cluster(gptb200_ctx *ctx, const GemmCall &c, int cluster, int groups)
+{
+    auto kernel = decode_gemm_cluster_kernel<MR>;
+    if (cluster > 8) {
+        const void *key = reinterpret_cast<const void *>(kernel);
+        if (!ctx->configured.count(key)) {
+            CUDA_TRY(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+            ctx->configured.insert(key);
+        }
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((c.N + 127) / 128, cluster, groups);
+    cfg.blockDim = dim3(kDecodeThreads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = cluster;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CUDA_TRY(ctx, cudaLaunchKernelEx(&cfg, kernel, c.out, c.act, c.a, c.b, c.bias, c.M, c.N, c.K));
+    ctx->launches++;
+    return GPTB200_OK;
+}
+
+// Decode-shaped forward GEMMs (m <= 64, x K-major): stream the weights once, split k over CTAs; the partial sums are added
+// by the last CTA of each column block (one launch) or, when splits * rows is large, by a second small kernel.
+// HBM-bound: 4*k*n bytes per call.
 int run_skinny(gptb200_ctx *ctx, const GemmCall &c, const GemmPlan &pl)
 {
     int mr = 1;
-    while (mr < c.M) mr *= 2;
+    while (mr < c.M && mr < 16) mr *= 2;
+    const int groups = (c.M + mr - 1) / mr;   // row groups of 16 beyond 16 rows
     const bool w_kn = c.b_mn;  // W stored [k][n]
+    if (w_kn && ctx->skinny_cluster > 0 && c.M <= ctx->skinny_cluster_rows) {
+        // largest cluster (power of two, at most the option) that leaves every warp at least four k-rows and does not
+        // put more than ~four CTAs on each SM; the non-portable size 16 only for layers so narrow that clusters of eight
+        // would occupy less than half of the SMs (n = 768: 48 CTAs)
+        int cluster = 1;
+        const long long blocks = 1LL * ((c.N + 127) / 128) * groups;
+        while (cluster * 2 <= std::min(ctx->skinny_cluster, 8) && c.K / (cluster * 2 * 8) >= 4 && blocks * cluster * 2 <= 4LL * ctx->num_sms) cluster *= 2;
+        if (cluster == 8 && ctx->skinny_cluster >= 16 && c.K / (16 * 8) >= 4 && (blocks * 16 <= ctx->num_sms || ctx->skinny_cluster >= 32)) cluster = 16;
+        switch (mr) {
+            case 1: return launch_decode_cluster<1>(ctx, c, cluster, groups);
+            case 2: return launch_decode_cluster<2>(ctx, c, cluster, groups);
+            case 4: return launch_decode_cluster<4>(ctx, c, cluster, groups);
+            case 8: return launch_decode_cluster<8>(ctx, c, cluster, groups);
+            default: return launch_decode_cluster<16>(ctx, c, cluster, groups);
+        }
+    }
     const int rc = ensure_workspace(ctx, pl.workspace_bytes);
     if (rc != GPTB200_OK) return rc;
-    const dim3 grid(pl.tiles_n, pl.splits);
-    const int rc2 = w_kn ? launch_skinny<true>(ctx, mr, grid, ctx->ws, c, pl.kb_per_split) : launch_skinny<false>(ctx, mr, grid, ctx->ws, c, pl.kb_per_split);
-    if (rc2 != GPTB200_OK) return rc2;
+    const dim3 grid(pl.tiles_n, pl.splits, groups);
+    // The last CTA adds the splits one dependent L2 load after the other: measured slower than a second launch beyond a few splits
+    // (48 splits: 14 us against 7.6 + launch).
+    const bool fused = pl.tiles_n * groups <= kSkinnyMaxTickets &&
+                       (ctx->skinny_fused > 0 || (ctx->skinny_fused == 0 && pl.splits <= 2));
+    unsigned int *tickets = fused ? ctx->d_pair_flags + size_t(ctx->num_sms) * 8 + 2 : nullptr;   // behind the pair kernel's words
+    const int rc2 = w_kn ? launch_skinny<true>(ctx, mr, grid, ctx->ws, c, pl.kb_per_split, tickets)
+                         : launch_skinny<false>(ctx, mr, grid, ctx->ws, c, pl.kb_per_split, tickets);
+    if (rc2 != GPTB200_OK || fused) return rc2;
     const long long total = 1LL * c.M * c.N;
     skinny_finish_kernel<<<static_cast<int>(std::min<long long>((total + 255) / 256, 1LL * ctx->num_sms * 4)), 256, 0, ctx->stream>>>(
         c.out, c.act, ctx->ws, c.bias, c.M, c.N, pl.splits);
@@ -186,7 +239,7 @@ GemmPlanInput plan_input(const gptb200_ctx *ctx, const GemmCall &c)
     in.accumulate = c.accumulate;
     in.aligned = aligned16(c.a) && aligned16(c.b) && aligned16(c.out) && (!c.act || aligned16(c.act));
     in.num_sms = ctx->max_sms > 0 ? std::min(ctx->max_sms, ctx->num_sms) : ctx->num_sms;
-    in.opt_tile_n = ctx->tile_n; in.opt_max_splits = ctx->max_splits; in.opt_pair = ctx->pair; in.opt_stream_k = ctx->stream_k; in.opt_skinny = ctx->skinny;
+    in.opt_tile_n = ctx->tile_n; in.opt_max_splits = ctx->max_splits; in.opt_pair = ctx->pair; in.opt_stream_k = ctx->stream_k; in.opt_skinny = ctx->skinny; in.opt_skinny_rows = ctx->skinny_rows;
     in.ws_limit = ctx->ws_limit;
     return in;
 }
@@ -373,7 +426,8 @@ int gptb200_ctx_create(gptb200_ctx **out, int device, void *cuda_stream, int mod
         return GPTB200_ERR_CUDA;
     }
     ctx->encode = reinterpret_cast<EncodeTiledFn>(fn);
-    const size_t flag_bytes = (size_t(ctx->num_sms) * 8 + 2) * sizeof(unsigned int);   // [pair][CTA][epilogue warp] + launch number, CTA count
+    // [pair][CTA][epilogue warp] + launch number, CTA count; then one ticket per column block of the decode kernel
+    const size_t flag_bytes = (size_t(ctx->num_sms) * 8 + 2 + kSkinnyMaxTickets) * sizeof(unsigned int);
     if (cudaMalloc(&ctx->d_status, sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_status, 0, sizeof(int)) != cudaSuccess ||
         cudaMalloc(&ctx->d_pair_flags, flag_bytes) != cudaSuccess || cudaMemset(ctx->d_pair_flags, 0, flag_bytes) != cudaSuccess) {
         if (ctx->d_status) cudaFree(ctx->d_status);
@@ -451,6 +505,27 @@ int gptb200_ctx_set_option(gptb200_ctx *ctx, const char *key, int value)
     }
     if (!strcmp(key, "skinny")) {
         ctx->skinny = value != 0;
+        return GPTB200_OK;
+    }
+    if (!strcmp(key, "skinny_rows")) {
+        if (value < 0 || value > kPlanSkinnyMaxRows) return fail(ctx, GPTB200_ERR_INVALID_ARG, "skinny_rows must be in [0, %d]", kPlanSkinnyMaxRows);
+        ctx->skinny_rows = value;
+        return GPTB200_OK;
+    }
+    if (!strcmp(key, "skinny_cluster_rows")) {
+        if (value < 0 || value > kPlanSkinnyMaxRows) return fail(ctx, GPTB200_ERR_INVALID_ARG, "skinny_cluster_rows must be in [0, %d]", kPlanSkinnyMaxRows);
+        ctx->skinny_cluster_rows = value;
+        return GPTB200_OK;
+    }
+    if (!strcmp(key, "skinny_cluster")) {
+        if (value != 0 && value != 1 && value != 2 && value != 4 && value != 8 && value != 16 && value != 32)
+            return fail(ctx, GPTB200_ERR_INVALID_ARG, "skinny_cluster must be 0, 1, 2, 4, 8, 16 or 32");
+        ctx->skinny_cluster = value;
+        return GPTB200_OK;
+    }
+    if (!strcmp(key, "skinny_fused")) {
+        if (value < -1 || value > 1) return fail(ctx, GPTB200_ERR_INVALID_ARG, "skinny_fused must be -1, 0 or 1");
+        ctx->skinny_fused = value;
         return GPTB200_OK;
     }
     if (!strcmp(key, "debug")) {

@@ -23,7 +23,12 @@ struct gptb200_ctx {
     int max_sms = 0;     // 0 = all; otherwise the GEMM planner uses at most this many SMs (leaves room for a concurrent collective)
     int tile_n = 0;      // 0 = automatic
     int max_splits = 0;  // 0 = automatic
-    bool skinny = true;  // weight-streaming kernel for forward calls with m <= 16
+    bool skinny = true;  // weight-streaming kernel for decode-shaped calls (x K-major, no accumulation)
+    int skinny_rows = 0; // most rows it takes: 0 = the planner's limit (64)
+    int skinny_cluster = 16; // W stored [k][n]: one-launch kernel that splits k over a thread-block cluster of up to this many CTAs
+                             // (0 = off; 16 = sixteen for narrow layers only; 32 = sixteen wherever k allows)
+    int skinny_cluster_rows = 16;  // ... for calls with at most this many rows (beyond: the k-split kernel, measured faster at 64 rows)
+    int skinny_fused = 0;  // that kernel adds its partial sums itself (one launch): 1 = always, 0 = with at most two splits, -1 = never
     int debug = 0;       // timing experiments (see GemmParams::debug)
     bool attention_tiled = true;  // head size 64: register-tiled attention kernels (false: the one-row-per-thread-group kernels)
     int pair = 0;        // CTA-pair (cta_group::2) kernel: 1 = always, 0 = heuristic, -1 = never
@@ -31,7 +36,8 @@ struct gptb200_ctx {
     long long *d_trace = nullptr;  // clock samples of the CTA-pair kernel (option "trace")
     int *d_status = nullptr;
     unsigned int *d_pair_flags = nullptr;  // per CTA pair, CTA and epilogue warp: number of the launch whose partial tile is complete;
-                                           // then the number of completed launches and a CTA counter (both kept by the kernel)
+                                           // then the number of completed launches and a CTA counter (both kept by the kernel);
+                                           // then the decode kernel's tickets (one per column block, zero between launches)
     float *ws = nullptr;  // scratch: split-K partial tiles, partial rows of column reductions
     size_t ws_bytes = 0;
     size_t ws_limit = size_t(1) << 30;

@@ -12,7 +12,7 @@ enum GemmKernelKind : int {
     KERNEL_NONE = 0,    // empty output: nothing to launch
     KERNEL_PAIR = 1,    // gemm_tcgen05_pair_kernel: CTA pairs, 256 x 256 tiles
     KERNEL_SINGLE = 2,  // gemm_tcgen05_kernel: one CTA per 128 x tile_n tile
-    KERNEL_SKINNY = 3,  // skinny_gemm_kernel: weight streaming for m <= 16
+    KERNEL_SKINNY = 3,  // skinny_gemm_kernel: weight streaming for m <= 64 (option: fewer)
     KERNEL_SIMT = 4,    // simt_gemm_kernel: shapes TMA cannot address
 };
 
@@ -28,6 +28,7 @@ struct GemmPlanInput {
     int opt_pair;            // 1 always, 0 heuristic, -1 never
     int opt_stream_k;        // CTA-pair kernel: 1 always cut ranges inside tiles, 0 heuristic, -1 whole tiles only
     bool opt_skinny;
+    int opt_skinny_rows;     // most rows the weight-streaming kernel takes; 0 = kPlanSkinnyMaxRows
     size_t ws_limit;         // scratch limit in bytes
 };
 
@@ -49,6 +50,7 @@ constexpr size_t kPairSlotBytes = 256 * 256 * sizeof(float);
 
 constexpr int kPlanBM = 128;
 constexpr int kPlanBK = 32;
+constexpr int kPlanSkinnyMaxRows = 64;   // beyond this the fp32 FMAs of the weight-streaming kernel cost more than a tensor-core tile
 
 // `units`: number of CTAs (or CTA pairs) that run concurrently
 inline int plan_splits(const GemmPlanInput &in, long long tiles, int num_kb, bool allowed, size_t bytes_per_split, int units)
@@ -77,15 +79,22 @@ inline GemmPlan plan_gemm(const GemmPlanInput &in)
     GemmPlan p{};
     if (in.M <= 0 || in.N <= 0) return p;
     const bool fours = in.K % 4 == 0 && in.N % 4 == 0;
-    if (in.opt_skinny && in.M <= 16 && !in.a_mn && !in.accumulate && in.K >= 32 && fours && in.aligned) {
+    // beyond 16 rows only for weight matrices of model size (small ones are launch-bound on any kernel)
+    const int skinny_rows = in.opt_skinny_rows > 0 ? std::min(in.opt_skinny_rows, kPlanSkinnyMaxRows) : kPlanSkinnyMaxRows;
+    if (in.opt_skinny && in.M <= skinny_rows && (in.M <= 16 || 1LL * in.K * in.N >= 512 * 512) && !in.a_mn && !in.accumulate && in.K >= 32 && fours && in.aligned) {
         p.kernel = KERNEL_SKINNY;
         const int cols_per_block = 128 * (in.b_mn ? 4 : 1);
         p.tiles_n = (in.N + cols_per_block - 1) / cols_per_block;
-        p.tiles_m = 1;
-        int splits = std::max(1, std::min((in.num_sms * 4 + p.tiles_n - 1) / p.tiles_n, in.K / 32));
+        p.tiles_m = (in.M + 15) / 16;   // row groups of up to 16 rows (blockIdx.z)
+        // Enough CTAs for four per SM (two beyond 16 rows, where registers allow three and the partial sums are no longer
+        // small against the weights), each with at least 32 k-rows (16 for up to four rows of x, where the partial sums are
+        // tiny: a short weight matrix then still puts ~200 CTAs' loads in flight).
+        const int blocks = p.tiles_n * p.tiles_m;
+        const int want = in.num_sms * (in.M > 16 ? 2 : 4);
+        int splits = std::max(1, std::min((want + blocks - 1) / blocks, in.K / (in.M <= 4 ? 16 : 32)));
         p.kb_per_split = (((in.K + splits - 1) / splits) + 3) & ~3;   // here: k ELEMENTS per split, a multiple of 4
         p.splits = (in.K + p.kb_per_split - 1) / p.kb_per_split;
-        p.grid = p.tiles_n * p.splits;
+        p.grid = blocks * p.splits;
         p.workspace_bytes = size_t(p.splits) * in.M * in.N * sizeof(float);
         return p;
     }

@@ -1,17 +1,25 @@
-// Weight-streaming GEMM for decode-shaped calls (m <= 16 rows): y[m x n] = x[m x k] . W (+ bias, GELU).
+// Weight-streaming GEMM for decode-shaped calls (m <= 64 rows): y[m x n] = x[m x k] . W (+ bias, GELU).
 //
 // With so few rows the operation is bound by reading the weight matrix once from HBM (4*k*n bytes; the
 // activations and outputs are negligible), so the kernel is organised around the weight stream, not around
 // tensor-core tiles: every thread owns output columns, keeps one fp32 accumulator per row and column in
 // registers, reads its part of the weight matrix exactly once with 16-byte loads and takes the activations from
-// a shared-memory copy (broadcast reads).  The k range is split over blockIdx.y so that even a 768-column layer
-// puts several hundred CTAs in flight; partial sums go to scratch and a second tiny kernel adds them in a fixed
-// order and applies bias / GELU.  Plain fp32 FMAs: no TF32 rounding in either precision mode.
+// a shared-memory copy (broadcast reads).  A CTA covers up to 16 rows; with more rows blockIdx.z selects the group of
+// 16 (the groups of a column block run at about the same time, so the weights still come from HBM once and from L2 for
+// the other groups; at 64 rows the fp32 FMAs, not the weight stream, set the time).  The k range is split over blockIdx.y so that even a 768-column layer
+// puts several hundred CTAs in flight; partial sums go to scratch and are added in a fixed order (split ascending),
+// then bias / GELU are applied.  Who adds them: with `tickets` the CTA that finishes a column block last (one
+// atomic ticket per column block, reset by that CTA, so the array stays zero between launches and under CUDA-graph
+// replay) - one launch per GEMM, which matters because a decode step is ~50 GEMMs of a few microseconds each;
+// without `tickets` the separate skinny_finish_kernel, used when splits * rows is large enough that one CTA
+// re-reading all partial sums would take longer than a second launch.  Both give the same bits.
+// Plain fp32 FMAs: no TF32 rounding in either precision mode.
 //
 //   W_KN = true : W stored [k][n] (linear layers):   thread = 4 adjacent columns, coalesced 16-byte loads along n
 //   W_KN = false: W stored [n][k] (tied un-embedding): thread = 1 column, 16-byte loads along its own row
 #pragma once
 
+#include <cooperative_groups.h>
 #include <cuda_runtime.h>
 
 #include "gemm_sm100.cuh"  // gelu_tanh
@@ -19,15 +27,21 @@
 namespace gptb200 {
 
 constexpr int kSkinnyThreads = 128;
+constexpr int kSkinnyMaxTickets = 1024;  // column blocks per launch that can finish in the kernel itself
 constexpr int kSkinnyKChunk = 256;  // activations staged per pass: MR * 256 floats of shared memory
 
 template <int MR, bool W_KN>
 __global__ void __launch_bounds__(kSkinnyThreads)
-skinny_gemm_kernel(float *__restrict__ partial, const float *__restrict__ x, const float *__restrict__ w, int M, int N, int K, int k_per_split)
+skinny_gemm_kernel(float *__restrict__ partial, const float *__restrict__ x, const float *__restrict__ w, int M, int N, int K, int k_per_split,
+                   float *__restrict__ y, float *__restrict__ act, const float *__restrict__ bias, unsigned int *__restrict__ tickets)
 {
     __shared__ __align__(16) float xs[MR][kSkinnyKChunk];
+    __shared__ int is_last;
     constexpr int CPT = W_KN ? 4 : 1;  // columns per thread
     const int col = (blockIdx.x * kSkinnyThreads + threadIdx.x) * CPT;
+    const int row0 = blockIdx.z * MR;       // first row of this CTA's group
+    const int rows = min(MR, M - row0);     // >= 1
+    x += size_t(row0) * K;
     const int k_begin = blockIdx.y * k_per_split;
     const int k_end = min(K, k_begin + k_per_split);
     const bool col_ok = col < N;  // N is a multiple of 4 on this path
@@ -43,7 +57,7 @@ skinny_gemm_kernel(float *__restrict__ partial, const float *__restrict__ x, con
         for (int i = threadIdx.x; i < MR * (kSkinnyKChunk / 4); i += kSkinnyThreads) {
             const int m = i / (kSkinnyKChunk / 4), q = i % (kSkinnyKChunk / 4);
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (m < M && 4 * q < kc) v = *reinterpret_cast<const float4 *>(x + size_t(m) * K + k0 + 4 * q);
+            if (m < rows && 4 * q < kc) v = *reinterpret_cast<const float4 *>(x + size_t(m) * K + k0 + 4 * q);
             *reinterpret_cast<float4 *>(&xs[m][4 * q]) = v;
         }
         __syncthreads();
@@ -78,16 +92,156 @@ skinny_gemm_kernel(float *__restrict__ partial, const float *__restrict__ x, con
             }
         }
     }
-    if (!col_ok) return;
-    float *out = partial + size_t(blockIdx.y) * M * N;
+    if (col_ok) {
+        float *out = partial + (size_t(blockIdx.y) * M + row0) * N;
+#pragma unroll
+        for (int m = 0; m < MR; ++m) {
+            if (m >= rows) break;
+            if (W_KN)
+                *reinterpret_cast<float4 *>(out + size_t(m) * N + col) = make_float4(acc[m][0], acc[m][1], acc[m][2], acc[m][3]);
+            else
+                out[size_t(m) * N + col] = acc[m][0];
+        }
+    }
+    if (!tickets) return;  // skinny_finish_kernel follows
+
+    // The last CTA of this column block to get here adds the partial sums of all splits.
+    __threadfence();  // this thread's partial sums are visible device-wide before the ticket is taken
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned int *ticket = tickets + blockIdx.z * gridDim.x + blockIdx.x;
+        const unsigned int t = atomicAdd(ticket, 1u);
+        is_last = (t == gridDim.y - 1);
+        if (is_last) *ticket = 0;  // every CTA of this launch has taken its ticket: ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last || !col_ok) return;
+    __threadfence();
+    const int splits = gridDim.y;
+    const size_t per_split = size_t(M) * N;
 #pragma unroll
     for (int m = 0; m < MR; ++m) {
-        if (m >= M) break;
-        if (W_KN)
-            *reinterpret_cast<float4 *>(out + size_t(m) * N + col) = make_float4(acc[m][0], acc[m][1], acc[m][2], acc[m][3]);
-        else
-            out[size_t(m) * N + col] = acc[m][0];
+        if (m >= rows) break;
+        const float *p0 = partial + size_t(row0 + m) * N + col;
+        float s[CPT];
+        if (W_KN) {
+            float4 v = __ldcg(reinterpret_cast<const float4 *>(p0));  // L2: other SMs wrote these
+            for (int p = 1; p < splits; ++p) {
+                const float4 u = __ldcg(reinterpret_cast<const float4 *>(p0 + p * per_split));
+                v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
+            }
+            s[0] = v.x; s[1 % CPT] = v.y; s[2 % CPT] = v.z; s[3 % CPT] = v.w;
+        } else {
+            float v = __ldcg(p0);
+            for (int p = 1; p < splits; ++p) v += __ldcg(p0 + p * per_split);
+            s[0] = v;
+        }
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+            if (bias) s[c] += bias[col + c];
+            y[size_t(row0 + m) * N + col + c] = s[c];
+            if (act) act[size_t(row0 + m) * N + col + c] = gelu_tanh(s[c]);
+        }
     }
+}
+
+// Decode-shaped linear layer with W stored [k][n], in ONE launch and without scratch: the k range is split 8 x S ways - over
+// the eight warps of a CTA and over the S CTAs of a thread-block cluster (cluster shape (1, S, 1)) - and the partial sums
+// meet in shared memory: first the eight warps of a CTA (fixed order), then the S CTAs of the cluster through distributed
+// shared memory (rank order; every CTA finishes 1/S of the block's outputs, adds the bias and applies GELU).  A warp reads
+// 512 contiguous bytes of a weight row per load; a CTA covers 128 columns.  With K = 768 and S = 8 a warp reads 12 rows, all
+// of its loads are in flight at once, and the layer is one dependent DRAM round trip plus two barrier rounds long - the
+// k-split kernel above needs a second pass over partial sums in global memory (a second launch, or a serial tail in the
+// last CTA) that costs more than the weight stream itself on these few-microsecond layers.
+//   grid (ceil(n / 128), S, ceil(m / MR)); x rows beyond the group are clamped (their sums are computed and dropped).
+constexpr int kDecodeThreads = 256;
+
+template <int MR>
+__global__ void __launch_bounds__(kDecodeThreads)
+decode_gemm_cluster_kernel(float *__restrict__ y, float *__restrict__ act, const float *__restrict__ x, const float *__restrict__ w,
+                           const float *__restrict__ bias, int M, int N, int K)
+{
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    constexpr int RH = MR < 8 ? MR : 8;                  // rows per in-CTA reduction pass
+    __shared__ __align__(16) float red[8][RH][128];      // per warp: partial sums of RH rows x 128 columns
+    __shared__ __align__(16) float cta_sum[MR * 128];    // this CTA's sums, read by the whole cluster
+    const int S = gridDim.y;
+    const int rank = blockIdx.y;                         // cluster shape (1, S, 1): the rank inside the cluster
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int col = blockIdx.x * 128 + lane * 4;
+    const bool col_ok = col < N;                         // n is a multiple of 4 on this path
+    const int row0 = blockIdx.z * MR;
+    const int rows = min(MR, M - row0);
+    x += size_t(row0) * K;
+    const int ks = (((K + S * 8 - 1) / (S * 8)) + 3) & ~3;     // k-rows per warp, a multiple of 4 (so is k)
+    const int k_begin = min(K, (rank * 8 + warp) * ks), k_end = min(K, k_begin + ks);
+
+    float acc[MR][4];
+#pragma unroll
+    for (int m = 0; m < MR; ++m)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[m][c] = 0.0f;
+    // Weight loads in flight per thread: the loop is one DRAM round trip per unrolled body (measured: 0.85 us per body with
+    // eight loads, whatever n), so with few rows of x the registers go to loads: 16 k-rows per body up to two rows of x.
+    constexpr int kUnroll = MR <= 2 ? 4 : MR <= 4 ? 3 : MR <= 8 ? 2 : 1;
+    if (col_ok) {
+        const float *wp = w + col;
+        for (int k = k_begin; k < k_end; k += 4 * kUnroll) {
+            float4 wv[4 * kUnroll];   // all loads of the body are issued before the first use
+#pragma unroll
+            for (int i = 0; i < 4 * kUnroll; ++i)
+                wv[i] = k + i < k_end ? __ldcs(reinterpret_cast<const float4 *>(wp + size_t(k + i) * N)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int g = 0; g < kUnroll; ++g) {
+                if (k + 4 * g >= k_end) break;   // warp-uniform
+                const float4 w0 = wv[4 * g], w1 = wv[4 * g + 1], w2 = wv[4 * g + 2], w3 = wv[4 * g + 3];
+#pragma unroll
+                for (int m = 0; m < MR; ++m) {
+                    const float4 xv = __ldg(reinterpret_cast<const float4 *>(x + size_t(min(m, rows - 1)) * K + k + 4 * g));   // warp-uniform
+                    acc[m][0] += xv.x * w0.x + xv.y * w1.x + xv.z * w2.x + xv.w * w3.x;
+                    acc[m][1] += xv.x * w0.y + xv.y * w1.y + xv.z * w2.y + xv.w * w3.y;
+                    acc[m][2] += xv.x * w0.z + xv.y * w1.z + xv.z * w2.z + xv.w * w3.z;
+                    acc[m][3] += xv.x * w0.w + xv.y * w1.w + xv.z * w2.w + xv.w * w3.w;
+                }
+            }
+        }
+    }
+    // the eight warps of this CTA, warp order
+#pragma unroll
+    for (int h = 0; h < MR; h += RH) {
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < RH; ++j)
+            *reinterpret_cast<float4 *>(&red[warp][j][lane * 4]) = make_float4(acc[h + j][0], acc[h + j][1], acc[h + j][2], acc[h + j][3]);
+        __syncthreads();
+        for (int e = threadIdx.x; e < RH * 128; e += kDecodeThreads) {
+            const int j = e >> 7, c = e & 127;
+            float s = red[0][j][c];
+#pragma unroll
+            for (int wv = 1; wv < 8; ++wv) s += red[wv][j][c];
+            cta_sum[(h + j) * 128 + c] = s;
+        }
+    }
+    cluster.sync();
+    // the S CTAs of the cluster, rank order; this CTA finishes every S-th group of 256 outputs
+    for (int e = rank * kDecodeThreads + threadIdx.x; e < rows * 128; e += S * kDecodeThreads) {
+        const int m = e >> 7, gc = blockIdx.x * 128 + (e & 127);
+        if (gc >= N) continue;
+        float s = 0.0f;
+        for (int q0 = 0; q0 < S; q0 += 8) {   // up to eight remote loads in flight, added in rank order
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = q0 + j < S ? cluster.map_shared_rank(cta_sum, q0 + j)[e] : 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (q0 + j < S) s += v[j];
+        }
+        if (bias) s += bias[gc];
+        y[size_t(row0 + m) * N + gc] = s;
+        if (act) act[size_t(row0 + m) * N + gc] = gelu_tanh(s);
+    }
+    cluster.sync();   // no CTA leaves while its sums may still be read
 }
 
 // y = sum_s partial[s] (s ascending) + bias; act = gelu_tanh(y)
@@ -98,7 +252,15 @@ __global__ void skinny_finish_kernel(float *__restrict__ y, float *__restrict__ 
     const long long stride = 1LL * gridDim.x * blockDim.x;
     for (long long i = 1LL * blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
         float s = partial[i];
-        for (int p = 1; p < splits; ++p) s += partial[p * total + i];
+        int p = 1;
+        for (; p + 8 <= splits; p += 8) {   // eight loads in flight, added in split order
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = partial[(p + j) * total + i];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s += v[j];
+        }
+        for (; p < splits; ++p) s += partial[p * total + i];
         if (bias) s += bias[i % N];
         y[i] = s;
         if (act) act[i] = gelu_tanh(s);

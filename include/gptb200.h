@@ -54,7 +54,15 @@ int gptb200_ctx_set_stream(gptb200_ctx *ctx, void *cuda_stream);
  * "pair" (CTA-pair kernel with 256 x 256 tiles: 1 = always, 0 = heuristic, -1 = never),
  * "stream_k" (CTA-pair kernel: give every pair the same number of k-blocks by letting a pair's range begin and end inside a
  * tile, partial tiles summed through scratch: 1 = always, 0 = when whole tiles would leave SMs idle, -1 = never),
- * "skinny" (weight-streaming kernel for forward calls with m <= 16: 1 = on (default), 0 = off),
+ * "skinny" (weight-streaming kernel for decode-shaped calls, up to 64 rows: 1 = on (default), 0 = off),
+ * "skinny_rows" (most rows that kernel takes: 0 = 64 (default), 1 .. 64),
+ * "skinny_cluster" (decode-shaped calls whose weight is stored [k][n]: one launch that splits k over the warps of a CTA and
+ * the CTAs of a thread-block cluster and adds the parts through distributed shared memory; value = largest cluster, 0 (off:
+ * k-split kernel with partial sums in scratch), 1, 2, 4, 8, 16 (default: sixteen only for layers too narrow to fill half of the
+ * SMs with clusters of eight) or 32 (sixteen wherever k allows)),
+ * "skinny_cluster_rows" (most rows of x for which that kernel is used: default 16),
+ * "skinny_fused" (the k-split kernel adds its partial sums itself instead of in a second launch: 1 = always, 0 = with at most
+ * two splits (default), -1 = never; same bits either way),
  * "max_sms" (0 = all SMs; otherwise the GEMM kernels occupy at most this many, which leaves SMs to a collective that runs
  * at the same time on another stream),
  * "trace" (record a kernel-phase trace of each CTA-pair GEMM launch: 1 = on, 0 = off (default)),

@@ -349,6 +349,62 @@ def test_full_size_lm_head_properties(be, torch):
     assert bool((gw[v:] == 0).all())
 
 
+@pytest.mark.parametrize("m,k,n,w_kn", [(1, 768, 3072, True), (2, 768, 768, True), (8, 3072, 768, True), (16, 768, 2304, True),
+                                        (1, 768, 50304, False), (8, 768, 1024, False), (5, 40, 132, False),
+                                        (40, 768, 2304, True), (64, 3072, 768, True), (33, 768, 1024, False)], ids=lambda v: str(v))
+def test_decode_kernel_variants_agree(torch, built_library, oracle, m, k, n, w_kn):
+    """Decode-shaped calls: the cluster kernel (k split over warps and cluster CTAs, summed through distributed shared memory;
+    every cluster size) and the k-split kernel (partial sums in scratch, added by the last CTA or by a second kernel: same
+    bits both ways, also on repeated calls, since the tickets reset themselves) all match the oracle."""
+    import gpt_b200
+    rng = np.random.default_rng(m * 131 + k + n)
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    d = Dev(torch)
+    be = gpt_b200.Backend(0, None, 0)
+    try:
+        if w_kn:
+            w = (0.02 * rng.standard_normal((k, n))).astype(np.float32)
+            b = (0.02 * rng.standard_normal(n)).astype(np.float32)
+            ref = oracle.linear_forward(x, w, b, True)
+            dx, dw, db = d.put(x), d.put(w), d.put(b)
+
+            def run():
+                y, act = d.nan(m, n), d.nan(m, n)
+                be.device_linear_activation_fused_forward(y, act, dx, dw, db, True, 1, m, k, n)
+                be.synchronize()
+                return y.cpu().numpy(), act.cpu().numpy()
+        else:
+            w = (0.02 * rng.standard_normal((n, k))).astype(np.float32)
+            ref = (oracle.unembed_forward(x, w),)
+            dx, dw = d.put(x), d.put(w)
+
+            def run():
+                y = d.nan(m, n)
+                be.device_unembedding_forward(y, dx, dw, 1, m, k, n)
+                be.synchronize()
+                return (y.cpu().numpy(),)
+        for cluster in ((16, 32, 8, 4, 1) if w_kn else ()):
+            be.set_option("skinny_cluster", cluster)
+            be.set_option("skinny_cluster_rows", 64)
+            first, again = run(), run()
+            for got, again_, want in zip(first, again, ref):
+                check(f"cluster {cluster}", got, want, 0)
+                assert np.array_equal(got, again_)
+        be.set_option("skinny_cluster", 0)
+        results = []
+        for fused in (1, -1, 1, 0):
+            be.set_option("skinny_fused", fused)
+            results.append(run())
+        d.check_canaries()
+        for got, want in zip(results[0], ref):
+            check("k-split", got, want, 0)
+        for r in results[1:]:
+            for a_, b_ in zip(results[0], r):
+                assert np.array_equal(a_, b_)
+    finally:
+        be.close()
+
+
 def test_bounded_wait_runs_out_and_is_reported(torch, built_library):
     """Failure detection: a wait on a barrier that nothing signals ends after its limit, the kernel returns, the host reads
     the status as GPTB200_ERR_DEVICE_TIMEOUT, and the context keeps working (no trap, no hang, no lost context)."""

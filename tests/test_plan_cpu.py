@@ -40,6 +40,9 @@ def test_small_and_odd_shapes(plan):
     assert plan(SMS, 64, 32, 256, False, True, True)["grid"] == 1
     assert plan(SMS, 8, 3072, 768, False, True, True)["kernel"] == "skinny"    # decode-shaped
     assert plan(SMS, 1, 50304, 768, False, False)["kernel"] == "skinny"
+    p64 = plan(SMS, 64, 2304, 768, False, True, True)                          # batch 64: four row groups of 16
+    assert p64["kernel"] == "skinny" and p64["tiles_m"] == 4 and p64["grid"] == 4 * p64["tiles_n"] * p64["splits"]
+    assert plan(SMS, 65, 2304, 768, False, True, True)["kernel"] != "skinny"
     assert plan(SMS, 16, 768, 768, True, True, False, True)["kernel"] != "skinny"   # weight gradients never stream
     assert plan(SMS, 77, 50, 30, False, True, True)["kernel"] == "simt"        # row pitch not a multiple of 16 bytes
     assert plan(SMS, 5, 9, 7, False, True, True)["kernel"] == "simt"
@@ -85,4 +88,4 @@ def test_plan_invariants_over_a_sweep(plan, sms):
                     assert p["scratch_kib"] == 0
                 assert p["tile_n"] in (128, 256)
             if p["kernel"] == "skinny":
-                assert m <= 16 and not acc and p["splits"] * p["k_per_split"] >= k and p["k_per_split"] % 4 == 0
+                assert m <= 64 and p["tiles_m"] == (m + 15) // 16 and not acc and p["splits"] * p["k_per_split"] >= k and p["k_per_split"] % 4 == 0

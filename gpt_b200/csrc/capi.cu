@@ -174,15 +174,31 @@ int launch_decode_cluster(gptb200_ctx *ctx, const GemmCall &c, int cluster, int 
     cfg.blockDim = dim3(kDecodeThreads);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = cluster;
     attr[0].val.clusterDim.z = 1;
+    // option "decode_early_launch": this kernel may start while the kernel before it on the stream still runs (it reads only
+    // w and bias until that kernel has completed) and lets its own successor start early in turn
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    CUDA_TRY(ctx, cudaLaunchKernelEx(&cfg, kernel, c.out, c.act, c.a, c.b, c.bias, c.M, c.N, c.K));
+    cfg.numAttrs = ctx->decode_early_launch ? 2 : 1;
+    CUDA_TRY(ctx, cudaLaunchKernelEx(&cfg, kernel, c.out, c.act, c.a, c.b, c.bias, c.M, c.N, c.K, ctx->decode_early_launch ? 1 : 0));
     ctx->launches++;
+    return GPTB200_OK;
+}
+
+// One-launch warp-per-row kernel for decode-shaped products with W stored [n][k] (see rowwise_gemv_kernel).
+template <int MR>
+int launch_rowwise(gptb200_ctx *ctx, const GemmCall &c)
+{
+    const int warps_needed = (c.N + 1) / 2;
+    const int grid = std::max(1, std::min(ctx->num_sms * 4, (warps_needed + kDecodeThreads / 32 - 1) / (kDecodeThreads / 32)));
+    rowwise_gemv_kernel<MR><<<grid, kDecodeThreads, size_t(MR) * c.K * sizeof(float), ctx->stream>>>(c.out, c.a, c.b, c.M, c.N, c.K);
+    ctx->launches++;
+    CUDA_TRY(ctx, cudaGetLastError());
     return GPTB200_OK;
 }
 
@@ -209,6 +225,14 @@ int run_skinny(gptb200_ctx *ctx, const GemmCall &c, const GemmPlan &pl)
             case 4: return launch_decode_cluster<4>(ctx, c, cluster, groups);
             case 8: return launch_decode_cluster<8>(ctx, c, cluster, groups);
             default: return launch_decode_cluster<16>(ctx, c, cluster, groups);
+        }
+    }
+    if (!w_kn && ctx->skinny_rowwise && c.M <= 8 && !c.bias && !c.act && 1LL * mr * c.K <= 8192) {
+        switch (mr) {
+            case 1: return launch_rowwise<1>(ctx, c);
+            case 2: return launch_rowwise<2>(ctx, c);
+            case 4: return launch_rowwise<4>(ctx, c);
+            default: return launch_rowwise<8>(ctx, c);
         }
     }
     const int rc = ensure_workspace(ctx, pl.workspace_bytes);
@@ -510,6 +534,14 @@ int gptb200_ctx_set_option(gptb200_ctx *ctx, const char *key, int value)
     if (!strcmp(key, "skinny_rows")) {
         if (value < 0 || value > kPlanSkinnyMaxRows) return fail(ctx, GPTB200_ERR_INVALID_ARG, "skinny_rows must be in [0, %d]", kPlanSkinnyMaxRows);
         ctx->skinny_rows = value;
+        return GPTB200_OK;
+    }
+    if (!strcmp(key, "skinny_rowwise")) {
+        ctx->skinny_rowwise = value != 0;
+        return GPTB200_OK;
+    }
+    if (!strcmp(key, "decode_early_launch")) {
+        ctx->decode_early_launch = value != 0;
         return GPTB200_OK;
     }
     if (!strcmp(key, "skinny_cluster_rows")) {

@@ -28,6 +28,9 @@ struct gptb200_ctx {
     int skinny_cluster = 16; // W stored [k][n]: one-launch kernel that splits k over a thread-block cluster of up to this many CTAs
                              // (0 = off; 16 = sixteen for narrow layers only; 32 = sixteen wherever k allows)
     int skinny_cluster_rows = 16;  // ... for calls with at most this many rows (beyond: the k-split kernel, measured faster at 64 rows)
+    bool decode_early_launch = false;  // that kernel is launched with programmatic stream serialization: it prefetches weights while
+                                       // its predecessor on the stream still runs (caller's promise: the predecessor does not write them)
+    bool skinny_rowwise = true;  // W stored [n][k], up to eight rows of x, no bias: one-launch warp-per-row kernel
     int skinny_fused = 0;  // that kernel adds its partial sums itself (one launch): 1 = always, 0 = with at most two splits, -1 = never
     int debug = 0;       // timing experiments (see GemmParams::debug)
     bool attention_tiled = true;  // head size 64: register-tiled attention kernels (false: the one-row-per-thread-group kernels)

@@ -159,7 +159,7 @@ constexpr int kDecodeThreads = 256;
 template <int MR>
 __global__ void __launch_bounds__(kDecodeThreads)
 decode_gemm_cluster_kernel(float *__restrict__ y, float *__restrict__ act, const float *__restrict__ x, const float *__restrict__ w,
-                           const float *__restrict__ bias, int M, int N, int K)
+                           const float *__restrict__ bias, int M, int N, int K, int early_launch)
 {
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
@@ -185,6 +185,12 @@ decode_gemm_cluster_kernel(float *__restrict__ y, float *__restrict__ act, const
     // Weight loads in flight per thread: the loop is one DRAM round trip per unrolled body (measured: 0.85 us per body with
     // eight loads, whatever n), so with few rows of x the registers go to loads: 16 k-rows per body up to two rows of x.
     constexpr int kUnroll = MR <= 2 ? 4 : MR <= 4 ? 3 : MR <= 8 ? 2 : 1;
+    // Programmatic dependent launch (early_launch): the next kernel on the stream may start as soon as every CTA of this one
+    // is running, and this kernel may have started while its predecessor was still running.  Only the weights (and, later,
+    // the bias) are read before griddepcontrol.wait, which returns once the predecessor has completed and its writes are
+    // visible; x is read and y written after it.  The caller promises that the predecessor does not write w or bias.
+    bool waited = !early_launch;
+    if (early_launch) asm volatile("griddepcontrol.launch_dependents;");
     if (col_ok) {
         const float *wp = w + col;
         for (int k = k_begin; k < k_end; k += 4 * kUnroll) {
@@ -192,6 +198,10 @@ decode_gemm_cluster_kernel(float *__restrict__ y, float *__restrict__ act, const
 #pragma unroll
             for (int i = 0; i < 4 * kUnroll; ++i)
                 wv[i] = k + i < k_end ? __ldcs(reinterpret_cast<const float4 *>(wp + size_t(k + i) * N)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (!waited) {
+                asm volatile("griddepcontrol.wait;" ::: "memory");   // the first body's weight loads are already in flight
+                waited = true;
+            }
 #pragma unroll
             for (int g = 0; g < kUnroll; ++g) {
                 if (k + 4 * g >= k_end) break;   // warp-uniform
@@ -207,6 +217,7 @@ decode_gemm_cluster_kernel(float *__restrict__ y, float *__restrict__ act, const
             }
         }
     }
+    if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");   // threads without columns or k-rows: before any output
     // the eight warps of this CTA, warp order
 #pragma unroll
     for (int h = 0; h < MR; h += RH) {
@@ -242,6 +253,67 @@ decode_gemm_cluster_kernel(float *__restrict__ y, float *__restrict__ act, const
         if (act) act[size_t(row0 + m) * N + gc] = gelu_tanh(s);
     }
     cluster.sync();   // no CTA leaves while its sums may still be read
+}
+
+// Decode-shaped product with W stored [n][k] (the tied un-embedding: logits = x . wte^T; also grad_x = grad_y . w^T) for up to
+// eight rows of x: one warp per pair of weight rows.  A lane reads 16 contiguous bytes and the warp 512 contiguous bytes of
+// a row per load (the k-split kernel above lets every thread walk its own row, 32 rows per load instruction, and reaches
+// about half of the HBM bandwidth); x sits in shared memory; the 32 partial sums of a row meet in a butterfly of shuffles
+// (fixed order).  One launch, no scratch.  HBM-bound: 4 * n * k bytes.
+//   dynamic shared memory: MR * K floats (at most 32 KiB);  grid: any, warps stride over row pairs.
+template <int MR>
+__global__ void __launch_bounds__(kDecodeThreads)
+rowwise_gemv_kernel(float *__restrict__ y, const float *__restrict__ x, const float *__restrict__ w, int M, int N, int K)
+{
+    extern __shared__ __align__(16) float xs_dyn[];   // [MR][K]
+    const int kq = K >> 2;
+    for (int i = threadIdx.x; i < MR * kq; i += kDecodeThreads) {
+        const int m = i / kq, q = i - m * kq;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (m < M) v = *reinterpret_cast<const float4 *>(x + size_t(m) * K + 4 * q);
+        *reinterpret_cast<float4 *>(xs_dyn + size_t(m) * K + 4 * q) = v;
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warps = gridDim.x * (kDecodeThreads / 32);
+    constexpr int U = 3;   // loads in flight per lane and row
+    for (int n0 = (blockIdx.x * (kDecodeThreads / 32) + warp) * 2; n0 < N; n0 += warps * 2) {
+        const float *wa = w + size_t(n0) * K;
+        const float *wb = w + size_t(min(n0 + 1, N - 1)) * K;   // odd n: the last row twice, second result dropped
+        float acc[2][MR];
+#pragma unroll
+        for (int m = 0; m < MR; ++m) acc[0][m] = acc[1][m] = 0.0f;
+        for (int k0 = lane * 4; k0 < K; k0 += 128 * U) {
+            float4 a[U], b[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int k = k0 + 128 * u;
+                a[u] = k < K ? __ldcs(reinterpret_cast<const float4 *>(wa + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                b[u] = k < K ? __ldcs(reinterpret_cast<const float4 *>(wb + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int k = k0 + 128 * u;
+                if (k < K) {
+#pragma unroll
+                    for (int m = 0; m < MR; ++m) {
+                        const float4 xv = *reinterpret_cast<const float4 *>(xs_dyn + size_t(m) * K + k);
+                        acc[0][m] += xv.x * a[u].x + xv.y * a[u].y + xv.z * a[u].z + xv.w * a[u].w;
+                        acc[1][m] += xv.x * b[u].x + xv.y * b[u].y + xv.z * b[u].z + xv.w * b[u].w;
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+            for (int m = 0; m < MR; ++m) {
+                float v = acc[r][m];
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+                if (lane == ((m * 2 + r) & 31) && m < M && n0 + r < N) y[size_t(m) * N + n0 + r] = v;
+            }
+    }
 }
 
 // y = sum_s partial[s] (s ascending) + bias; act = gelu_tanh(y)

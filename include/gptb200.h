@@ -61,6 +61,12 @@ int gptb200_ctx_set_stream(gptb200_ctx *ctx, void *cuda_stream);
  * k-split kernel with partial sums in scratch), 1, 2, 4, 8, 16 (default: sixteen only for layers too narrow to fill half of the
  * SMs with clusters of eight) or 32 (sixteen wherever k allows)),
  * "skinny_cluster_rows" (most rows of x for which that kernel is used: default 16),
+ * "skinny_rowwise" (decode-shaped calls whose weight is stored [n][k] - the un-embedding, grad_x - with at most eight rows:
+ * one-launch kernel, a warp per pair of weight rows: 1 = on (default), 0 = off (k-split kernel)),
+ * "decode_early_launch" (inference only, 0 = off (default), 1 = on: that kernel is launched with programmatic stream
+ * serialization, starts while the kernel before it on the stream is still running and reads w and b meanwhile - x is read and
+ * y / act are written only once that kernel has completed.  The caller promises that no kernel writes weights or biases
+ * immediately before a decode-shaped forward call on the same stream (an optimizer step does: leave this off when training)),
  * "skinny_fused" (the k-split kernel adds its partial sums itself instead of in a second launch: 1 = always, 0 = with at most
  * two splits (default), -1 = never; same bits either way),
  * "max_sms" (0 = all SMs; otherwise the GEMM kernels occupy at most this many, which leaves SMs to a collective that runs

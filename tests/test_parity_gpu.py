@@ -350,7 +350,7 @@ def test_full_size_lm_head_properties(be, torch):
 
 
 @pytest.mark.parametrize("m,k,n,w_kn", [(1, 768, 3072, True), (2, 768, 768, True), (8, 3072, 768, True), (16, 768, 2304, True),
-                                        (1, 768, 50304, False), (8, 768, 1024, False), (5, 40, 132, False),
+                                        (1, 768, 50304, False), (8, 768, 1024, False), (5, 40, 132, False), (2, 3072, 767 * 4, False), (3, 100, 132, False),
                                         (40, 768, 2304, True), (64, 3072, 768, True), (33, 768, 1024, False)], ids=lambda v: str(v))
 def test_decode_kernel_variants_agree(torch, built_library, oracle, m, k, n, w_kn):
     """Decode-shaped calls: the cluster kernel (k split over warps and cluster CTAs, summed through distributed shared memory;
@@ -390,6 +390,11 @@ def test_decode_kernel_variants_agree(torch, built_library, oracle, m, k, n, w_k
             for got, again_, want in zip(first, again, ref):
                 check(f"cluster {cluster}", got, want, 0)
                 assert np.array_equal(got, again_)
+        if not w_kn:
+            first, again = run(), run()     # warp-per-row kernel (up to eight rows), else the k-split kernel
+            check("rowwise", first[0], ref[0], 0)
+            assert np.array_equal(first[0], again[0])
+            be.set_option("skinny_rowwise", 0)
         be.set_option("skinny_cluster", 0)
         results = []
         for fused in (1, -1, 1, 0):
@@ -499,3 +504,58 @@ def test_cut_ranges_replayed_from_a_cuda_graph(torch, built_library):
         assert float((y.double() - ref).abs().max() / ref.abs().max()) <= 1e-5
     b.synchronize()
     b.close()
+
+
+@pytest.mark.parametrize("m", [1, 4, 16])
+def test_decode_chain_with_early_launch_matches_plain_launches(torch, built_library, m):
+    """Option "decode_early_launch": every decode-shaped layer may start while its predecessor still runs (it prefetches weights
+    and reads its input only after the predecessor has completed).  A chain in which each layer reads the previous layer's
+    output must give the same bits as with ordinary launches, eagerly and replayed from a CUDA graph."""
+    import gpt_b200
+    d = 768
+    g = torch.Generator(device="cuda").manual_seed(40 + m)
+    ws = [torch.randn(d, d, device="cuda", generator=g) * 0.05 for _ in range(8)]
+    bs = [torch.randn(d, device="cuda", generator=g) * 0.02 for _ in range(8)]
+    x = torch.randn(m, d, device="cuda", generator=g)
+    side = torch.cuda.Stream()
+    be = gpt_b200.Backend(0, side.cuda_stream)
+
+    def chain(bufs):
+        cur = x
+        for i, (w, b_) in enumerate(zip(ws, bs)):
+            be.device_linear_activation_fused_forward(bufs[2 * i], bufs[2 * i + 1], cur, w, b_, True, 1, m, d, d)
+            cur = bufs[2 * i + 1]     # the GELU output feeds the next layer
+        return cur
+
+    try:
+        with torch.cuda.stream(side):
+            plain = [torch.full((m, d), float("nan"), device="cuda") for _ in range(16)]
+            chain(plain)
+            side.synchronize()
+            be.set_option("decode_early_launch", 1)
+            for _ in range(3):
+                early = [torch.full((m, d), float("nan"), device="cuda") for _ in range(16)]
+                side.synchronize()
+                chain(early)
+                side.synchronize()
+                for a, b_ in zip(plain, early):
+                    assert torch.equal(a, b_)
+            bufs = [torch.empty(m, d, device="cuda") for _ in range(16)]
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                chain(bufs)
+        for _ in range(3):
+            for t_ in bufs:
+                t_.fill_(float("nan"))
+            torch.cuda.synchronize()
+            graph.replay()
+            torch.cuda.synchronize()
+            for a, b_ in zip(plain, bufs):
+                assert torch.equal(a, b_)
+        ref = x.double()
+        for w, b_ in zip(ws, bs):
+            ref = torch.nn.functional.gelu(ref @ w.double() + b_.double(), approximate="tanh")
+        assert float((plain[-1].double() - ref).abs().max() / ref.abs().max()) <= 3e-5   # eight layers deep
+    finally:
+        be.synchronize()
+        be.close()

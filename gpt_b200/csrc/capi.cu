@@ -145,12 +145,23 @@ int make_out_tmap(gptb200_ctx *ctx, CUtensorMap *map, float *base, long long dep
 template <bool W_KN>
 int launch_skinny(gptb200_ctx *ctx, int mr, dim3 grid, float *partial, const GemmCall &c, int k_per_split, unsigned int *tickets)
 {
+    // 16-row groups of a [k][n] weight: weight loads pipelined through shared memory (see the kernel)
+    const bool pipe = W_KN && mr == 16 && ctx->skinny_pipelined;
+    const size_t smem = pipe ? size_t(kSkinnyPipe) * 4 * kSkinnyThreads * sizeof(float4) : 0;
+    if (pipe) {
+        auto kernel = skinny_gemm_kernel<16, W_KN>;
+        const void *key = reinterpret_cast<const void *>(kernel);
+        if (!ctx->configured.count(key)) {
+            CUDA_TRY(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+            ctx->configured.insert(key);
+        }
+    }
     switch (mr) {
-        case 1: skinny_gemm_kernel<1, W_KN><<<grid, kSkinnyThreads, 0, ctx->stream>>>(partial, c.a, c.b, c.M, c.N, c.K, k_per_split, c.out, c.act, c.bias, tickets); break;
-        case 2: skinny_gemm_kernel<2, W_KN><<<grid, kSkinnyThreads, 0, ctx->stream>>>(partial, c.a, c.b, c.M, c.N, c.K, k_per_split, c.out, c.act, c.bias, tickets); break;
-        case 4: skinny_gemm_kernel<4, W_KN><<<grid, kSkinnyThreads, 0, ctx->stream>>>(partial, c.a, c.b, c.M, c.N, c.K, k_per_split, c.out, c.act, c.bias, tickets); break;
-        case 8: skinny_gemm_kernel<8, W_KN><<<grid, kSkinnyThreads, 0, ctx->stream>>>(partial, c.a, c.b, c.M, c.N, c.K, k_per_split, c.out, c.act, c.bias, tickets); break;
-        default: skinny_gemm_kernel<16, W_KN><<<grid, kSkinnyThreads, 0, ctx->stream>>>(partial, c.a, c.b, c.M, c.N, c.K, k_per_split, c.out, c.act, c.bias, tickets); break;
+        case 1: skinny_gemm_kernel<1, W_KN><<<grid, kSkinnyThreads, 0, ctx->stream>>>(partial, c.a, c.b, c.M, c.N, c.K, k_per_split, c.out, c.act, c.bias, tickets, 0); break;
+        case 2: skinny_gemm_kernel<2, W_KN><<<grid, kSkinnyThreads, 0, ctx->stream>>>(partial, c.a, c.b, c.M, c.N, c.K, k_per_split, c.out, c.act, c.bias, tickets, 0); break;
+        case 4: skinny_gemm_kernel<4, W_KN><<<grid, kSkinnyThreads, 0, ctx->stream>>>(partial, c.a, c.b, c.M, c.N, c.K, k_per_split, c.out, c.act, c.bias, tickets, 0); break;
+        case 8: skinny_gemm_kernel<8, W_KN><<<grid, kSkinnyThreads, 0, ctx->stream>>>(partial, c.a, c.b, c.M, c.N, c.K, k_per_split, c.out, c.act, c.bias, tickets, 0); break;
+        default: skinny_gemm_kernel<16, W_KN><<<grid, kSkinnyThreads, smem, ctx->stream>>>(partial, c.a, c.b, c.M, c.N, c.K, k_per_split, c.out, c.act, c.bias, tickets, pipe ? 1 : 0); break;
     }
     ctx->launches++;
     CUDA_TRY(ctx, cudaGetLastError());
@@ -190,13 +201,48 @@ int launch_decode_cluster(gptb200_ctx *ctx, const GemmCall &c, int cluster, int 
     return GPTB200_OK;
 }
 
+// One-launch register-tiled cluster kernel for 9 .. 64 rows with W stored [k][n] (see decode_tile_cluster_kernel).
+template <int TM, bool W_NK>
+int launch_decode_tile(gptb200_ctx *ctx, const GemmCall &c, int cluster)
+{
+    auto kernel = decode_tile_cluster_kernel<TM, W_NK>;
+    const size_t smem = size_t(kTileStages) * ((W_NK ? 128 * kTileNkPitch : kTileK * 128) + TM * kTileK) * sizeof(float);
+    const void *key = reinterpret_cast<const void *>(kernel);
+    if (!ctx->configured.count(key)) {
+        CUDA_TRY(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        CUDA_TRY(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+        ctx->configured.insert(key);
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((c.N + 127) / 128, cluster, 1);
+    cfg.blockDim = dim3(kDecodeThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = cluster;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    // Early launch is measured slower for this kernel (its waiting CTAs hold 74 - 100 KiB of shared memory each; 64 rows: 1.13
+    // against 1.04 ms per decode step): option value 2 forces it, 1 applies to the per-warp cluster kernel only.
+    const bool early = ctx->decode_early_launch >= 2;
+    cfg.numAttrs = early ? 2 : 1;
+    CUDA_TRY(ctx, cudaLaunchKernelEx(&cfg, kernel, c.out, c.act, c.a, c.b, c.bias, c.M, c.N, c.K, early ? 1 : 0));
+    ctx->launches++;
+    return GPTB200_OK;
+}
+
 // One-launch warp-per-row kernel for decode-shaped products with W stored [n][k] (see rowwise_gemv_kernel).
 template <int MR>
 int launch_rowwise(gptb200_ctx *ctx, const GemmCall &c)
 {
     const int warps_needed = (c.N + 1) / 2;
-    const int grid = std::max(1, std::min(ctx->num_sms * 4, (warps_needed + kDecodeThreads / 32 - 1) / (kDecodeThreads / 32)));
-    rowwise_gemv_kernel<MR><<<grid, kDecodeThreads, size_t(MR) * c.K * sizeof(float), ctx->stream>>>(c.out, c.a, c.b, c.M, c.N, c.K);
+    const int groups = (c.M + MR - 1) / MR;
+    const int ctas = std::max(1, std::min(std::max(1, ctx->num_sms * 4 / groups), (warps_needed + kDecodeThreads / 32 - 1) / (kDecodeThreads / 32)));
+    rowwise_gemv_kernel<MR><<<dim3(groups, ctas), kDecodeThreads, size_t(MR) * c.K * sizeof(float), ctx->stream>>>(c.out, c.a, c.b, c.M, c.N, c.K);
     ctx->launches++;
     CUDA_TRY(ctx, cudaGetLastError());
     return GPTB200_OK;
@@ -227,12 +273,39 @@ int run_skinny(gptb200_ctx *ctx, const GemmCall &c, const GemmPlan &pl)
             default: return launch_decode_cluster<16>(ctx, c, cluster, groups);
         }
     }
-    if (!w_kn && ctx->skinny_rowwise && c.M <= 8 && !c.bias && !c.act && 1LL * mr * c.K <= 8192) {
-        switch (mr) {
-            case 1: return launch_rowwise<1>(ctx, c);
-            case 2: return launch_rowwise<2>(ctx, c);
-            case 4: return launch_rowwise<4>(ctx, c);
-            default: return launch_rowwise<8>(ctx, c);
+    if (w_kn && ctx->skinny_tile && c.M > ctx->skinny_cluster_rows && ctx->skinny_cluster > 0) {
+        // cluster size: as above, with at least one 32-row chunk of k per CTA
+        int cluster = 1;
+        const long long blocks = (c.N + 127) / 128;
+        while (cluster * 2 <= std::min(ctx->skinny_cluster, 8) && c.K / (cluster * 2) >= kTileK && blocks * cluster * 2 <= 2LL * ctx->num_sms) cluster *= 2;
+        if (cluster == 8 && ctx->skinny_cluster >= 16 && c.K / 16 >= kTileK && (blocks * 16 <= ctx->num_sms || ctx->skinny_cluster >= 32)) cluster = 16;
+        if (c.M <= 16) return launch_decode_tile<16, false>(ctx, c, cluster);
+        if (c.M <= 32) return launch_decode_tile<32, false>(ctx, c, cluster);
+        return launch_decode_tile<64, false>(ctx, c, cluster);
+    }
+    if (!w_kn && ctx->skinny_tile && c.M > ctx->skinny_rowwise_rows && ctx->skinny_cluster > 0 && !c.bias && !c.act) {
+        // W stored [n][k], more rows than the warp-per-row kernel takes: the same tile kernel; k is split over a cluster only
+        // when the column tiles alone leave SMs idle
+        int cluster = 1;
+        const long long blocks = (c.N + 127) / 128;
+        while (cluster * 2 <= std::min(ctx->skinny_cluster, 8) && c.K / (cluster * 2) >= 4 * kTileK && blocks * cluster * 2 <= 2LL * ctx->num_sms) cluster *= 2;
+        if (c.M <= 16) return launch_decode_tile<16, true>(ctx, c, cluster);
+        if (c.M <= 32) return launch_decode_tile<32, true>(ctx, c, cluster);
+        return launch_decode_tile<64, true>(ctx, c, cluster);
+    }
+    if (!w_kn && ctx->skinny_rowwise && !c.bias && !c.act && c.M <= ctx->skinny_rowwise_rows) {
+        // groups of up to 16 rows of x (8 when 16 rows of x exceed 48 KiB of shared memory); beyond one group the weights are
+        // re-read from L2 once per group
+        int rows = mr;
+        while (rows > 1 && 1LL * rows * c.K > 12288) rows /= 2;
+        if (1LL * rows * c.K <= 12288 && (rows >= 8 || rows == mr)) {
+            switch (rows) {
+                case 1: return launch_rowwise<1>(ctx, c);
+                case 2: return launch_rowwise<2>(ctx, c);
+                case 4: return launch_rowwise<4>(ctx, c);
+                case 8: return launch_rowwise<8>(ctx, c);
+                default: return launch_rowwise<16>(ctx, c);
+            }
         }
     }
     const int rc = ensure_workspace(ctx, pl.workspace_bytes);
@@ -536,12 +609,26 @@ int gptb200_ctx_set_option(gptb200_ctx *ctx, const char *key, int value)
         ctx->skinny_rows = value;
         return GPTB200_OK;
     }
+    if (!strcmp(key, "skinny_tile")) {
+        ctx->skinny_tile = value != 0;
+        return GPTB200_OK;
+    }
+    if (!strcmp(key, "skinny_pipelined")) {
+        ctx->skinny_pipelined = value != 0;
+        return GPTB200_OK;
+    }
+    if (!strcmp(key, "skinny_rowwise_rows")) {
+        if (value < 0 || value > kPlanSkinnyMaxRows) return fail(ctx, GPTB200_ERR_INVALID_ARG, "skinny_rowwise_rows must be in [0, %d]", kPlanSkinnyMaxRows);
+        ctx->skinny_rowwise_rows = value;
+        return GPTB200_OK;
+    }
     if (!strcmp(key, "skinny_rowwise")) {
         ctx->skinny_rowwise = value != 0;
         return GPTB200_OK;
     }
     if (!strcmp(key, "decode_early_launch")) {
-        ctx->decode_early_launch = value != 0;
+        if (value < 0 || value > 2) return fail(ctx, GPTB200_ERR_INVALID_ARG, "decode_early_launch must be 0, 1 or 2");
+        ctx->decode_early_launch = value;
         return GPTB200_OK;
     }
     if (!strcmp(key, "skinny_cluster_rows")) {

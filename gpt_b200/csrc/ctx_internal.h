@@ -27,10 +27,13 @@ struct gptb200_ctx {
     int skinny_rows = 0; // most rows it takes: 0 = the planner's limit (64)
     int skinny_cluster = 16; // W stored [k][n]: one-launch kernel that splits k over a thread-block cluster of up to this many CTAs
                              // (0 = off; 16 = sixteen for narrow layers only; 32 = sixteen wherever k allows)
-    int skinny_cluster_rows = 16;  // ... for calls with at most this many rows (beyond: the k-split kernel, measured faster at 64 rows)
-    bool decode_early_launch = false;  // that kernel is launched with programmatic stream serialization: it prefetches weights while
+    int skinny_cluster_rows = 8;   // ... for calls with at most this many rows
+    bool skinny_tile = true;       // beyond that many rows: one-launch register-tiled cluster kernel (false: the k-split kernel)
+    int decode_early_launch = 0;     // that kernel is launched with programmatic stream serialization: it prefetches weights while
                                        // its predecessor on the stream still runs (caller's promise: the predecessor does not write them)
-    bool skinny_rowwise = true;  // W stored [n][k], up to eight rows of x, no bias: one-launch warp-per-row kernel
+    bool skinny_rowwise = true;  // W stored [n][k], no bias: one-launch warp-per-row kernel ...
+    int skinny_rowwise_rows = 8;  // ... for calls with at most this many rows (beyond: the register-tiled kernel)
+    bool skinny_pipelined = true;  // k-split kernel, 16-row groups, W stored [k][n]: weight loads pipelined through shared memory
     int skinny_fused = 0;  // that kernel adds its partial sums itself (one launch): 1 = always, 0 = with at most two splits, -1 = never
     int debug = 0;       // timing experiments (see GemmParams::debug)
     bool attention_tiled = true;  // head size 64: register-tiled attention kernels (false: the one-row-per-thread-group kernels)

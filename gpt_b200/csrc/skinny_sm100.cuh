@@ -28,13 +28,15 @@ namespace gptb200 {
 
 constexpr int kSkinnyThreads = 128;
 constexpr int kSkinnyMaxTickets = 1024;  // column blocks per launch that can finish in the kernel itself
+constexpr int kSkinnyPipe = 6;      // pipelined variant: bodies of four k-rows in the shared-memory ring (8 KiB each; three CTAs per SM fit)
 constexpr int kSkinnyKChunk = 256;  // activations staged per pass: MR * 256 floats of shared memory
 
 template <int MR, bool W_KN>
 __global__ void __launch_bounds__(kSkinnyThreads)
 skinny_gemm_kernel(float *__restrict__ partial, const float *__restrict__ x, const float *__restrict__ w, int M, int N, int K, int k_per_split,
-                   float *__restrict__ y, float *__restrict__ act, const float *__restrict__ bias, unsigned int *__restrict__ tickets)
+                   float *__restrict__ y, float *__restrict__ act, const float *__restrict__ bias, unsigned int *__restrict__ tickets, int pipelined)
 {
+    extern __shared__ __align__(16) float4 w_ring[];   // pipelined: [kSkinnyPipe][4][kSkinnyThreads], thread-private slots
     __shared__ __align__(16) float xs[MR][kSkinnyKChunk];
     __shared__ int is_last;
     constexpr int CPT = W_KN ? 4 : 1;  // columns per thread
@@ -62,7 +64,40 @@ skinny_gemm_kernel(float *__restrict__ partial, const float *__restrict__ x, con
         }
         __syncthreads();
         if (!col_ok) continue;
-        if (W_KN) {
+        if (W_KN && pipelined) {
+            // Weight loads run kSkinnyPipe - 1 bodies (of four k-rows) ahead of the FMAs through cp.async into shared-memory slots
+            // that only the issuing thread reads back: no barrier, and 20 loads in flight per thread instead of the eight that
+            // registers allow next to 64 accumulators (with 16 rows of x the FMAs of a body take far less than a DRAM round trip).
+            const float *wp = w + size_t(k0) * N + col;
+            const int bodies = kc >> 2;
+            auto issue = [&](int body) {
+                if (body < bodies) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(&w_ring[((body % kSkinnyPipe) * 4 + i) * kSkinnyThreads + threadIdx.x]));
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(wp + size_t(body * 4 + i) * N) : "memory");
+                    }
+                }
+                asm volatile("cp.async.commit_group;" ::: "memory");   // one group per body, empty past the end
+            };
+            for (int b = 0; b < kSkinnyPipe - 1; ++b) issue(b);
+            for (int body = 0; body < bodies; ++body) {
+                issue(body + kSkinnyPipe - 1);   // into the slot this thread finished reading in the previous iteration
+                asm volatile("cp.async.wait_group %0;" ::"n"(kSkinnyPipe - 1) : "memory");
+                const float4 *slot = &w_ring[(body % kSkinnyPipe) * 4 * kSkinnyThreads + threadIdx.x];
+                const float4 w0 = slot[0], w1 = slot[kSkinnyThreads], w2 = slot[2 * kSkinnyThreads], w3 = slot[3 * kSkinnyThreads];
+                const int k = body * 4;
+#pragma unroll
+                for (int m = 0; m < MR; ++m) {
+                    const float4 xv = *reinterpret_cast<const float4 *>(&xs[m][k]);
+                    acc[m][0] += xv.x * w0.x + xv.y * w1.x + xv.z * w2.x + xv.w * w3.x;
+                    acc[m][1 % CPT] += xv.x * w0.y + xv.y * w1.y + xv.z * w2.y + xv.w * w3.y;
+                    acc[m][2 % CPT] += xv.x * w0.z + xv.y * w1.z + xv.z * w2.z + xv.w * w3.z;
+                    acc[m][3 % CPT] += xv.x * w0.w + xv.y * w1.w + xv.z * w2.w + xv.w * w3.w;
+                }
+            }
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        } else if (W_KN) {
             const float *wp = w + size_t(k0) * N + col;
 #pragma unroll 2
             for (int k = 0; k < kc; k += 4) {
@@ -255,17 +290,180 @@ decode_gemm_cluster_kernel(float *__restrict__ y, float *__restrict__ act, const
     cluster.sync();   // no CTA leaves while its sums may still be read
 }
 
-// Decode-shaped product with W stored [n][k] (the tied un-embedding: logits = x . wte^T; also grad_x = grad_y . w^T) for up to
-// eight rows of x: one warp per pair of weight rows.  A lane reads 16 contiguous bytes and the warp 512 contiguous bytes of
+// Decode-shaped linear layer with W stored [k][n] and 9 .. 64 rows of x: a register-tiled fp32 GEMM in one launch.  At these
+// row counts the fp32 FMAs weigh as much as the weight stream, so every weight element is loaded to shared memory once per
+// CTA (cp.async, four-stage ring of 32 k-rows) and used for all rows: a CTA computes a TM x 128 tile (TM = 16, 32 or 64 rows,
+// zero-padded), a thread TM/8 rows x 4 columns.  k is split over the S CTAs of a thread-block cluster (cluster shape
+// (1, S, 1)); the partial tiles meet through distributed shared memory in rank order, each CTA finishing 1/S of the rows
+// (bias, GELU).  No scratch, no second launch; results do not depend on timing.
+//   grid (ceil(n / 128), S); dynamic shared memory kTileStages * (32 * 128 + TM * 32) floats.
+constexpr int kTileStages = 4;
+constexpr int kTileK = 32;
+
+//   W_NK: W stored [n][k] instead (the tied un-embedding, grad_x): the stage holds w[128 n][32 k] with rows padded to 36 floats
+//   (16-byte reads of 32 consecutive rows then touch every bank once) and a thread owns columns lane, lane + 32, + 64, + 96.
+constexpr int kTileNkPitch = 36;
+
+template <int TM, bool W_NK>
+__global__ void __launch_bounds__(kDecodeThreads)
+decode_tile_cluster_kernel(float *__restrict__ y, float *__restrict__ act, const float *__restrict__ x, const float *__restrict__ w,
+                           const float *__restrict__ bias, int M, int N, int K, int early_launch)
+{
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    constexpr int RT = TM / 8;                                   // rows per thread
+    constexpr int kWFloats = W_NK ? 128 * kTileNkPitch : kTileK * 128;
+    constexpr int kStageFloats = kWFloats + TM * kTileK;         // w[32][128] (or w[128][36]) then x[TM][32]
+    extern __shared__ __align__(16) float tile_smem[];
+    const int S = gridDim.y, rank = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int col0 = blockIdx.x * 128;
+    const int k_per_cta = (((K + S - 1) / S) + 3) & ~3;
+    const int k_begin = min(K, rank * k_per_cta), k_end = min(K, k_begin + k_per_cta);
+    const int chunks = (k_end - k_begin + kTileK - 1) / kTileK;
+
+    auto load_w = [&](int chunk) {   // weights: 32 rows of 32 16-byte pieces
+        if (chunk >= chunks) return;
+        float *ws = tile_smem + (chunk % kTileStages) * kStageFloats;
+        const int k0 = k_begin + chunk * kTileK;
+#pragma unroll
+        for (int i = 0; i < (kTileK * 32) / kDecodeThreads; ++i) {
+            const int c = threadIdx.x + i * kDecodeThreads;
+            bool ok;
+            const float *src;
+            unsigned dst;
+            if (W_NK) {   // 128 rows (n) of 8 pieces along k
+                const int r = c >> 3, q = c & 7;
+                ok = col0 + r < N && k0 + 4 * q < k_end;
+                src = ok ? w + size_t(col0 + r) * K + k0 + 4 * q : w;
+                dst = static_cast<unsigned>(__cvta_generic_to_shared(ws + r * kTileNkPitch + 4 * q));
+            } else {
+                const int r = c >> 5, q = c & 31;
+                ok = k0 + r < k_end && col0 + 4 * q < N;
+                src = ok ? w + size_t(k0 + r) * N + col0 + 4 * q : w;
+                dst = static_cast<unsigned>(__cvta_generic_to_shared(ws + r * 128 + 4 * q));
+            }
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(ok ? 16 : 0) : "memory");   // out of range: zero fill
+        }
+    };
+    auto load_x = [&](int chunk) {   // x: TM rows of 8 pieces
+        if (chunk >= chunks) return;
+        float *xs = tile_smem + (chunk % kTileStages) * kStageFloats + kWFloats;
+        const int k0 = k_begin + chunk * kTileK;
+#pragma unroll
+        for (int i = 0; i < (TM * 8 + kDecodeThreads - 1) / kDecodeThreads; ++i) {
+            const int c = threadIdx.x + i * kDecodeThreads, r = c >> 3, q = c & 7;
+            if (c < TM * 8) {
+                const bool ok = r < M && k0 + 4 * q < k_end;
+                const float *src = ok ? x + size_t(r) * K + k0 + 4 * q : x;
+                const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(xs + r * kTileK + 4 * q));
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(ok ? 16 : 0) : "memory");
+            }
+        }
+    };
+    auto commit = [] { asm volatile("cp.async.commit_group;" ::: "memory"); };   // one group per chunk, empty past the end
+
+    float acc[RT][4];
+#pragma unroll
+    for (int j = 0; j < RT; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[j][c] = 0.0f;
+
+    // Early launch: the first stages' weights are requested before the predecessor on the stream is known to have finished,
+    // x only after (the first group then holds all of those weights and the first x chunk: still in chunk order).
+    for (int sidx = 0; sidx < kTileStages - 1; ++sidx) load_w(sidx);
+    if (early_launch) asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (int sidx = 0; sidx < kTileStages - 1; ++sidx) {
+        load_x(sidx);
+        commit();
+    }
+    for (int chunk = 0; chunk < chunks; ++chunk) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(kTileStages - 2) : "memory");   // this chunk has landed (own copies)
+        __syncthreads();                                                              // ... everyone's; and the slot refilled below is free
+        load_w(chunk + kTileStages - 1);
+        load_x(chunk + kTileStages - 1);
+        commit();
+        const float *ws = tile_smem + (chunk % kTileStages) * kStageFloats;
+        const float *xs = ws + kWFloats + warp * RT * kTileK;
+#pragma unroll
+        for (int kk = 0; kk < kTileK; kk += 4) {
+            float4 xv[RT];
+#pragma unroll
+            for (int j = 0; j < RT; ++j) xv[j] = *reinterpret_cast<const float4 *>(xs + j * kTileK + kk);   // warp-uniform: broadcast
+            if (W_NK) {
+                float4 wc[4];   // four k-values of each of this thread's four columns
+#pragma unroll
+                for (int c = 0; c < 4; ++c) wc[c] = *reinterpret_cast<const float4 *>(ws + (lane + 32 * c) * kTileNkPitch + kk);
+#pragma unroll
+                for (int j = 0; j < RT; ++j)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) acc[j][c] += xv[j].x * wc[c].x + xv[j].y * wc[c].y + xv[j].z * wc[c].z + xv[j].w * wc[c].w;
+                continue;
+            }
+            const float4 w0 = *reinterpret_cast<const float4 *>(ws + (kk + 0) * 128 + lane * 4);
+            const float4 w1 = *reinterpret_cast<const float4 *>(ws + (kk + 1) * 128 + lane * 4);
+            const float4 w2 = *reinterpret_cast<const float4 *>(ws + (kk + 2) * 128 + lane * 4);
+            const float4 w3 = *reinterpret_cast<const float4 *>(ws + (kk + 3) * 128 + lane * 4);
+#pragma unroll
+            for (int j = 0; j < RT; ++j) {
+                acc[j][0] += xv[j].x * w0.x + xv[j].y * w1.x + xv[j].z * w2.x + xv[j].w * w3.x;
+                acc[j][1] += xv[j].x * w0.y + xv[j].y * w1.y + xv[j].z * w2.y + xv[j].w * w3.y;
+                acc[j][2] += xv[j].x * w0.z + xv[j].y * w1.z + xv[j].z * w2.z + xv[j].w * w3.z;
+                acc[j][3] += xv[j].x * w0.w + xv[j].y * w1.w + xv[j].z * w2.w + xv[j].w * w3.w;
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    // the successor may start now (its CTAs hold shared memory while they wait: not before this kernel's main loop is over)
+    if (early_launch) asm volatile("griddepcontrol.launch_dependents;");
+    __syncthreads();   // all reads of the ring are done: it becomes this CTA's partial tile [TM][128]
+#pragma unroll
+    for (int j = 0; j < RT; ++j) {
+        if (W_NK) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tile_smem[(warp * RT + j) * 128 + lane + 32 * c] = acc[j][c];
+        } else {
+            *reinterpret_cast<float4 *>(tile_smem + (warp * RT + j) * 128 + lane * 4) = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
+        }
+    }
+    cluster.sync();
+    // rank order; this CTA finishes every S-th group of 256 four-column pieces
+    for (int e = rank * kDecodeThreads + threadIdx.x; e < M * 32; e += S * kDecodeThreads) {
+        const int m = e >> 5, gc = col0 + 4 * (e & 31);
+        if (gc >= N) continue;
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int q0 = 0; q0 < S; q0 += 4) {   // up to four remote loads in flight
+            float4 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                v[j] = q0 + j < S ? reinterpret_cast<const float4 *>(cluster.map_shared_rank(tile_smem, q0 + j))[e] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (q0 + j < S) { sum.x += v[j].x; sum.y += v[j].y; sum.z += v[j].z; sum.w += v[j].w; }
+        }
+        if (bias) { sum.x += bias[gc]; sum.y += bias[gc + 1]; sum.z += bias[gc + 2]; sum.w += bias[gc + 3]; }   // bias need not be 16-byte aligned
+        *reinterpret_cast<float4 *>(y + size_t(m) * N + gc) = sum;
+        if (act) *reinterpret_cast<float4 *>(act + size_t(m) * N + gc) = make_float4(gelu_tanh(sum.x), gelu_tanh(sum.y), gelu_tanh(sum.z), gelu_tanh(sum.w));
+    }
+    cluster.sync();   // no CTA leaves while its tile may still be read
+}
+
+// Decode-shaped product with W stored [n][k] (the tied un-embedding: logits = x . wte^T; also grad_x = grad_y . w^T): one warp
+// per pair of weight rows and group of up to MR rows of x (blockIdx.x = group, the fastest-varying index, so that the CTAs
+// that read the same weight rows for different groups run at the same time and all but one of them hit L2).  A lane reads 16 contiguous bytes and the warp 512 contiguous bytes of
 // a row per load (the k-split kernel above lets every thread walk its own row, 32 rows per load instruction, and reaches
 // about half of the HBM bandwidth); x sits in shared memory; the 32 partial sums of a row meet in a butterfly of shuffles
 // (fixed order).  One launch, no scratch.  HBM-bound: 4 * n * k bytes.
-//   dynamic shared memory: MR * K floats (at most 32 KiB);  grid: any, warps stride over row pairs.
+//   dynamic shared memory: MR * K floats (at most 48 KiB);  grid (groups, any): warps stride over row pairs.
 template <int MR>
 __global__ void __launch_bounds__(kDecodeThreads)
 rowwise_gemv_kernel(float *__restrict__ y, const float *__restrict__ x, const float *__restrict__ w, int M, int N, int K)
 {
     extern __shared__ __align__(16) float xs_dyn[];   // [MR][K]
+    const int row0 = blockIdx.x * MR;
+    x += size_t(row0) * K;
+    y += size_t(row0) * N;
+    M = min(MR, M - row0);   // rows of this group
     const int kq = K >> 2;
     for (int i = threadIdx.x; i < MR * kq; i += kDecodeThreads) {
         const int m = i / kq, q = i - m * kq;
@@ -275,9 +473,9 @@ rowwise_gemv_kernel(float *__restrict__ y, const float *__restrict__ x, const fl
     }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int warps = gridDim.x * (kDecodeThreads / 32);
+    const int warps = gridDim.y * (kDecodeThreads / 32);
     constexpr int U = 3;   // loads in flight per lane and row
-    for (int n0 = (blockIdx.x * (kDecodeThreads / 32) + warp) * 2; n0 < N; n0 += warps * 2) {
+    for (int n0 = (blockIdx.y * (kDecodeThreads / 32) + warp) * 2; n0 < N; n0 += warps * 2) {
         const float *wa = w + size_t(n0) * K;
         const float *wb = w + size_t(min(n0 + 1, N - 1)) * K;   // odd n: the last row twice, second result dropped
         float acc[2][MR];

@@ -60,10 +60,14 @@ int gptb200_ctx_set_stream(gptb200_ctx *ctx, void *cuda_stream);
  * the CTAs of a thread-block cluster and adds the parts through distributed shared memory; value = largest cluster, 0 (off:
  * k-split kernel with partial sums in scratch), 1, 2, 4, 8, 16 (default: sixteen only for layers too narrow to fill half of the
  * SMs with clusters of eight) or 32 (sixteen wherever k allows)),
- * "skinny_cluster_rows" (most rows of x for which that kernel is used: default 16),
- * "skinny_rowwise" (decode-shaped calls whose weight is stored [n][k] - the un-embedding, grad_x - with at most eight rows:
- * one-launch kernel, a warp per pair of weight rows: 1 = on (default), 0 = off (k-split kernel)),
- * "decode_early_launch" (inference only, 0 = off (default), 1 = on: that kernel is launched with programmatic stream
+ * "skinny_cluster_rows" (most rows of x for which that kernel is used: default 8),
+ * "skinny_tile" (more rows than that, weight stored [k][n]: one-launch register-tiled kernel whose k split also runs over a
+ * cluster: 1 = on (default), 0 = off (k-split kernel with partial sums in scratch)),
+ * "skinny_pipelined" (the k-split kernel's 16-row groups fetch weights through a shared-memory ring: 1 = on (default), 0 = off),
+ * "skinny_rowwise" (decode-shaped calls whose weight is stored [n][k] - the un-embedding, grad_x: one-launch kernel, a warp
+ * per pair of weight rows and group of up to 16 rows of x: 1 = on (default), 0 = off (k-split kernel)),
+ * "skinny_rowwise_rows" (most rows of x for which that kernel is used: default 8; beyond, the register-tiled kernel),
+ * "decode_early_launch" (inference only, 0 = off (default), 1 = on (2: also for the register-tiled kernel, measured slower): that kernel is launched with programmatic stream
  * serialization, starts while the kernel before it on the stream is still running and reads w and b meanwhile - x is read and
  * y / act are written only once that kernel has completed.  The caller promises that no kernel writes weights or biases
  * immediately before a decode-shaped forward call on the same stream (an optimizer step does: leave this off when training)),

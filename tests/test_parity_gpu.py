@@ -351,10 +351,12 @@ def test_full_size_lm_head_properties(be, torch):
 
 @pytest.mark.parametrize("m,k,n,w_kn", [(1, 768, 3072, True), (2, 768, 768, True), (8, 3072, 768, True), (16, 768, 2304, True),
                                         (1, 768, 50304, False), (8, 768, 1024, False), (5, 40, 132, False), (2, 3072, 767 * 4, False), (3, 100, 132, False),
-                                        (40, 768, 2304, True), (64, 3072, 768, True), (33, 768, 1024, False)], ids=lambda v: str(v))
+                                        (40, 768, 2304, True), (64, 3072, 768, True), (33, 768, 1024, False),
+                                        (9, 100, 132, True), (17, 36, 260, True), (61, 3072, 3072, True),
+                                        (64, 768, 2048, False), (16, 1024, 512, False), (11, 3072, 768, False)], ids=lambda v: str(v))
 def test_decode_kernel_variants_agree(torch, built_library, oracle, m, k, n, w_kn):
-    """Decode-shaped calls: the cluster kernel (k split over warps and cluster CTAs, summed through distributed shared memory;
-    every cluster size) and the k-split kernel (partial sums in scratch, added by the last CTA or by a second kernel: same
+    """Decode-shaped calls: the cluster kernels (k split over warps and / or cluster CTAs, summed through distributed shared
+    memory; every cluster size) and the k-split kernel (partial sums in scratch, added by the last CTA or by a second kernel: same
     bits both ways, also on repeated calls, since the tickets reset themselves) all match the oracle."""
     import gpt_b200
     rng = np.random.default_rng(m * 131 + k + n)
@@ -383,23 +385,32 @@ def test_decode_kernel_variants_agree(torch, built_library, oracle, m, k, n, w_k
                 be.device_unembedding_forward(y, dx, dw, 1, m, k, n)
                 be.synchronize()
                 return (y.cpu().numpy(),)
-        for cluster in ((16, 32, 8, 4, 1) if w_kn else ()):
+        # [k][n] weights: the per-warp cluster kernel at every row count (limit 64) and, beyond eight rows, the register-tiled
+        # cluster kernel (limit 8, the default), each at every cluster size
+        for cluster, row_limit in (((16, 8), (32, 8), (8, 8), (2, 8), (16, 64), (32, 64), (8, 64), (4, 64), (1, 64)) if w_kn else ()):
             be.set_option("skinny_cluster", cluster)
-            be.set_option("skinny_cluster_rows", 64)
+            be.set_option("skinny_cluster_rows", row_limit)
             first, again = run(), run()
             for got, again_, want in zip(first, again, ref):
-                check(f"cluster {cluster}", got, want, 0)
+                check(f"cluster {cluster} rows {row_limit}", got, want, 0)
                 assert np.array_equal(got, again_)
         if not w_kn:
-            first, again = run(), run()     # warp-per-row kernel (up to eight rows), else the k-split kernel
-            check("rowwise", first[0], ref[0], 0)
-            assert np.array_equal(first[0], again[0])
+            # [n][k] weights: warp-per-row kernel up to eight rows and register-tiled kernel beyond (defaults), then the
+            # warp-per-row kernel with row groups at every row count
+            for row_limit in (8, 64):
+                be.set_option("skinny_rowwise_rows", row_limit)
+                first, again = run(), run()
+                check(f"rowwise rows {row_limit}", first[0], ref[0], 0)
+                assert np.array_equal(first[0], again[0])
             be.set_option("skinny_rowwise", 0)
+            be.set_option("skinny_tile", 0)
         be.set_option("skinny_cluster", 0)
         results = []
         for fused in (1, -1, 1, 0):
             be.set_option("skinny_fused", fused)
             results.append(run())
+        be.set_option("skinny_pipelined", 0)     # 16-row groups: weight loads straight into registers
+        results.append(run())
         d.check_canaries()
         for got, want in zip(results[0], ref):
             check("k-split", got, want, 0)

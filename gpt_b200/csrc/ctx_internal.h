@@ -28,6 +28,7 @@ struct gptb200_ctx {
     int skinny_cluster = 16; // W stored [k][n]: one-launch kernel that splits k over a thread-block cluster of up to this many CTAs
                              // (0 = off; 16 = sixteen for narrow layers only; 32 = sixteen wherever k allows)
     int skinny_cluster_rows = 8;   // ... for calls with at most this many rows
+    int skinny_tile_rows = 0;      // that kernel's row tile beyond 32 rows: 0 or 64 = one tile of 64, 32 = row groups of 32
     bool skinny_tile = true;       // beyond that many rows: one-launch register-tiled cluster kernel (false: the k-split kernel)
     int decode_early_launch = 0;     // that kernel is launched with programmatic stream serialization: it prefetches weights while
                                        // its predecessor on the stream still runs (caller's promise: the predecessor does not write them)

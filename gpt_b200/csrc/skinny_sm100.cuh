@@ -296,7 +296,7 @@ decode_gemm_cluster_kernel(float *__restrict__ y, float *__restrict__ act, const
 // zero-padded), a thread TM/8 rows x 4 columns.  k is split over the S CTAs of a thread-block cluster (cluster shape
 // (1, S, 1)); the partial tiles meet through distributed shared memory in rank order, each CTA finishing 1/S of the rows
 // (bias, GELU).  No scratch, no second launch; results do not depend on timing.
-//   grid (ceil(n / 128), S); dynamic shared memory kTileStages * (32 * 128 + TM * 32) floats.
+//   grid (ceil(n / 128), S, ceil(m / TM)); dynamic shared memory kTileStages * (32 * 128 + TM * 32) floats.
 constexpr int kTileStages = 4;
 constexpr int kTileK = 32;
 
@@ -318,6 +318,13 @@ decode_tile_cluster_kernel(float *__restrict__ y, float *__restrict__ act, const
     const int S = gridDim.y, rank = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int col0 = blockIdx.x * 128;
+    {   // row group of this cluster (blockIdx.z)
+        const int row0 = blockIdx.z * TM;
+        x += size_t(row0) * K;
+        y += size_t(row0) * N;
+        if (act) act += size_t(row0) * N;
+        M = min(TM, M - row0);
+    }
     const int k_per_cta = (((K + S - 1) / S) + 3) & ~3;
     const int k_begin = min(K, rank * k_per_cta), k_end = min(K, k_begin + k_per_cta);
     const int chunks = (k_end - k_begin + kTileK - 1) / kTileK;
@@ -432,13 +439,13 @@ decode_tile_cluster_kernel(float *__restrict__ y, float *__restrict__ act, const
         const int m = e >> 5, gc = col0 + 4 * (e & 31);
         if (gc >= N) continue;
         float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int q0 = 0; q0 < S; q0 += 4) {   // up to four remote loads in flight
-            float4 v[4];
+        for (int q0 = 0; q0 < S; q0 += 8) {   // up to eight remote loads in flight, added in rank order
+            float4 v[8];
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
+            for (int j = 0; j < 8; ++j)
                 v[j] = q0 + j < S ? reinterpret_cast<const float4 *>(cluster.map_shared_rank(tile_smem, q0 + j))[e] : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
+            for (int j = 0; j < 8; ++j)
                 if (q0 + j < S) { sum.x += v[j].x; sum.y += v[j].y; sum.z += v[j].z; sum.w += v[j].w; }
         }
         if (bias) { sum.x += bias[gc]; sum.y += bias[gc + 1]; sum.z += bias[gc + 2]; sum.w += bias[gc + 3]; }   // bias need not be 16-byte aligned

@@ -63,6 +63,7 @@ int gptb200_ctx_set_stream(gptb200_ctx *ctx, void *cuda_stream);
  * "skinny_cluster_rows" (most rows of x for which that kernel is used: default 8),
  * "skinny_tile" (more rows than that, weight stored [k][n]: one-launch register-tiled kernel whose k split also runs over a
  * cluster: 1 = on (default), 0 = off (k-split kernel with partial sums in scratch)),
+ * "skinny_tile_rows" (that kernel's row tile beyond 32 rows: 0 or 64 = one 64-row tile (default), 32 = row groups of 32),
  * "skinny_pipelined" (the k-split kernel's 16-row groups fetch weights through a shared-memory ring: 1 = on (default), 0 = off),
  * "skinny_rowwise" (decode-shaped calls whose weight is stored [n][k] - the un-embedding, grad_x: one-launch kernel, a warp
  * per pair of weight rows and group of up to 16 rows of x: 1 = on (default), 0 = off (k-split kernel)),

@@ -390,6 +390,7 @@ def test_decode_kernel_variants_agree(torch, built_library, oracle, m, k, n, w_k
         for cluster, row_limit in (((16, 8), (32, 8), (8, 8), (2, 8), (16, 64), (32, 64), (8, 64), (4, 64), (1, 64)) if w_kn else ()):
             be.set_option("skinny_cluster", cluster)
             be.set_option("skinny_cluster_rows", row_limit)
+            be.set_option("skinny_tile_rows", 64 if cluster == 8 else 32 if cluster == 2 else 0)
             first, again = run(), run()
             for got, again_, want in zip(first, again, ref):
                 check(f"cluster {cluster} rows {row_limit}", got, want, 0)

@@ -219,7 +219,7 @@ decode_gemm_cluster_kernel(float *__restrict__ y, float *__restrict__ act, const
         for (int c = 0; c < 4; ++c) acc[m][c] = 0.0f;
     // Weight loads in flight per thread: the loop is one DRAM round trip per unrolled body (measured: 0.85 us per body with
     // eight loads, whatever n), so with few rows of x the registers go to loads: 16 k-rows per body up to two rows of x.
-    constexpr int kUnroll = MR <= 2 ? 4 : MR <= 4 ? 3 : MR <= 8 ? 2 : 1;
+    constexpr int kUnroll = MR <= 2 ? 4 : MR <= 8 ? 3 : 1;
     // Programmatic dependent launch (early_launch): the next kernel on the stream may start as soon as every CTA of this one
     // is running, and this kernel may have started while its predecessor was still running.  Only the weights (and, later,
     // the bias) are read before griddepcontrol.wait, which returns once the predecessor has completed and its writes are

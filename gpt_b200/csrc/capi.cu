@@ -196,7 +196,7 @@ int launch_decode_cluster(gptb200_ctx *ctx, const GemmCall &c, int cluster, int 
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ctx->decode_early_launch ? 2 : 1;
-    CUDA_TRY(ctx, cudaLaunchKernelEx(&cfg, kernel, c.out, c.act, c.a, c.b, c.bias, c.M, c.N, c.K, ctx->decode_early_launch ? 1 : 0));
+    CUDA_TRY(ctx, cudaLaunchKernelEx(&cfg, kernel, c.out, c.act, c.a, c.b, c.bias, c.M, c.N, c.K, ctx->decode_early_launch ? 1 : 0, ctx->skinny_push ? 1 : 0));
     ctx->launches++;
     return GPTB200_OK;
 }
@@ -609,6 +609,10 @@ int gptb200_ctx_set_option(gptb200_ctx *ctx, const char *key, int value)
     if (!strcmp(key, "skinny_rows")) {
         if (value < 0 || value > kPlanSkinnyMaxRows) return fail(ctx, GPTB200_ERR_INVALID_ARG, "skinny_rows must be in [0, %d]", kPlanSkinnyMaxRows);
         ctx->skinny_rows = value;
+        return GPTB200_OK;
+    }
+    if (!strcmp(key, "skinny_push")) {
+        ctx->skinny_push = value != 0;
         return GPTB200_OK;
     }
     if (!strcmp(key, "skinny_tile_rows")) {

@@ -194,13 +194,20 @@ constexpr int kDecodeThreads = 256;
 template <int MR>
 __global__ void __launch_bounds__(kDecodeThreads)
 decode_gemm_cluster_kernel(float *__restrict__ y, float *__restrict__ act, const float *__restrict__ x, const float *__restrict__ w,
-                           const float *__restrict__ bias, int M, int N, int K, int early_launch)
+                           const float *__restrict__ bias, int M, int N, int K, int early_launch, int push)
 {
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
-    constexpr int RH = MR < 8 ? MR : 8;                  // rows per in-CTA reduction pass
+    constexpr int RH = MR < 4 ? MR : 4;                  // rows per in-CTA reduction pass
+    constexpr int kBlocks = (MR * 128 + 255) / 256;      // groups of 256 outputs
     __shared__ __align__(16) float red[8][RH][128];      // per warp: partial sums of RH rows x 128 columns
-    __shared__ __align__(16) float cta_sum[MR * 128];    // this CTA's sums, read by the whole cluster
+    __shared__ __align__(16) float cta_sum[MR * 128];    // this CTA's sums, read by the whole cluster (pull form)
+    __shared__ __align__(16) float recv[(kBlocks + 15) * 256];   // push form: [S ranks][the output groups this CTA finishes]
+    // Push form: every CTA stores its sums straight into the shared memory of the CTA that finishes them, ONE cluster barrier
+    // later each CTA adds what it received (local reads) and leaves - no remote round trip, no barrier before exit.  Remote
+    // shared memory may only be touched once its CTA runs: all CTAs arrive on the cluster barrier first thing and wait for
+    // that phase just before the first remote store, by which time it has long completed.
+    if (push) cluster.barrier_arrive();
     const int S = gridDim.y;
     const int rank = blockIdx.y;                         // cluster shape (1, S, 1): the rank inside the cluster
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -269,8 +276,32 @@ decode_gemm_cluster_kernel(float *__restrict__ y, float *__restrict__ act, const
             cta_sum[(h + j) * 128 + c] = s;
         }
     }
+    if (push) {
+        // group g of 256 outputs is finished by rank g % S, which keeps it as its (g / S)-th group
+        const int groups = (rows * 128 + 255) >> 8;
+        const int per_owner = ((groups + S - 1) / S) * 256;
+        __syncthreads();          // cta_sum complete
+        cluster.barrier_wait();   // every CTA of the cluster is running
+        for (int e = threadIdx.x; e < rows * 128; e += kDecodeThreads) {
+            const int g = e >> 8;
+            cluster.map_shared_rank(recv, g % S)[rank * per_owner + (g / S) * 256 + (e & 255)] = cta_sum[e];
+        }
+        cluster.sync();           // all parts have arrived; nothing remote is touched after this
+        for (int g = rank; g < groups; g += S) {
+            const int e = g * 256 + threadIdx.x;
+            const int m = e >> 7, gc = blockIdx.x * 128 + (e & 127);
+            if (e >= rows * 128 || gc >= N) continue;
+            const float *part = recv + (g / S) * 256 + threadIdx.x;
+            float s = 0.0f;
+            for (int q = 0; q < S; ++q) s += part[q * per_owner];   // rank order
+            if (bias) s += bias[gc];
+            y[size_t(row0 + m) * N + gc] = s;
+            if (act) act[size_t(row0 + m) * N + gc] = gelu_tanh(s);
+        }
+        return;
+    }
     cluster.sync();
-    // the S CTAs of the cluster, rank order; this CTA finishes every S-th group of 256 outputs
+    // pull form: the S CTAs of the cluster, rank order; this CTA finishes every S-th group of 256 outputs
     for (int e = rank * kDecodeThreads + threadIdx.x; e < rows * 128; e += S * kDecodeThreads) {
         const int m = e >> 7, gc = blockIdx.x * 128 + (e & 127);
         if (gc >= N) continue;

@@ -60,6 +60,8 @@ int gptb200_ctx_set_stream(gptb200_ctx *ctx, void *cuda_stream);
  * the CTAs of a thread-block cluster and adds the parts through distributed shared memory; value = largest cluster, 0 (off:
  * k-split kernel with partial sums in scratch), 1, 2, 4, 8, 16 (default: sixteen only for layers too narrow to fill half of the
  * SMs with clusters of eight) or 32 (sixteen wherever k allows)),
+ * "skinny_push" (that kernel's cluster sum: 1 = every CTA stores its part into the shared memory of the CTA that finishes it
+ * (default), 0 = the finishing CTA loads the parts; same bits either way),
  * "skinny_cluster_rows" (most rows of x for which that kernel is used: default 8),
  * "skinny_tile" (more rows than that, weight stored [k][n]: one-launch register-tiled kernel whose k split also runs over a
  * cluster: 1 = on (default), 0 = off (k-split kernel with partial sums in scratch)),

@@ -391,6 +391,7 @@ def test_decode_kernel_variants_agree(torch, built_library, oracle, m, k, n, w_k
             be.set_option("skinny_cluster", cluster)
             be.set_option("skinny_cluster_rows", row_limit)
             be.set_option("skinny_tile_rows", 64 if cluster == 8 else 32 if cluster == 2 else 0)
+            be.set_option("skinny_push", 0 if cluster in (4, 32) else 1)
             first, again = run(), run()
             for got, again_, want in zip(first, again, ref):
                 check(f"cluster {cluster} rows {row_limit}", got, want, 0)

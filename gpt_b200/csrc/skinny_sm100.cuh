@@ -225,8 +225,8 @@ decode_gemm_cluster_kernel(float *__restrict__ y, float *__restrict__ act, const
 #pragma unroll
         for (int c = 0; c < 4; ++c) acc[m][c] = 0.0f;
     // Weight loads in flight per thread: the loop is one DRAM round trip per unrolled body (measured: 0.85 us per body with
-    // eight loads, whatever n), so with few rows of x the registers go to loads: 16 k-rows per body up to two rows of x.
-    constexpr int kUnroll = MR <= 2 ? 4 : MR <= 8 ? 3 : 1;
+    // eight loads, whatever n), so with few rows of x the registers go to loads: 24 k-rows per body up to two rows of x (a whole warp share of k = 3072 in a cluster of 16), 12 up to eight.
+    constexpr int kUnroll = MR <= 2 ? 6 : MR <= 8 ? 3 : 1;
     // Programmatic dependent launch (early_launch): the next kernel on the stream may start as soon as every CTA of this one
     // is running, and this kernel may have started while its predecessor was still running.  Only the weights (and, later,
     // the bias) are read before griddepcontrol.wait, which returns once the predecessor has completed and its writes are

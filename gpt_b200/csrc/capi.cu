@@ -168,6 +168,34 @@ int launch_skinny(gptb200_ctx *ctx, int mr, dim3 grid, float *partial, const Gem
     return GPTB200_OK;
 }
 
+// Clusters of 16 CTAs are a non-portable size: whether this device (or this slice of it) can schedule one is asked once per
+// context, for the most demanding of the decode kernels; if not, clusters stay at eight.
+bool cluster16_allowed(gptb200_ctx *ctx)
+{
+    if (ctx->cluster16 < 0) {
+        auto kernel = decode_tile_cluster_kernel<64, false>;
+        const size_t smem = size_t(kTileStages) * (kTileK * 128 + 64 * kTileK) * sizeof(float);
+        int clusters = 0;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(1, 16, 1);
+        cfg.blockDim = dim3(kDecodeThreads);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = 16;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        const bool ok = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) == cudaSuccess &&
+                        cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess &&
+                        cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) == cudaSuccess && clusters >= 1;
+        if (!ok) cudaGetLastError();   // a refused query must not surface as the next launch's error
+        ctx->cluster16 = ok ? 1 : 0;
+    }
+    return ctx->cluster16 == 1;
+}
+
 // One-launch cluster kernel for decode-shaped linear layers with W stored [k][n] (see decode_gemm_cluster_kernel).
 template <int MR>
 int launch_decode_cluster(gptb200_ctx *ctx, const GemmCall &c, int cluster, int groups)
@@ -264,7 +292,7 @@ int run_skinny(gptb200_ctx *ctx, const GemmCall &c, const GemmPlan &pl)
         int cluster = 1;
         const long long blocks = 1LL * ((c.N + 127) / 128) * groups;
         while (cluster * 2 <= std::min(ctx->skinny_cluster, 8) && c.K / (cluster * 2 * 8) >= 4 && blocks * cluster * 2 <= 4LL * ctx->num_sms) cluster *= 2;
-        if (cluster == 8 && ctx->skinny_cluster >= 16 && c.K / (16 * 8) >= 4 && (blocks * 16 <= ctx->num_sms || ctx->skinny_cluster >= 32)) cluster = 16;
+        if (cluster == 8 && ctx->skinny_cluster >= 16 && c.K / (16 * 8) >= 4 && (blocks * 16 <= ctx->num_sms || ctx->skinny_cluster >= 32) && cluster16_allowed(ctx)) cluster = 16;
         switch (mr) {
             case 1: return launch_decode_cluster<1>(ctx, c, cluster, groups);
             case 2: return launch_decode_cluster<2>(ctx, c, cluster, groups);
@@ -278,7 +306,7 @@ int run_skinny(gptb200_ctx *ctx, const GemmCall &c, const GemmPlan &pl)
         int cluster = 1;
         const long long blocks = (c.N + 127) / 128;
         while (cluster * 2 <= std::min(ctx->skinny_cluster, 8) && c.K / (cluster * 2) >= kTileK && blocks * cluster * 2 <= 2LL * ctx->num_sms) cluster *= 2;
-        if (cluster == 8 && ctx->skinny_cluster >= 16 && c.K / 16 >= kTileK && (blocks * 16 <= ctx->num_sms || ctx->skinny_cluster >= 32)) cluster = 16;
+        if (cluster == 8 && ctx->skinny_cluster >= 16 && c.K / 16 >= kTileK && (blocks * 16 <= ctx->num_sms || ctx->skinny_cluster >= 32) && cluster16_allowed(ctx)) cluster = 16;
         if (c.M <= 16) return launch_decode_tile<16, false>(ctx, c, cluster);
         // beyond 32 rows one 64-row tile: two row groups of 32 (option "skinny_tile_rows" = 32) were measured slower even where
         // they double the number of busy SMs (decode step at 64 rows: 0.888 ms against 0.944 for the narrow layers only, 1.007 for all)

@@ -27,6 +27,7 @@ struct gptb200_ctx {
     int skinny_rows = 0; // most rows it takes: 0 = the planner's limit (64)
     int skinny_cluster = 16; // W stored [k][n]: one-launch kernel that splits k over a thread-block cluster of up to this many CTAs
                              // (0 = off; 16 = sixteen for narrow layers only; 32 = sixteen wherever k allows)
+    int cluster16 = -1;            // can this device schedule a cluster of 16 CTAs of the decode kernels: -1 = not asked yet
     bool skinny_push = true;       // ... whose CTAs store their sums into the finishing CTA's shared memory (false: the finishing CTA loads them)
     int skinny_cluster_rows = 8;   // ... for calls with at most this many rows
     int skinny_tile_rows = 0;      // that kernel's row tile beyond 32 rows: 0 or 64 = one tile of 64, 32 = row groups of 32

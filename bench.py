@@ -521,7 +521,8 @@ def run_decode(args):
                config=dict(workload="GPT-2 124M decode step, linear layers only (49 GEMMs with m = batch)", mode=args.mode, options=options,
                            weight_bytes=weight_bytes, l2="494 MB of weights per step exceed the 126 MB L2"),
                per_batch=results,
-               roofline=dict(bound="hbm", achieved=r8["gbs"], peak=peaks["hbm_gbs"], unit="GB/s", frac=r8["hbm_frac"], traffic=None,
+               roofline=dict(bound="hbm", achieved=r8["gbs"], peak=peaks["hbm_gbs"], unit="GB/s", frac=r8["hbm_frac"], traffic=496.4e6,
+                             traffic_note="dram read+write bytes of the 49 kernels of a batch-1 step from ncu (profiles/decode_step_batch1_ncu.md); algorithmic 494.27e6",
                              note="algorithmic bytes = fp32 weights read once per step (494.27 MB); batch 8", peak_source="of measured (MEASURED_PEAKS.json copy bandwidth)"),
                gpu_launches=int(launches), clocks=clocks)
     print(json.dumps(out), flush=True)

@@ -1,19 +1,27 @@
-// Weight-streaming GEMM for decode-shaped calls (m <= 64 rows): y[m x n] = x[m x k] . W (+ bias, GELU).
+// Decode-shaped products (m <= 64 rows): y[m x n] = x[m x k] . W (+ bias, GELU), fp32 FMAs, no TF32 rounding in either mode.
 //
-// With so few rows the operation is bound by reading the weight matrix once from HBM (4*k*n bytes; the
-// activations and outputs are negligible), so the kernel is organised around the weight stream, not around
-// tensor-core tiles: every thread owns output columns, keeps one fp32 accumulator per row and column in
-// registers, reads its part of the weight matrix exactly once with 16-byte loads and takes the activations from
-// a shared-memory copy (broadcast reads).  A CTA covers up to 16 rows; with more rows blockIdx.z selects the group of
-// 16 (the groups of a column block run at about the same time, so the weights still come from HBM once and from L2 for
-// the other groups; at 64 rows the fp32 FMAs, not the weight stream, set the time).  The k range is split over blockIdx.y so that even a 768-column layer
-// puts several hundred CTAs in flight; partial sums go to scratch and are added in a fixed order (split ascending),
-// then bias / GELU are applied.  Who adds them: with `tickets` the CTA that finishes a column block last (one
-// atomic ticket per column block, reset by that CTA, so the array stays zero between launches and under CUDA-graph
-// replay) - one launch per GEMM, which matters because a decode step is ~50 GEMMs of a few microseconds each;
-// without `tickets` the separate skinny_finish_kernel, used when splits * rows is large enough that one CTA
-// re-reading all partial sums would take longer than a second launch.  Both give the same bits.
-// Plain fp32 FMAs: no TF32 rounding in either precision mode.
+// With so few rows the operation is bound by reading the weight matrix once from HBM (4*k*n bytes; activations and outputs
+// are negligible) and, for the 2 - 10 MB layers of a small model, by latencies: launch, one DRAM round trip, barriers.  The
+// kernels are therefore organised around the weight stream, not around tensor-core tiles, and all but the fallback need one
+// launch and no scratch:
+//
+//   decode_gemm_cluster_kernel   W [k][n], up to 8 rows (16 behind an option): k split over the 8 warps of a CTA and the CTAs
+//                                of a thread-block cluster; sums through (distributed) shared memory
+//   rowwise_gemv_kernel          W [n][k], up to 8 rows (64 behind an option): a warp per pair of weight rows
+//   decode_tile_cluster_kernel   either layout, 9 - 64 rows: register-tiled TM x 128 tile per CTA, cp.async ring, k split over
+//                                a cluster
+//   skinny_gemm_kernel           the fallback behind the options (described next), + skinny_finish_kernel
+//
+// skinny_gemm_kernel: every thread owns output columns, keeps one fp32 accumulator per row and column in registers, reads
+// its part of the weight matrix exactly once with 16-byte loads and takes the activations from a shared-memory copy
+// (broadcast reads).  A CTA covers up to 16 rows; with more rows blockIdx.z selects the group of 16 (the groups of a column
+// block run at about the same time, so the weights still come from HBM once and from L2 for the other groups).  The k range
+// is split over blockIdx.y so that even a 768-column layer puts several hundred CTAs in flight; partial sums go to scratch
+// and are added in a fixed order (split ascending), then bias / GELU are applied.  Who adds them: with `tickets` the CTA that
+// finishes a column block last (one atomic ticket per column block, reset by that CTA, so the array stays zero between
+// launches and under CUDA-graph replay); without `tickets` the separate skinny_finish_kernel, used beyond two splits, where
+// one CTA re-reading all partial sums one dependent load after the other takes longer than a second launch.  Both give the
+// same bits.
 //
 //   W_KN = true : W stored [k][n] (linear layers):   thread = 4 adjacent columns, coalesced 16-byte loads along n
 //   W_KN = false: W stored [n][k] (tied un-embedding): thread = 1 column, 16-byte loads along its own row

@@ -26,7 +26,7 @@ MODE_TF32 = 1
 EXPORTED_SYMBOLS = [
     "gptb200_ctx_create", "gptb200_ctx_destroy", "gptb200_ctx_set_mode", "gptb200_ctx_get_mode",
     "gptb200_ctx_set_stream", "gptb200_ctx_set_option", "gptb200_ctx_synchronize", "gptb200_ctx_launch_count", "gptb200_ctx_read_trace",
-    "gptb200_status_string", "gptb200_last_error", "gptb200_plan_gemm", "gptb200_selftest_wait_timeout",
+    "gptb200_status_string", "gptb200_last_error", "gptb200_plan_gemm", "gptb200_plan_decode", "gptb200_selftest_wait_timeout",
     "gptb200_linear_forward", "gptb200_linear_backward", "gptb200_linear_backward_weights", "gptb200_linear_backward_input",
     "gptb200_gelu_backward",
     "gptb200_unembed_forward", "gptb200_unembed_backward",
@@ -70,6 +70,7 @@ def load_library(path: str | None = None) -> ctypes.CDLL:
         "gptb200_ctx_launch_count": (ctypes.c_longlong, [vp]),
         "gptb200_selftest_wait_timeout": (i, [vp, i]),
         "gptb200_plan_gemm": (i, [i, i, i, i, i, i, i, i, ctypes.POINTER(i)]),
+        "gptb200_plan_decode": (i, [i, i, i, i, i, i, ctypes.POINTER(i)]),
         "gptb200_status_string": (ctypes.c_char_p, [i]),
         "gptb200_last_error": (ctypes.c_char_p, [vp]),
         "gptb200_linear_forward": (i, [vp, fp, fp, fp, fp, fp, i, i, i, i]),
@@ -129,6 +130,21 @@ def plan_gemm(num_sms: int, m: int, n: int, k: int, a_mn: bool, b_mn: bool, has_
     keys = ["kernel", "tile_n", "tiles_m", "tiles_n", "splits", "k_per_split", "grid", "scratch_kib"]
     d = dict(zip(keys, list(out)))
     d["kernel"] = PLAN_KERNELS[d["kernel"]]
+    return d
+
+
+DECODE_KERNELS = {0: "k_split", 1: "warp_cluster", 2: "tile_cluster", 3: "rowwise"}
+
+
+def plan_decode(num_sms: int, m: int, n: int, k: int, w_kn: bool, has_epilogue: bool = False) -> dict:
+    """Which decode kernel a call of at most 64 rows runs (host logic only); see gptb200_plan_decode in include/gptb200.h."""
+    lib = load_library()
+    out = (ctypes.c_int * 4)()
+    rc = lib.gptb200_plan_decode(num_sms, m, n, k, int(w_kn), int(has_epilogue), out)
+    if rc != 0:
+        raise GptB200Error(rc, "gptb200_plan_decode")
+    d = dict(zip(["kernel", "rows", "groups", "cluster"], list(out)))
+    d["kernel"] = DECODE_KERNELS[d["kernel"]]
     return d
 
 

@@ -281,63 +281,42 @@ int launch_rowwise(gptb200_ctx *ctx, const GemmCall &c)
 // HBM-bound: 4*k*n bytes per call.
 int run_skinny(gptb200_ctx *ctx, const GemmCall &c, const GemmPlan &pl)
 {
-    int mr = 1;
-    while (mr < c.M && mr < 16) mr *= 2;
-    const int groups = (c.M + mr - 1) / mr;   // row groups of 16 beyond 16 rows
     const bool w_kn = c.b_mn;  // W stored [k][n]
-    if (w_kn && ctx->skinny_cluster > 0 && c.M <= ctx->skinny_cluster_rows) {
-        // largest cluster (power of two, at most the option) that leaves every warp at least four k-rows and does not
-        // put more than ~four CTAs on each SM; the non-portable size 16 only for layers so narrow that clusters of eight
-        // would occupy less than half of the SMs (n = 768: 48 CTAs)
-        int cluster = 1;
-        const long long blocks = 1LL * ((c.N + 127) / 128) * groups;
-        while (cluster * 2 <= std::min(ctx->skinny_cluster, 8) && c.K / (cluster * 2 * 8) >= 4 && blocks * cluster * 2 <= 4LL * ctx->num_sms) cluster *= 2;
-        if (cluster == 8 && ctx->skinny_cluster >= 16 && c.K / (16 * 8) >= 4 && (blocks * 16 <= ctx->num_sms || ctx->skinny_cluster >= 32) && cluster16_allowed(ctx)) cluster = 16;
-        switch (mr) {
-            case 1: return launch_decode_cluster<1>(ctx, c, cluster, groups);
-            case 2: return launch_decode_cluster<2>(ctx, c, cluster, groups);
-            case 4: return launch_decode_cluster<4>(ctx, c, cluster, groups);
-            case 8: return launch_decode_cluster<8>(ctx, c, cluster, groups);
-            default: return launch_decode_cluster<16>(ctx, c, cluster, groups);
+    DecodeOptions o;
+    o.cluster = ctx->skinny_cluster; o.cluster_rows = ctx->skinny_cluster_rows;
+    o.tile = ctx->skinny_tile; o.tile_rows = ctx->skinny_tile_rows;
+    o.rowwise = ctx->skinny_rowwise; o.rowwise_rows = ctx->skinny_rowwise_rows;
+    o.cluster16_ok = ctx->skinny_cluster >= 16 ? cluster16_allowed(ctx) : false;
+    const DecodePlan d = plan_decode(c.M, c.N, c.K, w_kn, c.bias != nullptr || c.act != nullptr, ctx->num_sms, o);
+    if (d.kernel == DECODE_WARP_CLUSTER) {
+        switch (d.rows) {
+            case 1: return launch_decode_cluster<1>(ctx, c, d.cluster, d.groups);
+            case 2: return launch_decode_cluster<2>(ctx, c, d.cluster, d.groups);
+            case 4: return launch_decode_cluster<4>(ctx, c, d.cluster, d.groups);
+            case 8: return launch_decode_cluster<8>(ctx, c, d.cluster, d.groups);
+            default: return launch_decode_cluster<16>(ctx, c, d.cluster, d.groups);
         }
     }
-    if (w_kn && ctx->skinny_tile && c.M > ctx->skinny_cluster_rows && ctx->skinny_cluster > 0) {
-        // cluster size: as above, with at least one 32-row chunk of k per CTA
-        int cluster = 1;
-        const long long blocks = (c.N + 127) / 128;
-        while (cluster * 2 <= std::min(ctx->skinny_cluster, 8) && c.K / (cluster * 2) >= kTileK && blocks * cluster * 2 <= 2LL * ctx->num_sms) cluster *= 2;
-        if (cluster == 8 && ctx->skinny_cluster >= 16 && c.K / 16 >= kTileK && (blocks * 16 <= ctx->num_sms || ctx->skinny_cluster >= 32) && cluster16_allowed(ctx)) cluster = 16;
-        if (c.M <= 16) return launch_decode_tile<16, false>(ctx, c, cluster);
-        // beyond 32 rows one 64-row tile: two row groups of 32 (option "skinny_tile_rows" = 32) were measured slower even where
-        // they double the number of busy SMs (decode step at 64 rows: 0.888 ms against 0.944 for the narrow layers only, 1.007 for all)
-        if (c.M <= 32 || ctx->skinny_tile_rows == 32) return launch_decode_tile<32, false>(ctx, c, cluster);
-        return launch_decode_tile<64, false>(ctx, c, cluster);
+    if (d.kernel == DECODE_TILE_CLUSTER) {
+        if (w_kn) {
+            if (d.rows == 16) return launch_decode_tile<16, false>(ctx, c, d.cluster);
+            if (d.rows == 32) return launch_decode_tile<32, false>(ctx, c, d.cluster);
+            return launch_decode_tile<64, false>(ctx, c, d.cluster);
+        }
+        if (d.rows == 16) return launch_decode_tile<16, true>(ctx, c, d.cluster);
+        if (d.rows == 32) return launch_decode_tile<32, true>(ctx, c, d.cluster);
+        return launch_decode_tile<64, true>(ctx, c, d.cluster);
     }
-    if (!w_kn && ctx->skinny_tile && c.M > ctx->skinny_rowwise_rows && ctx->skinny_cluster > 0 && !c.bias && !c.act) {
-        // W stored [n][k], more rows than the warp-per-row kernel takes: the same tile kernel; k is split over a cluster only
-        // when the column tiles alone leave SMs idle
-        int cluster = 1;
-        const long long blocks = (c.N + 127) / 128;
-        while (cluster * 2 <= std::min(ctx->skinny_cluster, 8) && c.K / (cluster * 2) >= 4 * kTileK && blocks * cluster * 2 <= 2LL * ctx->num_sms) cluster *= 2;
-        if (c.M <= 16) return launch_decode_tile<16, true>(ctx, c, cluster);
-        if (c.M <= 32) return launch_decode_tile<32, true>(ctx, c, cluster);
-        return launch_decode_tile<64, true>(ctx, c, cluster);
-    }
-    if (!w_kn && ctx->skinny_rowwise && !c.bias && !c.act && c.M <= ctx->skinny_rowwise_rows) {
-        // groups of up to 16 rows of x (8 when 16 rows of x exceed 48 KiB of shared memory); beyond one group the weights are
-        // re-read from L2 once per group
-        int rows = mr;
-        while (rows > 1 && 1LL * rows * c.K > 12288) rows /= 2;
-        if (1LL * rows * c.K <= 12288 && (rows >= 8 || rows == mr)) {
-            switch (rows) {
-                case 1: return launch_rowwise<1>(ctx, c);
-                case 2: return launch_rowwise<2>(ctx, c);
-                case 4: return launch_rowwise<4>(ctx, c);
-                case 8: return launch_rowwise<8>(ctx, c);
-                default: return launch_rowwise<16>(ctx, c);
-            }
+    if (d.kernel == DECODE_ROWWISE) {
+        switch (d.rows) {
+            case 1: return launch_rowwise<1>(ctx, c);
+            case 2: return launch_rowwise<2>(ctx, c);
+            case 4: return launch_rowwise<4>(ctx, c);
+            case 8: return launch_rowwise<8>(ctx, c);
+            default: return launch_rowwise<16>(ctx, c);
         }
     }
+    const int mr = d.rows, groups = d.groups;   // k-split kernel
     const int rc = ensure_workspace(ctx, pl.workspace_bytes);
     if (rc != GPTB200_OK) return rc;
     const dim3 grid(pl.tiles_n, pl.splits, groups);
@@ -749,6 +728,14 @@ int gptb200_plan_gemm(int num_sms, int m, int n, int k, int a_mn_major, int b_mn
     const int kb_each = p.kernel == KERNEL_PAIR ? static_cast<int>((p.sk_total + pairs - 1) / pairs) : p.kb_per_split;
     const int out[8] = {p.kernel, p.tile_n, p.tiles_m, p.tiles_n, p.kernel == KERNEL_PAIR ? p.sk_max_share : p.splits, kb_each, p.grid, static_cast<int>(std::min<long long>(ws >> 10, 0x7fffffff))};
     for (int i = 0; i < 8; ++i) plan8[i] = out[i];
+    return GPTB200_OK;
+}
+
+int gptb200_plan_decode(int num_sms, int m, int n, int k, int w_kn_major, int has_epilogue, int *plan4)
+{
+    if (!plan4 || num_sms <= 0 || m <= 0 || n <= 0 || k <= 0) return GPTB200_ERR_INVALID_ARG;
+    const DecodePlan d = plan_decode(m, n, k, w_kn_major != 0, has_epilogue != 0, num_sms, DecodeOptions{});
+    plan4[0] = d.kernel; plan4[1] = d.rows; plan4[2] = d.groups; plan4[3] = d.cluster;
     return GPTB200_OK;
 }
 

@@ -74,6 +74,92 @@ inline int plan_splits(const GemmPlanInput &in, long long tiles, int num_kb, boo
     return best;
 }
 
+// ---- decode-shaped calls (KERNEL_SKINNY): which of the weight-streaming kernels runs, and its launch shape ------------------
+enum DecodeKernelKind : int {
+    DECODE_KSPLIT = 0,        // skinny_gemm_kernel (+ finish): k split over CTAs, partial sums in scratch
+    DECODE_WARP_CLUSTER = 1,  // decode_gemm_cluster_kernel: W [k][n], k split over warps and cluster CTAs
+    DECODE_TILE_CLUSTER = 2,  // decode_tile_cluster_kernel: register-tiled, k split over a cluster
+    DECODE_ROWWISE = 3,       // rowwise_gemv_kernel: W [n][k], a warp per pair of weight rows
+};
+
+struct DecodeOptions {
+    int cluster = 16;        // largest cluster: 0 off, 1 .. 8, 16 = sixteen for narrow layers only, 32 = sixteen wherever k allows
+    int cluster_rows = 8;    // most rows for the per-warp cluster kernel
+    bool tile = true;        // register-tiled kernel beyond that
+    int tile_rows = 0;       // its row tile beyond 32 rows: 0 / 64 = one tile of 64, 32 = row groups of 32
+    bool rowwise = true;     // W [n][k]: warp-per-row kernel ...
+    int rowwise_rows = 8;    // ... up to this many rows
+    bool cluster16_ok = true;   // the device can schedule a cluster of 16 CTAs
+};
+
+struct DecodePlan {
+    int kernel;     // DecodeKernelKind
+    int rows;       // rows of x per CTA (per-warp kernel: MR; tiled kernel: TM; row-wise kernel: MR; k-split: MR)
+    int groups;     // row groups (blockIdx.z, or blockIdx.x of the row-wise kernel)
+    int cluster;    // CTAs per cluster (1 for the kernels without clusters)
+};
+
+constexpr int kPlanTileK = 32;   // k-rows per stage of the tiled kernel
+
+// w_kn: W stored [k][n] (linear layers); else [n][k] (un-embedding, grad_x).  has_epilogue: bias and / or GELU output.
+inline DecodePlan plan_decode(int M, int N, int K, bool w_kn, bool has_epilogue, int num_sms, const DecodeOptions &o)
+{
+    DecodePlan d{};
+    int mr = 1;
+    while (mr < M && mr < 16) mr *= 2;
+    d.kernel = DECODE_KSPLIT;
+    d.rows = mr;
+    d.groups = (M + mr - 1) / mr;
+    d.cluster = 1;
+    const auto sixteen = [&](long long blocks, bool k_ok) {
+        return o.cluster >= 16 && k_ok && (blocks * 16 <= num_sms || o.cluster >= 32) && o.cluster16_ok;
+    };
+    if (w_kn && o.cluster > 0 && M <= o.cluster_rows) {
+        // largest cluster (power of two, at most the option) that leaves every warp at least four k-rows and does not put
+        // more than ~four CTAs on each SM; the non-portable size 16 only for layers so narrow that clusters of eight would
+        // occupy less than half of the SMs (n = 768: 48 CTAs)
+        d.kernel = DECODE_WARP_CLUSTER;
+        const long long blocks = 1LL * ((N + 127) / 128) * d.groups;
+        while (d.cluster * 2 <= std::min(o.cluster, 8) && K / (d.cluster * 2 * 8) >= 4 && blocks * d.cluster * 2 <= 4LL * num_sms) d.cluster *= 2;
+        if (d.cluster == 8 && sixteen(blocks, K / (16 * 8) >= 4)) d.cluster = 16;
+        return d;
+    }
+    if (w_kn && o.tile && o.cluster > 0 && M > o.cluster_rows) {
+        // as above, with at least one 32-row chunk of k per CTA.  Beyond 32 rows one 64-row tile: two row groups of 32 were
+        // measured slower even where they double the number of busy SMs.
+        d.kernel = DECODE_TILE_CLUSTER;
+        const long long blocks = (N + 127) / 128;
+        while (d.cluster * 2 <= std::min(o.cluster, 8) && K / (d.cluster * 2) >= kPlanTileK && blocks * d.cluster * 2 <= 2LL * num_sms) d.cluster *= 2;
+        if (d.cluster == 8 && sixteen(blocks, K / 16 >= kPlanTileK)) d.cluster = 16;
+        d.rows = M <= 16 ? 16 : (M <= 32 || o.tile_rows == 32) ? 32 : 64;
+        d.groups = (M + d.rows - 1) / d.rows;
+        return d;
+    }
+    if (!w_kn && o.rowwise && !has_epilogue && M <= o.rowwise_rows) {
+        // groups of up to 16 rows of x (fewer when they exceed 48 KiB of shared memory); beyond one group the weights are
+        // re-read from L2 once per group
+        int rows = mr;
+        while (rows > 1 && 1LL * rows * K > 12288) rows /= 2;
+        if (1LL * rows * K <= 12288 && (rows >= 8 || rows == mr)) {
+            d.kernel = DECODE_ROWWISE;
+            d.rows = rows;
+            d.groups = (M + rows - 1) / rows;
+            return d;
+        }
+    }
+    if (!w_kn && o.tile && o.cluster > 0 && !has_epilogue && M > o.rowwise_rows) {
+        // W [n][k], more rows than the warp-per-row kernel takes: the tiled kernel; k is split over a cluster only when the
+        // column tiles alone leave SMs idle
+        d.kernel = DECODE_TILE_CLUSTER;
+        const long long blocks = (N + 127) / 128;
+        while (d.cluster * 2 <= std::min(o.cluster, 8) && K / (d.cluster * 2) >= 4 * kPlanTileK && blocks * d.cluster * 2 <= 2LL * num_sms) d.cluster *= 2;
+        d.rows = M <= 16 ? 16 : M <= 32 ? 32 : 64;
+        d.groups = 1;
+        return d;
+    }
+    return d;
+}
+
 inline GemmPlan plan_gemm(const GemmPlanInput &in)
 {
     GemmPlan p{};

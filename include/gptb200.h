@@ -103,6 +103,11 @@ int gptb200_selftest_wait_timeout(gptb200_ctx *ctx, int limit_us);
  * largest number of CTA pairs that work on one 256 x 256 tile (1: every pair computes whole tiles) and the next field the
  * k-blocks per CTA pair. */
 int gptb200_plan_gemm(int num_sms, int m, int n, int k, int a_mn_major, int b_mn_major, int has_epilogue, int accumulate, int *plan8);
+/* For a call that gptb200_plan_gemm sends to the weight-streaming kernels (kernel 3: at most 64 rows): which of them runs with
+ * default options, host logic only.  w_kn_major: the weight is stored [k][n] (linear layers) rather than [n][k] (un-embedding,
+ * grad_x).  plan4 = {kernel (0 k-split with scratch, 1 per-warp cluster kernel, 2 register-tiled cluster kernel, 3 warp per
+ * weight-row pair), rows of x per CTA, row groups, CTAs per cluster}; clusters of 16 are assumed to be schedulable. */
+int gptb200_plan_decode(int num_sms, int m, int n, int k, int w_kn_major, int has_epilogue, int *plan4);
 const char *gptb200_status_string(int status);
 const char *gptb200_last_error(const gptb200_ctx *ctx);
 

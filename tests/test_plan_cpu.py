@@ -89,3 +89,40 @@ def test_plan_invariants_over_a_sweep(plan, sms):
                 assert p["tile_n"] in (128, 256)
             if p["kernel"] == "skinny":
                 assert m <= 64 and p["tiles_m"] == (m + 15) // 16 and not acc and p["splits"] * p["k_per_split"] >= k and p["k_per_split"] % 4 == 0
+
+
+def test_decode_kernel_choice_for_gpt2_124m():
+    """Which weight-streaming kernel a decode-shaped call runs (gptb200_plan_decode, default options)."""
+    import gpt_b200
+    D, F, V = 768, 3072, 50304
+    pd = lambda *a, **k: gpt_b200.plan_decode(SMS, *a, **k)
+    # batch 1 / 8: per-warp cluster kernel, clusters of 8, and 16 for the 768-wide layers (48 CTAs otherwise)
+    for m in (1, 8):
+        rows = m
+        assert pd(m, 3 * D, D, True, True) == dict(kernel="warp_cluster", rows=rows, groups=1, cluster=8)
+        assert pd(m, D, D, True, True) == dict(kernel="warp_cluster", rows=rows, groups=1, cluster=16)
+        assert pd(m, F, D, True, True) == dict(kernel="warp_cluster", rows=rows, groups=1, cluster=8)
+        assert pd(m, D, F, True, True) == dict(kernel="warp_cluster", rows=rows, groups=1, cluster=16)
+        assert pd(m, V, D, False) == dict(kernel="rowwise", rows=rows, groups=1, cluster=1)      # un-embedding
+    assert pd(3, D, D, True)["rows"] == 4 and pd(5, D, D, True)["rows"] == 8                     # next power of two
+    # 9 .. 64 rows: register-tiled kernel, 16 / 32 / 64-row tiles, k over a cluster
+    assert pd(9, 3 * D, D, True, True) == dict(kernel="tile_cluster", rows=16, groups=1, cluster=8)
+    assert pd(32, D, F, True, True) == dict(kernel="tile_cluster", rows=32, groups=1, cluster=16)
+    assert pd(64, F, D, True, True) == dict(kernel="tile_cluster", rows=64, groups=1, cluster=8)  # 24 column tiles x 8 = 192 CTAs
+    assert pd(64, V, D, False) == dict(kernel="tile_cluster", rows=64, groups=1, cluster=1)      # 393 column tiles fill the GPU
+    assert pd(40, D, 3 * D, False)["kernel"] == "tile_cluster"                                    # grad_x of the QKV layer
+    # k too short to split: one CTA per column tile
+    assert pd(2, 132, 36, True)["cluster"] == 1 and pd(12, 260, 36, True)["cluster"] == 1
+    # [n][k] weights with bias never take the bias-free kernels
+    assert pd(4, D, D, False, True)["kernel"] == "k_split"
+    # x too large for the row-wise kernel's shared memory: k-split kernel
+    assert pd(8, D, F, False)["kernel"] == "k_split"
+    for m, n, k, w_kn in itertools.product((1, 2, 7, 8, 9, 16, 33, 64), (132, 768, 50304), (36, 768, 3072), (True, False)):
+        p = pd(m, n, k, w_kn)
+        assert p["rows"] * p["groups"] >= m and p["cluster"] in (1, 2, 4, 8, 16)
+        if p["kernel"] == "warp_cluster":
+            assert k // (p["cluster"] * 8) >= 4 or p["cluster"] == 1
+        if p["kernel"] == "tile_cluster":
+            assert k // p["cluster"] >= 32 or p["cluster"] == 1
+        if p["kernel"] == "rowwise":
+            assert p["rows"] * k <= 12288

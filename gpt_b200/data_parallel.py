@@ -64,6 +64,9 @@ class DataParallelStep:
     they overlap the remaining backward kernels.  Gradients are averaged over ranks: every rank's cross-entropy
     backward divides by its local token count, so the mean over ranks equals the single-GPU gradient of the
     global batch.
+
+    With a host tensor as `grad_tensor` (no CUDA: the gloo tests) the same sequence runs without streams: each bucket is
+    reduced synchronously when its layers are reported done.
     """
 
     def __init__(self, model, grad_tensor, world_size: int, layers_per_group: int = 3, all_reduce: Callable | None = None,
@@ -76,9 +79,10 @@ class DataParallelStep:
         self.grads = grad_tensor
         self.world = world_size
         self.buckets = GradientBuckets(model.config, model.param_offsets, model.num_params, layers_per_group)
-        self.compute_stream = torch.cuda.current_stream()
+        self.on_gpu = bool(getattr(grad_tensor, "is_cuda", False))
+        self.compute_stream = torch.cuda.current_stream() if self.on_gpu else None
         # high priority: the collective's CTAs are placed before the pending CTAs of the compute kernels
-        self.comm_stream = torch.cuda.Stream(priority=-1) if world_size > 1 else None
+        self.comm_stream = torch.cuda.Stream(priority=-1) if (world_size > 1 and self.on_gpu) else None
         self._all_reduce = all_reduce or (lambda t: dist.all_reduce(t, op=dist.ReduceOp.AVG))
         self.collectives = 0
         # While collectives are in flight the persistent GEMM kernels leave `comm_sms` SMs free: NCCL's CTAs otherwise wait for
@@ -90,7 +94,7 @@ class DataParallelStep:
         self._sms_limited = False
 
     def _limit_sms(self, on: bool) -> None:
-        if self.comm_sms <= 0 or on == self._sms_limited or not hasattr(self.model, "set_option"):
+        if not self.on_gpu or self.comm_sms <= 0 or on == self._sms_limited or not hasattr(self.model, "set_option"):
             return
         num_sms = self.torch.cuda.get_device_properties(self.torch.cuda.current_device()).multi_processor_count
         self.model.set_option("max_sms", max(2, num_sms - self.comm_sms) if on else 0)
@@ -99,6 +103,11 @@ class DataParallelStep:
     def _on_layer_done(self, layer: int) -> None:
         slices = self.buckets.ready_after(layer)
         if not slices or self.world == 1:
+            return
+        if not self.on_gpu:
+            for off, n in slices:
+                self._all_reduce(self.grads[off:off + n])
+                self.collectives += 1
             return
         self._limit_sms(True)
         ev = self.torch.cuda.Event()
@@ -115,5 +124,5 @@ class DataParallelStep:
         m.forward(tokens)
         m.backward(tokens, labels, self._on_layer_done)
         self._limit_sms(False)
-        if self.world > 1:
+        if self.world > 1 and self.on_gpu:
             self.compute_stream.wait_stream(self.comm_stream)

@@ -105,3 +105,93 @@ def test_bucketed_allreduce_equals_whole_buffer_allreduce_gloo():
         assert p.exitcode == 0
     assert all(ok for _, ok, _ in res)
     assert all(calls == 2 + 2 * 12 for _, _, calls in res)   # ln_f, two layer groups x 12 kinds, embeddings
+
+
+class _FakeModel:
+    """Stands in for gpt_b200.Model on the host: its 'gradient' of a batch is the mean over the batch's tokens of a fixed
+    pseudo-random vector per token id, written into the packed buffer in the order the real backward pass finishes tensors
+    (un-embedding part of wte and the final LayerNorm first, layers from the last to the first, then the embedding part of
+    wte - an accumulation into what the un-embedding left there - and wpe), reporting each event through the callback."""
+
+    def __init__(self, cfg):
+        self.config = cfg
+        self.param_offsets, self.num_params = offsets(cfg)
+        self.grads = torch.zeros(self.num_params)
+
+    def _token_grad(self, tokens):
+        idx = torch.arange(self.num_params, dtype=torch.float64)
+        g = torch.zeros(self.num_params, dtype=torch.float64)
+        for t in tokens.flatten().tolist():
+            g += torch.sin(idx * 1e-3 * (t + 1)) + 0.01 * t
+        return (g / tokens.numel()).float()
+
+    def zero_grad(self):
+        self.grads.zero_()
+
+    def forward(self, tokens):
+        pass
+
+    def backward(self, tokens, labels, layer_done):
+        cfg, off = self.config, self.param_offsets
+        L, D = cfg["num_layers"], cfg["d_model"]
+        g = self._token_grad(tokens)
+        s = per_layer_sizes(cfg)
+        n_wte = cfg["vocab_size_padded"] * D
+        self.grads[off["wte"]:off["wte"] + n_wte] += 0.25 * g[off["wte"]:off["wte"] + n_wte]      # un-embedding backward
+        self.grads[off["ln_f_w"]:off["ln_f_w"] + 2 * D] = g[off["ln_f_w"]:off["ln_f_w"] + 2 * D]
+        layer_done(L)
+        for l in range(L - 1, -1, -1):
+            for k in LAYER_KINDS:
+                a = off[k] + l * s[k]
+                self.grads[a:a + s[k]] = g[a:a + s[k]]
+            layer_done(l)
+        self.grads[off["wte"]:off["wte"] + n_wte] += 0.75 * g[off["wte"]:off["wte"] + n_wte]      # embedding backward, at the very end
+        a, b = off["wpe"], off["ln_1_w"]
+        self.grads[a:b] = g[a:b]
+        layer_done(-1)
+
+
+def _dp_worker(rank, world, port, q):
+    from gpt_b200.data_parallel import DataParallelStep
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    g = torch.Generator().manual_seed(7)
+    tokens = torch.randint(0, TINY["vocab_size"], (4, 16), generator=g)       # the global batch: four sequences
+    model = _FakeModel(TINY)
+
+    def avg(t):
+        dist.all_reduce(t)
+        t /= world
+
+    dp = DataParallelStep(model, model.grads, world, layers_per_group=3, all_reduce=avg)
+    per = tokens.shape[0] // world
+    for _ in range(2):                                                        # two steps: zero_grad starts each from zero
+        dp.step(tokens[rank * per:(rank + 1) * per], None)
+    whole = _FakeModel(TINY)
+    whole.zero_grad()
+    whole.backward(tokens, None, lambda l: None)                              # single process, whole batch
+    err = float((model.grads - whole.grads).abs().max())
+    q.put((rank, err, dp.collectives))
+    dist.destroy_process_group()
+
+
+def test_data_parallel_step_gives_the_gradient_of_the_global_batch_gloo():
+    """DataParallelStep on two gloo ranks, each with half of the sequences: after the step every rank holds the gradient a single
+    process computes on the whole batch - which also requires every bucket to be reduced only after its last write (wte after
+    the embedding backward)."""
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_dp_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for _, err, calls in res:
+        assert err <= 2e-6
+        assert calls == 2 * (2 + 2 * 12)      # per step: ln_f, two layer groups x 12 kinds, embeddings

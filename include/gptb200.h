@@ -63,15 +63,15 @@ int gptb200_ctx_set_stream(gptb200_ctx *ctx, void *cuda_stream);
  * "skinny_push" (that kernel's cluster sum: 1 = every CTA stores its part into the shared memory of the CTA that finishes it
  * (default), 0 = the finishing CTA loads the parts; same bits either way),
  * "skinny_cluster_rows" (most rows of x for which that kernel is used: default 8),
- * "skinny_tile" (more rows than that, weight stored [k][n]: one-launch register-tiled kernel whose k split also runs over a
- * cluster: 1 = on (default), 0 = off (k-split kernel with partial sums in scratch)),
+ * "skinny_tile" (more rows than the per-warp / row-wise kernels take, either weight layout: one-launch register-tiled kernel
+ * whose k split also runs over a cluster: 1 = on (default), 0 = off (k-split kernel with partial sums in scratch)),
  * "skinny_tile_rows" (that kernel's row tile beyond 32 rows: 0 or 64 = one 64-row tile (default), 32 = row groups of 32),
  * "skinny_pipelined" (the k-split kernel's 16-row groups fetch weights through a shared-memory ring: 1 = on (default), 0 = off),
  * "skinny_rowwise" (decode-shaped calls whose weight is stored [n][k] - the un-embedding, grad_x: one-launch kernel, a warp
  * per pair of weight rows and group of up to 16 rows of x: 1 = on (default), 0 = off (k-split kernel)),
  * "skinny_rowwise_rows" (most rows of x for which that kernel is used: default 8; beyond, the register-tiled kernel),
- * "decode_early_launch" (inference only, 0 = off (default), 1 = on (2: also for the register-tiled kernel, measured slower): that kernel is launched with programmatic stream
- * serialization, starts while the kernel before it on the stream is still running and reads w and b meanwhile - x is read and
+ * "decode_early_launch" (inference only, 0 = off (default), 1 = on (2: also for the register-tiled kernel, measured
+ * slower): the per-warp cluster kernel is launched with programmatic stream serialization, starts while the kernel before it on the stream is still running and reads w and b meanwhile - x is read and
  * y / act are written only once that kernel has completed.  The caller promises that no kernel writes weights or biases
  * immediately before a decode-shaped forward call on the same stream (an optimizer step does: leave this off when training)),
  * "skinny_fused" (the k-split kernel adds its partial sums itself instead of in a second launch: 1 = always, 0 = with at most

@@ -25,7 +25,7 @@ MODE_TF32 = 1
 # Every symbol include/gptb200.h declares (checked by the CPU test-suite against the built library).
 EXPORTED_SYMBOLS = [
     "gptb200_ctx_create", "gptb200_ctx_destroy", "gptb200_ctx_set_mode", "gptb200_ctx_get_mode",
-    "gptb200_ctx_set_stream", "gptb200_ctx_set_option", "gptb200_ctx_synchronize", "gptb200_ctx_launch_count", "gptb200_ctx_read_trace",
+    "gptb200_ctx_set_stream", "gptb200_ctx_set_option", "gptb200_ctx_synchronize", "gptb200_ctx_launch_count", "gptb200_ctx_tensor_map_encodes", "gptb200_ctx_read_trace",
     "gptb200_status_string", "gptb200_last_error", "gptb200_plan_gemm", "gptb200_plan_decode", "gptb200_selftest_wait_timeout",
     "gptb200_linear_forward", "gptb200_linear_backward", "gptb200_linear_backward_weights", "gptb200_linear_backward_input",
     "gptb200_gelu_backward",
@@ -68,6 +68,7 @@ def load_library(path: str | None = None) -> ctypes.CDLL:
         "gptb200_ctx_read_trace": (i, [vp, vp, i]),
         "gptb200_ctx_synchronize": (i, [vp]),
         "gptb200_ctx_launch_count": (ctypes.c_longlong, [vp]),
+        "gptb200_ctx_tensor_map_encodes": (ctypes.c_longlong, [vp]),
         "gptb200_selftest_wait_timeout": (i, [vp, i]),
         "gptb200_plan_gemm": (i, [i, i, i, i, i, i, i, i, ctypes.POINTER(i)]),
         "gptb200_plan_decode": (i, [i, i, i, i, i, i, ctypes.POINTER(i)]),
@@ -214,6 +215,9 @@ class Backend:
 
     def launch_count(self) -> int:
         return int(self._lib.gptb200_ctx_launch_count(self._ctx))
+
+    def tensor_map_encodes(self) -> int:
+        return int(self._lib.gptb200_ctx_tensor_map_encodes(self._ctx))
 
     # ---- operators (names of the reference interface)
     def device_linear_activation_fused_forward(self, y, act, x, w, b, activation: bool, batch_size: int, seq_len: int,

@@ -48,6 +48,12 @@ namespace {
 // for K-major tiles, 32-byte chunks for MN-major tiles of 32-bit elements.
 int make_tmap(gptb200_ctx *ctx, CUtensorMap *map, const float *base, long long rows, long long cols, int box_cols, int box_rows, bool mn_major)
 {
+    const TmapKey key{reinterpret_cast<uintptr_t>(base), cols, rows, 0, box_cols, box_rows, mn_major ? 1 : 0};
+    const auto hit = ctx->tmaps.find(key);
+    if (hit != ctx->tmaps.end()) {
+        *map = hit->second;
+        return GPTB200_OK;
+    }
     cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
     cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * sizeof(float)};
     cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
@@ -56,8 +62,11 @@ int make_tmap(gptb200_ctx *ctx, CUtensorMap *map, const float *base, long long r
                                    CU_TENSOR_MAP_INTERLEAVE_NONE, mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    ctx->tmap_encodes++;
     if (r != CUDA_SUCCESS)
         return fail(ctx, GPTB200_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) rows=%lld cols=%lld box=%dx%d", int(r), rows, cols, box_rows, box_cols);
+    if (ctx->tmaps.size() >= kTmapCacheMax) ctx->tmaps.clear();
+    ctx->tmaps.emplace(key, *map);
     return GPTB200_OK;
 }
 
@@ -73,6 +82,7 @@ struct GemmCall {
     float *act;      // optional
     const float *bias;
     bool accumulate;  // out += result
+    float *dbias = nullptr;  // grad_w form only: dbias[N] += column sums of b, inside the same launch when the CTA-pair kernel runs
 };
 
 template <int BN, bool A_MN, bool B_MN, bool X3>
@@ -101,12 +111,12 @@ cudaError_t launch_majors(gptb200_ctx *ctx, bool a_mn, bool b_mn, const CUtensor
     return cudaErrorInvalidValue;  // (MN, K) does not occur on this path
 }
 
-template <bool A_MN, bool B_MN, bool X3>
+template <bool A_MN, bool B_MN, bool X3, bool DB = false>
 cudaError_t launch_pair_instance(gptb200_ctx *ctx, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &to, const CUtensorMap &tact,
                                  const GemmParams &p, int grid)
 {
     using C = PairCfg<X3>;
-    auto kernel = gemm_tcgen05_pair_kernel<A_MN, B_MN, X3>;
+    auto kernel = gemm_tcgen05_pair_kernel<A_MN, B_MN, X3, DB>;
     const void *key = reinterpret_cast<const void *>(kernel);
     if (!ctx->configured.count(key)) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
@@ -123,7 +133,10 @@ cudaError_t launch_pair(gptb200_ctx *ctx, bool a_mn, bool b_mn, const CUtensorMa
 {
     if (!a_mn && b_mn) return launch_pair_instance<false, true, X3>(ctx, ta, tb, to, tact, p, grid);
     if (!a_mn && !b_mn) return launch_pair_instance<false, false, X3>(ctx, ta, tb, to, tact, p, grid);
-    if (a_mn && b_mn) return launch_pair_instance<true, true, X3>(ctx, ta, tb, to, tact, p, grid);
+    if (a_mn && b_mn) {
+        if (p.dbias) return launch_pair_instance<true, true, X3, true>(ctx, ta, tb, to, tact, p, grid);
+        return launch_pair_instance<true, true, X3>(ctx, ta, tb, to, tact, p, grid);
+    }
     return cudaErrorInvalidValue;
 }
 
@@ -131,14 +144,23 @@ cudaError_t launch_pair(gptb200_ctx *ctx, bool a_mn, bool b_mn, const CUtensorMa
 // [32 x 32] pieces from 128-byte-swizzled staging tiles.
 int make_out_tmap(gptb200_ctx *ctx, CUtensorMap *map, float *base, long long depth, long long rows, long long cols)
 {
+    const TmapKey key{reinterpret_cast<uintptr_t>(base), cols, rows, depth, 32, 32, 2};
+    const auto hit = ctx->tmaps.find(key);
+    if (hit != ctx->tmaps.end()) {
+        *map = hit->second;
+        return GPTB200_OK;
+    }
     cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(depth)};
     cuuint64_t strides[2] = {static_cast<cuuint64_t>(cols) * sizeof(float), static_cast<cuuint64_t>(rows) * cols * sizeof(float)};
     cuuint32_t box[3] = {32, 32, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     const CUresult r = ctx->encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    ctx->tmap_encodes++;
     if (r != CUDA_SUCCESS)
         return fail(ctx, GPTB200_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed (%d) depth=%lld rows=%lld cols=%lld", int(r), depth, rows, cols);
+    if (ctx->tmaps.size() >= kTmapCacheMax) ctx->tmaps.clear();
+    ctx->tmaps.emplace(key, *map);
     return GPTB200_OK;
 }
 
@@ -350,8 +372,11 @@ GemmPlanInput plan_input(const gptb200_ctx *ctx, const GemmCall &c)
     return in;
 }
 
-int run_gemm(gptb200_ctx *ctx, const GemmCall &c)
+// *dbias_fused (optional) reports whether c.dbias was computed inside the GEMM launch; if not, the caller runs the
+// separate column-sum kernels.
+int run_gemm(gptb200_ctx *ctx, const GemmCall &c, bool *dbias_fused = nullptr)
 {
+    if (dbias_fused) *dbias_fused = false;
     const GemmPlan pl = plan_gemm(plan_input(ctx, c));
     if (pl.kernel == KERNEL_NONE) return GPTB200_OK;
     if (pl.kernel == KERNEL_SKINNY) return run_skinny(ctx, c, pl);
@@ -383,7 +408,6 @@ int run_gemm(gptb200_ctx *ctx, const GemmCall &c)
     p.kb_per_split = pl.kb_per_split;
     p.splits = splits;
     p.status = ctx->d_status;
-    p.debug = ctx->debug;
 
     float *out_base = c.out;
     if (pair && ctx->d_trace) {
@@ -393,10 +417,19 @@ int run_gemm(gptb200_ctx *ctx, const GemmCall &c)
     if (pair) {
         p.sk_total = pl.sk_total;
         p.sk_unit = pl.sk_unit;
+        const bool fuse_dbias = c.dbias && c.a_mn && c.b_mn && c.accumulate && ctx->fuse_dbias;
+        if (fuse_dbias) {
+            p.dbias = c.dbias;
+            p.dbias_src = c.b;
+            if (dbias_fused) *dbias_fused = true;
+        }
         if (pl.sk_max_share > 1) {
-            const int rc = ensure_workspace(ctx, pl.workspace_bytes);
+            // behind the partial tiles: 128 column sums per CTA for tiles of the first tile row that are cut by a range boundary
+            const size_t dbias_bytes = fuse_dbias ? size_t(pl.grid) * PairCfg<false>::kBRows * sizeof(float) : 0;
+            const int rc = ensure_workspace(ctx, pl.workspace_bytes + dbias_bytes);
             if (rc != GPTB200_OK) return rc;
             p.sk_slots = ctx->ws;
+            p.sk_dbias = ctx->ws + pl.workspace_bytes / sizeof(float);
             p.sk_flags = ctx->d_pair_flags;
             p.sk_state = ctx->d_pair_flags + size_t(ctx->num_sms) * 8;   // two words behind the flags
         }
@@ -665,8 +698,8 @@ int gptb200_ctx_set_option(gptb200_ctx *ctx, const char *key, int value)
         ctx->skinny_fused = value;
         return GPTB200_OK;
     }
-    if (!strcmp(key, "debug")) {
-        ctx->debug = value;
+    if (!strcmp(key, "fuse_dbias")) {
+        ctx->fuse_dbias = value != 0;
         return GPTB200_OK;
     }
     if (!strcmp(key, "max_splits")) {
@@ -701,6 +734,8 @@ int gptb200_ctx_synchronize(gptb200_ctx *ctx)
 }
 
 long long gptb200_ctx_launch_count(const gptb200_ctx *ctx) { return ctx ? ctx->launches : -1; }
+
+long long gptb200_ctx_tensor_map_encodes(const gptb200_ctx *ctx) { return ctx ? ctx->tmap_encodes : -1; }
 
 int gptb200_selftest_wait_timeout(gptb200_ctx *ctx, int limit_us)
 {
@@ -773,12 +808,14 @@ int gptb200_linear_backward_weights(gptb200_ctx *ctx, float *grad_w, float *grad
     if ((1LL * k * n > 0 && !grad_w) || (n > 0 && !grad_b) || (1LL * m * n > 0 && !grad_y) || (1LL * m * k > 0 && !x))
         return fail(ctx, GPTB200_ERR_INVALID_ARG, "null tensor pointer");
     // grad_w[k x n] += x^T . grad_y : A = x stored [m x k] = [K' x M'] (MN-major), B = grad_y [m x n] = [K' x N'] (MN-major)
+    bool dbias_fused = false;
     if (m > 0 && k > 0 && n > 0) {
-        GemmCall dw{k, n, m, x, true, grad_y, true, grad_w, nullptr, nullptr, true};
-        rc = run_gemm(ctx, dw);
+        GemmCall dw{k, n, m, x, true, grad_y, true, grad_w, nullptr, nullptr, true, grad_b};
+        rc = run_gemm(ctx, dw, &dbias_fused);
         if (rc) return rc;
     }
-    return run_bias_grad(ctx, grad_b, grad_y, m, n);
+    // shapes that do not run the CTA-pair kernel: the two-stage column-sum kernels
+    return dbias_fused ? GPTB200_OK : run_bias_grad(ctx, grad_b, grad_y, m, n);
 }
 
 int gptb200_linear_backward(gptb200_ctx *ctx, float *grad_x, float *grad_w, float *grad_b, const float *grad_y, const float *x,

@@ -4,7 +4,9 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdint>
 #include <set>
+#include <unordered_map>
 
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -14,6 +16,24 @@
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// A tensor map is a pure function of (base address, extents, box, layout): the context keeps the encoded maps so that a
+// repeated call (every layer of every step uses the same few dozen tensors) costs a hash lookup instead of a driver call.
+struct TmapKey {
+    uintptr_t base;
+    long long d0, d1, d2;   // extents (innermost first; d2 = 0 for 2-D maps)
+    int box0, box1, kind;   // kind: 0 K-major operand, 1 MN-major operand, 2 output
+    bool operator==(const TmapKey &o) const { return base == o.base && d0 == o.d0 && d1 == o.d1 && d2 == o.d2 && box0 == o.box0 && box1 == o.box1 && kind == o.kind; }
+};
+struct TmapKeyHash {
+    size_t operator()(const TmapKey &k) const
+    {
+        uint64_t h = k.base * 0x9E3779B97F4A7C15ull;
+        for (uint64_t v : {uint64_t(k.d0), uint64_t(k.d1), uint64_t(k.d2), uint64_t(k.box0) << 32 | uint64_t(k.box1) << 8 | uint64_t(k.kind)})
+            h = (h ^ v) * 0x100000001B3ull + (h >> 29);
+        return size_t(h);
+    }
+};
 
 struct gptb200_ctx {
     int device = 0;
@@ -38,8 +58,8 @@ struct gptb200_ctx {
     int skinny_rowwise_rows = 8;  // ... for calls with at most this many rows (beyond: the register-tiled kernel)
     bool skinny_pipelined = true;  // k-split kernel, 16-row groups, W stored [k][n]: weight loads pipelined through shared memory
     int skinny_fused = 0;  // that kernel adds its partial sums itself (one launch): 1 = always, 0 = with at most two splits, -1 = never
-    int debug = 0;       // timing experiments (see GemmParams::debug)
     bool attention_tiled = true;  // head size 64: register-tiled attention kernels (false: the one-row-per-thread-group kernels)
+    bool fuse_dbias = true;  // grad_w launches of the CTA-pair kernel also produce the bias gradient (false: separate column-sum kernels)
     int pair = 0;        // CTA-pair (cta_group::2) kernel: 1 = always, 0 = heuristic, -1 = never
     int stream_k = 0;    // CTA-pair kernel, ranges cut inside tiles: 1 = always, 0 = heuristic, -1 = never
     long long *d_trace = nullptr;  // clock samples of the CTA-pair kernel (option "trace")
@@ -53,10 +73,14 @@ struct gptb200_ctx {
     EncodeTiledFn encode = nullptr;
     long long launches = 0;
     std::set<const void *> configured;  // kernels whose dynamic shared-memory limit has been raised
+    std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> tmaps;  // encoded tensor maps (emptied when it reaches kTmapCacheMax entries)
+    long long tmap_encodes = 0;         // cuTensorMapEncodeTiled calls so far
     char last_error[512] = {0};
 };
 
 namespace gptb200 {
+
+constexpr size_t kTmapCacheMax = 4096;
 
 inline int fail(gptb200_ctx *ctx, int code, const char *fmt, ...)
 {

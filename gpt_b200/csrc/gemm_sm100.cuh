@@ -64,7 +64,6 @@ struct GemmParams {
     int num_kb;          // ceil(K / 32)
     int epi_mode;
     int *status;         // device status word
-    int debug;           // timing experiments only: bit 0 = no TMA loads, bit 1 = no MMAs (results are garbage)
     // CTA-pair kernel only: the tiles' k-blocks form one line of sk_total = tiles * num_kb entries that is cut into
     // one range per pair, at multiples of sk_unit (1: anywhere, num_kb: whole tiles only).
     long long sk_total;
@@ -73,6 +72,12 @@ struct GemmParams {
     unsigned int *sk_flags;  // one word per pair, CTA and epilogue warp: the number of the launch whose partial tile is complete
     unsigned int *sk_state;  // [0] number of completed launches that used the flags, [1] CTAs of this launch that have finished
     long long *trace;        // optional [kTraceEvents][kTraceSlots] clock64 samples of the first k-blocks of CTA 0
+    // CTA-pair kernel, grad_w form (both operands MN-major) only: the bias gradient rides this launch.  The epilogue warps of
+    // the pairs that work on the first tile row add up the rows of B (= grad_y [K x N], row pitch N) of their k-block range
+    // and the tile's owner adds the total into dbias[N] (+=).
+    float *dbias;
+    const float *dbias_src;
+    float *sk_dbias;         // [pair][CTA][128] column sums of tiles cut by a range boundary (published with the partial tile)
 };
 
 constexpr int kTraceSlots = 128;
@@ -267,11 +272,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         ok = false;
                         break;
                     }
-                    if (p.debug & 1) {
-                        if (lane == 0) ptx::mbar_arrive(full_bar(s));
-                        __syncwarp();
-                        continue;
-                    }
                     if (lane == 0) ptx::mbar_arrive_expect_tx(full_bar(s), C::kHiBytes);
                     __syncwarp();
                     const uint32_t a_dst = smem_base + s * C::kStageBytes;
@@ -332,7 +332,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                             const uint32_t a_lo = a_hi + C::kHiBytes;
                             const uint32_t b_lo = b_hi + C::kHiBytes;
 #pragma unroll
-                            for (int k = 0; k < ((p.debug & 2) ? 0 : kBK / kUmmaK); ++k) {
+                            for (int k = 0; k < kBK / kUmmaK; ++k) {
                                 // K-major tile: rows of 128 B (32 k), 16-byte-chunk swizzle over 8-row atoms of 1024 B;
                                 //   a k-step (8 floats) is 32 bytes along the row, 8-row groups are 1024 B apart (SBO).
                                 // MN-major tile: boxes of [32 k-rows x 32 floats], 32-byte-chunk swizzle over 4-row atoms
@@ -508,7 +508,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 float4 *lo = reinterpret_cast<float4 *>(smem_gen + s * C::kStageBytes + C::kHiBytes);
                 constexpr int kVec = C::kHiBytes / 16;
 #pragma unroll 4
-                for (int i = ctid; i < ((p.debug & 8) ? 0 : kVec); i += 4 * 32) {
+                for (int i = ctid; i < kVec; i += 4 * 32) {
                     const float4 h = hi[i];
                     float4 l;
                     l.x = h.x - __uint_as_float(__float_as_uint(h.x) & 0xFFFFE000u);
@@ -517,7 +517,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     l.w = h.w - __uint_as_float(__float_as_uint(h.w) & 0xFFFFE000u);
                     lo[i] = l;
                 }
-                if (!(p.debug & 4)) ptx::fence_proxy_async_smem();
+                ptx::fence_proxy_async_smem();
                 ptx::mbar_arrive(conv_bar(s));
             }
         }

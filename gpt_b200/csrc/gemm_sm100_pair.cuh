@@ -242,7 +242,46 @@ __device__ __forceinline__ bool bounded_flag_wait(const unsigned int *flag, unsi
     return ok != 0;
 }
 
-template <bool A_MN, bool B_MN, bool X3>
+// Bias gradient inside the grad_w GEMM: sums of rows [r0, r1) of src (row pitch ld floats) for 16 consecutive columns per
+// warp.  A quarter of four lanes covers the 16 columns of one row with a 16-byte load each, the eight quarters take eight
+// consecutive rows; `s` carries the lane's running sums of its four columns (col .. col + 3) from call to call.  The rows were
+// (or are about to be) fetched by the operand loads of the same CTA, so these loads are served by L2.
+template <int UNROLL>
+__device__ __forceinline__ void column_sums_16(float4 &s, const float *__restrict__ src, long long ld, int r0, int r1, int col, bool col_ok, int lane)
+{
+    const int g = lane >> 2;
+    for (int rb = r0; rb < r1; rb += 8 * UNROLL) {
+        float4 v[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int r = rb + 8 * u + g;
+            v[u] = (col_ok && r < r1) ? __ldg(reinterpret_cast<const float4 *>(src + static_cast<long long>(r) * ld + col)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            s.x += v[u].x;
+            s.y += v[u].y;
+            s.z += v[u].z;
+            s.w += v[u].w;
+        }
+    }
+}
+
+// Adds the eight quarters' sums: afterwards every lane holds the total of its four columns (the same bits in all lanes of a
+// column group: each butterfly step adds the same two numbers on both sides).
+__device__ __forceinline__ void column_sums_finish(float4 &s)
+{
+#pragma unroll
+    for (int off = 4; off < 32; off <<= 1) {
+        s.x += __shfl_xor_sync(0xffffffffu, s.x, off);
+        s.y += __shfl_xor_sync(0xffffffffu, s.y, off);
+        s.z += __shfl_xor_sync(0xffffffffu, s.z, off);
+        s.w += __shfl_xor_sync(0xffffffffu, s.w, off);
+    }
+}
+
+// DB: the bias gradient is computed in this launch (see GemmParams::dbias); instantiated for the grad_w form only.
+template <bool A_MN, bool B_MN, bool X3, bool DB = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<X3>::kThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_act, const GemmParams p)
@@ -394,11 +433,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                         break;
                     }
                     if (lane == 0) trace(TRACE_LOAD_ISSUE, it);
-                    if (p.debug & 1) {
-                        if (lane == 0 && (X3 || leader)) ptx::mbar_arrive(full_bar(s));
-                        __syncwarp();
-                        continue;
-                    }
                     // TF32: every load of the pair reports to the leader's barrier, armed by the leader for both CTAs.
                     // 3xTF32: each CTA's loads report to its own barrier (its converter warps wait on it).
                     const uint32_t bar = X3 ? full_bar(s) : ptx::map_to_cta(full_bar(s), 0u);
@@ -462,7 +496,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                             constexpr uint32_t b_lbo = B_MN ? kBoxBytesMN : 16, b_sbo = B_MN ? 512 : 1024;
                             constexpr uint32_t a_lay = A_MN ? ptx::kLayoutSw128Base32B : ptx::kLayoutSw128;
                             constexpr uint32_t b_lay = B_MN ? ptx::kLayoutSw128Base32B : ptx::kLayoutSw128;
-                            if (X3 && !(p.debug & 2)) {
+                            if (X3) {
                                 // correction terms a_lo.b + a.b_lo: bf16 tiles with 64 k-positions (low parts and whole values
                                 // side by side), 16 of them per instruction.  K-major: 128-byte rows, +32 bytes per step;
                                 // MN-major: [8 k x 64 m] atoms, 1 KiB per group of 8 k, 8 KiB to the next 64 rows.
@@ -475,7 +509,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                                 }
                             }
 #pragma unroll
-                            for (int k = 0; k < ((p.debug & 2) ? 0 : kBK / kUmmaK); ++k) {
+                            for (int k = 0; k < kBK / kUmmaK; ++k) {
                                 const uint32_t a_off = A_MN ? k * 1024 : k * 32;
                                 const uint32_t b_off = B_MN ? k * 1024 : k * 32;
                                 const uint64_t da_hi = ptx::make_smem_desc(a_hi + a_off, a_lbo, a_sbo, a_lay);
@@ -567,6 +601,23 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             // slot of pair r: [CTA][epilogue warp][128 values][lane]
             auto slot_of = [&](long long r) { return p.sk_slots + ((r * 2 + rank) * C::kEpiWarps + e) * 4096 + lane; };
             auto flag_of = [&](long long r) { return p.sk_flags + (r * 2 + rank) * C::kEpiWarps + e; };
+            // bias gradient: pairs on the first tile row sum the rows of B of their k-block range, 16 columns per epilogue warp
+            const bool duty = DB && p.dbias != nullptr && tm2 == 0;
+            const int bcol = tn * BN + static_cast<int>(rank) * C::kBRows + e * 16 + (lane & 3) * 4;
+            float4 bsum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            auto dbias_slot = [&](long long r) { return reinterpret_cast<float4 *>(p.sk_dbias + (r * 2 + rank) * C::kBRows + e * 16) + (lane & 3); };
+            auto dbias_add_partner = [&](long long r) {
+                if (duty && lane < 4) {
+                    const float4 t = __ldcg(dbias_slot(r));
+                    bsum.x += t.x; bsum.y += t.y; bsum.z += t.z; bsum.w += t.w;
+                }
+            };
+            auto dbias_write = [&]() {   // owner: grad_b += total (one writer per column: the owner of tile (0, tn))
+                if (duty && lane < 4 && bcol < p.N) {
+                    float *dst = p.dbias + bcol;
+                    dst[0] += bsum.x; dst[1] += bsum.y; dst[2] += bsum.z; dst[3] += bsum.w;
+                }
+            };
             float bias_pre[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             if (owner && p.bias && p.epi_mode == EPI_STORE) {
 #pragma unroll
@@ -596,12 +647,15 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     ptx::tc_fence_before();
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive_cluster(leader_tmem_empty[buf]);
-
+                    // the rows of B that belong to the chunk just drained (fetched by the operand loads a moment ago)
+                    if (duty) column_sums_16<8>(bsum, p.dbias_src, p.N, kb * kBK, min(min(kb + pair_chunk_kb(kb == kb0), kb1) * kBK, p.K), bcol, bcol < p.N, lane);
                 }
+                if (duty) column_sums_finish(bsum);
                 if (ok && !owner) {
                     float *slot = slot_of(pair_id);
 #pragma unroll
                     for (int j = 0; j < 128; ++j) __stcg(slot + j * 32, acc[j]);
+                    if (duty && lane < 4) __stcg(dbias_slot(pair_id), bsum);
                     __threadfence();
                     __syncwarp();
                     if (lane == 0) flag_release(flag_of(pair_id), sk_epoch);
@@ -613,9 +667,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                             const float *slot = slot_of(r);
 #pragma unroll
                             for (int j = 0; j < 128; ++j) acc[j] += __ldcg(slot + j * 32);
+                            dbias_add_partner(r);
                         }
                     }
                     if (ok) {
+                        dbias_write();
                         if (e == 0 && lane == 0) trace(TRACE_EPI_BEGIN, tile_count);
 #pragma unroll
                         for (int c = 0; c < 4; ++c) {
@@ -632,6 +688,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 const uint32_t buf = g & 1u;
                 const uint32_t use = (g >> 1) & 1u;
                 ++g;
+                // while the tensor cores work on this range: the column sums of its rows of B
+                if (duty) {
+                    column_sums_16<16>(bsum, p.dbias_src, p.N, kb0 * kBK, min(kb1 * kBK, p.K), bcol, bcol < p.N, lane);
+                    column_sums_finish(bsum);
+                }
                 if (!bounded_wait_cluster(tmem_full_bar(buf), use, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE)) {
                     ok = false;
                     break;
@@ -640,8 +701,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 long long r_end = pair_id + 1;   // pairs [pair_id + 1, r_end) hold the rest of this tile
                 if (owner && !complete) {
                     while (r_end < num_pairs && pair_range_start(p, r_end, num_pairs) < tile_end) ++r_end;
-                    for (long long r = pair_id + 1; ok && r < r_end; ++r) ok = bounded_flag_wait(flag_of(r), sk_epoch, lane, abort_flag, p.status);
+                    for (long long r = pair_id + 1; ok && r < r_end; ++r) {
+                        ok = bounded_flag_wait(flag_of(r), sk_epoch, lane, abort_flag, p.status);
+                        if (ok) dbias_add_partner(r);
+                    }
                 }
+                if (ok && owner) dbias_write();
 #pragma unroll 1
                 for (int c = 0; c < C::kColsPerEpiWarp / 32; ++c) {
                     uint32_t r[32];
@@ -670,6 +735,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     }
                 }
                 if (ok && !owner) {
+                    if (duty && lane < 4) __stcg(dbias_slot(pair_id), bsum);
                     __threadfence();
                     __syncwarp();
                     if (lane == 0) flag_release(flag_of(pair_id), sk_epoch);

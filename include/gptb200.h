@@ -76,6 +76,8 @@ int gptb200_ctx_set_stream(gptb200_ctx *ctx, void *cuda_stream);
  * immediately before a decode-shaped forward call on the same stream (an optimizer step does: leave this off when training)),
  * "skinny_fused" (the k-split kernel adds its partial sums itself instead of in a second launch: 1 = always, 0 = with at most
  * two splits (default), -1 = never; same bits either way),
+ * "fuse_dbias" (weight-gradient launches of the CTA-pair kernel also produce the bias gradient: 1 = on (default), 0 = the
+ * separate column-sum kernels; results differ only in summation order),
  * "max_sms" (0 = all SMs; otherwise the GEMM kernels occupy at most this many, which leaves SMs to a collective that runs
  * at the same time on another stream),
  * "trace" (record a kernel-phase trace of each CTA-pair GEMM launch: 1 = on, 0 = off (default)),
@@ -93,6 +95,9 @@ int gptb200_ctx_read_trace(gptb200_ctx *ctx, long long *samples, int capacity);
 int gptb200_ctx_synchronize(gptb200_ctx *ctx);
 /* Number of kernels this context has launched so far. */
 long long gptb200_ctx_launch_count(const gptb200_ctx *ctx);
+/* Number of tensor maps this context has encoded so far (cuTensorMapEncodeTiled calls).  Encoded maps are kept per
+ * (address, extents, tile box): a call on tensors it has seen before encodes nothing. */
+long long gptb200_ctx_tensor_map_encodes(const gptb200_ctx *ctx);
 /* Failure-detection self-test: launches a one-CTA kernel whose bounded wait (limit_us microseconds, at most 100 ms) is on a
  * barrier that nothing signals.  The wait runs out, the kernel returns normally, and the next gptb200_ctx_synchronize reports
  * GPTB200_ERR_DEVICE_TIMEOUT (and clears the device status); the context stays usable. */

@@ -18,6 +18,17 @@ the same step through the C ABI starting from pinned HOST buffers: x and the ups
 the device, and act / grad_x / grad_w / grad_b are copied back, inside the timed region; consecutive steps are
 pipelined over a copy-in, a compute and a copy-out stream with two buffer sets.
 
+Beside those headline keys the default line carries sub-records, each a few hundred milliseconds of GPU time:
+  shapes         (N = 1) every linear layer of GPT-2 124M at M = 8192 -- QKV, attention projection, FFN up, FFN down, the tied
+                 LM head -- and FFN up at M = 1024 and 32768: forward / backward ms, TFLOP/s and fraction of the TF32 peak, in
+                 both precision modes;
+  reference_gpu  (N = 1) the reference's own CUDA backend (cuBLAS TF32 + its unfused kernels, unmodified sources) on the same
+                 shapes and on the training step, run in a child process so that cuBLAS never enters this one;
+  decode         (N = 1) the linear layers of a decode step at batch 1 / 8 / 64: GB/s of weight stream and fraction of HBM peak;
+  train_step     (every N) the full GPT-2 124M training step at a global batch of 64 x 256 tokens sharded over the ranks
+                 (strong scaling): tokens/s, phase times, collectives per step, and dp_parity -- the distance per gradient
+                 tensor between the all-reduced N-rank gradients and rank 0 computing the whole batch alone.
+
 --impl reference times the reference's own CPU implementation (unmodified sources, oracle/_ref) of the same
 step on the host, on a bounded row sample per step (its cost is exactly linear in M).
 """
@@ -38,6 +49,9 @@ sys.path.insert(0, ROOT)
 
 M_PER_GPU, K_IN, N_OUT = 8192, 768, 3072
 FLOPS_PER_STEP = 6.0 * M_PER_GPU * K_IN * N_OUT          # forward + dX + dW, 2*M*K*N each
+# DRAM read + write bytes per launch (or per step) from ncu captures of these workloads (dram__bytes_read.sum +
+# dram__bytes_write.sum); re-captured whenever the kernel they describe changes.
+NCU_DRAM_BYTES = {"ffn_up_forward_M8192_3xtf32": 204.4e6, "decode_step_batch1": 496.4e6}
 METRIC = "linear_layer_tflops"
 UNIT = "TFLOP/s"
 WORKLOAD = "GPT-2 124M FFN fc (x[8192x768].w[768x3072]+b, GELU-tanh) forward+backward per GPU"
@@ -71,15 +85,26 @@ class ClockSampler:
                                          stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
 
     def stop(self, t_begin: float, t_end: float):
-        """Summary of the samples taken between the two time.time() stamps (the timed region and the
-        measurement loops that follow it)."""
+        """Ends the sampling; summary of the samples taken between the two time.time() stamps."""
+        out = self.summary(t_begin, t_end)
+        self.close()
+        return out
+
+    def close(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+            self.proc = None
+        if self.path and os.path.exists(self.path):
+            os.unlink(self.path)
+
+    def summary(self, t_begin: float, t_end: float):
+        """Summary of the samples taken so far between the two time.time() stamps (sampling goes on)."""
         if not self.proc:
             return None
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
         sm, smax, reasons, n_all = [], 0.0, set(), 0
         for line in open(self.path):
             f = [s.strip() for s in line.split(",")]
@@ -98,10 +123,146 @@ class ClockSampler:
             for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[6:10]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        os.unlink(self.path)
         if not sm:
             return dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0, samples_total=n_all)
         return dict(sm_mhz=statistics.median(sm), sm_max_mhz=smax, reasons=sorted(reasons), samples=len(sm), samples_total=n_all)
+
+
+# (name, K, N, GELU output) of the four per-layer linears of GPT-2 124M; the tied LM head is handled apart
+LAYER_SHAPES = (("qkv", 768, 2304, False), ("attn_proj", 768, 768, False), ("ffn_up", 768, 3072, True), ("ffn_down", 3072, 768, False))
+LM_HEAD = (768, 50304)
+
+
+def _event_ms(torch, fn, reps, sets, rounds=3):
+    """Milliseconds per call of fn(buffer set): CUDA events on the current stream around `reps` back-to-back calls with the
+    buffer sets rotating, after three warm-up calls; the best of `rounds` such measurements."""
+    for i in range(3):
+        fn(sets[i % len(sets)])
+    best = float("inf")
+    for _ in range(rounds):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(reps):
+            fn(sets[i % len(sets)])
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1) / reps)
+    return best
+
+
+def shapes_record(torch, dev, sampler, reps=20):
+    """Every linear layer of GPT-2 124M at M = 8192 (BASELINE.json configs 1 and 2), plus FFN up at M = 1024 and 32768, in
+    both precision modes: forward and backward (grad_x, grad_w +=, grad_b += in two launches) apart.  Buffer sets rotate so
+    that each call's operands and outputs exceed the 126 MB L2 wherever the shape allows."""
+    import gpt_b200
+    peaks = measured_peaks()
+    out = {}
+    g = torch.Generator(device=dev).manual_seed(11)
+    cases = [(name, 8192, k, n, act) for name, k, n, act in LAYER_SHAPES] + [("ffn_up", 1024, 768, 3072, True), ("ffn_up", 32768, 768, 3072, True)]
+    for mode_name, mode in (("tf32", gpt_b200.MODE_TF32), ("3xtf32", gpt_b200.MODE_3XTF32)):
+        be = gpt_b200.Backend(dev.index, torch.cuda.current_stream().cuda_stream, mode)
+        t0 = time.time()
+        rec = {}
+        for name, M, K, N, act in cases:
+            nsets = 2 if M >= 32768 else 4
+            sets = [dict(x=torch.randn(M, K, device=dev, generator=g), gy=torch.randn(M, N, device=dev, generator=g), y=torch.empty(M, N, device=dev),
+                         a=torch.empty(M, N, device=dev) if act else None, gx=torch.empty(M, K, device=dev)) for _ in range(nsets)]
+            w = torch.randn(K, N, device=dev, generator=g) * 0.02
+            b = torch.randn(N, device=dev, generator=g) * 0.02
+            gw, gb = torch.zeros(K, N, device=dev), torch.zeros(N, device=dev)
+            l0 = be.launch_count()
+            f_ms = _event_ms(torch, lambda s: be.device_linear_activation_fused_forward(s["y"], s["a"], s["x"], w, b, act, 1, M, K, N), reps, sets)
+            l1 = be.launch_count()
+            b_ms = _event_ms(torch, lambda s: be.device_linear_backward(s["gx"], gw, gb, s["gy"], s["x"], w, 1, M, K, N), reps, sets)
+            l2 = be.launch_count()
+            fl = 2.0 * M * K * N
+            rec[f"{name}_M{M}"] = dict(m=M, k=K, n=N, gelu=act, forward_ms=f_ms, backward_ms=b_ms, forward_tflops=fl / f_ms / 1e9,
+                                       backward_tflops=2 * fl / b_ms / 1e9, forward_frac=fl / f_ms / 1e9 / peaks["tf32_tflops"],
+                                       backward_frac=2 * fl / b_ms / 1e9 / peaks["tf32_tflops"],
+                                       forward_launches=(l1 - l0) // (3 * reps + 3), backward_launches=(l2 - l1) // (3 * reps + 3))
+            del sets, w, b, gw, gb
+        # the tied LM head (config 2): logits = x . wte^T; backward = grad_x and grad_wte +=
+        D, Vp = LM_HEAD
+        M = 8192
+        x = torch.randn(M, D, device=dev, generator=g)
+        wte = torch.randn(Vp, D, device=dev, generator=g) * 0.02
+        logits = torch.empty(M, Vp, device=dev)
+        gy = torch.randn(M, Vp, device=dev, generator=g) / M
+        gx, gwte = torch.empty(M, D, device=dev), torch.zeros(Vp, D, device=dev)
+        f_ms = _event_ms(torch, lambda s: be.device_unembedding_forward(logits, x, wte, 1, M, D, Vp), 5, [None])
+        b_ms = _event_ms(torch, lambda s: be.device_unembedding_backward(gx, gwte, gy, x, wte, 1, M, D, Vp), 5, [None])
+        fl = 2.0 * M * D * Vp
+        rec[f"lm_head_M{M}"] = dict(m=M, k=D, n=Vp, gelu=False, forward_ms=f_ms, backward_ms=b_ms, forward_tflops=fl / f_ms / 1e9,
+                                    backward_tflops=2 * fl / b_ms / 1e9, forward_frac=fl / f_ms / 1e9 / peaks["tf32_tflops"],
+                                    backward_frac=2 * fl / b_ms / 1e9 / peaks["tf32_tflops"])
+        del x, wte, logits, gy, gx, gwte
+        be.synchronize()
+        clk = sampler.summary(t0, time.time()) if sampler else None
+        mhz = (clk or {}).get("sm_mhz")
+        if mhz:   # time x median SM clock of this phase: separates clock (power cap) effects from stalls
+            for r in rec.values():
+                r["forward_sm_cycles"] = r["forward_ms"] * 1e-3 * mhz * 1e6
+                r["backward_sm_cycles"] = r["backward_ms"] * 1e-3 * mhz * 1e6
+        out[mode_name] = dict(shapes=rec, clocks=clk)
+        be.close()
+        torch.cuda.empty_cache()
+    out["peak_tflops"] = peaks["tf32_tflops"]
+    out["note"] = ("frac = 2*M*K*N (forward) or 4*M*K*N (backward: grad_x and grad_w) algorithmic flops / CUDA-event time / peak; "
+                   "3xtf32 issues twice that work on the tensor pipe (one TF32 chain and one bf16 chain of the same duration)")
+    return out
+
+
+def reference_gpu_record(steps=10, warmup=3):
+    """The reference's own CUDA backend on the same shapes and on the training step, timed in a child process (cuBLAS is
+    loaded there, never here)."""
+    cmd = [sys.executable, os.path.abspath(__file__), "--impl", "reference_cuda_shapes", "--steps", str(steps), "--warmup", str(warmup)]
+    try:
+        res = subprocess.run(cmd, capture_output=True, text=True, timeout=240)
+        line = [l for l in res.stdout.splitlines() if l.startswith("{")]
+        return json.loads(line[-1]) if line else dict(unavailable=f"child process printed no record (exit code {res.returncode}): {res.stderr[-200:]}")
+    except Exception as e:   # a missing prebuilt library or a timeout must not lose the rest of the line
+        return dict(unavailable=f"{type(e).__name__}: {e}")
+
+
+def run_reference_cuda_shapes(args):
+    """--impl reference_cuda_shapes (child process of the default run): the reference's CUDA backend -- cublasSgemm in TF32
+    tensor-op mode plus its own bias / GELU and bias-gradient kernels (src/backend/cuda/kernels/linear.cu:36-159,
+    embedding.cu:47-63,140-170) -- compiled unmodified into oracle/_ref/libref_cuda.so, on the shapes of `shapes`."""
+    import ctypes
+    path = os.path.join(ROOT, "oracle", "_ref", "libref_cuda.so")
+    if not os.path.exists(path):
+        print(json.dumps(dict(impl="reference_cuda", unavailable="the reference's CUDA backend was not prebuilt (oracle/_ref/libref_cuda.so)")))
+        return
+    lib = ctypes.CDLL(path)
+    lib.refcuda_linear_ms.restype = ctypes.c_int
+    lib.refcuda_linear_ms.argtypes = [ctypes.c_int] * 7 + [ctypes.POINTER(ctypes.c_float)]
+    lib.refcuda_unembed_ms.restype = ctypes.c_int
+    lib.refcuda_unembed_ms.argtypes = [ctypes.c_int] * 5 + [ctypes.POINTER(ctypes.c_float)]
+    lib.refcuda_gpt_step_ms.restype = ctypes.c_float
+    lib.refcuda_gpt_step_ms.argtypes = [ctypes.POINTER(ctypes.c_int)] + [ctypes.c_int] * 4
+    peaks = measured_peaks()
+    rec = {}
+    out2 = (ctypes.c_float * 2)()
+    cases = [(name, 8192, k, n, act) for name, k, n, act in LAYER_SHAPES] + [("ffn_up", 1024, 768, 3072, True), ("ffn_up", 32768, 768, 3072, True)]
+    for name, M, K, N, act in cases:
+        if lib.refcuda_linear_ms(M, K, N, int(act), args.steps, args.warmup, 2 if M >= 32768 else 4, out2) != 0:
+            continue
+        fl = 2.0 * M * K * N
+        rec[f"{name}_M{M}"] = dict(m=M, k=K, n=N, gelu=act, forward_ms=out2[0], backward_ms=out2[1], forward_tflops=fl / out2[0] / 1e9,
+                                   backward_tflops=2 * fl / out2[1] / 1e9, forward_frac=fl / out2[0] / 1e9 / peaks["tf32_tflops"],
+                                   backward_frac=2 * fl / out2[1] / 1e9 / peaks["tf32_tflops"])
+    D, Vp = LM_HEAD
+    if lib.refcuda_unembed_ms(8192, D, Vp, max(3, args.steps // 2), args.warmup, out2) == 0:
+        fl = 2.0 * 8192 * D * Vp
+        rec["lm_head_M8192"] = dict(m=8192, k=D, n=Vp, gelu=False, forward_ms=out2[0], backward_ms=out2[1], forward_tflops=fl / out2[0] / 1e9,
+                                    backward_tflops=2 * fl / out2[1] / 1e9, forward_frac=fl / out2[0] / 1e9 / peaks["tf32_tflops"],
+                                    backward_frac=2 * fl / out2[1] / 1e9 / peaks["tf32_tflops"])
+    cfg = (ctypes.c_int * 7)(256, 50257, 50304, 12, 12, 768, 3072)
+    ms = float(lib.refcuda_gpt_step_ms(cfg, 64, 256, 3, 1))
+    train = dict(ms_per_step=ms, tokens_per_s=64 * 256 / (ms * 1e-3), global_batch=64, seq_len=256) if ms > 0 else None
+    print(json.dumps(dict(impl="reference_cuda", dtype="tf32 (cuBLAS tensor-op math)", shapes=rec, train_step=train,
+                          note="the reference's CUDABackend, unmodified sources: cublasSgemm + add_bias/GELU kernel forward, two cublasSgemm "
+                               "+ bias-gradient kernel backward; same shapes, same rotation of buffer sets")), flush=True)
 
 
 def run_ours(args):
@@ -119,7 +280,7 @@ def run_ours(args):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        _init_process_group(dist, dev)
 
     mode = gpt_b200.MODE_TF32 if args.mode == "tf32" else gpt_b200.MODE_3XTF32
     stream = torch.cuda.current_stream()
@@ -208,6 +369,15 @@ def run_ours(args):
         kern[name] = dict(ms=t_ms, tflops=flops / t_ms / 1e9)
     be.synchronize()
 
+    # ---- host time of one call of the C ABI (plan, tensor-map lookup, launch; ctypes included), with the GPU idle at the start
+    torch.cuda.synchronize()
+    n_host = 0 if args.profile else 200
+    t0 = time.perf_counter()
+    for i in range(n_host):
+        be.linear_backward_input(sets[0]["gx"], sets[0]["gy"], w, 64, K, N)   # a small call: the launch queue never fills up
+    host_us = (time.perf_counter() - t0) / max(1, n_host) * 1e6
+    torch.cuda.synchronize()
+
     # ---- end to end from pinned host buffers through the C ABI (rank-local; max over ranks)
     hx = torch.randn(M, K).pin_memory()
     hgy = torch.randn(M, N).pin_memory()
@@ -271,16 +441,40 @@ def run_ours(args):
     for i in range(0 if args.profile else int(min(5000, max(10, 1000.0 / (ms / args.steps))))):
         step(i)
     torch.cuda.synchronize()
-    clocks = sampler.stop(t_begin, time.time()) if sampler else None
+    clocks = sampler.summary(t_begin, time.time()) if sampler else None
+    be.close()
+
+    # ---- sub-records (see the module docstring); the headline keys above are not affected by them
+    sub = {}
+    if not args.profile and not args.no_subrecords:
+        del sets, s0, hx, hgy, hact, hgx, hgw, hgb, snaps, grads, gw, gb
+        torch.cuda.empty_cache()
+        if world == 1:
+            sub["shapes"] = shapes_record(torch, dev, sampler)
+            torch.cuda.empty_cache()
+            sub["decode"] = decode_record(torch, dev, "3xtf32", (1, 8, 64), 20, 3)
+            sub["decode"]["value_gbs"] = {k: v["gbs"] for k, v in sub["decode"]["per_batch"].items()}
+            sub["decode"]["frac"] = {k: v["hbm_frac"] for k, v in sub["decode"]["per_batch"].items()}
+            torch.cuda.empty_cache()
+        sub["train_step"] = train_record(torch, dist, world, rank, dev, "3xtf32", 64, 5, 2, sampler, parity=True)
+        torch.cuda.empty_cache()
+        if world == 1 and rank == 0:
+            sub["reference_gpu"] = reference_gpu_record()
+    if sampler:
+        sampler.close()
 
     if rank == 0:
         ms_per_step = ms / args.steps
         value = flops_per_step * world / (ms_per_step * 1e-3) / 1e12
         x3 = mode == gpt_b200.MODE_3XTF32
         fwd = kern["forward_gemm_bias_gelu"]
+        mhz = (clocks or {}).get("sm_mhz")
+        if mhz:   # time x median SM clock: separates clock (power cap) effects from stalls
+            for kv in kern.values():
+                kv["sm_cycles"] = kv["ms"] * 1e-3 * mhz * 1e6
         roof = dict(bound="tensor", achieved=fwd["tflops"], peak=peaks["tf32_tflops"], unit="TFLOP/s", frac=fwd["tflops"] / peaks["tf32_tflops"],
-                    traffic=204.4e6 if (M == M_PER_GPU and x3) else None,
-                    traffic_note="dram read+write bytes per launch from ncu (profiles/ffn_fc_step_M8192_launch_list.md); algorithmic 235.9e6",
+                    traffic=NCU_DRAM_BYTES["ffn_up_forward_M8192_3xtf32"] if (M == M_PER_GPU and x3) else None,
+                    traffic_note="dram read+write bytes per launch from an ncu capture of this kernel at this shape; algorithmic 235.9e6",
                     kernel="gemm_tcgen05_pair_kernel<A=K-major, B=MN-major> (forward: x.w + bias, GELU)", peak_source=peaks["source"],
                     issued_tflops=fwd["tflops"] * (2 if x3 else 1),
                     issued_frac=fwd["tflops"] * (2 if x3 else 1) / peaks["tf32_tflops"],
@@ -296,53 +490,86 @@ def run_ours(args):
                    e2e=None if not e2e_steps else dict(value=flops_per_step * world / (e2e_s / e2e_steps) / 1e12, unit=UNIT,
                                                        h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
                                                        ms_per_step=e2e_s / e2e_steps * 1e3, steps=e2e_steps),
-                   clocks=clocks)
+                   clocks=clocks, host_us_per_call=host_us, **sub)
         if world == 1 and not args.no_cpu_baseline and not args.profile:
             out["cpu_baseline"] = cpu_reference_sample(rows=args.cpu_rows)
         print(json.dumps(out), flush=True)
-    be.close()
     if world > 1:
         dist.destroy_process_group()
 
 
-def run_train(args):
-    """--workload train: one full GPT-2 124M training step (BASELINE.json configs[3]) -- zero_grad, forward, backward
-    with bucketed NCCL all-reduce of every weight gradient overlapped with the backward pass, gradient clipping and
-    AdamW -- global batch 64 x 256 tokens sharded over the ranks (strong scaling).  Seeded random-init weights and
-    uniform random token ids.  Reports tokens/s."""
+def train_record(torch, dist, world, rank, dev, mode_name="3xtf32", global_batch=64, steps=5, warmup=2, sampler=None, parity=True):
+    """One full GPT-2 124M training step (BASELINE.json configs[3]) -- zero_grad, forward, backward with bucketed NCCL
+    all-reduce of every weight gradient overlapped with the backward pass, gradient clipping and AdamW -- global batch
+    `global_batch` x 256 tokens sharded over the ranks (strong scaling).  Seeded random-init weights (the same on every rank)
+    and uniform random token ids.  Returns the record on every rank (timings are the maximum over ranks).
+
+    dp_parity: the gradients that the ranks hold after the all-reduce against rank 0 computing the whole global batch alone,
+    per tensor max|a - b| / max|b|: only the order of summation differs."""
     import numpy as np
-    import torch
-    import torch.distributed as dist
     import gpt_b200
     from gpt_b200.data_parallel import DataParallelStep
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
     cfg = gpt_b200.GPT2_124M
-    GB, T = args.global_batch, 256
+    GB, T = global_batch, 256
     assert GB % world == 0
     B = GB // world
-    mode = gpt_b200.MODE_TF32 if args.mode == "tf32" else gpt_b200.MODE_3XTF32
+    mode = gpt_b200.MODE_TF32 if mode_name == "tf32" else gpt_b200.MODE_3XTF32
     stream = torch.cuda.current_stream()
-    model = gpt_b200.Model(cfg, local_rank, stream.cuda_stream, mode, seed=42)
+    model = gpt_b200.Model(cfg, dev.index, stream.cuda_stream, mode, seed=42)
     model.init(0.0, 0.02)           # same seed on every rank: identical replicas
     model.set_size(B, T)
-    # torch view of the packed gradient buffer (no copy) for the collectives
-    class _Raw:
+
+    class _Raw:   # torch view of the packed gradient buffer (no copy) for the collectives
         __cuda_array_interface__ = dict(shape=(model.num_params,), typestr="<f4", data=(model.grads_ptr, False), version=3, strides=None)
     grads = torch.as_tensor(_Raw(), device=dev)
     dp = DataParallelStep(model, grads, world, layers_per_group=3)
     rng = np.random.default_rng(1000)
-    seqs = rng.integers(0, cfg["vocab_size"], size=(GB, T + 1)).astype(np.int32)[rank * B:(rank + 1) * B]
+    all_seqs = rng.integers(0, cfg["vocab_size"], size=(GB, T + 1)).astype(np.int32)
+    seqs = all_seqs[rank * B:(rank + 1) * B]
     h_in = torch.from_numpy(np.ascontiguousarray(seqs[:, :T])).pin_memory()
     h_lbl = torch.from_numpy(np.ascontiguousarray(seqs[:, 1:])).pin_memory()
     d_in, d_lbl = h_in.to(dev), h_lbl.to(dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- dp_parity first, on the untouched initial weights
+    dp_parity = None
+    if parity and world > 1:
+        dp.step(d_in, d_lbl)
+        torch.cuda.synchronize()
+        g_dp = grads.clone()
+        barrier()
+        per_tensor = {}
+        if rank == 0:
+            model.set_size(GB, T)
+            f_in = torch.from_numpy(np.ascontiguousarray(all_seqs[:, :T])).to(dev)
+            f_lbl = torch.from_numpy(np.ascontiguousarray(all_seqs[:, 1:])).to(dev)
+            model.zero_grad()
+            model.forward(f_in)
+            model.backward(f_in, f_lbl)
+            model.synchronize()
+            names = sorted(model.param_offsets, key=model.param_offsets.get)
+            offs = [model.param_offsets[n] for n in names] + [model.num_params]
+            for i, n in enumerate(names):
+                a, b = g_dp[offs[i]:offs[i + 1]], grads[offs[i]:offs[i + 1]]
+                per_tensor[n] = float((a - b).abs().max() / b.abs().max().clamp_min(1e-30))
+            model.set_size(B, T)
+            del f_in, f_lbl
+        del g_dp
+        barrier()
+        if rank == 0:
+            dp_parity = dict(max=max(per_tensor.values()), per_tensor=per_tensor,
+                             note=f"all-reduced gradients of {world} ranks (per-GPU batch {B}) vs rank 0 alone on the whole batch of {GB}")
 
     def step(e2e=False):
         if e2e:  # the step as a host program sees it: tokens from pinned host memory in, loss back out
@@ -353,31 +580,23 @@ def run_train(args):
         model.optimizer_step(6e-4, 0.9, 0.95, 0.1)
         return model.loss(d_lbl) if e2e else None
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    sampler = ClockSampler(local_rank) if rank == 0 else None
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         step()
     model.synchronize()
     barrier()
     t_begin = time.time()
     l0 = model.launch_count()
+    c0 = dp.collectives
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         step()
     e1.record()
     barrier()
-    ms = e0.elapsed_time(e1)
+    ms = max_over_ranks(e0.elapsed_time(e1))
     launches = model.launch_count() - l0
-    if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    # where the step's time goes (rank 0's view, three steps): the same calls as dp.step with events in between
+    collectives = (dp.collectives - c0) // max(1, steps)
+    # where the step's time goes (this rank's view, three steps): the same calls as dp.step with events in between
     phase_names = ("zero_grad+forward", "backward", "wait_for_allreduce", "clip", "adamw")
     phases = dict.fromkeys(phase_names, 0.0)
     for _ in range(3):
@@ -400,63 +619,89 @@ def run_train(args):
         for i, name in enumerate(phase_names):
             phases[name] += ev[i].elapsed_time(ev[i + 1]) / 3.0
     barrier()
-    n_e2e = max(2, min(args.steps, 5))
+    n_e2e = max(2, min(steps, 5))
     loss = step(True)
     barrier()
     t0 = time.perf_counter()
     for _ in range(n_e2e):
         loss = step(True)
     barrier()
-    e2e_s = time.perf_counter() - t0
-    if world > 1:
-        t = torch.tensor([e2e_s], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
-    clocks = sampler.stop(t_begin, time.time()) if sampler else None
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    clocks = sampler.summary(t_begin, time.time()) if sampler else None
     model.synchronize()
+    ms_step = ms / steps
+    tokens = GB * T
+    lin_flops = 3 * 247.1e6 * tokens  # forward + backward of all linear layers: 741.4 MFLOP per token
+    rec = dict(tokens_per_s=tokens / (ms_step * 1e-3), ms_per_step=ms_step, global_batch=GB, seq_len=T, per_gpu_batch=B, n_gpus=world,
+               mode=mode_name, scaling="strong", steps=steps, warmup=warmup, phases_ms=phases, collectives_per_step=int(collectives),
+               gpu_launches_per_step=int(launches // max(1, steps)), linear_path_tflops=lin_flops / (ms_step * 1e-3) / 1e12,
+               e2e=dict(value=tokens / (e2e_s / n_e2e), unit="tokens/s", h2d_bytes_per_step=int(2 * B * T * 4), d2h_bytes_per_step=4,
+                        ms_per_step=e2e_s / n_e2e * 1e3, loss=loss),
+               dp_parity=dp_parity, clocks=clocks, comm_sms=dp.comm_sms)
+    model.close()
+    return rec
+
+
+def run_train(args):
+    """--workload train: the training step of train_record as the line's own metric (tokens/s, strong scaling)."""
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        _init_process_group(dist, dev)
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    rec = train_record(torch, dist, world, rank, dev, args.mode, args.global_batch, args.steps, args.warmup, sampler, parity=not args.no_parity)
+    if sampler:
+        sampler.close()
     if rank == 0:
-        ms_step = ms / args.steps
-        tokens = GB * T
-        lin_flops = 3 * 247.1e6 * tokens  # forward + backward of all linear layers: 741.4 MFLOP per token
         peaks = measured_peaks()
-        out = dict(metric="train_tokens_per_s", value=tokens / (ms_step * 1e-3), unit="tokens/s", n_gpus=world, steps=args.steps,
-                   warmup=args.warmup, ms_per_step=ms_step, higher_is_better=True, scaling="strong", vs_baseline=None,
-                   dtype="tf32x3 (fp32-accurate split)" if mode == gpt_b200.MODE_3XTF32 else "tf32", data="synthetic", impl="ours",
-                   config=dict(workload="GPT-2 124M full training step (forward, backward, grad all-reduce, clip, AdamW)", global_batch=GB,
-                               seq_len=T, per_gpu_batch=B, mode=args.mode, parallelism=f"dp{world}",
+        per_gpu = rec["linear_path_tflops"] / world
+        out = dict(metric="train_tokens_per_s", value=rec["tokens_per_s"], unit="tokens/s", n_gpus=world, steps=args.steps,
+                   warmup=args.warmup, ms_per_step=rec["ms_per_step"], higher_is_better=True, scaling="strong", vs_baseline=None,
+                   dtype="tf32x3 (fp32-accurate split)" if args.mode != "tf32" else "tf32", data="synthetic", impl="ours",
+                   config=dict(workload="GPT-2 124M full training step (forward, backward, grad all-reduce, clip, AdamW)", global_batch=rec["global_batch"],
+                               seq_len=256, per_gpu_batch=rec["per_gpu_batch"], mode=args.mode, parallelism=f"dp{world}",
                                l2="activations and weights (>10 GB per step) exceed the 126 MB L2"),
-                   linear_path_tflops=lin_flops / (ms_step * 1e-3) / 1e12,
-                   roofline=dict(bound="tensor", achieved=lin_flops / world / (ms_step * 1e-3) / 1e12, peak=peaks["tf32_tflops"], unit="TFLOP/s",
-                                 frac=lin_flops / world / (ms_step * 1e-3) / 1e12 / peaks["tf32_tflops"], traffic=None,
+                   linear_path_tflops=rec["linear_path_tflops"],
+                   roofline=dict(bound="tensor", achieved=per_gpu, peak=peaks["tf32_tflops"], unit="TFLOP/s", frac=per_gpu / peaks["tf32_tflops"], traffic=None,
                                  note="linear-path algorithmic flops per GPU over the WHOLE step time (attention, LayerNorm, softmax, "
                                       "optimizer included in the time)", peak_source=peaks["source"]),
-                   phases_ms=phases, gpu_launches=int(launches), collectives_per_step=dp.collectives // max(1, args.warmup + args.steps + n_e2e + 4),
-                   e2e=dict(value=tokens / (e2e_s / n_e2e), unit="tokens/s", h2d_bytes_per_step=int(2 * B * T * 4), d2h_bytes_per_step=4,
-                            ms_per_step=e2e_s / n_e2e * 1e3, loss=loss),
-                   clocks=clocks)
+                   phases_ms=rec["phases_ms"], gpu_launches=rec["gpu_launches_per_step"] * args.steps, collectives_per_step=rec["collectives_per_step"],
+                   dp_parity=rec["dp_parity"], e2e=rec["e2e"], clocks=rec["clocks"])
         print(json.dumps(out), flush=True)
-    model.close()
     if world > 1:
         dist.destroy_process_group()
 
 
-def run_decode(args):
-    """--workload decode: the linear layers of one GPT-2 124M decode step (BASELINE.json configs[4]) for batch 1, 8, 64:
-    per layer QKV, attention projection, FFN up (GELU), FFN down, then the 50304-wide LM head, with m = batch rows.
-    HBM-bound: 494.27 MB of fp32 weights are read once per step.  Reports GB/s (weights bytes / time) per batch; the
-    JSON `value` is the batch-8 figure.  The reference has no KV-cached decode (src/infer/infer.cpp:121 recomputes the
-    whole prefix), so this measures the GEMM shapes of such a step, not end-to-end generation."""
-    import torch
+def _init_process_group(dist, dev):
+    """NCCL process group whose collectives run on a high-priority stream (their CTAs are placed before pending GEMM CTAs)."""
+    try:
+        from torch.distributed import ProcessGroupNCCL
+        opts = ProcessGroupNCCL.Options(is_high_priority_stream=True)
+        dist.init_process_group("nccl", device_id=dev, pg_options=opts)
+    except Exception:
+        if not dist.is_initialized():
+            dist.init_process_group("nccl", device_id=dev)
+
+
+def decode_record(torch, dev, mode_name="3xtf32", batches=(1, 8, 64), steps=20, warmup=3, ctx_options=()):
+    """The linear layers of one GPT-2 124M decode step (BASELINE.json configs[4]) for each batch size: per layer QKV,
+    attention projection, FFN up (GELU), FFN down, then the 50304-wide LM head, with m = batch rows.  HBM-bound: 494.27 MB
+    of fp32 weights are read once per step.  GB/s = weight bytes / time (CUDA events around replays of the step captured
+    as one CUDA graph, so that the time is the kernels', not the host's launch loop)."""
     import gpt_b200
-    torch.cuda.set_device(0)
-    dev = torch.device("cuda", 0)
     cfg = gpt_b200.GPT2_124M
     L, D, F, Vp = cfg["num_layers"], cfg["d_model"], cfg["d_ffn"], cfg["vocab_size_padded"]
-    mode = gpt_b200.MODE_TF32 if args.mode == "tf32" else gpt_b200.MODE_3XTF32
-    be = gpt_b200.Backend(0, torch.cuda.current_stream().cuda_stream, mode)
+    mode = gpt_b200.MODE_TF32 if mode_name == "tf32" else gpt_b200.MODE_3XTF32
+    be = gpt_b200.Backend(dev.index, torch.cuda.current_stream().cuda_stream, mode)
     # inference: nothing writes the weights between layers, so each layer may prefetch them while its predecessor still runs
     options = dict(decode_early_launch=1)
-    for kv in args.ctx_option:
+    for kv in ctx_options:
         key, _, val = kv.partition("=")
         options[key] = int(val)
     for key, val in options.items():
@@ -471,10 +716,8 @@ def run_decode(args):
     weight_bytes = 4.0 * (L * (D * 3 * D + D * D + 2 * D * F) + Vp * D)
     peaks = measured_peaks()
     results = {}
-    sampler = ClockSampler(0)
-    t_begin = time.time()
     launches = 0
-    for batch in [int(b) for b in args.decode_batches.split(",")]:
+    for batch in batches:
         x = torch.randn(batch, D, device=dev, generator=g)
         q, a, u, ua, dn, lg = (torch.empty(batch, n, device=dev) for n in (3 * D, D, F, F, D, Vp))
 
@@ -486,13 +729,11 @@ def run_decode(args):
                 be.device_linear_activation_fused_forward(dn, None, ua, W["down"][l], bias["down"], False, 1, batch, F, D)
             be.device_unembedding_forward(lg, x, wte, 1, batch, D, Vp)
 
-        # a decode step is 49 small GEMMs (about 100 launches): replay it as one CUDA graph so that the time is the
-        # kernels', not the host's launch loop
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             be.set_stream(side.cuda_stream)
-            for _ in range(max(args.warmup, 3)):   # sizes the scratch buffer and sets kernel attributes before capture
+            for _ in range(max(warmup, 3)):   # sizes the scratch buffer and sets kernel attributes before capture
                 step()
             side.synchronize()
             l0 = be.launch_count()
@@ -504,29 +745,45 @@ def run_decode(args):
             side.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record(side)
-            for _ in range(args.steps):
+            for _ in range(steps):
                 graph.replay()
             e1.record(side)
             side.synchronize()
-        launches += per_step * args.steps
-        ms = e0.elapsed_time(e1) / args.steps
+        torch.cuda.current_stream().wait_stream(side)
+        launches += per_step * steps
+        ms = e0.elapsed_time(e1) / steps
         results[f"batch{batch}"] = dict(ms_per_step=ms, gbs=weight_bytes / (ms * 1e-3) / 1e9, tokens_per_s=batch / (ms * 1e-3),
-                                         hbm_frac=weight_bytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"])
+                                         hbm_frac=weight_bytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], launches_per_step=per_step)
+    be.set_stream(torch.cuda.current_stream().cuda_stream)
     be.synchronize()
+    be.close()
+    return dict(per_batch=results, weight_bytes=weight_bytes, peak_gbs=peaks["hbm_gbs"], options=options, gpu_launches=int(launches),
+                note="fp32 FMA kernels (no TF32 rounding); algorithmic bytes = the fp32 weights read once per step")
+
+
+def run_decode(args):
+    """--workload decode: see decode_record; the JSON `value` is the batch-8 figure.  The reference has no KV-cached decode
+    (src/infer/infer.cpp:121 recomputes the whole prefix), so this measures the GEMM shapes of such a step."""
+    import torch
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    sampler = ClockSampler(0)
+    t_begin = time.time()
+    rec = decode_record(torch, dev, args.mode, [int(b) for b in args.decode_batches.split(",")], args.steps, args.warmup, args.ctx_option)
     clocks = sampler.stop(t_begin, time.time())
+    results = rec["per_batch"]
     r8 = results.get("batch8") or next(iter(results.values()))
     out = dict(metric="decode_linear_weight_stream_gbs", value=r8["gbs"], unit="GB/s", n_gpus=1, steps=args.steps, warmup=args.warmup,
                ms_per_step=r8["ms_per_step"], higher_is_better=True, scaling="weak", vs_baseline=None,
-               dtype="f32" if True else "tf32", data="synthetic", impl="ours",
-               config=dict(workload="GPT-2 124M decode step, linear layers only (49 GEMMs with m = batch)", mode=args.mode, options=options,
-                           weight_bytes=weight_bytes, l2="494 MB of weights per step exceed the 126 MB L2"),
+               dtype="f32", data="synthetic", impl="ours",
+               config=dict(workload="GPT-2 124M decode step, linear layers only (49 GEMMs with m = batch)", mode=args.mode, options=rec["options"],
+                           weight_bytes=rec["weight_bytes"], l2="494 MB of weights per step exceed the 126 MB L2"),
                per_batch=results,
-               roofline=dict(bound="hbm", achieved=r8["gbs"], peak=peaks["hbm_gbs"], unit="GB/s", frac=r8["hbm_frac"], traffic=496.4e6,
-                             traffic_note="dram read+write bytes of the 49 kernels of a batch-1 step from ncu (profiles/decode_step_batch1_ncu.md); algorithmic 494.27e6",
+               roofline=dict(bound="hbm", achieved=r8["gbs"], peak=rec["peak_gbs"], unit="GB/s", frac=r8["hbm_frac"], traffic=NCU_DRAM_BYTES["decode_step_batch1"],
+                             traffic_note="dram read+write bytes of the 49 kernels of a batch-1 step (ncu); algorithmic 494.27e6",
                              note="algorithmic bytes = fp32 weights read once per step (494.27 MB); batch 8", peak_source="of measured (MEASURED_PEAKS.json copy bandwidth)"),
-               gpu_launches=int(launches), clocks=clocks)
+               gpu_launches=rec["gpu_launches"], clocks=clocks)
     print(json.dumps(out), flush=True)
-    be.close()
 
 
 def run_generate(args):
@@ -669,7 +926,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--mode", choices=["3xtf32", "tf32"], default="3xtf32")
-    ap.add_argument("--impl", choices=["ours", "reference", "reference_cuda"], default="ours")
+    ap.add_argument("--impl", choices=["ours", "reference", "reference_cuda", "reference_cuda_shapes"], default="ours")
     ap.add_argument("--cpu-rows", type=int, default=256, help="rows of the workload the cpu_baseline leg runs")
     ap.add_argument("--ref-rows", type=int, default=32, help="rows per step of the --impl reference arm")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -683,12 +940,16 @@ def main():
     ap.add_argument("--decode-batches", default="1,8,64", help="decode workload: batch sizes (the JSON value is the batch-8 figure)")
     ap.add_argument("--ctx-option", action="append", default=[], metavar="KEY=VALUE",
                     help="gptb200_ctx_set_option before the run (decode workload; experiments)")
-    ap.add_argument("--profile", action="store_true", help="only the timed steps: no end-to-end, clock-load or CPU legs")
+    ap.add_argument("--profile", action="store_true", help="only the timed steps: no end-to-end, clock-load or CPU legs, no sub-records")
+    ap.add_argument("--no-subrecords", action="store_true", help="leave out the shapes / decode / train_step / reference_gpu sub-records")
+    ap.add_argument("--no-parity", action="store_true", help="train workload: skip the N-rank vs one-rank gradient comparison")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
     elif args.impl == "reference_cuda":
         run_reference_cuda(args)
+    elif args.impl == "reference_cuda_shapes":
+        run_reference_cuda_shapes(args)
     elif args.workload == "train":
         run_train(args)
     elif args.workload == "decode":

@@ -39,7 +39,17 @@ def _stale(target: str, deps: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(verbose: bool = False, force: bool = False) -> str:
+def build(verbose: bool = False, force: bool = False, out: str | None = None, defines: list[str] | None = None) -> str:
+    """`out` / `defines`: build a variant of the library somewhere else with extra -D flags (kernel experiments)."""
+    if out:
+        cu = [f for f in _sources("capi.cu", "backend_capi.cu", "b200_backend.cu", "gpt_model.cu", "noalloc.cu") if os.path.exists(f)]
+        cmd = [_nvcc(), "-std=c++17", "-O3", *ARCH_FLAGS, "-lineinfo", "-Xcompiler", "-fPIC", "-shared", *[f"-D{d}" for d in (defines or [])],
+               "-I", os.path.join(HERE, "..", "include"), "-I", CSRC, "-I", os.path.join(CSRC, "iface"), "-o", out, *cu]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            sys.stderr.write(res.stdout + res.stderr)
+            raise RuntimeError("nvcc failed building " + out)
+        return out
     os.makedirs(LIBDIR, exist_ok=True)
     deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(HERE, "..", "include", "gptb200.h")]
     cu = _sources("capi.cu", "backend_capi.cu", "b200_backend.cu", "gpt_model.cu", "noalloc.cu")

@@ -8,17 +8,26 @@
 #include "b200_backend.h"
 #include "../../include/gptb200.h"
 
+// Two error conventions.  As a drop-in for the reference's backend object (gptb200_backend_create) an error is printed with
+// file and line and the process is aborted, as the reference does (src/backend/cuda/utils/cuda_utils.cuh:21-48).  Behind
+// this library's own model driver (abort_on_error = false) the first failing status is kept in the object, every later
+// operator becomes a no-op, and the gptb200_model_* entry point returns that status to its caller.
 #define B200_CHECK(expr)                                                                                     \
     do {                                                                                                     \
+        if (status_ != 0) return;                                                                            \
         const int rc_ = (expr);                                                                              \
         if (rc_ != 0) {                                                                                      \
-            printf("B200Backend error: %s:%i:%d = %s (%s)\n", __FILE__, __LINE__, rc_, gptb200_status_string(rc_), \
-                   ctx_ ? gptb200_last_error(ctx_) : "");                                                   \
-            abort();                                                                                         \
+            if (abort_on_error_) {                                                                           \
+                printf("B200Backend error: %s:%i:%d = %s (%s)\n", __FILE__, __LINE__, rc_, gptb200_status_string(rc_), \
+                       ctx_ ? gptb200_last_error(ctx_) : "");                                               \
+                abort();                                                                                     \
+            }                                                                                                \
+            status_ = rc_;                                                                                   \
+            return;                                                                                          \
         }                                                                                                    \
     } while (0)
 
-B200Backend::B200Backend(unsigned long seed, int device, void *stream, int mode) : seed_(seed)
+B200Backend::B200Backend(unsigned long seed, int device, void *stream, int mode, bool abort_on_error) : seed_(seed), abort_on_error_(abort_on_error)
 {
     B200_CHECK(gptb200_ctx_create(&ctx_, device, stream, mode));
 }
@@ -29,8 +38,20 @@ B200Backend::~B200Backend()
 }
 
 void B200Backend::device_get_memory_info(float *free_mb, float *total_mb) { B200_CHECK(gptb200_memory_info(ctx_, free_mb, total_mb)); }
-void B200Backend::device_malloc(void **ptr, size_t size) { B200_CHECK(gptb200_malloc(ctx_, ptr, size)); }
-void B200Backend::device_free(void *ptr) { B200_CHECK(gptb200_free(ctx_, ptr)); }
+void B200Backend::device_malloc(void **ptr, size_t size)
+{
+    if (ptr) *ptr = nullptr;   // a failed (or skipped) allocation leaves a null pointer, never an indeterminate one
+    B200_CHECK(gptb200_malloc(ctx_, ptr, size));
+}
+void B200Backend::device_free(void *ptr)
+{
+    // memory is released also after an earlier operator failed (teardown of a model that met an error)
+    if (status_ != 0) {
+        if (ctx_) gptb200_free(ctx_, ptr);
+        return;
+    }
+    B200_CHECK(gptb200_free(ctx_, ptr));
+}
 void B200Backend::device_memset(void *ptr, int value, size_t size) { B200_CHECK(gptb200_memset(ctx_, ptr, value, size)); }
 
 void B200Backend::device_fill_normal(float *ptr, float mean, float stddev, size_t size)

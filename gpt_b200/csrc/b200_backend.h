@@ -4,7 +4,9 @@
 // include/gptb200.h); a gptb200_ctx takes the place of the cuBLAS handle that the reference's CUDABackend
 // owns (src/backend/cuda/cuda_backend.h:40).  The remaining operators are plain kernels (backend_ops.cuh).
 // As in the reference (src/backend/cuda/utils/cuda_utils.cuh:21-48) the interface returns void: any error is
-// printed with file and line and the process is aborted.  Everything runs on one stream, in call order.
+// printed with file and line and the process is aborted.  With abort_on_error = false (this library's own model
+// driver) the first failing status is kept instead (status()), and every later operator is skipped.
+// Everything runs on one stream, in call order.
 #pragma once
 
 #include "backend_interface.h"  // this library's copy of the declaration, or the reference's own header
@@ -16,10 +18,12 @@ class B200Backend : public IGPTBackend
 public:
     // `stream` is a cudaStream_t (nullptr = the legacy default stream, as in the reference);
     // `mode`: 0 = 3xTF32 (default), 1 = TF32.
-    explicit B200Backend(unsigned long seed = 42, int device = 0, void *stream = nullptr, int mode = 0);
+    explicit B200Backend(unsigned long seed = 42, int device = 0, void *stream = nullptr, int mode = 0, bool abort_on_error = true);
     ~B200Backend() override;
 
     gptb200_ctx *context() const { return ctx_; }
+    int status() const { return status_; }      // first failing gptb200_status since construction / clear_status (0 = none)
+    void clear_status() { status_ = 0; }
 
     void device_get_memory_info(float *free_mb, float *total_mb) override;
     void device_malloc(void **ptr, size_t size) override;
@@ -50,4 +54,6 @@ private:
     gptb200_ctx *ctx_ = nullptr;
     unsigned long seed_ = 42;
     unsigned long long fill_offset_ = 0;  // elements drawn so far by device_fill_normal
+    bool abort_on_error_ = true;
+    int status_ = 0;
 };

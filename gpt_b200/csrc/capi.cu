@@ -41,6 +41,8 @@ int ensure_workspace(gptb200_ctx *ctx, size_t bytes)
 
 namespace {
 
+constexpr int kDbiasTickets = 4096;   // tile columns x 16 that the fused bias gradient can serve (n <= 65536)
+
 // One GEMM operand as stored: `rows` x `cols` fp32, row pitch `cols`.
 // K-major operand: rows = free extent (M or N), cols = reduction extent.
 // MN-major operand: rows = reduction extent, cols = free extent.
@@ -141,10 +143,10 @@ cudaError_t launch_pair(gptb200_ctx *ctx, bool a_mn, bool b_mn, const CUtensorMa
 }
 
 // Output tensor [depth][rows][cols] (depth > 1 only for split-K partial tiles), written in
-// [32 x 32] pieces from 128-byte-swizzled staging tiles.
-int make_out_tmap(gptb200_ctx *ctx, CUtensorMap *map, float *base, long long depth, long long rows, long long cols)
+// [32 rows x box_cols] pieces from swizzled staging tiles (128-byte swizzle for 32 columns, 64-byte swizzle for 16).
+int make_out_tmap(gptb200_ctx *ctx, CUtensorMap *map, float *base, long long depth, long long rows, long long cols, int box_cols = 32)
 {
-    const TmapKey key{reinterpret_cast<uintptr_t>(base), cols, rows, depth, 32, 32, 2};
+    const TmapKey key{reinterpret_cast<uintptr_t>(base), cols, rows, depth, box_cols, 32, 2};
     const auto hit = ctx->tmaps.find(key);
     if (hit != ctx->tmaps.end()) {
         *map = hit->second;
@@ -152,10 +154,10 @@ int make_out_tmap(gptb200_ctx *ctx, CUtensorMap *map, float *base, long long dep
     }
     cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(depth)};
     cuuint64_t strides[2] = {static_cast<cuuint64_t>(cols) * sizeof(float), static_cast<cuuint64_t>(rows) * cols * sizeof(float)};
-    cuuint32_t box[3] = {32, 32, 1};
+    cuuint32_t box[3] = {static_cast<cuuint32_t>(box_cols), 32, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     const CUresult r = ctx->encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                                   box_cols == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     ctx->tmap_encodes++;
     if (r != CUDA_SUCCESS)
         return fail(ctx, GPTB200_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed (%d) depth=%lld rows=%lld cols=%lld", int(r), depth, rows, cols);
@@ -417,17 +419,26 @@ int run_gemm(gptb200_ctx *ctx, const GemmCall &c, bool *dbias_fused = nullptr)
     if (pair) {
         p.sk_total = pl.sk_total;
         p.sk_unit = pl.sk_unit;
-        const bool fuse_dbias = c.dbias && c.a_mn && c.b_mn && c.accumulate && ctx->fuse_dbias;
+        const bool fuse_dbias = c.dbias && c.a_mn && c.b_mn && c.accumulate && ctx->fuse_dbias && pl.tiles_n * 16 <= kDbiasTickets;
+        // scratch: [partial tiles of cut ranges][their column sums, 128 per CTA][the tiles' shares of the bias gradient, one row per tile row]
+        const size_t cut_dbias_bytes = fuse_dbias && pl.sk_max_share > 1 ? size_t(pl.grid) * PairCfg<false>::kBRows * sizeof(float) : 0;
+        const size_t part_bytes = fuse_dbias ? size_t((pl.tiles_m + 1) / 2) * pl.tiles_n * 256 * sizeof(float) : 0;
+        if (fuse_dbias || pl.sk_max_share > 1) {
+            const int rc = ensure_workspace(ctx, pl.workspace_bytes + cut_dbias_bytes + part_bytes);
+            if (rc != GPTB200_OK) return rc;
+        }
         if (fuse_dbias) {
             p.dbias = c.dbias;
             p.dbias_src = c.b;
+            // TF32 mode is bound by the operand traffic from L2 to the SMs, which the column sums add to: spread them over all tile
+            // rows.  3xTF32 has that bandwidth to spare and its epilogue warps drain an accumulator every four k-blocks: fewer,
+            // longer batches of loads in the first tile row were measured faster there.
+            p.dbias_rows = x3 ? 1 : (pl.tiles_m + 1) / 2;
+            p.dbias_part = ctx->ws + (pl.workspace_bytes + cut_dbias_bytes) / sizeof(float);
+            p.dbias_tickets = ctx->d_pair_flags + size_t(ctx->num_sms) * 8 + 2 + kSkinnyMaxTickets;
             if (dbias_fused) *dbias_fused = true;
         }
         if (pl.sk_max_share > 1) {
-            // behind the partial tiles: 128 column sums per CTA for tiles of the first tile row that are cut by a range boundary
-            const size_t dbias_bytes = fuse_dbias ? size_t(pl.grid) * PairCfg<false>::kBRows * sizeof(float) : 0;
-            const int rc = ensure_workspace(ctx, pl.workspace_bytes + dbias_bytes);
-            if (rc != GPTB200_OK) return rc;
             p.sk_slots = ctx->ws;
             p.sk_dbias = ctx->ws + pl.workspace_bytes / sizeof(float);
             p.sk_flags = ctx->d_pair_flags;
@@ -448,10 +459,11 @@ int run_gemm(gptb200_ctx *ctx, const GemmCall &c, bool *dbias_fused = nullptr)
     }
 
     CUtensorMap ta, tb, to, tact;
-    int rc = make_out_tmap(ctx, &to, out_base, splits, c.M, c.N);
+    const int out_box_cols = pair ? PairCfg<false>::kStageCols : 32;
+    int rc = make_out_tmap(ctx, &to, out_base, splits, c.M, c.N, out_box_cols);
     if (rc != GPTB200_OK) return rc;
     if (p.has_act) {
-        rc = make_out_tmap(ctx, &tact, c.act, 1, c.M, c.N);
+        rc = make_out_tmap(ctx, &tact, c.act, 1, c.M, c.N, out_box_cols);
         if (rc != GPTB200_OK) return rc;
     } else {
         tact = to;
@@ -565,8 +577,9 @@ int gptb200_ctx_create(gptb200_ctx **out, int device, void *cuda_stream, int mod
         return GPTB200_ERR_CUDA;
     }
     ctx->encode = reinterpret_cast<EncodeTiledFn>(fn);
-    // [pair][CTA][epilogue warp] + launch number, CTA count; then one ticket per column block of the decode kernel
-    const size_t flag_bytes = (size_t(ctx->num_sms) * 8 + 2 + kSkinnyMaxTickets) * sizeof(unsigned int);
+    // [pair][CTA][epilogue warp] + launch number, CTA count; then one ticket per column block of the decode kernel; then the
+    // tickets of the bias gradient inside the grad_w GEMM (per tile column, CTA and epilogue warp)
+    const size_t flag_bytes = (size_t(ctx->num_sms) * 8 + 2 + kSkinnyMaxTickets + kDbiasTickets) * sizeof(unsigned int);
     if (cudaMalloc(&ctx->d_status, sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_status, 0, sizeof(int)) != cudaSuccess ||
         cudaMalloc(&ctx->d_pair_flags, flag_bytes) != cudaSuccess || cudaMemset(ctx->d_pair_flags, 0, flag_bytes) != cudaSuccess) {
         if (ctx->d_status) cudaFree(ctx->d_status);
@@ -728,6 +741,8 @@ int gptb200_ctx_synchronize(gptb200_ctx *ctx)
     CUDA_TRY(ctx, cudaMemcpy(&st, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost));
     if (st != 0) {
         cudaMemset(ctx->d_status, 0, sizeof(int));
+        // a kernel that gave up may have left tickets half counted: they must be zero between launches
+        cudaMemset(ctx->d_pair_flags + size_t(ctx->num_sms) * 8 + 2, 0, (kSkinnyMaxTickets + kDbiasTickets) * sizeof(unsigned int));
         return fail(ctx, GPTB200_ERR_DEVICE_TIMEOUT, "device status %d: a bounded wait inside a kernel ran out", st);
     }
     return GPTB200_OK;

@@ -101,6 +101,8 @@ int ensure_workspace(gptb200_ctx *ctx, size_t bytes);
 #define CUDA_TRY(ctx, expr)                                                                                          \
     do {                                                                                                             \
         cudaError_t e_ = (expr);                                                                                     \
-        if (e_ != cudaSuccess)                                                                                       \
+        if (e_ != cudaSuccess) {                                                                                     \
+            cudaGetLastError(); /* reported here: a later, unrelated call must not find it as the runtime's last error */ \
             return gptb200::fail(ctx, GPTB200_ERR_CUDA, "%s:%d %s -> %s", __FILE__, __LINE__, #expr, cudaGetErrorString(e_)); \
+        }                                                                                                            \
     } while (0)

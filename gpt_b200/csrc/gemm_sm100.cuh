@@ -72,12 +72,15 @@ struct GemmParams {
     unsigned int *sk_flags;  // one word per pair, CTA and epilogue warp: the number of the launch whose partial tile is complete
     unsigned int *sk_state;  // [0] number of completed launches that used the flags, [1] CTAs of this launch that have finished
     long long *trace;        // optional [kTraceEvents][kTraceSlots] clock64 samples of the first k-blocks of CTA 0
-    // CTA-pair kernel, grad_w form (both operands MN-major) only: the bias gradient rides this launch.  The epilogue warps of
-    // the pairs that work on the first tile row add up the rows of B (= grad_y [K x N], row pitch N) of their k-block range
-    // and the tile's owner adds the total into dbias[N] (+=).
+    // CTA-pair kernel, grad_w form (both operands MN-major) only: the bias gradient rides this launch.  The tiles of one tile
+    // column read the same columns of B (= grad_y [K x N], row pitch N); each of them adds up its share of the k-blocks (epilogue
+    // warps, plain loads), the shares are parked in dbias_part and the last tile to finish adds them, in tile order, into dbias[N].
     float *dbias;
     const float *dbias_src;
     float *sk_dbias;         // [pair][CTA][128] column sums of tiles cut by a range boundary (published with the partial tile)
+    int dbias_rows;          // tile rows that share the column sums (1: the first tile row does them all)
+    float *dbias_part;       // [tile row][tiles_n * 256] the tiles' shares
+    unsigned int *dbias_tickets;   // [tile column][CTA][epilogue warp] shares parked so far (reset by the last one)
 };
 
 constexpr int kTraceSlots = 128;

@@ -35,6 +35,44 @@
 
 namespace gptb200 {
 
+#ifndef GPTB200_PAIR_STAGE_COLS
+#define GPTB200_PAIR_STAGE_COLS 32
+#endif
+#ifndef GPTB200_PAIR_STAGING_KIB
+#define GPTB200_PAIR_STAGING_KIB 32
+#endif
+#ifndef GPTB200_PAIR_STAGES_TF32
+#define GPTB200_PAIR_STAGES_TF32 6
+#endif
+
+// Ring of an epilogue warp's staging tiles (only lane 0 issues stores and waits on their bulk groups).
+template <int kBufs, int kPieceBytes>
+struct PieceRing {
+    uint32_t base;   // shared-memory address of tile 0 (1024-byte aligned)
+    uint32_t count;
+    __device__ __forceinline__ uint32_t acquire(int lane)
+    {
+        if (lane == 0) ptx::tma_store_wait_read<kBufs - 1>();   // the store that last read this tile has finished reading
+        __syncwarp();
+        return base + (count % kBufs) * kPieceBytes;
+    }
+};
+
+// Writes this thread's COLS consecutive values (row = lane) into a staging tile with the swizzle that the output tensor map
+// undoes: rows of 128 bytes with the 16-byte chunk index XOR-ed with (row mod 8), or rows of 64 bytes with the chunk index
+// XOR-ed with (row / 2 mod 4).  Either way the eight lanes of a store phase hit all 32 banks.
+template <int COLS>
+__device__ __forceinline__ void stage_piece(uint32_t buf, int lane, const float *v)
+{
+#pragma unroll
+    for (int j = 0; j < COLS / 4; ++j) {
+        const uint32_t addr = COLS == 32 ? buf + lane * 128 + ((j ^ (lane & 7)) << 4) : buf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4);
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v[4 * j]), "f"(v[4 * j + 1]), "f"(v[4 * j + 2]),
+                     "f"(v[4 * j + 3])
+                     : "memory");
+    }
+}
+
 template <bool X3>
 struct PairCfg {
     static constexpr int BN = 256;                     // tile columns (both CTAs together)
@@ -42,8 +80,14 @@ struct PairCfg {
     static constexpr bool kChunked = X3;
     static constexpr int kEpiWarps = 8;                // two warps per TMEM lane quarter, 128 columns each
     static constexpr int kColsPerEpiWarp = BN / (kEpiWarps / 4);
-    static constexpr int kStageBufsPerWarp = kEpiWarps == 8 ? 1 : 2;
-    static constexpr int kStagingBytes = kEpiWarps * kStageBufsPerWarp * kStageTileBytes;
+    // Output staging: every epilogue warp owns a ring of [32 rows x kStageCols] tiles; a ring of two lets the warp fill one
+    // tile while the TMA store of the other is still reading shared memory.
+    static constexpr int kStageCols = GPTB200_PAIR_STAGE_COLS;
+    static constexpr int kStagePieceBytes = 32 * kStageCols * 4;
+    static constexpr int kStagingBytes = (X3 ? 32 : GPTB200_PAIR_STAGING_KIB) * 1024;   // 3xTF32: the operand rings leave 32 KiB
+    static constexpr int kStageBufsPerWarp = kStagingBytes / (kEpiWarps * kStagePieceBytes);
+    static_assert(kStageCols == 16 || kStageCols == 32, "staging tiles are 16 or 32 columns wide");
+    static_assert(kStageBufsPerWarp >= 1 && kStageBufsPerWarp * kEpiWarps * kStagePieceBytes == kStagingBytes, "staging ring does not tile its memory");
     static constexpr int kConvWarps = X3 ? 4 : 0;
     static constexpr int kThreads = (4 + kEpiWarps + kConvWarps) * 32;
     static constexpr int kBTileBytes = kBRows * kBK * 4;             // 16 KiB
@@ -53,7 +97,7 @@ struct PairCfg {
     // conversion to the MMAs that read it).  Measured on the FFN shapes: 3 + 3 stages (1246 ns per k-block) beat
     // 4 + 2 (1628 ns): with two low-part buffers the convert -> MMA -> release chain of a buffer becomes the
     // critical path.
-    static constexpr int kStages = X3 ? 3 : 6;
+    static constexpr int kStages = X3 ? 3 : GPTB200_PAIR_STAGES_TF32;
     static constexpr int kLoStages = X3 ? 3 : 0;
     static constexpr int kNumBarriers = 2 * kStages + 2 * (X3 ? kLoStages : 1) + 5;
     static constexpr int kSmemBytes = (kStages + kLoStages) * kHiBytes + kStagingBytes + 1024 + 256;
@@ -242,20 +286,25 @@ __device__ __forceinline__ bool bounded_flag_wait(const unsigned int *flag, unsi
     return ok != 0;
 }
 
-// Bias gradient inside the grad_w GEMM: sums of rows [r0, r1) of src (row pitch ld floats) for 16 consecutive columns per
-// warp.  A quarter of four lanes covers the 16 columns of one row with a 16-byte load each, the eight quarters take eight
-// consecutive rows; `s` carries the lane's running sums of its four columns (col .. col + 3) from call to call.  The rows were
-// (or are about to be) fetched by the operand loads of the same CTA, so these loads are served by L2.
+// Bias gradient inside the grad_w GEMM: column sums of B (= grad_y [K x N], row pitch ld) over the k-blocks kb_first,
+// kb_first + kb_step, ... < kb_end, for 16 consecutive columns per warp.  A quarter of four lanes covers the 16 columns of one
+// row with a 16-byte load each, the eight quarters take eight consecutive rows; `s` carries the lane's running sums of its four
+// columns (col .. col + 3) from call to call.  The rows are fetched by the operand loads of the same CTA at about the same time,
+// so these loads are served by L2.
 template <int UNROLL>
-__device__ __forceinline__ void column_sums_16(float4 &s, const float *__restrict__ src, long long ld, int r0, int r1, int col, bool col_ok, int lane)
+__device__ __forceinline__ void column_sums_16(float4 &s, const float *__restrict__ src, long long ld, int kb_first, int kb_step, int kb_end, int K,
+                                               int col, bool col_ok, int lane)
 {
+    if (kb_first >= kb_end) return;
+    const int groups = 4 * ((kb_end - 1 - kb_first) / kb_step + 1);   // groups of eight rows: four per k-block
     const int g = lane >> 2;
-    for (int rb = r0; rb < r1; rb += 8 * UNROLL) {
+    for (int t0 = 0; t0 < groups; t0 += UNROLL) {
         float4 v[UNROLL];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            const int r = rb + 8 * u + g;
-            v[u] = (col_ok && r < r1) ? __ldg(reinterpret_cast<const float4 *>(src + static_cast<long long>(r) * ld + col)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            const int t = t0 + u;
+            const int r = (kb_first + (t >> 2) * kb_step) * kBK + (t & 3) * 8 + g;
+            v[u] = (col_ok && t < groups && r < K) ? __ldg(reinterpret_cast<const float4 *>(src + static_cast<long long>(r) * ld + col)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
@@ -542,8 +591,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         const int q = warp & 3;
         const int col_base = (e >> 2) * C::kColsPerEpiWarp;
         const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
-        StageRing<C::kStageBufsPerWarp> ring;
-        ring.base = staging_base + e * C::kStageBufsPerWarp * kStageTileBytes;
+        PieceRing<C::kStageBufsPerWarp, C::kStagePieceBytes> ring;
+        ring.base = staging_base + e * C::kStageBufsPerWarp * C::kStagePieceBytes;
         ring.count = 0;
         uint32_t g = 0, tile_count = 0;
         bool ok = true;
@@ -558,18 +607,19 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, bias_lane, j);
             }
-            const bool in_range = row0 < p.M && col0 < p.N;
-            {
+            constexpr int kPieces = 32 / C::kStageCols;
+#pragma unroll
+            for (int h = 0; h < kPieces; ++h) {
                 const uint32_t buf = ring.acquire(lane);
-                    stage_row(buf, lane, v);
-                    ptx::fence_proxy_async_smem();
+                stage_piece<C::kStageCols>(buf, lane, &v[h * C::kStageCols]);
+                ptx::fence_proxy_async_smem();
                 __syncwarp();
-                    if (lane == 0) {
-                    if (in_range) {
+                if (lane == 0) {
+                    if (row0 < p.M && col0 + h * C::kStageCols < p.N) {
                         if (p.epi_mode == EPI_ACCUM)
-                            ptx::tma_reduce_add_3d(&tmap_out, col0, row0, 0, buf);
+                            ptx::tma_reduce_add_3d(&tmap_out, col0 + h * C::kStageCols, row0, 0, buf);
                         else
-                            ptx::tma_store_3d(&tmap_out, col0, row0, 0, buf);
+                            ptx::tma_store_3d(&tmap_out, col0 + h * C::kStageCols, row0, 0, buf);
                     }
                     ptx::tma_store_commit();
                 }
@@ -578,16 +628,19 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             if (p.has_act) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+#pragma unroll
+                for (int h = 0; h < kPieces; ++h) {
                     const uint32_t buf = ring.acquire(lane);
-                stage_row(buf, lane, v);
-                ptx::fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) {
-                    if (in_range) ptx::tma_store_3d(&tmap_act, col0, row0, 0, buf);
-                    ptx::tma_store_commit();
+                    stage_piece<C::kStageCols>(buf, lane, &v[h * C::kStageCols]);
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (row0 < p.M && col0 + h * C::kStageCols < p.N) ptx::tma_store_3d(&tmap_act, col0 + h * C::kStageCols, row0, 0, buf);
+                        ptx::tma_store_commit();
+                    }
+                    ring.count++;
                 }
-                ring.count++;
-                }
+            }
         };
 
         PairWork work = my_work();
@@ -601,8 +654,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             // slot of pair r: [CTA][epilogue warp][128 values][lane]
             auto slot_of = [&](long long r) { return p.sk_slots + ((r * 2 + rank) * C::kEpiWarps + e) * 4096 + lane; };
             auto flag_of = [&](long long r) { return p.sk_flags + (r * 2 + rank) * C::kEpiWarps + e; };
-            // bias gradient: pairs on the first tile row sum the rows of B of their k-block range, 16 columns per epilogue warp
-            const bool duty = DB && p.dbias != nullptr && tm2 == 0;
+            // bias gradient: the tiles of a tile column read the same columns of B; the first db_rows of them share the column
+            // sums, tile (tm2, tn) taking the k-blocks kb = tm2 (mod db_rows); 16 columns per epilogue warp
+            // (p.dbias_rows = number of tile rows that share the work: all of them, or only the first)
+            const int db_rows = DB ? p.dbias_rows : 1;
+            const bool duty = DB && p.dbias != nullptr && tm2 < db_rows;
+            const int db_first = kb0 + (tm2 - kb0 % db_rows + db_rows) % db_rows;   // first k-block >= kb0 of this tile's share
             const int bcol = tn * BN + static_cast<int>(rank) * C::kBRows + e * 16 + (lane & 3) * 4;
             float4 bsum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             auto dbias_slot = [&](long long r) { return reinterpret_cast<float4 *>(p.sk_dbias + (r * 2 + rank) * C::kBRows + e * 16) + (lane & 3); };
@@ -612,8 +669,35 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     bsum.x += t.x; bsum.y += t.y; bsum.z += t.z; bsum.w += t.w;
                 }
             };
-            auto dbias_write = [&]() {   // owner: grad_b += total (one writer per column: the owner of tile (0, tn))
-                if (duty && lane < 4 && bcol < p.N) {
+            // Owner of the tile: bsum is the tile's share.  The shares of the db_rows tiles of this column are parked in scratch;
+            // the warp that parks the last one (a ticket per tile column, CTA and epilogue warp, which it also resets) adds them
+            // in tile order, so the sum does not depend on who came last, and adds the total into grad_b.
+            auto dbias_write = [&]() {
+                if (!duty) return;
+                if (db_rows > 1) {
+                    const long long npad = static_cast<long long>(p.tiles_n) * BN;
+                    float *part = p.dbias_part + tn * BN + static_cast<int>(rank) * C::kBRows + e * 16 + (lane & 3) * 4;
+                    if (lane < 4) __stcg(reinterpret_cast<float4 *>(part + tm2 * npad), bsum);
+                    __threadfence();
+                    __syncwarp();
+                    int last = 0;
+                    if (lane == 0) {
+                        unsigned int *ticket = p.dbias_tickets + (tn * 2 + rank) * C::kEpiWarps + e;
+                        last = atomicAdd(ticket, 1u) == static_cast<unsigned int>(db_rows - 1);
+                        if (last) atomicExch(ticket, 0u);
+                        __threadfence();
+                    }
+                    last = __shfl_sync(0xffffffffu, last, 0);
+                    if (!last) return;
+                    bsum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    if (lane < 4) {
+                        for (int t = 0; t < db_rows; ++t) {
+                            const float4 v = __ldcg(reinterpret_cast<const float4 *>(part + t * npad));
+                            bsum.x += v.x; bsum.y += v.y; bsum.z += v.z; bsum.w += v.w;
+                        }
+                    }
+                }
+                if (lane < 4 && bcol < p.N) {
                     float *dst = p.dbias + bcol;
                     dst[0] += bsum.x; dst[1] += bsum.y; dst[2] += bsum.z; dst[3] += bsum.w;
                 }
@@ -647,8 +731,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     ptx::tc_fence_before();
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive_cluster(leader_tmem_empty[buf]);
-                    // the rows of B that belong to the chunk just drained (fetched by the operand loads a moment ago)
-                    if (duty) column_sums_16<8>(bsum, p.dbias_src, p.N, kb * kBK, min(min(kb + pair_chunk_kb(kb == kb0), kb1) * kBK, p.K), bcol, bcol < p.N, lane);
+                    // this tile's share of the k-blocks of the chunk just drained (fetched by the operand loads a moment ago)
+                    if (duty) {
+                        const int first = kb + (tm2 - kb % db_rows + db_rows) % db_rows;
+                        column_sums_16<8>(bsum, p.dbias_src, p.N, first, db_rows, min(kb + pair_chunk_kb(kb == kb0), kb1), p.K, bcol, bcol < p.N, lane);
+                    }
                 }
                 if (duty) column_sums_finish(bsum);
                 if (ok && !owner) {
@@ -690,7 +777,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 ++g;
                 // while the tensor cores work on this range: the column sums of its rows of B
                 if (duty) {
-                    column_sums_16<16>(bsum, p.dbias_src, p.N, kb0 * kBK, min(kb1 * kBK, p.K), bcol, bcol < p.N, lane);
+                    column_sums_16<16>(bsum, p.dbias_src, p.N, db_first, db_rows, kb1, p.K, bcol, bcol < p.N, lane);
                     column_sums_finish(bsum);
                 }
                 if (!bounded_wait_cluster(tmem_full_bar(buf), use, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE)) {

@@ -85,15 +85,17 @@ public:
     size_t num_params() const { return lay_.total; }
     const ParamLayout &layout() const { return lay_; }
 
-    // Same initialisation as the reference (src/model/gpt.cpp:297-325) plus zeroed padding rows of wte.
+    // Same initialisation as the reference (src/model/gpt.cpp:297-325: the residual projections are drawn with mean 0
+    // whatever `mean` is) plus zeroed padding rows of wte (the reference leaves them normal-filled; zero rows give exactly
+    // zero logits and gradients in the padding columns).
     void init(float mean, float stddev)
     {
         float *w = weights();
         const size_t L = c_.layers, D = c_.d_model, F = c_.d_ffn;
         be_->device_fill_normal(w, mean, stddev, lay_.total);
         const float resid = stddev / sqrtf(2.0f * c_.layers);
-        be_->device_fill_normal(w + lay_.proj_w, mean, resid, L * D * D);
-        be_->device_fill_normal(w + lay_.down_w, mean, resid, L * F * D);
+        be_->device_fill_normal(w + lay_.proj_w, 0.0f, resid, L * D * D);
+        be_->device_fill_normal(w + lay_.down_w, 0.0f, resid, L * F * D);
         for (size_t off : {lay_.ln1_w, lay_.ln2_w}) be_->device_fill_const(w + off, 1.0f, L * D);
         be_->device_fill_const(w + lay_.lnf_w, 1.0f, D);
         for (size_t off : {lay_.ln1_b, lay_.proj_b, lay_.ln2_b, lay_.down_b}) be_->device_fill_const(w + off, 0.0f, L * D);
@@ -105,42 +107,55 @@ public:
 
     // Unlike the reference (src/model/gpt.cpp:399-424 frees and reallocates on every call, i.e. once per generated
     // token in its inference loop), buffers are kept when the new shape fits into what is already allocated.
-    void set_size(int batch, int seq)
+    // Returns false when memory for the new shape cannot be had: the model then keeps its previous shape and buffers.
+    bool set_size(int batch, int seq)
     {
-        B_ = batch;
-        T_ = seq;
         const size_t M = size_t(batch) * seq, L = c_.layers, D = c_.d_model, F = c_.d_ffn, H = c_.heads, Vp = c_.vocab_padded;
         size_t o = 0;
         auto take = [&](size_t n) { const size_t at = o; o += pad4(n); return at; };
-        a_.x_emb = take(M * D);
-        a_.ln1 = take(L * M * D); a_.ln1_mean = take(L * M); a_.ln1_var = take(L * M);
-        a_.qkv = take(L * M * 3 * D); a_.lse = take(L * M * H); a_.attn = take(L * M * D); a_.proj = take(L * M * D);
-        a_.ln2 = take(L * M * D); a_.ln2_mean = take(L * M); a_.ln2_var = take(L * M);
-        a_.up = take(L * M * F); a_.act = take(L * M * F); a_.down = take(L * M * D);
-        a_.lnf = take(M * D); a_.lnf_mean = take(M); a_.lnf_var = take(M);
-        a_.logits = take(M * Vp); a_.probs = take(M * Vp);
-        a_.total = o;
-        void *p = nullptr;
-        if (a_.total > acts_capacity_) {
-            if (acts_) be_->device_free(acts_);
-            be_->device_malloc(&p, a_.total * sizeof(float));
-            acts_ = static_cast<float *>(p);
-            acts_capacity_ = a_.total;
-        }
+        ActLayout a{};
+        a.x_emb = take(M * D);
+        a.ln1 = take(L * M * D); a.ln1_mean = take(L * M); a.ln1_var = take(L * M);
+        a.qkv = take(L * M * 3 * D); a.lse = take(L * M * H); a.attn = take(L * M * D); a.proj = take(L * M * D);
+        a.ln2 = take(L * M * D); a.ln2_mean = take(L * M); a.ln2_var = take(L * M);
+        a.up = take(L * M * F); a.act = take(L * M * F); a.down = take(L * M * D);
+        a.lnf = take(M * D); a.lnf_mean = take(M); a.lnf_var = take(M);
+        a.logits = take(M * Vp); a.probs = take(M * Vp);
+        a.total = o;
+        GradLayout g{};
         if (use_grad_) {
             // activation gradients are consumed right after they are produced: one set of buffers serves all layers
             o = 0;
-            g_.d_ln = take(M * D); g_.d_res = take(M * D); g_.d_x = take(M * D); g_.d_qkv = take(M * 3 * D); g_.d_helper = take(M * H);
-            g_.d_f1 = take(M * F); g_.d_f2 = take(M * F); g_.d_logits = take(M * Vp);
-            g_.total = o;
-            if (g_.total > agrads_capacity_) {
-                if (agrads_) be_->device_free(agrads_);
-                be_->device_malloc(&p, g_.total * sizeof(float));
-                agrads_ = static_cast<float *>(p);
-                agrads_capacity_ = g_.total;
-            }
-            be_->device_memset(agrads_, 0, g_.total * sizeof(float));  // the padding columns of d_logits must be zero
+            g.d_ln = take(M * D); g.d_res = take(M * D); g.d_x = take(M * D); g.d_qkv = take(M * 3 * D); g.d_helper = take(M * H);
+            g.d_f1 = take(M * F); g.d_f2 = take(M * F); g.d_logits = take(M * Vp);
+            g.total = o;
         }
+        // the new buffers first: if one cannot be had, nothing has changed
+        void *new_acts = nullptr, *new_grads = nullptr;
+        const bool need_acts = a.total > acts_capacity_, need_grads = use_grad_ && g.total > agrads_capacity_;
+        if (need_acts) be_->device_malloc(&new_acts, a.total * sizeof(float));
+        if (need_grads) be_->device_malloc(&new_grads, g.total * sizeof(float));
+        if ((need_acts && !new_acts) || (need_grads && !new_grads)) {   // a non-aborting backend leaves a null pointer
+            if (new_acts) be_->device_free(new_acts);
+            if (new_grads) be_->device_free(new_grads);
+            return false;
+        }
+        if (new_acts) {
+            if (acts_) be_->device_free(acts_);
+            acts_ = static_cast<float *>(new_acts);
+            acts_capacity_ = a.total;
+        }
+        if (new_grads) {
+            if (agrads_) be_->device_free(agrads_);
+            agrads_ = static_cast<float *>(new_grads);
+            agrads_capacity_ = g.total;
+        }
+        a_ = a;
+        g_ = g;
+        B_ = batch;
+        T_ = seq;
+        if (use_grad_) be_->device_memset(agrads_, 0, g_.total * sizeof(float));  // the padding columns of d_logits must be zero
+        return true;
     }
 
     void zero_grad()
@@ -299,13 +314,18 @@ int gptb200_model_create(gptb200_model **out, const int *cfg, int device, void *
         if (cfg[i] <= 0) return GPTB200_ERR_INVALID_ARG;
     Config c{cfg[0], cfg[1], cfg[2], cfg[3], cfg[4], cfg[5], cfg[6]};
     if (c.vocab_padded < c.vocab || c.d_model % c.heads != 0) return GPTB200_ERR_INVALID_ARG;
-    gptb200_ctx *probe = nullptr;
-    const int rc = gptb200_ctx_create(&probe, device, stream, mode);  // report a missing device as a status, not an abort
-    if (rc != GPTB200_OK) return rc;
-    gptb200_ctx_destroy(probe);
+    // the optimiser-side operators of the interface take the element count as int (backend_interface.h:219-237)
+    if (ParamLayout(c).total > size_t(0x7fffffff)) return GPTB200_ERR_TOO_LARGE;
     auto *m = new gptb200_model();
-    m->h.backend = new B200Backend(seed, device, stream, mode);
-    m->h.model = new GptModel(m->h.backend, c, use_grad != 0);
+    m->h.backend = new B200Backend(seed, device, stream, mode, /*abort_on_error=*/false);
+    m->h.model = m->h.backend->status() == 0 ? new GptModel(m->h.backend, c, use_grad != 0) : nullptr;
+    const int rc = m->h.backend->status();   // no device, or the parameter buffers could not be allocated
+    if (rc != GPTB200_OK) {
+        delete m->h.model;
+        delete m->h.backend;
+        delete m;
+        return rc;
+    }
     *out = m;
     return GPTB200_OK;
 }
@@ -341,7 +361,7 @@ int gptb200_model_init(gptb200_model *m, float mean, float stddev)
 {
     if (!m) return GPTB200_ERR_INVALID_ARG;
     m->h.model->init(mean, stddev);
-    return GPTB200_OK;
+    return m->h.backend->status();
 }
 
 // Raw fp32 parameter image in the reference's checkpoint layout (src/model/gpt.cpp:327-397), from / to host memory.
@@ -349,14 +369,14 @@ int gptb200_model_load_weights(gptb200_model *m, const float *host, long long co
 {
     if (!m || !host || count != static_cast<long long>(m->h.model->num_params())) return GPTB200_ERR_INVALID_ARG;
     m->h.backend->device_memcpy_h2d(m->h.model->weights(), host, size_t(count) * sizeof(float));
-    return GPTB200_OK;
+    return m->h.backend->status();
 }
 
 int gptb200_model_read(gptb200_model *m, float *host, long long count, int which)
 {
     if (!m || !host || count != static_cast<long long>(m->h.model->num_params()) || which < 0 || which > 1) return GPTB200_ERR_INVALID_ARG;
     m->h.backend->device_memcpy_d2h(host, which == 0 ? m->h.model->weights() : m->h.model->grads(), size_t(count) * sizeof(float));
-    return GPTB200_OK;
+    return m->h.backend->status();
 }
 
 int gptb200_model_load_checkpoint(gptb200_model *m, const char *path)
@@ -387,7 +407,13 @@ int gptb200_model_save_checkpoint(gptb200_model *m, const char *path)
 int gptb200_model_set_size(gptb200_model *m, int batch, int seq)
 {
     if (!m || batch <= 0 || seq <= 0 || seq > m->h.model->config().max_seq_len) return GPTB200_ERR_INVALID_ARG;
-    m->h.model->set_size(batch, seq);
+    if (m->h.backend->status() != 0) return m->h.backend->status();
+    if (size_t(batch) * seq * m->h.model->config().vocab_padded > size_t(0x7fffffff)) return GPTB200_ERR_TOO_LARGE;   // the logits tensor is indexed with int
+    if (!m->h.model->set_size(batch, seq)) {
+        const int rc = m->h.backend->status();
+        m->h.backend->clear_status();   // nothing was changed: the model keeps working at its previous size
+        return rc;
+    }
     return GPTB200_OK;
 }
 
@@ -395,42 +421,44 @@ int gptb200_model_zero_grad(gptb200_model *m)
 {
     if (!m) return GPTB200_ERR_INVALID_ARG;
     m->h.model->zero_grad();
-    return GPTB200_OK;
+    return m->h.backend->status();
 }
 
 int gptb200_model_forward(gptb200_model *m, const int *tokens_dev)
 {
     if (!m || !tokens_dev || m->h.model->batch() == 0) return GPTB200_ERR_INVALID_ARG;
     m->h.model->forward(tokens_dev);
-    return GPTB200_OK;
+    return m->h.backend->status();
 }
 
 int gptb200_model_backward(gptb200_model *m, const int *tokens_dev, const int *labels_dev, void (*layer_done)(int, void *), void *user)
 {
     if (!m || !tokens_dev || !labels_dev || m->h.model->batch() == 0) return GPTB200_ERR_INVALID_ARG;
     m->h.model->backward(tokens_dev, labels_dev, layer_done, user);
-    return GPTB200_OK;
+    return m->h.backend->status();
 }
 
 int gptb200_model_loss(gptb200_model *m, const int *labels_dev, float *loss_out)
 {
     if (!m || !labels_dev || !loss_out) return GPTB200_ERR_INVALID_ARG;
     *loss_out = m->h.model->loss(labels_dev);
-    return GPTB200_OK;
+    if (m->h.backend->status() != 0) return m->h.backend->status();
+    // the copy of the loss has waited for the stream: report a bounded wait that ran out in any kernel of the step
+    return gptb200_ctx_synchronize(m->h.backend->context());
 }
 
 int gptb200_model_clip(gptb200_model *m, float max_norm, int accum_steps)
 {
     if (!m || accum_steps <= 0) return GPTB200_ERR_INVALID_ARG;
     m->h.model->clip(max_norm, accum_steps);
-    return GPTB200_OK;
+    return m->h.backend->status();
 }
 
 int gptb200_model_optimizer_step(gptb200_model *m, float lr, float beta1, float beta2, float weight_decay)
 {
     if (!m) return GPTB200_ERR_INVALID_ARG;
     m->h.model->optimizer_step(lr, beta1, beta2, weight_decay);
-    return GPTB200_OK;
+    return m->h.backend->status();
 }
 
 }  // extern "C"

@@ -2,8 +2,8 @@
 // callers that must not allocate device memory.
 //
 // Who that is: a host program that has handed the whole GPU to its own memory pool (a raw cudaMalloc from a
-// plug-in would fail or fragment the pool), code that runs where the CUDA runtime forbids allocation (inside a
-// stream capture, inside a host callback), and services with a fixed memory budget that is audited at start-up.
+// plug-in would fail or fragment the pool), code that runs where the CUDA runtime forbids allocation (while a
+// stream is being captured), and services with a fixed memory budget that is audited at start-up.
 // The regular entry point (gptb200_linear_backward) keeps the partial row sums of this reduction in the
 // context's scratch buffer, which it grows with cudaMalloc on demand; this one keeps them in a fixed array that
 // is part of the library image, so a call never allocates, frees or touches a context.
@@ -15,7 +15,8 @@
 // threads without ordering) race on the array -- order them on one stream or with events.
 //
 // The first call on each device looks up the array's device address (cudaGetSymbolAddress) and caches it.  That
-// first call should be made before any stream capture begins.
+// first call should be made before any stream capture begins.  The array used is the current device's copy:
+// `cuda_stream` must be a stream of the device that is current when the call is made.
 #include <mutex>
 
 #include <cuda_runtime.h>
@@ -99,6 +100,7 @@ extern "C" int gptb200_bias_grad_noalloc(float *grad_b, const float *grad_y, int
     chunks = (m + rows_per_chunk - 1) / rows_per_chunk;
     cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
     bias_grad_partial_static_kernel<<<dim3((n + 31) / 32, chunks), dim3(32, 8), 0, stream>>>(partials, grad_y, m, n, rows_per_chunk);
+    if (cudaGetLastError() != cudaSuccess) return GPTB200_ERR_CUDA;
     bias_grad_final_static_kernel<<<(n + 127) / 128, 128, 0, stream>>>(grad_b, partials, n, chunks);
     return cudaGetLastError() == cudaSuccess ? GPTB200_OK : GPTB200_ERR_CUDA;
 }

@@ -81,7 +81,9 @@ class DataParallelStep:
         self.buckets = GradientBuckets(model.config, model.param_offsets, model.num_params, layers_per_group)
         self.on_gpu = bool(getattr(grad_tensor, "is_cuda", False))
         self.compute_stream = torch.cuda.current_stream() if self.on_gpu else None
-        # high priority: the collective's CTAs are placed before the pending CTAs of the compute kernels
+        # Collectives are enqueued from this stream.  Which stream NCCL's kernels run on, and its priority, is decided by the
+        # process group (ProcessGroupNCCL.Options(is_high_priority_stream=True) at init_process_group), not by this stream's
+        # priority; this stream only carries the ordering (event wait before, wait_stream after).
         self.comm_stream = torch.cuda.Stream(priority=-1) if (world_size > 1 and self.on_gpu) else None
         self._all_reduce = all_reduce or (lambda t: dist.all_reduce(t, op=dist.ReduceOp.AVG))
         self.collectives = 0

@@ -191,7 +191,14 @@ int gptb200_memory_info(gptb200_ctx *ctx, float *free_mb, float *total_mb);
  *      sequence (src/model/gpt.cpp:426-690) over the operators above, with the reference's parameter packing
  *      (src/model/gpt.cpp:46-62) so that its raw fp32 checkpoints load unchanged.
  *      cfg = {max_seq_len, vocab_size, vocab_size_padded, num_layers, num_heads, d_model, d_ffn}.
- *      Token / label arrays are int32 in device memory, [batch x seq]. */
+ *      Token / label arrays are int32 in device memory, [batch x seq].
+ *      Errors: every call returns a gptb200_status and nothing aborts.  The first operator that fails inside a call (a CUDA
+ *      error, a scratch request beyond the limit) makes that call and every later one return its status, and the operators
+ *      behind them become no-ops: destroy the model.  Two cases leave the model usable: gptb200_model_set_size that cannot
+ *      get memory (GPTB200_ERR_CUDA) or whose logits tensor would exceed 2^31-1 elements (GPTB200_ERR_TOO_LARGE) changes
+ *      nothing, and gptb200_model_loss reports a bounded wait that ran out in any kernel of the step
+ *      (GPTB200_ERR_DEVICE_TIMEOUT) and clears it.  A configuration with more than 2^31-1 parameters is refused
+ *      (GPTB200_ERR_TOO_LARGE). */
 typedef struct gptb200_model gptb200_model;
 int gptb200_model_create(gptb200_model **out, const int *cfg, int device, void *cuda_stream, int mode, unsigned long seed, int use_grad);
 int gptb200_model_destroy(gptb200_model *m);
@@ -222,7 +229,8 @@ int gptb200_model_optimizer_step(gptb200_model *m, float lr, float beta1, float 
  *   for callers that cannot allocate device memory (the GPU's memory belongs to the host program's own pool, or
  *   the call happens where the runtime forbids allocation).  The partial sums live in a fixed 1 MiB array inside
  *   the library instead of the context's growable scratch buffer; no context is needed.  n <= 8192, otherwise
- *   GPTB200_ERR_TOO_LARGE.  Runs on `cuda_stream` of the current device.  The first call on a device looks up the
+ *   GPTB200_ERR_TOO_LARGE.  Runs on `cuda_stream`, which must belong to the device that is current at the call (the array
+ *   used is that device's copy).  The first call on a device looks up the
  *   array's address; make it before any stream capture.  Calls share the array: calls that overlap on the GPU race. */
 int gptb200_bias_grad_noalloc(float *grad_b, const float *grad_y, int m, int n, void *cuda_stream);
 

@@ -23,11 +23,20 @@ _i = np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")
 _c = ctypes.c_int
 
 
+def reference_tree() -> str | None:
+    """Path of a checkout of the reference: environment variable REF, else a directory `reference` beside this repository."""
+    for cand in (os.environ.get("REF"), os.path.join(HERE, "..", "..", "reference")):
+        if cand and os.path.isdir(os.path.join(cand, "src", "backend", "cpu")):
+            return os.path.abspath(cand)
+    return None
+
+
 def build(force: bool = False) -> None:
-    """Compile the restatement, and the reference shim when the reference tree is present."""
+    """Compile the restatement, and the reference shims when a reference tree is found (else prebuilt ones are kept)."""
     if force or not os.path.exists(ORACLE_LIB) or os.path.getmtime(ORACLE_LIB) < os.path.getmtime(os.path.join(HERE, "linear_oracle.c")):
         subprocess.run(["make", "-C", HERE, os.path.join(HERE, "liboracle.so")], check=True, capture_output=True)
-    subprocess.run(["make", "-C", HERE, "ref"], check=True, capture_output=True)
+    ref = reference_tree()
+    subprocess.run(["make", "-C", HERE, "ref"] + ([f"REF={ref}"] if ref else []), check=True, capture_output=True)
 
 
 def _f32(a) -> np.ndarray:
@@ -134,6 +143,24 @@ class Reference(_Ops):
         self.lib.ref_gpt_forward_backward.restype = _c
         self.lib.ref_gpt_forward_backward_on.argtypes = [ctypes.c_void_p, _i, _f, ctypes.c_longlong, _i, _i, _c, _c, _f, _f, ctypes.c_void_p]
         self.lib.ref_gpt_forward_backward_on.restype = _c
+
+    def adamw_step(self, params, g, m, v, lr, beta1, beta2, eps, weight_decay, step: int):
+        """Returns the updated (params, m, v) of the reference's AdamW operator (cpu_backend.cpp:517-532)."""
+        fn = self.lib.ref_adamw_step
+        fn.argtypes = [_f, _f, _f, _f, _c] + [ctypes.c_float] * 5 + [_c]
+        fn.restype = None
+        p, g, m, v = _f32(params).copy(), _f32(g).copy(), _f32(m).copy(), _f32(v).copy()
+        fn(p, g, m, v, p.size, lr, beta1, beta2, eps, weight_decay, step)
+        return p, m, v
+
+    def scale_and_clip_grad(self, g, max_norm: float, accum_steps: int):
+        """Returns the gradient after the reference's 1/accum scaling and norm clipping (cpu_backend.cpp:534-556)."""
+        fn = self.lib.ref_scale_and_clip_grad
+        fn.argtypes = [_f, _c, ctypes.c_float, _c]
+        fn.restype = None
+        g = _f32(g).copy()
+        fn(g, g.size, max_norm, accum_steps)
+        return g
 
     def softmax_forward(self, logits, vocab_size: int):
         logits = _f32(logits)

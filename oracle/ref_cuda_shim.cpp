@@ -61,6 +61,98 @@ float refcuda_ffn_step_ms(int m, int k, int n, int steps, int warmup, int nsets)
     return ms;
 }
 
+// One linear layer through the reference CUDABackend, forward and backward timed apart: out2 = {forward ms, backward ms} per
+// call (CUDA events; the reference's forward is cublasSgemm + its bias/GELU kernel, its backward two cublasSgemm + its
+// bias-gradient kernel, src/backend/cuda/kernels/linear.cu:36-159).  Returns 0, or -1 on failure.
+int refcuda_linear_ms(int m, int k, int n, int activation, int steps, int warmup, int nsets, float *out2)
+{
+    CUDABackend be(42);
+    IGPTBackend *b = &be;
+    std::vector<float *> x(nsets), gy(nsets), y(nsets), act(nsets), gx(nsets);
+    float *w, *bias, *gw, *gb;
+    for (int i = 0; i < nsets; ++i) {
+        b->device_malloc((void **)&x[i], sizeof(float) * m * k);
+        b->device_malloc((void **)&gy[i], sizeof(float) * m * n);
+        b->device_malloc((void **)&y[i], sizeof(float) * m * n);
+        b->device_malloc((void **)&act[i], sizeof(float) * m * n);
+        b->device_malloc((void **)&gx[i], sizeof(float) * m * k);
+        b->device_fill_normal(x[i], 0.0f, 1.0f, (size_t)m * k);
+        b->device_fill_normal(gy[i], 0.0f, 1.0f, (size_t)m * n);
+    }
+    b->device_malloc((void **)&w, sizeof(float) * k * n);
+    b->device_malloc((void **)&bias, sizeof(float) * n);
+    b->device_malloc((void **)&gw, sizeof(float) * k * n);
+    b->device_malloc((void **)&gb, sizeof(float) * n);
+    b->device_fill_normal(w, 0.0f, 0.02f, (size_t)k * n);
+    b->device_fill_normal(bias, 0.0f, 0.02f, (size_t)n & ~(size_t)1);
+    b->device_memset(gw, 0, sizeof(float) * k * n);
+    b->device_memset(gb, 0, sizeof(float) * n);
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    int rc = 0;
+    for (int pass = 0; pass < 2 && rc == 0; ++pass) {
+        for (int it = 0; it < warmup + steps; ++it) {
+            if (it == warmup) cudaEventRecord(e0);
+            const int s = it % nsets;
+            if (pass == 0)
+                b->device_linear_activation_fused_forward(y[s], act[s], x[s], w, bias, activation != 0, 1, m, k, n);
+            else
+                b->device_linear_backward(gx[s], gw, gb, gy[s], x[s], w, 1, m, k, n);
+        }
+        cudaEventRecord(e1);
+        float ms = -1.0f;
+        if (cudaEventSynchronize(e1) != cudaSuccess || cudaEventElapsedTime(&ms, e0, e1) != cudaSuccess) rc = -1;
+        out2[pass] = ms / steps;
+    }
+    for (int i = 0; i < nsets; ++i) {
+        b->device_free(x[i]); b->device_free(gy[i]); b->device_free(y[i]); b->device_free(act[i]); b->device_free(gx[i]);
+    }
+    b->device_free(w); b->device_free(bias); b->device_free(gw); b->device_free(gb);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    return rc;
+}
+
+// The tied un-embedding through the reference CUDABackend (embedding.cu:47-63,140-170): out2 = {forward ms, backward ms}.
+int refcuda_unembed_ms(int m, int d, int vp, int steps, int warmup, float *out2)
+{
+    CUDABackend be(42);
+    IGPTBackend *b = &be;
+    float *x, *wte, *y, *gy, *gx, *gw;
+    b->device_malloc((void **)&x, sizeof(float) * m * d);
+    b->device_malloc((void **)&wte, sizeof(float) * (size_t)vp * d);
+    b->device_malloc((void **)&y, sizeof(float) * (size_t)m * vp);
+    b->device_malloc((void **)&gy, sizeof(float) * (size_t)m * vp);
+    b->device_malloc((void **)&gx, sizeof(float) * m * d);
+    b->device_malloc((void **)&gw, sizeof(float) * (size_t)vp * d);
+    b->device_fill_normal(x, 0.0f, 1.0f, (size_t)m * d);
+    b->device_fill_normal(wte, 0.0f, 0.02f, (size_t)vp * d);
+    b->device_fill_normal(gy, 0.0f, 1e-4f, (size_t)m * vp);
+    b->device_memset(gw, 0, sizeof(float) * (size_t)vp * d);
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    int rc = 0;
+    for (int pass = 0; pass < 2 && rc == 0; ++pass) {
+        for (int it = 0; it < warmup + steps; ++it) {
+            if (it == warmup) cudaEventRecord(e0);
+            if (pass == 0)
+                b->device_unembedding_forward(y, x, wte, 1, m, d, vp);
+            else
+                b->device_unembedding_backward(gx, gw, gy, x, wte, 1, m, d, vp);
+        }
+        cudaEventRecord(e1);
+        float ms = -1.0f;
+        if (cudaEventSynchronize(e1) != cudaSuccess || cudaEventElapsedTime(&ms, e0, e1) != cudaSuccess) rc = -1;
+        out2[pass] = ms / steps;
+    }
+    b->device_free(x); b->device_free(wte); b->device_free(y); b->device_free(gy); b->device_free(gx); b->device_free(gw);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    return rc;
+}
+
 // One training step of the reference's GPT class on its CUDA backend (zero_grad, forward, backward, clip, AdamW), random-init
 // weights and uniform random tokens.  cfg = {max_seq_len, vocab_size, vocab_size_padded, num_layers, num_heads, d_model, d_ffn}.
 // Returns milliseconds per step (host clock around device-synchronised steps), < 0 on failure.

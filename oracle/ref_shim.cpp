@@ -199,6 +199,19 @@ void ref_cross_entropy_loss(float *loss, const float *probs, const int *labels, 
     be.device_cross_entropy_loss(loss, probs, labels, 1, rows, vp);
 }
 
+// the optimiser-side operators (src/backend/cpu/cpu_backend.cpp:517-556), updating the caller's arrays in place
+void ref_adamw_step(float *params, float *g, float *m, float *v, int size, float lr, float beta1, float beta2, float eps, float weight_decay, int step)
+{
+    CPUBackend be;
+    be.device_adamw_step(params, g, m, v, size, lr, beta1, beta2, eps, weight_decay, step);
+}
+
+void ref_scale_and_clip_grad(float *g, int size, float max_norm, int accum_steps)
+{
+    CPUBackend be;
+    be.device_scale_and_clip_grad(g, size, max_norm, accum_steps);
+}
+
 // cfg = {max_seq_len, vocab_size, vocab_size_padded, num_layers, num_heads, d_model, d_ffn}
 int ref_gpt_forward_backward(const int *cfg, const float *weights, long long n_weights, const int *inputs, const int *labels, int batch,
                              int seq, int use_restated_ops, float *grads_out, float *loss_out, float *logits_out)

@@ -22,7 +22,9 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 sys.path.insert(0, ROOT)
-REF = os.environ.get("REF", "/root/reference")
+REF = os.environ.get("REF")
+if not REF or not os.path.isdir(os.path.join(REF, "tools")):
+    raise SystemExit("set REF to a checkout of the reference (its tools/ and src/ are used)")
 OUT = os.path.join(ROOT, "tests", "golden")
 
 from oracle.oracle import Reference  # noqa: E402

@@ -55,6 +55,23 @@ def test_invalid_arguments_are_rejected_without_a_device(built_library):
     assert lib.gptb200_linear_forward(None, None, None, None, None, None, 0, 1, 1, 1) == 1  # null context
 
 
+def test_model_entry_points_return_errors_instead_of_aborting(built_library):
+    """gptb200_model_create reports a configuration beyond the interface's int element counts, and a missing device, as
+    status codes (the C++ backend object behind the model driver does not abort the process)."""
+    import torch
+    import gpt_b200
+    lib = gpt_b200.load_library()
+    m = ctypes.c_void_p()
+    huge = (ctypes.c_int * 7)(1024, 50257, 50304, 96, 96, 12288, 49152)          # 175 B parameters: more than 2^31 - 1
+    assert lib.gptb200_model_create(ctypes.byref(m), huge, 0, None, 0, 42, 1) == 6   # GPTB200_ERR_TOO_LARGE
+    bad = (ctypes.c_int * 7)(64, 507, 512, 4, 5, 32, 256)                          # d_model not a multiple of the heads
+    assert lib.gptb200_model_create(ctypes.byref(m), bad, 0, None, 0, 42, 1) == 1
+    if not torch.cuda.is_available():
+        tiny = (ctypes.c_int * 7)(64, 507, 512, 4, 4, 32, 256)
+        assert lib.gptb200_model_create(ctypes.byref(m), tiny, 0, None, 0, 42, 1) == 3   # GPTB200_ERR_NO_DEVICE, and we are still alive
+        assert not m.value
+
+
 def test_no_cublas_or_oracle_in_the_product_library(built_library):
     import subprocess
     out = subprocess.run(["ldd", built_library], capture_output=True, text=True).stdout

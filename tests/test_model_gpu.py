@@ -175,7 +175,9 @@ def test_own_model_driver_matches_reference_driver_and_goldens(lib, reference):
     model.close()
 
 
-def test_adamw_and_clip_follow_the_reference_formulas(lib):
+def test_adamw_and_clip_match_the_reference_operators(lib, reference):
+    """AdamW and the 1/accum scaling + norm clipping against the reference CPU backend's own operators
+    (cpu_backend.cpp:517-556) on the same arrays."""
     import torch
     import gpt_b200
     be = gpt_b200.Backend(0)
@@ -187,20 +189,39 @@ def test_adamw_and_clip_follow_the_reference_formulas(lib):
     lr, b1, b2, eps, wd, step = 6e-4, 0.9, 0.95, 1e-8, 0.1, 3
     assert lib.gptb200_adamw_step(be.handle, dp.data_ptr(), dg.data_ptr(), dm.data_ptr(), dv.data_ptr(), n, lr, b1, b2, eps, wd, step) == 0
     be.synchronize()
-    m2 = b1 * m.astype(np.float64) + (1 - b1) * g
-    v2 = b2 * v.astype(np.float64) + (1 - b2) * g.astype(np.float64) ** 2
-    p2 = p - lr * ((m2 / (1 - b1 ** step)) / (np.sqrt(v2 / (1 - b2 ** step)) + eps) + wd * p)
-    assert np.abs(dp.cpu().numpy() - p2).max() <= 2e-6 and np.abs(dm.cpu().numpy() - m2).max() <= 1e-6
-    # clipping: g /= accum, then scaled to max_norm when the norm exceeds it (cpu_backend.cpp:528-556)
-    dg2 = torch.from_numpy(g.copy()).cuda()
-    assert lib.gptb200_scale_and_clip_grad(be.handle, dg2.data_ptr(), n, 1.0, 4) == 0
-    be.synchronize()
-    gs = g.astype(np.float64) / 4
-    norm = np.sqrt((gs ** 2).sum())
-    expect = gs * (1.0 / (norm + 1e-6)) if norm > 1.0 else gs
-    assert np.abs(dg2.cpu().numpy() - expect).max() <= 1e-6
-    dg3 = torch.from_numpy((g * 1e-4).astype(np.float32)).cuda()   # small norm: only the 1/accum scaling applies
-    assert lib.gptb200_scale_and_clip_grad(be.handle, dg3.data_ptr(), n, 1.0, 2) == 0
-    be.synchronize()
-    assert np.abs(dg3.cpu().numpy() - g * 1e-4 / 2).max() <= 1e-9
+    rp, rm, rv = reference.adamw_step(p, g, m, v, lr, b1, b2, eps, wd, step)
+    assert np.abs(dp.cpu().numpy() - rp).max() <= 2e-6 and np.abs(dm.cpu().numpy() - rm).max() <= 1e-6 and np.abs(dv.cpu().numpy() - rv).max() <= 1e-6
+    # clipping: g /= accum, then scaled to max_norm when the norm exceeds it
+    for scale, accum in ((1.0, 4), (1e-4, 2)):      # norm above the bound; small norm: only the 1/accum scaling applies
+        gs = (g * scale).astype(np.float32)
+        dg2 = torch.from_numpy(gs.copy()).cuda()
+        assert lib.gptb200_scale_and_clip_grad(be.handle, dg2.data_ptr(), n, 1.0, accum) == 0
+        be.synchronize()
+        ref = reference.scale_and_clip_grad(gs, 1.0, accum)
+        # the reference adds 100 003 squares one after the other in fp32; the kernels add them pairwise: 1e-5 of the result's scale
+        assert np.abs(dg2.cpu().numpy() - ref).max() <= 1e-5 * np.abs(ref).max()
     be.close()
+
+
+def test_set_size_beyond_memory_is_an_error_and_the_model_keeps_working(lib):
+    """A shape whose activations cannot be allocated returns a status (nothing aborts, nothing changes); so does a
+    logits tensor beyond the interface's int indexing.  The model then still runs at its previous size."""
+    import torch
+    import gpt_b200
+    cfg = dict(max_seq_len=64, vocab_size=507, vocab_size_padded=512, num_layers=12, num_heads=4, d_model=32, d_ffn=512)
+    model = gpt_b200.Model(cfg, 0, None, 0, seed=1)
+    model.init(0.0, 0.02)
+    model.set_size(2, 16)
+    tokens = torch.randint(0, 507, (2, 16), dtype=torch.int32, device="cuda")
+    labels = torch.randint(0, 507, (2, 16), dtype=torch.int32, device="cuda")
+    model.zero_grad(); model.forward(tokens); model.backward(tokens, labels)
+    loss0 = model.loss(labels)
+    with pytest.raises(gpt_b200.GptB200Error) as e:
+        model.set_size(60_000_000, 64)         # 3.8e9 rows: the logits tensor alone would exceed 2^31 - 1 elements
+    assert e.value.status == 6
+    with pytest.raises(gpt_b200.GptB200Error) as e:
+        model.set_size(62_500, 64)             # 4e6 rows x ~16 400 floats of activations = 262 GB: one cudaMalloc that cannot succeed
+    assert e.value.status == 2                 # GPTB200_ERR_CUDA
+    model.zero_grad(); model.forward(tokens); model.backward(tokens, labels)
+    assert model.loss(labels) == loss0
+    model.close()

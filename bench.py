@@ -576,8 +576,7 @@ def train_record(torch, dist, world, rank, dev, mode_name="3xtf32", global_batch
             d_in.copy_(h_in, non_blocking=True)
             d_lbl.copy_(h_lbl, non_blocking=True)
         dp.step(d_in, d_lbl)
-        model.unscale_and_clip_grads(1.0, 1)
-        model.optimizer_step(6e-4, 0.9, 0.95, 0.1)
+        model.clip_and_optimizer_step(1.0, 1, 6e-4, 0.9, 0.95, 0.1)    # clipping and AdamW over the packed buffers: two launches
         return model.loss(d_lbl) if e2e else None
 
     for _ in range(warmup):
@@ -597,10 +596,10 @@ def train_record(torch, dist, world, rank, dev, mode_name="3xtf32", global_batch
     launches = model.launch_count() - l0
     collectives = (dp.collectives - c0) // max(1, steps)
     # where the step's time goes (this rank's view, three steps): the same calls as dp.step with events in between
-    phase_names = ("zero_grad+forward", "backward", "wait_for_allreduce", "clip", "adamw")
+    phase_names = ("zero_grad+forward", "backward", "wait_for_allreduce", "clip+adamw")
     phases = dict.fromkeys(phase_names, 0.0)
     for _ in range(3):
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
         ev[0].record()
         model.zero_grad()
         model.forward(d_in)
@@ -611,10 +610,8 @@ def train_record(torch, dist, world, rank, dev, mode_name="3xtf32", global_batch
         if world > 1:
             dp.compute_stream.wait_stream(dp.comm_stream)
         ev[3].record()
-        model.unscale_and_clip_grads(1.0, 1)
+        model.clip_and_optimizer_step(1.0, 1, 6e-4, 0.9, 0.95, 0.1)
         ev[4].record()
-        model.optimizer_step(6e-4, 0.9, 0.95, 0.1)
-        ev[5].record()
         torch.cuda.synchronize()
         for i, name in enumerate(phase_names):
             phases[name] += ev[i].elapsed_time(ev[i + 1]) / 3.0

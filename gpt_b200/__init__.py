@@ -34,7 +34,8 @@ EXPORTED_SYMBOLS = [
     "gptb200_fill_normal", "gptb200_fill_const", "gptb200_embedding_forward", "gptb200_embedding_backward",
     "gptb200_layernorm_forward", "gptb200_layernorm_backward", "gptb200_attention_forward", "gptb200_attention_backward",
     "gptb200_softmax_forward", "gptb200_cross_entropy_softmax_backward", "gptb200_cross_entropy_loss",
-    "gptb200_adamw_step", "gptb200_scale_and_clip_grad", "gptb200_memory_info",
+    "gptb200_adamw_step", "gptb200_scale_and_clip_grad", "gptb200_memory_info", "gptb200_clip_adamw_packed",
+    "gptb200_loader_create", "gptb200_loader_destroy", "gptb200_loader_num_samples", "gptb200_loader_reset_epoch", "gptb200_loader_next_batch",
     "gptb200_bias_grad_noalloc",
 ]
 
@@ -103,6 +104,13 @@ def load_library(path: str | None = None) -> ctypes.CDLL:
         "gptb200_adamw_step": (i, [vp, fp, fp, fp, fp, sz, f32, f32, f32, f32, f32, i]),
         "gptb200_scale_and_clip_grad": (i, [vp, fp, sz, f32, i]),
         "gptb200_memory_info": (i, [vp, ctypes.POINTER(f32), ctypes.POINTER(f32)]),
+        "gptb200_clip_adamw_packed": (i, [vp, fp, fp, fp, fp, sz, ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(ctypes.c_ubyte), i, f32, i, f32, f32, f32,
+                                          f32, f32, i, fp]),
+        "gptb200_loader_create": (i, [ctypes.POINTER(vp), ctypes.c_char_p, i]),
+        "gptb200_loader_destroy": (i, [vp]),
+        "gptb200_loader_num_samples": (ctypes.c_longlong, [vp]),
+        "gptb200_loader_reset_epoch": (i, [vp]),
+        "gptb200_loader_next_batch": (i, [vp, i, i, i, vp, vp]),
         # C++ object factory: an IGPTBackend* for host programs written against the reference's interface
         "gptb200_bias_grad_noalloc": (i, [fp, fp, i, i, vp]),
         "gptb200_backend_create": (vp, [ctypes.c_ulong, i, vp, i]),
@@ -310,6 +318,10 @@ def _declare_model(lib: ctypes.CDLL) -> None:
         "gptb200_model_loss": (i, [vp, vp, ctypes.POINTER(f32)]),
         "gptb200_model_clip": (i, [vp, f32, i]),
         "gptb200_model_optimizer_step": (i, [vp, f32, f32, f32, f32]),
+        "gptb200_model_clip_and_optimizer_step": (i, [vp, f32, i, f32, f32, f32, f32]),
+        "gptb200_model_save_state": (i, [vp, ctypes.c_char_p]),
+        "gptb200_model_load_state": (i, [vp, ctypes.c_char_p]),
+        "gptb200_model_step_count": (i, [vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
@@ -428,3 +440,59 @@ class Model:
 
     def optimizer_step(self, learning_rate: float, beta1: float, beta2: float, decay: float) -> None:
         self._check(self._lib.gptb200_model_optimizer_step(self._m, learning_rate, beta1, beta2, decay))
+
+    def clip_and_optimizer_step(self, max_norm: float, accum_steps: int, learning_rate: float, beta1: float, beta2: float, decay: float) -> None:
+        """unscale_and_clip_grads + optimizer_step in two launches over the packed buffers (the gradients stay unscaled)."""
+        self._check(self._lib.gptb200_model_clip_and_optimizer_step(self._m, max_norm, accum_steps, learning_rate, beta1, beta2, decay))
+
+    def save_state(self, filename: str) -> None:
+        """Parameters + AdamW moments + step counter behind a header that names the configuration."""
+        self._check(self._lib.gptb200_model_save_state(self._m, filename.encode()))
+
+    def load_state(self, filename: str) -> None:
+        self._check(self._lib.gptb200_model_load_state(self._m, filename.encode()))
+
+    @property
+    def step_count(self) -> int:
+        return int(self._lib.gptb200_model_step_count(self._m))
+
+
+class Loader:
+    """Sharded token loader (include/gptb200.h: gptb200_loader_*): the reference's DataLoader (src/train/data_loader.h) with the
+    global batch split over ranks.  Seed the C library's rand() alike on every rank before reset_epoch (seed_libc_rand)."""
+
+    def __init__(self, token_file: str, seq_len: int):
+        self._lib = load_library()
+        self._ld = ctypes.c_void_p()
+        self.seq_len = seq_len
+        rc = self._lib.gptb200_loader_create(ctypes.byref(self._ld), token_file.encode(), seq_len)
+        if rc != 0:
+            raise GptB200Error(rc, "gptb200_loader_create", "cannot read the token file, or it holds less than two sequences")
+
+    @staticmethod
+    def seed_libc_rand(seed: int) -> None:
+        ctypes.CDLL(None).srand(ctypes.c_uint(seed))
+
+    def close(self) -> None:
+        if self._ld:
+            self._lib.gptb200_loader_destroy(self._ld)
+            self._ld = ctypes.c_void_p()
+
+    @property
+    def num_samples(self) -> int:
+        return int(self._lib.gptb200_loader_num_samples(self._ld))
+
+    def reset_epoch(self) -> None:
+        rc = self._lib.gptb200_loader_reset_epoch(self._ld)
+        if rc != 0:
+            raise GptB200Error(rc, "gptb200_loader_reset_epoch")
+
+    def next_batch(self, rank: int, world: int, batch: int):
+        """(inputs, labels) as int32 numpy arrays [batch x seq_len], or None when the epoch is exhausted."""
+        import numpy as np
+        inputs = np.empty((batch, self.seq_len), np.int32)
+        labels = np.empty((batch, self.seq_len), np.int32)
+        rc = self._lib.gptb200_loader_next_batch(self._ld, rank, world, batch, inputs.ctypes.data, labels.ctypes.data)
+        if rc < 0:
+            raise GptB200Error(-rc, "gptb200_loader_next_batch")
+        return (inputs, labels) if rc == 1 else None

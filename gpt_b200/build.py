@@ -42,7 +42,7 @@ def _stale(target: str, deps: list[str]) -> bool:
 def build(verbose: bool = False, force: bool = False, out: str | None = None, defines: list[str] | None = None) -> str:
     """`out` / `defines`: build a variant of the library somewhere else with extra -D flags (kernel experiments)."""
     if out:
-        cu = [f for f in _sources("capi.cu", "backend_capi.cu", "b200_backend.cu", "gpt_model.cu", "noalloc.cu") if os.path.exists(f)]
+        cu = [f for f in _sources("capi.cu", "backend_capi.cu", "b200_backend.cu", "gpt_model.cu", "noalloc.cu", "loader.cpp") if os.path.exists(f)]
         cmd = [_nvcc(), "-std=c++17", "-O3", *ARCH_FLAGS, "-lineinfo", "-Xcompiler", "-fPIC", "-shared", *[f"-D{d}" for d in (defines or [])],
                "-I", os.path.join(HERE, "..", "include"), "-I", CSRC, "-I", os.path.join(CSRC, "iface"), "-o", out, *cu]
         res = subprocess.run(cmd, capture_output=True, text=True)
@@ -52,7 +52,7 @@ def build(verbose: bool = False, force: bool = False, out: str | None = None, de
         return out
     os.makedirs(LIBDIR, exist_ok=True)
     deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(HERE, "..", "include", "gptb200.h")]
-    cu = _sources("capi.cu", "backend_capi.cu", "b200_backend.cu", "gpt_model.cu", "noalloc.cu")
+    cu = _sources("capi.cu", "backend_capi.cu", "b200_backend.cu", "gpt_model.cu", "noalloc.cu", "loader.cpp")
     cu = [f for f in cu if os.path.exists(f)]
     if force or _stale(LIB, deps):
         cmd = [_nvcc(), "-std=c++17", "-O3", *ARCH_FLAGS, "-lineinfo", "-Xcompiler", "-fPIC", "-shared",

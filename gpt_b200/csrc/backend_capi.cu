@@ -8,6 +8,7 @@
 #include "backend_ops.cuh"
 #include "attention_tiled.cuh"
 #include "layernorm_warp.cuh"
+#include "optimizer_fused.cuh"
 
 using namespace gptb200;
 
@@ -310,6 +311,36 @@ int gptb200_scale_and_clip_grad(gptb200_ctx *ctx, float *g, size_t count, float 
     ops::clip_factor_kernel<<<1, 32, 0, ctx->stream>>>(factor, partial, blocks, max_norm);
     ops::clip_apply_kernel<<<blocks_for(ctx, count, 256), 256, 0, ctx->stream>>>(g, factor, count);
     return launched(ctx, 3);
+}
+
+int gptb200_clip_adamw_packed(gptb200_ctx *ctx, float *params, const float *g, float *m, float *v, size_t count, const long long *segment_ends,
+                              const unsigned char *segment_decay, int segments, float max_norm, int accum_steps, float lr, float beta1, float beta2,
+                              float eps, float weight_decay, int step, float *grad_norm_dev)
+{
+    NEED(ctx, (count == 0 || (params && g && m && v)) && accum_steps > 0 && step > 0);
+    NEED(ctx, segments >= 1 && segments <= ops::kMaxParamSegments && segment_ends && segment_decay);
+    if (count == 0) return GPTB200_OK;
+    ops::ParamSegments seg{};
+    seg.count = segments;
+    bool vec_ok = aligned16_all({params, g, m, v});
+    long long prev = 0;
+    for (int t = 0; t < segments; ++t) {
+        NEED(ctx, segment_ends[t] >= prev);
+        seg.end[t] = prev = segment_ends[t];
+        seg.decay[t] = segment_decay[t];
+        if (t < segments - 1 && (segment_ends[t] & 3)) vec_ok = false;
+    }
+    NEED(ctx, static_cast<size_t>(prev) == count);
+    const int blocks = static_cast<int>(std::min<size_t>(size_t(ctx->num_sms) * 8, (count + 4095) / 4096));
+    const int rc = ensure_workspace(ctx, size_t(blocks) * sizeof(float));
+    if (rc) return rc;
+    const float bc1 = 1.0f - powf(beta1, static_cast<float>(step));
+    const float bc2 = 1.0f - powf(beta2, static_cast<float>(step));
+    ops::grad_sumsq_kernel<<<blocks, 256, 0, ctx->stream>>>(ctx->ws, g, static_cast<long long>(count));
+    ops::adamw_packed_kernel<<<ctx->num_sms * 8, 256, 0, ctx->stream>>>(params, g, m, v, static_cast<long long>(count), ctx->ws, blocks,
+                                                                         1.0f / static_cast<float>(accum_steps), max_norm, lr, beta1, beta2, eps,
+                                                                         weight_decay, bc1, bc2, seg, vec_ok ? 1 : 0, grad_norm_dev);
+    return launched(ctx, 2);
 }
 
 int gptb200_memory_info(gptb200_ctx *ctx, float *free_mb, float *total_mb)

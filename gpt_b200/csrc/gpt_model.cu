@@ -261,6 +261,27 @@ public:
                                    1e-8f, s.decay ? decay : 0.0f, step_);
     }
 
+    // the sixteen tensors in packing order: end offset and whether weight decay applies (src/model/gpt.cpp:649-677)
+    int segments(long long *ends, unsigned char *decay) const
+    {
+        const size_t L = c_.layers, D = c_.d_model, F = c_.d_ffn;
+        const size_t sizes[16] = {size_t(c_.vocab_padded) * D, size_t(c_.max_seq_len) * D, L * D, L * D, L * D * 3 * D, L * 3 * D, L * D * D, L * D,
+                                  L * D, L * D, L * D * F, L * F, L * F * D, L * D, D, D};
+        const unsigned char dec[16] = {1, 1, 0, 0, 1, 0, 1, 0, 0, 0, 1, 0, 1, 0, 0, 0};
+        long long o = 0;
+        for (int t = 0; t < 16; ++t) {
+            o += static_cast<long long>(sizes[t]);
+            ends[t] = o;
+            decay[t] = dec[t];
+        }
+        return 16;
+    }
+    float *moment(int which) { return bufs_[2 + which]; }
+    bool has_optimizer_state() const { return use_grad_; }
+    int step_count() const { return step_; }
+    void set_step_count(int s) { step_ = s; }
+    int next_step() { return ++step_; }
+
     float *logits() { return acts_ ? acts_ + a_.logits : nullptr; }
     int batch() const { return B_; }
     int seq() const { return T_; }
@@ -459,6 +480,92 @@ int gptb200_model_optimizer_step(gptb200_model *m, float lr, float beta1, float 
     if (!m) return GPTB200_ERR_INVALID_ARG;
     m->h.model->optimizer_step(lr, beta1, beta2, weight_decay);
     return m->h.backend->status();
+}
+
+int gptb200_model_clip_and_optimizer_step(gptb200_model *m, float max_norm, int accum_steps, float lr, float beta1, float beta2, float weight_decay)
+{
+    if (!m || accum_steps <= 0 || !m->h.model->has_optimizer_state()) return GPTB200_ERR_INVALID_ARG;
+    if (m->h.backend->status() != 0) return m->h.backend->status();
+    long long ends[16];
+    unsigned char decay[16];
+    const int n = m->h.model->segments(ends, decay);
+    GptModel *g = m->h.model;
+    return gptb200_clip_adamw_packed(m->h.backend->context(), g->weights(), g->grads(), g->moment(0), g->moment(1), g->num_params(), ends, decay, n,
+                                     max_norm, accum_steps, lr, beta1, beta2, 1e-8f, weight_decay, g->next_step(), nullptr);
+}
+
+namespace {
+
+struct StateHeader {          // 64 bytes, little-endian
+    char magic[8];            // "GPTB200S"
+    int version;              // 1
+    int cfg[7];               // max_seq_len, vocab_size, vocab_size_padded, num_layers, num_heads, d_model, d_ffn
+    int step;                 // optimiser steps taken
+    int has_optimizer;        // 1: the two moment buffers follow the parameters
+    long long num_params;
+    int reserved[2];
+};
+static_assert(sizeof(StateHeader) == 64, "header layout");
+
+}  // namespace
+
+int gptb200_model_step_count(gptb200_model *m) { return m ? m->h.model->step_count() : -1; }
+
+int gptb200_model_save_state(gptb200_model *m, const char *path)
+{
+    if (!m || !path) return GPTB200_ERR_INVALID_ARG;
+    if (m->h.backend->status() != 0) return m->h.backend->status();
+    GptModel *g = m->h.model;
+    StateHeader h{};
+    memcpy(h.magic, "GPTB200S", 8);
+    h.version = 1;
+    const Config &c = g->config();
+    const int cfg[7] = {c.max_seq_len, c.vocab, c.vocab_padded, c.layers, c.heads, c.d_model, c.d_ffn};
+    memcpy(h.cfg, cfg, sizeof(cfg));
+    h.step = g->step_count();
+    h.has_optimizer = g->has_optimizer_state() ? 1 : 0;
+    h.num_params = static_cast<long long>(g->num_params());
+    FILE *fp = fopen(path, "wb");
+    if (!fp) return GPTB200_ERR_INVALID_ARG;
+    bool ok = fwrite(&h, sizeof(h), 1, fp) == 1;
+    std::vector<float> host(g->num_params());
+    float *bufs[3] = {g->weights(), h.has_optimizer ? g->moment(0) : nullptr, h.has_optimizer ? g->moment(1) : nullptr};
+    for (float *b : bufs) {
+        if (!b || !ok) continue;
+        m->h.backend->device_memcpy_d2h(host.data(), b, host.size() * sizeof(float));
+        ok = m->h.backend->status() == 0 && fwrite(host.data(), sizeof(float), host.size(), fp) == host.size();
+    }
+    fclose(fp);
+    if (m->h.backend->status() != 0) return m->h.backend->status();
+    return ok ? GPTB200_OK : GPTB200_ERR_INVALID_ARG;
+}
+
+int gptb200_model_load_state(gptb200_model *m, const char *path)
+{
+    if (!m || !path) return GPTB200_ERR_INVALID_ARG;
+    if (m->h.backend->status() != 0) return m->h.backend->status();
+    GptModel *g = m->h.model;
+    FILE *fp = fopen(path, "rb");
+    if (!fp) return GPTB200_ERR_INVALID_ARG;
+    StateHeader h{};
+    const Config &c = g->config();
+    const int cfg[7] = {c.max_seq_len, c.vocab, c.vocab_padded, c.layers, c.heads, c.d_model, c.d_ffn};
+    bool ok = fread(&h, sizeof(h), 1, fp) == 1 && memcmp(h.magic, "GPTB200S", 8) == 0 && h.version == 1 && memcmp(h.cfg, cfg, sizeof(cfg)) == 0 &&
+              h.num_params == static_cast<long long>(g->num_params()) && h.step >= 0;
+    if (ok) {
+        // the whole file is read and checked before anything on the device changes
+        const int nbuf = (h.has_optimizer && g->has_optimizer_state()) ? 3 : 1;
+        std::vector<std::vector<float>> host(nbuf, std::vector<float>(g->num_params()));
+        for (int i = 0; i < nbuf && ok; ++i) ok = fread(host[i].data(), sizeof(float), host[i].size(), fp) == host[i].size();
+        if (ok) {
+            float *dst[3] = {g->weights(), g->has_optimizer_state() ? g->moment(0) : nullptr, g->has_optimizer_state() ? g->moment(1) : nullptr};
+            for (int i = 0; i < nbuf; ++i) m->h.backend->device_memcpy_h2d(dst[i], host[i].data(), host[i].size() * sizeof(float));
+            g->set_step_count(nbuf == 3 ? h.step : 0);
+        }
+    }
+    fclose(fp);
+    if (m->h.backend->status() != 0) return m->h.backend->status();
+    return ok ? GPTB200_OK : GPTB200_ERR_INVALID_ARG;
 }
 
 }  // extern "C"

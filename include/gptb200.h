@@ -186,6 +186,15 @@ int gptb200_adamw_step(gptb200_ctx *ctx, float *params, const float *g, float *m
                        float beta2, float eps, float weight_decay, int step);
 int gptb200_scale_and_clip_grad(gptb200_ctx *ctx, float *g, size_t count, float max_norm, int accum_steps);
 int gptb200_memory_info(gptb200_ctx *ctx, float *free_mb, float *total_mb);
+/* Gradient scaling, norm clipping and AdamW over one packed buffer of `segments` tensors in two launches: what the reference
+ * does with device_scale_and_clip_grad followed by one device_adamw_step per tensor (src/model/gpt.cpp:644-677,
+ * cuda/kernels/gradient_clip.cu:35-59, adamw.cu:71-97).  Tensor t covers elements [segment_ends[t-1], segment_ends[t]);
+ * segment_decay[t] != 0: weight_decay applies to it.  The gradients are read twice and never rewritten: the factor
+ * (1 / accum_steps) * min(1, max_norm / (norm + 1e-6)) is applied on their way into the moment updates.  grad_norm_dev
+ * (optional, device memory) receives the norm of the scaled gradients.  At most 32 segments. */
+int gptb200_clip_adamw_packed(gptb200_ctx *ctx, float *params, const float *g, float *m, float *v, size_t count, const long long *segment_ends,
+                              const unsigned char *segment_decay, int segments, float max_norm, int accum_steps, float lr, float beta1, float beta2,
+                              float eps, float weight_decay, int step, float *grad_norm_dev);
 
 /* ---- model driver: one GPT-2 forward / backward / optimiser step issued as the reference's operator
  *      sequence (src/model/gpt.cpp:426-690) over the operators above, with the reference's parameter packing
@@ -223,6 +232,30 @@ int gptb200_model_backward(gptb200_model *m, const int *tokens_dev, const int *l
 int gptb200_model_loss(gptb200_model *m, const int *labels_dev, float *loss_out);
 int gptb200_model_clip(gptb200_model *m, float max_norm, int accum_steps);
 int gptb200_model_optimizer_step(gptb200_model *m, float lr, float beta1, float beta2, float weight_decay);
+/* gptb200_model_clip followed by gptb200_model_optimizer_step in two launches over the packed buffers (see
+ * gptb200_clip_adamw_packed): same update, the gradient buffer is left unscaled. */
+int gptb200_model_clip_and_optimizer_step(gptb200_model *m, float max_norm, int accum_steps, float lr, float beta1, float beta2, float weight_decay);
+/* Self-describing training state (the reference's checkpoint is a raw fp32 parameter image, src/model/gpt.cpp:327-397, and
+ * its header is a TODO, src/model/gpt.h:141): a 64-byte header -- magic "GPTB200S", format version, the seven configuration
+ * values, the optimiser step, the parameter count, a flag for optimiser state -- followed by the parameters and, when the
+ * model holds them, the two AdamW moment buffers, all in the reference's packing.  load checks the header against the
+ * model's configuration (GPTB200_ERR_INVALID_ARG on mismatch or a short file) and restores the step counter. */
+int gptb200_model_save_state(gptb200_model *m, const char *path);
+int gptb200_model_load_state(gptb200_model *m, const char *path);
+int gptb200_model_step_count(gptb200_model *m);
+
+/* ---- token loader for data-parallel training: the reference's DataLoader (src/train/data_loader.h, data_loader.cpp:57-160)
+ *      with the batch sharded over ranks.  Same file format (flat uint16 token ids) and the same sampling from the C
+ *      library's rand() (seed it with srand, as src/train/train.cpp:73 does, identically on every rank): with world = 1 the
+ *      batches are the reference's; with world > 1 rank r receives sequences [r * batch, (r + 1) * batch) of the global batch
+ *      of world * batch sequences.  Host memory only.  next_batch returns 1 (batch produced), 0 (epoch exhausted) or a
+ *      negative status. */
+typedef struct gptb200_loader gptb200_loader;
+int gptb200_loader_create(gptb200_loader **out, const char *token_file, int seq_len);
+int gptb200_loader_destroy(gptb200_loader *ld);
+long long gptb200_loader_num_samples(const gptb200_loader *ld);
+int gptb200_loader_reset_epoch(gptb200_loader *ld);
+int gptb200_loader_next_batch(gptb200_loader *ld, int rank, int world, int batch, int *inputs_host, int *labels_host);
 
 /* ---- no counterpart in the reference: bias-gradient column sums without any allocation.
  *   grad_b[n] += column sums of grad_y[m x n], the same result as the grad_b part of gptb200_linear_backward,

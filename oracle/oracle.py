@@ -162,6 +162,19 @@ class Reference(_Ops):
         fn(g, g.size, max_norm, accum_steps)
         return g
 
+    def loader_batches(self, token_file: str, batch: int, seq_len: int, seed: int, epochs: int, max_batches: int):
+        """The reference's own DataLoader (data_loader.cpp, unmodified) after srand(seed): (inputs, labels), each
+        [batches x batch x seq_len] int32, `epochs` epochs of at most `max_batches` batches."""
+        fn = self.lib.ref_loader_batches
+        fn.argtypes = [ctypes.c_char_p, _c, _c, ctypes.c_uint, _c, _c, _i, _i]
+        fn.restype = _c
+        inputs = np.zeros((epochs * max_batches, batch, seq_len), np.int32)
+        labels = np.zeros_like(inputs)
+        n = fn(token_file.encode(), batch, seq_len, seed, epochs, max_batches, inputs, labels)
+        if n < 0:
+            raise RuntimeError("the reference DataLoader could not read " + token_file)
+        return inputs[:n], labels[:n]
+
     def softmax_forward(self, logits, vocab_size: int):
         logits = _f32(logits)
         m, vp = logits.shape

@@ -15,6 +15,7 @@
 #include <unistd.h>
 
 #include "cpu_backend.h"
+#include "data_loader.h"
 #include "gpt.h"
 
 extern "C" {
@@ -210,6 +211,28 @@ void ref_scale_and_clip_grad(float *g, int size, float max_norm, int accum_steps
 {
     CPUBackend be;
     be.device_scale_and_clip_grad(g, size, max_norm, accum_steps);
+}
+
+// The reference's DataLoader (src/train/data_loader.cpp, unmodified) on the CPU backend: srand(seed), then `epochs` epochs of
+// up to `max_batches` batches each; every batch's inputs and labels are appended to the output arrays.  Returns the number
+// of batches written, < 0 on failure.
+int ref_loader_batches(const char *path, int batch, int seq_len, unsigned seed, int epochs, int max_batches, int *inputs_out, int *labels_out)
+{
+    CPUBackend be;
+    DataLoader ld(&be, batch, seq_len);
+    if (!ld.load_data(path)) return -1;
+    srand(seed);
+    const size_t per = (size_t)batch * seq_len;
+    int written = 0;
+    for (int e = 0; e < epochs; ++e) {
+        ld.reset_epoch();
+        for (int b = 0; b < max_batches && ld.next_batch(); ++b) {
+            be.device_memcpy_d2h(inputs_out + written * per, ld.inputs(), per * sizeof(int));
+            be.device_memcpy_d2h(labels_out + written * per, ld.labels(), per * sizeof(int));
+            ++written;
+        }
+    }
+    return written;
 }
 
 // cfg = {max_seq_len, vocab_size, vocab_size_padded, num_layers, num_heads, d_model, d_ffn}

@@ -225,3 +225,108 @@ def test_set_size_beyond_memory_is_an_error_and_the_model_keeps_working(lib):
     model.zero_grad(); model.forward(tokens); model.backward(tokens, labels)
     assert model.loss(labels) == loss0
     model.close()
+
+
+def test_fused_clip_and_adamw_matches_the_reference_operator_sequence(lib, reference):
+    """gptb200_model_clip_and_optimizer_step (two launches over the packed buffers) against the reference's own sequence --
+    device_scale_and_clip_grad on the whole gradient buffer, then device_adamw_step per tensor with weight decay on the
+    matrices and embeddings only (src/model/gpt.cpp:644-677, cpu_backend.cpp:517-556) -- over three steps, and against this
+    library's unfused calls."""
+    import torch
+    import gpt_b200
+    from oracle.oracle import weight_layout
+    cfg, tokens, weights, _ = _tiny()
+    T = cfg["max_seq_len"]
+    d_in = torch.from_numpy(tokens[:T].copy()).cuda()
+    d_lbl = torch.from_numpy(tokens[1:T + 1].copy()).cuda()
+    fused, plain = (gpt_b200.Model(cfg, 0, None, gpt_b200.MODE_3XTF32) for _ in range(2))
+    for m in (fused, plain):
+        m.load_weights(weights)
+        m.set_size(1, T)
+    n = fused.num_params
+    rp, rm, rv = weights.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)
+    decay_names = {"wte", "wpe", "qkv_proj_w", "attn_proj_w", "ffn_up_w", "ffn_down_w"}
+    lr, b1, b2, wd, max_norm, accum = 6e-4, 0.9, 0.95, 0.1, 0.05, 2     # a bound low enough that clipping is active
+    for step in (1, 2, 3):
+        for m in (fused, plain):
+            m.zero_grad(); m.forward(d_in); m.backward(d_in, d_lbl)
+        g = np.empty(n, np.float32)
+        fused.read_grads(g)
+        fused.clip_and_optimizer_step(max_norm, accum, lr, b1, b2, wd)
+        plain.unscale_and_clip_grads(max_norm, accum)
+        plain.optimizer_step(lr, b1, b2, wd)
+        # the reference's sequence on the same gradients
+        gc = reference.scale_and_clip_grad(g, max_norm, accum)
+        assert np.linalg.norm(g.astype(np.float64) / accum) > max_norm      # the clipping branch is exercised
+        off = 0
+        for name, shape in weight_layout(cfg):
+            cnt = int(np.prod(shape))
+            sl = slice(off, off + cnt)
+            rp[sl], rm[sl], rv[sl] = reference.adamw_step(rp[sl], gc[sl], rm[sl], rv[sl], lr, b1, b2, 1e-8, wd if name in decay_names else 0.0, step)
+            off += cnt
+        wf, wp = np.empty(n, np.float32), np.empty(n, np.float32)
+        fused.read_weights(wf); plain.read_weights(wp)
+        assert np.abs(wf - rp).max() <= 2e-6, (step, float(np.abs(wf - rp).max()))
+        assert np.abs(wf - wp).max() <= 2e-6
+        after = np.empty(n, np.float32)
+        fused.read_grads(after)
+        assert np.array_equal(after, g)                                    # the fused form leaves the gradients unscaled
+    assert fused.step_count == 3
+    fused.close(); plain.close()
+
+
+def test_training_state_round_trip_and_header_checks(lib):
+    """save_state / load_state: parameters, both AdamW moments and the step counter come back bit for bit and training
+    continues as it would have; a file of another configuration, a truncated file and a raw parameter image are refused without
+    touching the model."""
+    import tempfile
+    import torch
+    import gpt_b200
+    cfg, tokens, weights, _ = _tiny()
+    T = cfg["max_seq_len"]
+    d_in = torch.from_numpy(tokens[:T].copy()).cuda()
+    d_lbl = torch.from_numpy(tokens[1:T + 1].copy()).cuda()
+
+    def train(m, steps):
+        for _ in range(steps):
+            m.zero_grad(); m.forward(d_in); m.backward(d_in, d_lbl)
+            m.clip_and_optimizer_step(1.0, 1, 6e-4, 0.9, 0.95, 0.1)
+
+    a = gpt_b200.Model(cfg, 0, None, gpt_b200.MODE_3XTF32)
+    a.load_weights(weights); a.set_size(1, T)
+    train(a, 2)
+    with tempfile.TemporaryDirectory() as tmp:
+        path = tmp + "/state.bin"
+        a.save_state(path)
+        raw = np.fromfile(path, dtype=np.uint8)
+        assert raw[:8].tobytes() == b"GPTB200S" and raw.size == 64 + 3 * 4 * a.num_params
+        b = gpt_b200.Model(cfg, 0, None, gpt_b200.MODE_3XTF32)
+        b.set_size(1, T)
+        b.load_state(path)
+        assert b.step_count == 2
+        wa, wb = np.empty(a.num_params, np.float32), np.empty(a.num_params, np.float32)
+        a.read_weights(wa); b.read_weights(wb)
+        assert np.array_equal(wa, wb)                     # the parameters come back bit for bit
+        train(a, 2); train(b, 2)
+        wa, wb = np.empty(a.num_params, np.float32), np.empty(a.num_params, np.float32)
+        a.read_weights(wa); b.read_weights(wb)
+        # resumed training follows the original (not bit for bit: the embedding backward adds with atomics, in any order)
+        assert np.abs(wa - wb).max() <= 1e-6 * np.abs(wa).max()
+        # refusals
+        other = dict(cfg, num_layers=cfg["num_layers"] - 1)
+        c = gpt_b200.Model(other, 0, None, gpt_b200.MODE_3XTF32)
+        with pytest.raises(gpt_b200.GptB200Error):
+            c.load_state(path)
+        raw[:-100].tofile(tmp + "/short.bin")
+        before = np.empty(a.num_params, np.float32)
+        b.read_weights(before)
+        with pytest.raises(gpt_b200.GptB200Error):
+            b.load_state(tmp + "/short.bin")
+        weights.tofile(tmp + "/raw.bin")
+        with pytest.raises(gpt_b200.GptB200Error):
+            b.load_state(tmp + "/raw.bin")
+        after = np.empty(a.num_params, np.float32)
+        b.read_weights(after)
+        assert np.array_equal(before, after) and b.step_count == 4
+        b.close(); c.close()
+    a.close()

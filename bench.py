@@ -522,7 +522,8 @@ def train_record(torch, dist, world, rank, dev, mode_name="3xtf32", global_batch
     class _Raw:   # torch view of the packed gradient buffer (no copy) for the collectives
         __cuda_array_interface__ = dict(shape=(model.num_params,), typestr="<f4", data=(model.grads_ptr, False), version=3, strides=None)
     grads = torch.as_tensor(_Raw(), device=dev)
-    dp = DataParallelStep(model, grads, world, layers_per_group=3)
+    dp = DataParallelStep(model, grads, world, layers_per_group=int(os.environ.get("GPTB200_LAYERS_PER_GROUP", "3")), comm_sms=COMM_SMS if COMM_SMS >= 0 else None,
+                          early_wte=os.environ.get("GPTB200_EARLY_WTE", "1") != "0")
     rng = np.random.default_rng(1000)
     all_seqs = rng.integers(0, cfg["vocab_size"], size=(GB, T + 1)).astype(np.int32)
     seqs = all_seqs[rank * B:(rank + 1) * B]
@@ -551,6 +552,7 @@ def train_record(torch, dist, world, rank, dev, mode_name="3xtf32", global_batch
         barrier()
         per_tensor = {}
         if rank == 0:
+            model.defer_embedding_backward(False)
             model.set_size(GB, T)
             f_in = torch.from_numpy(np.ascontiguousarray(all_seqs[:, :T])).to(dev)
             f_lbl = torch.from_numpy(np.ascontiguousarray(all_seqs[:, 1:])).to(dev)
@@ -564,6 +566,7 @@ def train_record(torch, dist, world, rank, dev, mode_name="3xtf32", global_batch
                 a, b = g_dp[offs[i]:offs[i + 1]], grads[offs[i]:offs[i + 1]]
                 per_tensor[n] = float((a - b).abs().max() / b.abs().max().clamp_min(1e-30))
             model.set_size(B, T)
+            model.defer_embedding_backward(dp.early_wte)
             del f_in, f_lbl
         del g_dp
         barrier()
@@ -605,10 +608,8 @@ def train_record(torch, dist, world, rank, dev, mode_name="3xtf32", global_batch
         model.forward(d_in)
         ev[1].record()
         model.backward(d_in, d_lbl, dp._on_layer_done)
-        dp._limit_sms(False)
         ev[2].record()
-        if world > 1:
-            dp.compute_stream.wait_stream(dp.comm_stream)
+        dp.finish(d_in)      # wait for the collectives still in flight (+ gather and apply the embedding-backward rows)
         ev[3].record()
         model.clip_and_optimizer_step(1.0, 1, 6e-4, 0.9, 0.95, 0.1)
         ev[4].record()
@@ -634,7 +635,7 @@ def train_record(torch, dist, world, rank, dev, mode_name="3xtf32", global_batch
                gpu_launches_per_step=int(launches // max(1, steps)), linear_path_tflops=lin_flops / (ms_step * 1e-3) / 1e12,
                e2e=dict(value=tokens / (e2e_s / n_e2e), unit="tokens/s", h2d_bytes_per_step=int(2 * B * T * 4), d2h_bytes_per_step=4,
                         ms_per_step=e2e_s / n_e2e * 1e3, loss=loss),
-               dp_parity=dp_parity, clocks=clocks, comm_sms=dp.comm_sms)
+               dp_parity=dp_parity, clocks=clocks, comm_sms=dp.comm_sms, early_wte=dp.early_wte)
     model.close()
     return rec
 
@@ -675,13 +676,23 @@ def run_train(args):
         dist.destroy_process_group()
 
 
+NCCL_MAX_CTAS = int(os.environ.get("GPTB200_NCCL_MAX_CTAS", "0"))   # 0: NCCL's own choice
+COMM_SMS = int(os.environ.get("GPTB200_COMM_SMS", "-1"))             # SMs the GEMMs leave to NCCL meanwhile; -1: by world size
+
+
 def _init_process_group(dist, dev):
-    """NCCL process group whose collectives run on a high-priority stream (their CTAs are placed before pending GEMM CTAs)."""
+    """NCCL process group whose collectives run on a high-priority stream (their CTAs are placed before pending GEMM CTAs) and,
+    optionally, with a bound on the CTAs NCCL may use per collective (the gradient all-reduce overlaps the backward pass and
+    needs a fraction of the link bandwidth: every SM it does not take stays with the GEMMs)."""
     try:
         from torch.distributed import ProcessGroupNCCL
         opts = ProcessGroupNCCL.Options(is_high_priority_stream=True)
+        if NCCL_MAX_CTAS > 0:
+            opts.config.max_ctas = NCCL_MAX_CTAS
+            opts.config.min_ctas = min(NCCL_MAX_CTAS, 4)
         dist.init_process_group("nccl", device_id=dev, pg_options=opts)
-    except Exception:
+    except Exception as e:
+        print(f"[bench] process group options not applied ({type(e).__name__}: {e})", file=sys.stderr)
         if not dist.is_initialized():
             dist.init_process_group("nccl", device_id=dev)
 

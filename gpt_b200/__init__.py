@@ -31,7 +31,7 @@ EXPORTED_SYMBOLS = [
     "gptb200_gelu_backward",
     "gptb200_unembed_forward", "gptb200_unembed_backward",
     "gptb200_malloc", "gptb200_free", "gptb200_memset", "gptb200_memcpy_h2d", "gptb200_memcpy_d2h",
-    "gptb200_fill_normal", "gptb200_fill_const", "gptb200_embedding_forward", "gptb200_embedding_backward",
+    "gptb200_fill_normal", "gptb200_fill_const", "gptb200_embedding_forward", "gptb200_embedding_backward", "gptb200_embedding_backward_scaled",
     "gptb200_layernorm_forward", "gptb200_layernorm_backward", "gptb200_attention_forward", "gptb200_attention_backward",
     "gptb200_softmax_forward", "gptb200_cross_entropy_softmax_backward", "gptb200_cross_entropy_loss",
     "gptb200_adamw_step", "gptb200_scale_and_clip_grad", "gptb200_memory_info", "gptb200_clip_adamw_packed",
@@ -94,6 +94,7 @@ def load_library(path: str | None = None) -> ctypes.CDLL:
         "gptb200_fill_const": (i, [vp, fp, f32, sz]),
         "gptb200_embedding_forward": (i, [vp, fp, fp, fp, fp, i, i, i]),
         "gptb200_embedding_backward": (i, [vp, fp, fp, fp, fp, i, i, i]),
+        "gptb200_embedding_backward_scaled": (i, [vp, fp, fp, fp, fp, i, i, i, f32]),
         "gptb200_layernorm_forward": (i, [vp, fp, fp, fp, fp, fp, fp, fp, i, i]),
         "gptb200_layernorm_backward": (i, [vp, fp, fp, fp, fp, fp, fp, fp, fp, fp, i, i]),
         "gptb200_attention_forward": (i, [vp, fp, fp, fp, i, i, i, i]),
@@ -319,6 +320,9 @@ def _declare_model(lib: ctypes.CDLL) -> None:
         "gptb200_model_clip": (i, [vp, f32, i]),
         "gptb200_model_optimizer_step": (i, [vp, f32, f32, f32, f32]),
         "gptb200_model_clip_and_optimizer_step": (i, [vp, f32, i, f32, f32, f32, f32]),
+        "gptb200_model_defer_embedding_backward": (i, [vp, i]),
+        "gptb200_model_embedding_grad": (vp, [vp]),
+        "gptb200_model_apply_embedding_grad": (i, [vp, vp, vp, i, i, f32]),
         "gptb200_model_save_state": (i, [vp, ctypes.c_char_p]),
         "gptb200_model_load_state": (i, [vp, ctypes.c_char_p]),
         "gptb200_model_step_count": (i, [vp]),
@@ -440,6 +444,18 @@ class Model:
 
     def optimizer_step(self, learning_rate: float, beta1: float, beta2: float, decay: float) -> None:
         self._check(self._lib.gptb200_model_optimizer_step(self._m, learning_rate, beta1, beta2, decay))
+
+    def defer_embedding_backward(self, defer: bool) -> None:
+        """Backward passes stop before the embedding backward; see apply_embedding_grad (data-parallel training)."""
+        self._check(self._lib.gptb200_model_defer_embedding_backward(self._m, int(defer)))
+
+    @property
+    def embedding_grad_ptr(self) -> int:
+        """Device address of the gradient of the embedding output, [batch*seq x d_model], valid after a backward pass."""
+        return int(self._lib.gptb200_model_embedding_grad(self._m) or 0)
+
+    def apply_embedding_grad(self, rows, tokens, batch_size: int, seq_len: int, scale: float) -> None:
+        self._check(self._lib.gptb200_model_apply_embedding_grad(self._m, _ptr(rows), _ptr(tokens), batch_size, seq_len, scale))
 
     def clip_and_optimizer_step(self, max_norm: float, accum_steps: int, learning_rate: float, beta1: float, beta2: float, decay: float) -> None:
         """unscale_and_clip_grads + optimizer_step in two launches over the packed buffers (the gradients stay unscaled)."""

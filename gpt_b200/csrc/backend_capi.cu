@@ -151,6 +151,16 @@ int gptb200_embedding_backward(gptb200_ctx *ctx, float *grad_wte, float *grad_wp
     return launched(ctx);
 }
 
+int gptb200_embedding_backward_scaled(gptb200_ctx *ctx, float *grad_wte, float *grad_wpe, const float *grad_y, const int *tokens, int batch,
+                                      int seq_len, int d, float scale)
+{
+    NEED(ctx, batch >= 0 && seq_len >= 0 && d >= 0);
+    if (1LL * batch * seq_len == 0 || d == 0) return GPTB200_OK;
+    NEED(ctx, grad_wte && grad_wpe && grad_y && tokens);
+    ops::embedding_backward_scaled_kernel<<<seq_len, 256, 0, ctx->stream>>>(grad_wte, grad_wpe, grad_y, tokens, batch, seq_len, d, scale);
+    return launched(ctx);
+}
+
 int gptb200_layernorm_forward(gptb200_ctx *ctx, float *y, float *means, float *vars, float *x, const float *residual, const float *gamma,
                               const float *beta, int rows, int d)
 {

@@ -116,6 +116,24 @@ __global__ void embedding_backward_kernel(float *__restrict__ grad_wte, float *_
     }
 }
 
+// The same with every contribution multiplied by `scale` (a data-parallel step applies the rows of all ranks, each weighted
+// 1 / ranks, to gradients that were already averaged).
+__global__ void embedding_backward_scaled_kernel(float *__restrict__ grad_wte, float *__restrict__ grad_wpe, const float *__restrict__ grad_y,
+                                                 const int *__restrict__ tokens, int batch, int seq_len, int d, float scale)
+{
+    const int s = blockIdx.x;
+    for (int h = threadIdx.x; h < d; h += blockDim.x) {
+        float acc = 0.0f;
+        for (int b = 0; b < batch; ++b) {
+            const size_t r = size_t(b) * seq_len + s;
+            const float g = grad_y[r * d + h] * scale;
+            acc += g;
+            atomicAdd(grad_wte + size_t(tokens[r]) * d + h, g);
+        }
+        grad_wpe[size_t(s) * d + h] += acc;
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ LayerNorm
 
 // x += residual (in place); mean, biased variance; y = (x - mean) / sqrt(var + 1e-5) * gamma + beta

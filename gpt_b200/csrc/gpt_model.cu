@@ -231,9 +231,15 @@ public:
                                                           A + a_.ln1_mean + l * M, A + a_.ln1_var + l * M, w + lay_.ln1_w + l * D, B_, T_, c_.d_model);
             if (layer_done) layer_done(l, user);
         }
+        if (defer_embedding_) return;   // the caller applies the rows of all ranks itself (see apply_embedding_grad)
         be_->device_embedding_backward(gw + lay_.wte, gw + lay_.wpe, d_res, tokens, B_, T_, c_.d_model);
         if (layer_done) layer_done(-1, user);
     }
+
+    void set_defer_embedding(bool on) { defer_embedding_ = on; }
+    float *embedding_grad() { return agrads_ ? agrads_ + g_.d_res : nullptr; }
+    size_t wte_offset() const { return lay_.wte; }
+    size_t wpe_offset() const { return lay_.wpe; }
 
     float loss(const int *labels)
     {
@@ -311,6 +317,7 @@ private:
     float *acts_ = nullptr, *agrads_ = nullptr, *loss_dev_ = nullptr;
     size_t acts_capacity_ = 0, agrads_capacity_ = 0;
     int B_ = 0, T_ = 0, step_ = 0;
+    bool defer_embedding_ = false;
 };
 
 struct ModelHandle {
@@ -457,6 +464,24 @@ int gptb200_model_backward(gptb200_model *m, const int *tokens_dev, const int *l
     if (!m || !tokens_dev || !labels_dev || m->h.model->batch() == 0) return GPTB200_ERR_INVALID_ARG;
     m->h.model->backward(tokens_dev, labels_dev, layer_done, user);
     return m->h.backend->status();
+}
+
+int gptb200_model_defer_embedding_backward(gptb200_model *m, int defer)
+{
+    if (!m) return GPTB200_ERR_INVALID_ARG;
+    m->h.model->set_defer_embedding(defer != 0);
+    return GPTB200_OK;
+}
+
+float *gptb200_model_embedding_grad(gptb200_model *m) { return m ? m->h.model->embedding_grad() : nullptr; }
+
+int gptb200_model_apply_embedding_grad(gptb200_model *m, const float *rows_dev, const int *tokens_dev, int batch, int seq, float scale)
+{
+    if (!m || !rows_dev || !tokens_dev || batch <= 0 || seq <= 0 || seq > m->h.model->config().max_seq_len) return GPTB200_ERR_INVALID_ARG;
+    if (m->h.backend->status() != 0) return m->h.backend->status();
+    GptModel *g = m->h.model;
+    return gptb200_embedding_backward_scaled(m->h.backend->context(), g->grads() + g->wte_offset(), g->grads() + g->wpe_offset(), rows_dev, tokens_dev,
+                                             batch, seq, g->config().d_model, scale);
 }
 
 int gptb200_model_loss(gptb200_model *m, const int *labels_dev, float *loss_out)

@@ -11,6 +11,13 @@ are ready to be reduced: layers are grouped (default 3 per group), and when the 
 completes, each of the twelve per-layer kinds contributes one contiguous slice covering the group.  wte, wpe and
 the final LayerNorm go last (wte also receives the embedding backward at the very end).  The plan is pure
 index arithmetic and is tested on CPU with the gloo backend.
+
+The early form (`early_wte`, the default on GPUs): wte is the largest gradient tensor (154 MB of 494 MB for GPT-2 124M) and
+would otherwise be reduced after the whole pass, with nothing left to overlap it.  Its two contributions are the
+un-embedding backward at the START of the pass (dense) and the embedding backward at the END (one row per token).  The
+backward pass therefore stops before the embedding backward; wte / wpe are reduced together with the final LayerNorm right
+after the un-embedding backward; at the end the ranks all-gather the embedding backward's inputs (every rank's rows of the
+residual-stream gradient and its tokens: 50 MB in all) and each applies all of them with weight 1 / ranks.
 """
 from __future__ import annotations
 
@@ -37,13 +44,15 @@ class GradientBuckets:
         self.group = max(1, min(layers_per_group, self.L))
         self.sizes = per_layer_sizes(cfg)
 
-    def ready_after(self, event: int) -> list[tuple[int, int]]:
-        """event: the layer index reported by the backward pass (L, L-1, ..., 0, -1)."""
+    def ready_after(self, event: int, early_wte: bool = False) -> list[tuple[int, int]]:
+        """event: the layer index reported by the backward pass (L, L-1, ..., 0, -1).  early_wte: the embedding backward is
+        applied after the reduction (see the module text), so wte / wpe are ready with the final LayerNorm."""
         L, D = self.L, self.cfg["d_model"]
+        emb = (self.off["wte"], self.off["ln_1_w"] - self.off["wte"])   # wte and wpe are adjacent at the start of the buffer
         if event == L:      # un-embedding + final LayerNorm done: ln_f_w, ln_f_b are adjacent at the end of the buffer
-            return [(self.off["ln_f_w"], 2 * D)]
-        if event == -1:     # embedding backward done: wte and wpe are adjacent at the start of the buffer
-            return [(self.off["wte"], self.off["ln_1_w"] - self.off["wte"])]
+            return [(self.off["ln_f_w"], 2 * D)] + ([emb] if early_wte else [])
+        if event == -1:     # embedding backward done
+            return [] if early_wte else [emb]
         if event % self.group != 0:
             return []
         hi = min(event + self.group, L)  # layers [event, hi) are complete
@@ -70,7 +79,7 @@ class DataParallelStep:
     """
 
     def __init__(self, model, grad_tensor, world_size: int, layers_per_group: int = 3, all_reduce: Callable | None = None,
-                 comm_sms: int | None = None):
+                 comm_sms: int | None = None, early_wte: bool | None = None):
         import torch
         import torch.distributed as dist
         self.torch = torch
@@ -91,9 +100,17 @@ class DataParallelStep:
         # a GEMM CTA to finish, and the GEMM's equal k-block ranges assume that all of its CTAs run at once (measured on the
         # FFN step at 2 GPUs: 0.55 ms per step with all SMs claimed, 0.50 ms with 16 left free, 0.48 ms without any collective).
         if comm_sms is None:
-            comm_sms = 16 if world_size <= 2 else 32   # NCCL uses more channels with more ranks (measured: FFN step at 2 and 8 GPUs)
+            comm_sms = 0 if world_size <= 2 else 32   # NCCL uses more channels with more ranks (measured: training step at 2 GPUs, FFN step at 8)
         self.comm_sms = comm_sms if world_size > 1 else 0
         self._sms_limited = False
+        # early reduction of wte (module text): needs the model driver's hooks and device tensors
+        if early_wte is None:
+            early_wte = True
+        self.early_wte = bool(early_wte and world_size > 1 and self.on_gpu and hasattr(model, "defer_embedding_backward"))
+        if self.early_wte:
+            model.defer_embedding_backward(True)
+        self._gather_rows = self._gather_tokens = None
+        self._coalesce = all_reduce is None and hasattr(dist, "_coalescing_manager")
 
     def _limit_sms(self, on: bool) -> None:
         if not self.on_gpu or self.comm_sms <= 0 or on == self._sms_limited or not hasattr(self.model, "set_option"):
@@ -103,7 +120,7 @@ class DataParallelStep:
         self._sms_limited = on
 
     def _on_layer_done(self, layer: int) -> None:
-        slices = self.buckets.ready_after(layer)
+        slices = self.buckets.ready_after(layer, self.early_wte)
         if not slices or self.world == 1:
             return
         if not self.on_gpu:
@@ -116,15 +133,59 @@ class DataParallelStep:
         ev.record(self.compute_stream)
         with self.torch.cuda.stream(self.comm_stream):
             self.comm_stream.wait_event(ev)
-            for off, n in slices:
-                self._all_reduce(self.grads[off:off + n])
+            self._reduce_slices(slices)
+
+    def _reduce_slices(self, slices) -> None:
+        """All slices of one event as ONE NCCL group (one kernel, one host call) where torch offers it."""
+        views = [self.grads[off:off + n] for off, n in slices]
+        if self._coalesce and len(views) > 1:
+            try:
+                with self.dist._coalescing_manager(device=self.grads.device, async_ops=False):
+                    for v in views:
+                        self._all_reduce(v)
                 self.collectives += 1
+                return
+            except Exception:
+                self._coalesce = False       # this torch has no such manager: one call per slice from now on
+        for v in views:
+            self._all_reduce(v)
+            self.collectives += 1
+
+    def _apply_embedding_rows(self, tokens) -> None:
+        """End of a pass in the early form: gather every rank's embedding-backward inputs, apply them all."""
+        torch, m = self.torch, self.model
+        B, T = tokens.shape
+        D = m.config["d_model"]
+        if self._gather_rows is None or self._gather_rows.shape[1] != B * T * D:
+            self._gather_rows = torch.empty(self.world, B * T * D, device=tokens.device, dtype=torch.float32)
+            self._gather_tokens = torch.empty(self.world, B * T, device=tokens.device, dtype=torch.int32)
+
+        class _Raw:   # the model's gradient of the embedding output, in place
+            __cuda_array_interface__ = dict(shape=(B * T * D,), typestr="<f4", data=(m.embedding_grad_ptr, False), version=3, strides=None)
+        rows = torch.as_tensor(_Raw(), device=tokens.device)
+        ev = torch.cuda.Event()
+        ev.record(self.compute_stream)
+        with torch.cuda.stream(self.comm_stream):
+            self.comm_stream.wait_event(ev)
+            self.dist.all_gather_into_tensor(self._gather_rows.view(-1), rows)
+            self.dist.all_gather_into_tensor(self._gather_tokens.view(-1), tokens.reshape(-1).to(torch.int32))
+            self.collectives += 2
+        self.compute_stream.wait_stream(self.comm_stream)      # also: the reduction of wte / wpe has finished
+        for r in range(self.world):
+            m.apply_embedding_grad(self._gather_rows[r], self._gather_tokens[r], B, T, 1.0 / self.world)
 
     def step(self, tokens, labels) -> None:
         m = self.model
         m.zero_grad()
         m.forward(tokens)
         m.backward(tokens, labels, self._on_layer_done)
+        self.finish(tokens)
+
+    def finish(self, tokens) -> None:
+        """After the backward pass: the compute stream waits for the collectives (and, in the early form, applies the gathered
+        embedding-backward rows); afterwards every rank holds the averaged gradients."""
         self._limit_sms(False)
-        if self.world > 1 and self.on_gpu:
+        if self.early_wte:
+            self._apply_embedding_rows(tokens)
+        elif self.world > 1 and self.on_gpu:
             self.compute_stream.wait_stream(self.comm_stream)

@@ -170,6 +170,10 @@ int gptb200_embedding_forward(gptb200_ctx *ctx, float *y, const float *wte, cons
                               int d);
 int gptb200_embedding_backward(gptb200_ctx *ctx, float *grad_wte, float *grad_wpe, const float *grad_y, const int *tokens, int batch,
                                int seq_len, int d);
+/* gptb200_embedding_backward with every contribution multiplied by `scale`: a data-parallel step applies the rows of all ranks,
+ * each weighted 1 / ranks, to gradients that were averaged before (no counterpart in the reference, which has one process). */
+int gptb200_embedding_backward_scaled(gptb200_ctx *ctx, float *grad_wte, float *grad_wpe, const float *grad_y, const int *tokens, int batch,
+                                      int seq_len, int d, float scale);
 int gptb200_layernorm_forward(gptb200_ctx *ctx, float *y, float *means, float *vars, float *x, const float *residual, const float *gamma,
                               const float *beta, int rows, int d);
 int gptb200_layernorm_backward(gptb200_ctx *ctx, float *grad_x, float *grad_gamma, float *grad_beta, const float *grad_y,
@@ -229,6 +233,15 @@ int gptb200_model_forward(gptb200_model *m, const int *tokens_dev);
  * have been enqueued: l = num_layers after the un-embedding and final LayerNorm, l = num_layers-1 .. 0 after each
  * transformer layer, l = -1 after the embedding backward (wte, wpe complete).  May be NULL. */
 int gptb200_model_backward(gptb200_model *m, const int *tokens_dev, const int *labels_dev, void (*layer_done)(int, void *), void *user);
+/* Data-parallel training: with defer != 0 the backward pass stops before the embedding backward, the one operator that adds to
+ * grad_wte / grad_wpe at the very END of the pass (the un-embedding adds to grad_wte at its start).  The caller can then reduce
+ * grad_wte over the ranks while the layers still run, gather every rank's rows and tokens afterwards
+ * (gptb200_model_embedding_grad: [batch*seq x d_model], valid after the backward pass) and apply them all with
+ * gptb200_model_apply_embedding_grad (scale = 1 / ranks): the same sum as reducing after a complete pass, without the
+ * largest gradient tensor waiting for the end of it.  layer_done(-1) is not fired in a deferred pass. */
+int gptb200_model_defer_embedding_backward(gptb200_model *m, int defer);
+float *gptb200_model_embedding_grad(gptb200_model *m);
+int gptb200_model_apply_embedding_grad(gptb200_model *m, const float *rows_dev, const int *tokens_dev, int batch, int seq, float scale);
 int gptb200_model_loss(gptb200_model *m, const int *labels_dev, float *loss_out);
 int gptb200_model_clip(gptb200_model *m, float max_norm, int accum_steps);
 int gptb200_model_optimizer_step(gptb200_model *m, float lr, float beta1, float beta2, float weight_decay);

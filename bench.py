@@ -25,6 +25,8 @@ Beside those headline keys the default line carries sub-records, each a few hund
   reference_gpu  (N = 1) the reference's own CUDA backend (cuBLAS TF32 + its unfused kernels, unmodified sources) on the same
                  shapes and on the training step, run in a child process so that cuBLAS never enters this one;
   decode         (N = 1) the linear layers of a decode step at batch 1 / 8 / 64: GB/s of weight stream and fraction of HBM peak;
+  generate       (N = 1) generation of 192 tokens after a 64-token prompt at batch 1 / 8 / 64: tokens/s with the KV cache and
+                 in the reference's form (the whole prefix recomputed per token);
   train_step     (every N) the full GPT-2 124M training step at a global batch of 64 x 256 tokens sharded over the ranks
                  (strong scaling): tokens/s, phase times, collectives per step, and dp_parity -- the distance per gradient
                  tensor between the all-reduced N-rank gradients and rank 0 computing the whole batch alone.
@@ -456,6 +458,8 @@ def run_ours(args):
             sub["decode"]["value_gbs"] = {k: v["gbs"] for k, v in sub["decode"]["per_batch"].items()}
             sub["decode"]["frac"] = {k: v["hbm_frac"] for k, v in sub["decode"]["per_batch"].items()}
             torch.cuda.empty_cache()
+            sub["generate"] = generate_record(torch, dev, "3xtf32")
+            torch.cuda.empty_cache()
         sub["train_step"] = train_record(torch, dist, world, rank, dev, "3xtf32", 64, 5, 2, sampler, parity=True)
         torch.cuda.empty_cache()
         if world == 1 and rank == 0:
@@ -794,62 +798,119 @@ def run_decode(args):
     print(json.dumps(out), flush=True)
 
 
-def run_generate(args):
-    """--workload generate: autoregressive generation with GPT-2 124M random-init weights (BASELINE.json configs[4]): for batch
-    1, 8, 64 a random-id prompt of 64 tokens is extended to 256 tokens at temperature 1.0.  As in the reference
-    (src/infer/infer.cpp:112-148) there is no KV cache: every new token recomputes the whole prefix, so the linear layers see
-    m = batch * prefix rows (64 ... 255 per sequence).  Sampling (softmax at temperature 1 + multinomial over the 50257 real
-    tokens) runs on the GPU with torch; everything else goes through the model driver of this library."""
-    import numpy as np
-    import torch
+def generate_record(torch, dev, mode_name="3xtf32", batches=(1, 8, 64), with_prefix_recompute=True):
+    """Autoregressive generation with GPT-2 124M random-init weights (BASELINE.json configs[4]): a random-id prompt of 64 tokens
+    extended to 256 tokens at temperature 1.0, for each batch size, in two forms:
+      kv_cache           one forward pass over the prompt, then one row per sequence per step against cached keys / values
+                         (every linear layer runs with m = batch rows); the step is captured once as a CUDA graph (its position
+                         lives in device memory) and replayed per token, sampling in between;
+      prefix_recompute   the reference's way (src/infer/infer.cpp:112-148, no KV cache): every new token recomputes the whole
+                         prefix, m = batch * (64 ... 255) rows.
+    Sampling (softmax at temperature 1 + multinomial over the 50257 real tokens) runs on the GPU with torch."""
     import gpt_b200
-    torch.cuda.set_device(0)
-    dev = torch.device("cuda", 0)
     cfg = gpt_b200.GPT2_124M
     V, Vp = cfg["vocab_size"], cfg["vocab_size_padded"]
-    mode = gpt_b200.MODE_TF32 if args.mode == "tf32" else gpt_b200.MODE_3XTF32
-    model = gpt_b200.Model(cfg, 0, torch.cuda.current_stream().cuda_stream, mode, seed=42, use_grad=False)
-    model.init(0.0, 0.02)
+    mode = gpt_b200.MODE_TF32 if mode_name == "tf32" else gpt_b200.MODE_3XTF32
+    PROMPT, TOTAL = 64, 256
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
     results = {}
     launches = 0
-    PROMPT, TOTAL = 64, 256
-    for batch in (1, 8, 64):
-        torch.manual_seed(batch)
-        tokens = torch.zeros(batch, TOTAL, dtype=torch.int32, device=dev)
-        tokens[:, :PROMPT] = torch.randint(0, V, (batch, PROMPT), dtype=torch.int32, device=dev)
-        model.set_size(batch, TOTAL)          # allocate once at the largest shape; later calls reuse the buffers
+    with torch.cuda.stream(stream):
+        model = gpt_b200.Model(cfg, dev.index, stream.cuda_stream, mode, seed=42, use_grad=False)
+        model.init(0.0, 0.02)
+        model.set_option("decode_early_launch", 1)      # inference: nothing writes the weights between the layers
+        for batch in batches:
+            torch.manual_seed(batch)
+            prompt = torch.randint(0, V, (batch, PROMPT), dtype=torch.int32, device=dev)
+            tok = torch.empty(batch, dtype=torch.int32, device=dev)
+            logits = torch.empty(batch, Vp, device=dev)
 
-        class _Raw:
-            pass
+            def sample(lg):
+                probs = torch.softmax(lg[:, :V].float(), dim=-1)            # temperature 1.0
+                return torch.multinomial(probs, 1).squeeze(1).to(torch.int32)
 
-        def generate():
-            for t in range(PROMPT, TOTAL):
-                model.set_size(batch, t)
-                prefix = tokens[:, :t].contiguous()
-                model.forward(prefix)
-                raw = _Raw()
-                raw.__cuda_array_interface__ = dict(shape=(batch, t, Vp), typestr="<f4", data=(model.logits_ptr, False), version=3, strides=None)
-                logits = torch.as_tensor(raw, device=dev)[:, t - 1, :V]
-                probs = torch.softmax(logits.float(), dim=-1)            # temperature 1.0
-                tokens[:, t] = torch.multinomial(probs, 1).squeeze(1).to(torch.int32)
+            def prompt_logits():
+                class _Raw:
+                    __cuda_array_interface__ = dict(shape=(batch, PROMPT, Vp), typestr="<f4", data=(model.logits_ptr, False), version=3, strides=None)
+                return torch.as_tensor(_Raw(), device=dev)[:, PROMPT - 1, :]
 
-        generate()                            # warm-up pass (also sizes scratch buffers)
-        torch.cuda.synchronize()
-        l0 = model.launch_count()
-        t0 = time.perf_counter()
-        generate()
-        torch.cuda.synchronize()
-        dt = time.perf_counter() - t0
-        launches += model.launch_count() - l0
-        new_tokens = batch * (TOTAL - PROMPT)
-        results[f"batch{batch}"] = dict(seconds=dt, tokens_per_s=new_tokens / dt, ms_per_token_step=dt / (TOTAL - PROMPT) * 1e3)
-    out = dict(metric="generate_tokens_per_s", value=results["batch8"]["tokens_per_s"], unit="tokens/s", n_gpus=1, steps=1, warmup=1,
-               ms_per_step=results["batch8"]["ms_per_token_step"], higher_is_better=True, scaling="weak", vs_baseline=None,
-               dtype="tf32x3 (fp32-accurate split)" if mode == gpt_b200.MODE_3XTF32 else "tf32", data="synthetic", impl="ours",
-               config=dict(workload="GPT-2 124M generation, prompt 64 -> 256 tokens, temperature 1.0, full-prefix recompute (no KV cache, as the reference)",
-                           mode=args.mode), per_batch=results, gpu_launches=int(launches))
+            def generate(graph):
+                model.generate_begin(prompt, batch, PROMPT, TOTAL)
+                tok.copy_(sample(prompt_logits()))
+                out = [tok.clone()]
+                for _ in range(PROMPT + 1, TOTAL):
+                    if graph is not None:
+                        graph.replay()
+                    else:
+                        model.generate_step(tok, logits)
+                    tok.copy_(sample(logits))
+                    out.append(tok.clone())
+                return out
+
+            generate(None)                                   # eager pass: sizes scratch, sets kernel attributes
+            stream.synchronize()
+            model.generate_begin(prompt, batch, PROMPT, TOTAL)
+            tok.copy_(sample(prompt_logits()))
+            graph = torch.cuda.CUDAGraph()
+            l0 = model.launch_count()
+            with torch.cuda.graph(graph, stream=stream):
+                model.generate_step(tok, logits)
+            per_step = model.launch_count() - l0
+            generate(graph)                                  # warm replay pass
+            stream.synchronize()
+            t0 = time.perf_counter()
+            generate(graph)
+            stream.synchronize()
+            dt = time.perf_counter() - t0
+            new_tokens = batch * (TOTAL - PROMPT)
+            rec = dict(kv_cache=dict(seconds=dt, tokens_per_s=new_tokens / dt, ms_per_token_step=dt / (TOTAL - PROMPT) * 1e3, launches_per_step=per_step))
+            launches += per_step * (TOTAL - PROMPT - 1)
+            if with_prefix_recompute:
+                seq = torch.zeros(batch, TOTAL, dtype=torch.int32, device=dev)
+                seq[:, :PROMPT] = prompt
+                model.set_size(batch, TOTAL)
+
+                def recompute():
+                    for t in range(PROMPT, TOTAL):
+                        model.set_size(batch, t)
+                        model.forward(seq[:, :t].contiguous())
+
+                        class _Raw:
+                            __cuda_array_interface__ = dict(shape=(batch, t, Vp), typestr="<f4", data=(model.logits_ptr, False), version=3, strides=None)
+                        seq[:, t] = sample(torch.as_tensor(_Raw(), device=dev)[:, t - 1, :])
+
+                if batch <= 8:
+                    recompute()                              # warm-up pass (the batch-64 form takes seconds: timed cold)
+                stream.synchronize()
+                l0 = model.launch_count()
+                t0 = time.perf_counter()
+                recompute()
+                stream.synchronize()
+                dt2 = time.perf_counter() - t0
+                launches += model.launch_count() - l0
+                rec["prefix_recompute"] = dict(seconds=dt2, tokens_per_s=new_tokens / dt2, ms_per_token_step=dt2 / (TOTAL - PROMPT) * 1e3)
+                rec["kv_cache_speedup"] = dt2 / dt
+            results[f"batch{batch}"] = rec
+        model.close()
+    torch.cuda.current_stream().wait_stream(stream)
+    return dict(per_batch=results, prompt_len=PROMPT, total_len=TOTAL, temperature=1.0, mode=mode_name, gpu_launches=int(launches),
+                note="tokens/s counts generated tokens; host-side sampling with torch is inside the time")
+
+
+def run_generate(args):
+    """--workload generate: see generate_record; the JSON `value` is the batch-8 KV-cached figure."""
+    import torch
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    rec = generate_record(torch, dev, args.mode)
+    r8 = rec["per_batch"]["batch8"]["kv_cache"]
+    out = dict(metric="generate_tokens_per_s", value=r8["tokens_per_s"], unit="tokens/s", n_gpus=1, steps=1, warmup=1,
+               ms_per_step=r8["ms_per_token_step"], higher_is_better=True, scaling="weak", vs_baseline=None,
+               dtype="f32 (decode-shaped layers use fp32 FMA kernels)", data="synthetic", impl="ours",
+               config=dict(workload="GPT-2 124M generation, prompt 64 -> 256 tokens, temperature 1.0, KV cache (the reference recomputes the prefix: see prefix_recompute)",
+                           mode=args.mode), per_batch=rec["per_batch"], gpu_launches=rec["gpu_launches"])
     print(json.dumps(out), flush=True)
-    model.close()
 
 
 def cpu_reference_sample(rows: int):

@@ -35,6 +35,7 @@ EXPORTED_SYMBOLS = [
     "gptb200_layernorm_forward", "gptb200_layernorm_backward", "gptb200_attention_forward", "gptb200_attention_backward",
     "gptb200_softmax_forward", "gptb200_cross_entropy_softmax_backward", "gptb200_cross_entropy_loss",
     "gptb200_adamw_step", "gptb200_scale_and_clip_grad", "gptb200_memory_info", "gptb200_clip_adamw_packed",
+    "gptb200_embedding_decode", "gptb200_kv_cache_fill", "gptb200_attention_decode", "gptb200_advance_position",
     "gptb200_loader_create", "gptb200_loader_destroy", "gptb200_loader_num_samples", "gptb200_loader_reset_epoch", "gptb200_loader_next_batch",
     "gptb200_bias_grad_noalloc",
 ]
@@ -107,6 +108,10 @@ def load_library(path: str | None = None) -> ctypes.CDLL:
         "gptb200_memory_info": (i, [vp, ctypes.POINTER(f32), ctypes.POINTER(f32)]),
         "gptb200_clip_adamw_packed": (i, [vp, fp, fp, fp, fp, sz, ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(ctypes.c_ubyte), i, f32, i, f32, f32, f32,
                                           f32, f32, i, fp]),
+        "gptb200_embedding_decode": (i, [vp, fp, fp, fp, fp, fp, i, i]),
+        "gptb200_kv_cache_fill": (i, [vp, fp, fp, i, i, i, i]),
+        "gptb200_attention_decode": (i, [vp, fp, fp, fp, fp, i, i, i, i]),
+        "gptb200_advance_position": (i, [vp, fp]),
         "gptb200_loader_create": (i, [ctypes.POINTER(vp), ctypes.c_char_p, i]),
         "gptb200_loader_destroy": (i, [vp]),
         "gptb200_loader_num_samples": (ctypes.c_longlong, [vp]),
@@ -320,6 +325,9 @@ def _declare_model(lib: ctypes.CDLL) -> None:
         "gptb200_model_clip": (i, [vp, f32, i]),
         "gptb200_model_optimizer_step": (i, [vp, f32, f32, f32, f32]),
         "gptb200_model_clip_and_optimizer_step": (i, [vp, f32, i, f32, f32, f32, f32]),
+        "gptb200_model_generate_begin": (i, [vp, vp, i, i, i]),
+        "gptb200_model_generate_step": (i, [vp, vp, vp]),
+        "gptb200_model_generate_position": (i, [vp]),
         "gptb200_model_defer_embedding_backward": (i, [vp, i]),
         "gptb200_model_embedding_grad": (vp, [vp]),
         "gptb200_model_apply_embedding_grad": (i, [vp, vp, vp, i, i, f32]),
@@ -444,6 +452,18 @@ class Model:
 
     def optimizer_step(self, learning_rate: float, beta1: float, beta2: float, decay: float) -> None:
         self._check(self._lib.gptb200_model_optimizer_step(self._m, learning_rate, beta1, beta2, decay))
+
+    def generate_begin(self, prompt_tokens, batch_size: int, prompt_len: int, max_len: int) -> None:
+        """Forward pass over the prompt [batch x prompt_len] and the keys / values of every layer into a cache for max_len positions."""
+        self._check(self._lib.gptb200_model_generate_begin(self._m, _ptr(prompt_tokens), batch_size, prompt_len, max_len))
+
+    def generate_step(self, tokens, logits_out) -> None:
+        """One new position per sequence: tokens [batch] at that position in, logits [batch x vocab_size_padded] for the next one out."""
+        self._check(self._lib.gptb200_model_generate_step(self._m, _ptr(tokens), _ptr(logits_out)))
+
+    @property
+    def generate_position(self) -> int:
+        return int(self._lib.gptb200_model_generate_position(self._m))
 
     def defer_embedding_backward(self, defer: bool) -> None:
         """Backward passes stop before the embedding backward; see apply_embedding_grad (data-parallel training)."""

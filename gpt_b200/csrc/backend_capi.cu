@@ -9,6 +9,7 @@
 #include "attention_tiled.cuh"
 #include "layernorm_warp.cuh"
 #include "optimizer_fused.cuh"
+#include "decode_ops.cuh"
 
 using namespace gptb200;
 
@@ -351,6 +352,47 @@ int gptb200_clip_adamw_packed(gptb200_ctx *ctx, float *params, const float *g, f
                                                                          1.0f / static_cast<float>(accum_steps), max_norm, lr, beta1, beta2, eps,
                                                                          weight_decay, bc1, bc2, seg, vec_ok ? 1 : 0, grad_norm_dev);
     return launched(ctx, 2);
+}
+
+int gptb200_embedding_decode(gptb200_ctx *ctx, float *y, const float *wte, const float *wpe, const int *tokens, const int *pos_dev, int batch, int d)
+{
+    NEED(ctx, batch >= 0 && d >= 0);
+    if (batch == 0 || d == 0) return GPTB200_OK;
+    NEED(ctx, y && wte && wpe && tokens && pos_dev);
+    ops::embedding_decode_kernel<<<batch, 256, 0, ctx->stream>>>(y, wte, wpe, tokens, pos_dev, d);
+    return launched(ctx);
+}
+
+int gptb200_kv_cache_fill(gptb200_ctx *ctx, float *cache, const float *qkv, int batch, int seq_len, int max_len, int d)
+{
+    NEED(ctx, batch >= 0 && seq_len >= 0 && seq_len <= max_len && d >= 0);
+    if (batch == 0 || seq_len == 0 || d == 0) return GPTB200_OK;
+    NEED(ctx, cache && qkv);
+    ops::kv_fill_kernel<<<dim3(seq_len, batch), 256, 0, ctx->stream>>>(cache, qkv, seq_len, max_len, d);
+    return launched(ctx);
+}
+
+int gptb200_attention_decode(gptb200_ctx *ctx, float *y, float *cache, const float *qkv_new, const int *pos_dev, int batch, int max_len, int d,
+                             int heads)
+{
+    NEED(ctx, batch >= 0 && max_len > 0 && d > 0 && heads > 0 && d % heads == 0);
+    if (batch == 0) return GPTB200_OK;
+    NEED(ctx, y && cache && qkv_new && pos_dev);
+    const int hd = d / heads;
+    NEED(ctx, hd >= 4 && hd <= ops::kDecodeAttnThreads && (hd & (hd - 1)) == 0 && aligned16_all({cache}) && d % 4 == 0);
+    const size_t smem = (size_t(max_len) + hd + ops::kDecodeAttnThreads + 64) * sizeof(float);
+    NEED(ctx, smem <= 200 * 1024);
+    if (smem > 48 * 1024) CUDA_TRY(ctx, allow_smem(ctx, ops::attention_decode_kernel, static_cast<int>(smem)));
+    ops::attention_decode_kernel<<<dim3(heads, batch), ops::kDecodeAttnThreads, smem, ctx->stream>>>(y, cache, qkv_new, pos_dev, max_len, d, hd,
+                                                                                                     1.0f / sqrtf(static_cast<float>(hd)));
+    return launched(ctx);
+}
+
+int gptb200_advance_position(gptb200_ctx *ctx, int *pos_dev)
+{
+    NEED(ctx, pos_dev);
+    ops::advance_position_kernel<<<1, 1, 0, ctx->stream>>>(pos_dev);
+    return launched(ctx);
 }
 
 int gptb200_memory_info(gptb200_ctx *ctx, float *free_mb, float *total_mb)

@@ -236,6 +236,84 @@ public:
         if (layer_done) layer_done(-1, user);
     }
 
+    // ---- KV-cached generation ------------------------------------------------------------------------------------
+    // Prefill: forward over the prompt, then every layer's keys and values into the cache.  Returns a gptb200_status.
+    int generate_begin(gptb200_ctx *ctx, const int *prompt, int batch, int prompt_len, int max_len)
+    {
+        const size_t L = c_.layers, D = c_.d_model, F = c_.d_ffn, Vp = c_.vocab_padded;
+        if (!set_size(batch, prompt_len)) return GPTB200_ERR_CUDA;
+        const size_t cache_floats = L * size_t(batch) * max_len * 2 * D;
+        const size_t step_floats = size_t(batch) * (D * 7 + 3 * D + 2 * F + 6) + 8;
+        if (cache_floats + step_floats > gen_capacity_) {
+            void *p = nullptr;
+            be_->device_malloc(&p, (cache_floats + step_floats) * sizeof(float));
+            if (!p) return GPTB200_ERR_CUDA;
+            if (gen_) be_->device_free(gen_);
+            gen_ = static_cast<float *>(p);
+            gen_capacity_ = cache_floats + step_floats;
+        }
+        gen_batch_ = batch;
+        gen_max_len_ = max_len;
+        gen_pos_ = prompt_len;
+        forward(prompt);
+        const size_t M = size_t(batch) * prompt_len;
+        for (size_t l = 0; l < L; ++l) {
+            const int rc = gptb200_kv_cache_fill(ctx, gen_ + l * size_t(batch) * max_len * 2 * D, acts_ + a_.qkv + l * M * 3 * D, batch, prompt_len, max_len,
+                                                 c_.d_model);
+            if (rc) return rc;
+        }
+        gen_pos_off_ = cache_floats + step_floats - 8;
+        be_->device_memcpy_h2d(gen_ + gen_pos_off_, &gen_pos_, sizeof(int));
+        (void)Vp;
+        return GPTB200_OK;
+    }
+
+    // One new position for every sequence: the forward pass of one row per sequence, attention against the cache.
+    int generate_step(gptb200_ctx *ctx, const int *tokens, float *logits)
+    {
+        if (!gen_ || gen_pos_ >= gen_max_len_ || gen_pos_ >= c_.max_seq_len) return GPTB200_ERR_INVALID_ARG;
+        const size_t L = c_.layers, D = c_.d_model, F = c_.d_ffn;
+        const int b = gen_batch_;
+        const size_t cache_floats = L * size_t(b) * gen_max_len_ * 2 * D;
+        float *s = gen_ + cache_floats;
+        auto take = [&](size_t n) { float *at = s; s += n; return at; };
+        float *x = take(b * D), *ln = take(b * D), *qkv = take(b * 3 * D), *attn = take(b * D), *proj = take(b * D), *up = take(b * F),
+              *act = take(b * F), *down = take(b * D), *x2 = take(b * D), *mean = take(b), *var = take(b);
+        (void)x2;
+        int *pos_dev = reinterpret_cast<int *>(gen_ + gen_pos_off_);
+        float *w = weights();
+        int rc = gptb200_embedding_decode(ctx, x, w + lay_.wte, w + lay_.wpe, tokens, pos_dev, b, c_.d_model);
+        if (rc) return rc;
+        // same operator sequence as forward() with one row per sequence; the residual stream alternates between x / proj / down
+        float *stream = x, *resid = nullptr;
+        for (size_t l = 0; l < L; ++l) {
+            be_->device_layernorm_residual_fused_forward(ln, mean, var, stream, resid, w + lay_.ln1_w + l * D, w + lay_.ln1_b + l * D, b, 1, c_.d_model);
+            resid = stream;
+            be_->device_linear_activation_fused_forward(qkv, nullptr, ln, w + lay_.qkv_w + l * D * 3 * D, w + lay_.qkv_b + l * 3 * D, false, b, 1, c_.d_model,
+                                                        3 * c_.d_model);
+            rc = gptb200_attention_decode(ctx, attn, gen_ + l * size_t(b) * gen_max_len_ * 2 * D, qkv, pos_dev, b, gen_max_len_, c_.d_model, c_.heads);
+            if (rc) return rc;
+            float *pj = (resid == proj) ? x : proj;   // never overwrite the pending residual
+            be_->device_linear_activation_fused_forward(pj, nullptr, attn, w + lay_.proj_w + l * D * D, w + lay_.proj_b + l * D, false, b, 1, c_.d_model,
+                                                        c_.d_model);
+            be_->device_layernorm_residual_fused_forward(ln, mean, var, pj, resid, w + lay_.ln2_w + l * D, w + lay_.ln2_b + l * D, b, 1, c_.d_model);
+            resid = pj;
+            be_->device_linear_activation_fused_forward(up, act, ln, w + lay_.up_w + l * D * F, w + lay_.up_b + l * F, true, b, 1, c_.d_model, c_.d_ffn);
+            float *dn = (resid == down) ? x : down;
+            be_->device_linear_activation_fused_forward(dn, nullptr, act, w + lay_.down_w + l * F * D, w + lay_.down_b + l * D, false, b, 1, c_.d_ffn,
+                                                        c_.d_model);
+            stream = dn;
+        }
+        be_->device_layernorm_residual_fused_forward(ln, mean, var, stream, resid, w + lay_.lnf_w, w + lay_.lnf_b, b, 1, c_.d_model);
+        be_->device_unembedding_forward(logits, ln, w + lay_.wte, b, 1, c_.d_model, c_.vocab_padded);
+        rc = gptb200_advance_position(ctx, pos_dev);
+        if (rc) return rc;
+        ++gen_pos_;
+        return GPTB200_OK;
+    }
+
+    int generate_position() const { return gen_ ? gen_pos_ : -1; }
+
     void set_defer_embedding(bool on) { defer_embedding_ = on; }
     float *embedding_grad() { return agrads_ ? agrads_ + g_.d_res : nullptr; }
     size_t wte_offset() const { return lay_.wte; }
@@ -298,6 +376,9 @@ private:
     {
         if (acts_) be_->device_free(acts_);
         if (agrads_) be_->device_free(agrads_);
+        if (gen_) be_->device_free(gen_);
+        gen_ = nullptr;
+        gen_capacity_ = 0;
         acts_ = agrads_ = nullptr;
         acts_capacity_ = agrads_capacity_ = 0;
     }
@@ -318,6 +399,9 @@ private:
     size_t acts_capacity_ = 0, agrads_capacity_ = 0;
     int B_ = 0, T_ = 0, step_ = 0;
     bool defer_embedding_ = false;
+    float *gen_ = nullptr;        // KV cache of every layer, then the step's activations, then the device copy of the position
+    size_t gen_capacity_ = 0, gen_pos_off_ = 0;
+    int gen_batch_ = 0, gen_max_len_ = 0, gen_pos_ = 0;
 };
 
 struct ModelHandle {
@@ -465,6 +549,30 @@ int gptb200_model_backward(gptb200_model *m, const int *tokens_dev, const int *l
     m->h.model->backward(tokens_dev, labels_dev, layer_done, user);
     return m->h.backend->status();
 }
+
+int gptb200_model_generate_begin(gptb200_model *m, const int *prompt_dev, int batch, int prompt_len, int max_len)
+{
+    if (!m || !prompt_dev || batch <= 0 || prompt_len <= 0 || max_len < prompt_len || max_len > m->h.model->config().max_seq_len)
+        return GPTB200_ERR_INVALID_ARG;
+    if (m->h.backend->status() != 0) return m->h.backend->status();
+    const int rc = m->h.model->generate_begin(m->h.backend->context(), prompt_dev, batch, prompt_len, max_len);
+    if (m->h.backend->status() != 0) {
+        const int st = m->h.backend->status();
+        if (rc == GPTB200_ERR_CUDA) m->h.backend->clear_status();   // an allocation that could not be had: nothing was changed
+        return st;
+    }
+    return rc;
+}
+
+int gptb200_model_generate_step(gptb200_model *m, const int *tokens_dev, float *logits_dev)
+{
+    if (!m || !tokens_dev || !logits_dev) return GPTB200_ERR_INVALID_ARG;
+    if (m->h.backend->status() != 0) return m->h.backend->status();
+    const int rc = m->h.model->generate_step(m->h.backend->context(), tokens_dev, logits_dev);
+    return rc ? rc : m->h.backend->status();
+}
+
+int gptb200_model_generate_position(gptb200_model *m) { return m ? m->h.model->generate_position() : -1; }
 
 int gptb200_model_defer_embedding_backward(gptb200_model *m, int defer)
 {

@@ -190,6 +190,20 @@ int gptb200_adamw_step(gptb200_ctx *ctx, float *params, const float *g, float *m
                        float beta2, float eps, float weight_decay, int step);
 int gptb200_scale_and_clip_grad(gptb200_ctx *ctx, float *g, size_t count, float max_norm, int accum_steps);
 int gptb200_memory_info(gptb200_ctx *ctx, float *free_mb, float *total_mb);
+/* ---- operators of a KV-cached generation step (no counterpart in the reference: its inference loop recomputes the whole
+ *      prefix for every token, src/infer/infer.cpp:112-148, "TODO: Add KV Cache" at :120).  The cache of one layer is
+ *      [batch][max_len][k (d) | v (d)], the k and v thirds of the reference's packed qkv rows; the position of the new token
+ *      lives in device memory (*pos_dev) so that a captured step can be replayed for every position.
+ *   embedding_decode:  y[b, :] = wte[tokens[b], :] + wpe[*pos_dev, :]
+ *   kv_cache_fill:     cache[b][t] = k | v of qkv[b][t] for t < seq_len (after a forward pass over the prompt)
+ *   attention_decode:  stores the new position's k | v (from qkv_new [batch][3 d]) at *pos_dev, then per head
+ *                      y[b] = softmax_{t <= *pos_dev}(q . k_t / sqrt(d / heads)) . v_t; head size a power of two in 4 .. 128
+ *   advance_position:  *pos_dev += 1 */
+int gptb200_embedding_decode(gptb200_ctx *ctx, float *y, const float *wte, const float *wpe, const int *tokens, const int *pos_dev, int batch, int d);
+int gptb200_kv_cache_fill(gptb200_ctx *ctx, float *cache, const float *qkv, int batch, int seq_len, int max_len, int d);
+int gptb200_attention_decode(gptb200_ctx *ctx, float *y, float *cache, const float *qkv_new, const int *pos_dev, int batch, int max_len, int d,
+                             int heads);
+int gptb200_advance_position(gptb200_ctx *ctx, int *pos_dev);
 /* Gradient scaling, norm clipping and AdamW over one packed buffer of `segments` tensors in two launches: what the reference
  * does with device_scale_and_clip_grad followed by one device_adamw_step per tensor (src/model/gpt.cpp:644-677,
  * cuda/kernels/gradient_clip.cu:35-59, adamw.cu:71-97).  Tensor t covers elements [segment_ends[t-1], segment_ends[t]);
@@ -243,6 +257,17 @@ int gptb200_model_defer_embedding_backward(gptb200_model *m, int defer);
 float *gptb200_model_embedding_grad(gptb200_model *m);
 int gptb200_model_apply_embedding_grad(gptb200_model *m, const float *rows_dev, const int *tokens_dev, int batch, int seq, float scale);
 int gptb200_model_loss(gptb200_model *m, const int *labels_dev, float *loss_out);
+/* KV-cached generation (the reference's loop, src/infer/infer.cpp:112-148, recomputes the prefix for every token):
+ *   generate_begin  one forward pass over the prompt [batch x prompt_len] (device, int32), keys and values of every layer
+ *                   into a cache sized for max_len positions; afterwards gptb200_model_logits holds the prompt's logits
+ *                   ([batch*prompt_len x vocab_size_padded]: row b*prompt_len + prompt_len-1 predicts the first new token);
+ *   generate_step   one new position: tokens_dev [batch] are the tokens AT that position (sampled from the previous logits);
+ *                   logits_dev [batch x vocab_size_padded] receives the logits that predict the next one; every linear layer
+ *                   runs with m = batch rows.  The position advances by one; GPTB200_ERR_INVALID_ARG beyond max_len.
+ *   generate_position  the position the next generate_step will fill (prompt_len after generate_begin). */
+int gptb200_model_generate_begin(gptb200_model *m, const int *prompt_dev, int batch, int prompt_len, int max_len);
+int gptb200_model_generate_step(gptb200_model *m, const int *tokens_dev, float *logits_dev);
+int gptb200_model_generate_position(gptb200_model *m);
 int gptb200_model_clip(gptb200_model *m, float max_norm, int accum_steps);
 int gptb200_model_optimizer_step(gptb200_model *m, float lr, float beta1, float beta2, float weight_decay);
 /* gptb200_model_clip followed by gptb200_model_optimizer_step in two launches over the packed buffers (see

@@ -330,3 +330,53 @@ def test_training_state_round_trip_and_header_checks(lib):
         assert np.array_equal(before, after) and b.step_count == 4
         b.close(); c.close()
     a.close()
+
+
+@pytest.mark.parametrize("batch", [1, 3])
+def test_kv_cached_generation_matches_prefix_recomputation(lib, reference, batch):
+    """Greedy generation with the KV cache (one row per sequence per step) against the reference's way -- a full forward
+    pass over the whole prefix for every token (src/infer/infer.cpp:112-148) -- on this library, and the first steps also
+    against the reference CPU model: same logits (1e-5 of their scale), same tokens."""
+    import torch
+    import gpt_b200
+    cfg, tokens, weights, _ = _tiny()
+    V, Vp, Tmax = cfg["vocab_size"], cfg["vocab_size_padded"], cfg["max_seq_len"]
+    P, NEW = 9, 20
+    rng = np.random.default_rng(batch)
+    prompt = rng.integers(0, V, size=(batch, P)).astype(np.int32)
+    cached = gpt_b200.Model(cfg, 0, None, gpt_b200.MODE_3XTF32, use_grad=False)
+    full = gpt_b200.Model(cfg, 0, None, gpt_b200.MODE_3XTF32, use_grad=False)
+    for m in (cached, full):
+        m.load_weights(weights)
+
+    def logits_view(m, rows):
+        class _Raw:
+            __cuda_array_interface__ = dict(shape=(rows, Vp), typestr="<f4", data=(m.logits_ptr, False), version=3, strides=None)
+        return torch.as_tensor(_Raw(), device="cuda")
+
+    seq = torch.from_numpy(prompt).cuda()
+    cached.generate_begin(seq.contiguous(), batch, P, P + NEW)
+    assert cached.generate_position == P
+    step_logits = torch.empty(batch, Vp, device="cuda")
+    last = logits_view(cached, batch * P).view(batch, P, Vp)[:, P - 1, :].clone()
+    for t in range(P, P + NEW):
+        # the reference's way: the whole prefix again
+        full.set_size(batch, t)
+        full.forward(seq.contiguous())
+        ref_last = logits_view(full, batch * t).view(batch, t, Vp)[:, t - 1, :]
+        scale = float(ref_last.abs().max())
+        assert float((last - ref_last).abs().max()) <= 1e-5 * scale, (t, float((last - ref_last).abs().max()), scale)
+        if t < P + 2:   # and the reference CPU model itself on the same prefix
+            h = seq.cpu().numpy()
+            _, _, cpu_logits = reference.gpt_forward_backward(cfg, weights, h, np.roll(h, -1, axis=1), batch, t, want_logits=True)
+            cpu_last = cpu_logits.reshape(batch, t, Vp)[:, t - 1, :]
+            assert np.abs(last.cpu().numpy() - cpu_last).max() <= 1e-5 * np.abs(cpu_last).max()
+        nxt = ref_last[:, :V].argmax(dim=1).to(torch.int32)
+        assert torch.equal(nxt, last[:, :V].argmax(dim=1).to(torch.int32))
+        seq = torch.cat([seq, nxt[:, None]], dim=1)
+        cached.generate_step(nxt.contiguous(), step_logits)
+        last = step_logits.clone()
+    assert cached.generate_position == P + NEW
+    with pytest.raises(gpt_b200.GptB200Error):
+        cached.generate_step(nxt.contiguous(), step_logits)      # beyond max_len
+    cached.close(); full.close()

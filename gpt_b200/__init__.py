@@ -34,6 +34,7 @@ EXPORTED_SYMBOLS = [
     "gptb200_fill_normal", "gptb200_fill_const", "gptb200_embedding_forward", "gptb200_embedding_backward", "gptb200_embedding_backward_scaled",
     "gptb200_layernorm_forward", "gptb200_layernorm_backward", "gptb200_attention_forward", "gptb200_attention_backward",
     "gptb200_softmax_forward", "gptb200_cross_entropy_softmax_backward", "gptb200_cross_entropy_loss",
+    "gptb200_softmax_cross_entropy_inplace", "gptb200_row_loss_mean", "gptb200_cross_entropy_loss_from_logits",
     "gptb200_adamw_step", "gptb200_scale_and_clip_grad", "gptb200_memory_info", "gptb200_clip_adamw_packed",
     "gptb200_embedding_decode", "gptb200_kv_cache_fill", "gptb200_attention_decode", "gptb200_advance_position",
     "gptb200_loader_create", "gptb200_loader_destroy", "gptb200_loader_num_samples", "gptb200_loader_reset_epoch", "gptb200_loader_next_batch",
@@ -103,6 +104,9 @@ def load_library(path: str | None = None) -> ctypes.CDLL:
         "gptb200_softmax_forward": (i, [vp, fp, fp, i, i, i]),
         "gptb200_cross_entropy_softmax_backward": (i, [vp, fp, fp, fp, i, i, i]),
         "gptb200_cross_entropy_loss": (i, [vp, fp, fp, fp, i, i]),
+        "gptb200_softmax_cross_entropy_inplace": (i, [vp, fp, fp, fp, i, i, i]),
+        "gptb200_row_loss_mean": (i, [vp, fp, fp, i]),
+        "gptb200_cross_entropy_loss_from_logits": (i, [vp, fp, fp, fp, fp, i, i, i]),
         "gptb200_adamw_step": (i, [vp, fp, fp, fp, fp, sz, f32, f32, f32, f32, f32, i]),
         "gptb200_scale_and_clip_grad": (i, [vp, fp, sz, f32, i]),
         "gptb200_memory_info": (i, [vp, ctypes.POINTER(f32), ctypes.POINTER(f32)]),
@@ -325,6 +329,7 @@ def _declare_model(lib: ctypes.CDLL) -> None:
         "gptb200_model_clip": (i, [vp, f32, i]),
         "gptb200_model_optimizer_step": (i, [vp, f32, f32, f32, f32]),
         "gptb200_model_clip_and_optimizer_step": (i, [vp, f32, i, f32, f32, f32, f32]),
+        "gptb200_model_set_fused_cross_entropy": (i, [vp, i]),
         "gptb200_model_generate_begin": (i, [vp, vp, i, i, i]),
         "gptb200_model_generate_step": (i, [vp, vp, vp]),
         "gptb200_model_generate_position": (i, [vp]),
@@ -452,6 +457,11 @@ class Model:
 
     def optimizer_step(self, learning_rate: float, beta1: float, beta2: float, decay: float) -> None:
         self._check(self._lib.gptb200_model_optimizer_step(self._m, learning_rate, beta1, beta2, decay))
+
+    def set_fused_cross_entropy(self, on: bool) -> None:
+        """The logits become their gradient in place at the start of the backward pass (no probability / gradient tensors);
+        takes effect at the next set_size."""
+        self._check(self._lib.gptb200_model_set_fused_cross_entropy(self._m, int(on)))
 
     def generate_begin(self, prompt_tokens, batch_size: int, prompt_len: int, max_len: int) -> None:
         """Forward pass over the prompt [batch x prompt_len] and the keys / values of every layer into a cache for max_len positions."""

@@ -291,6 +291,38 @@ int gptb200_cross_entropy_softmax_backward(gptb200_ctx *ctx, float *grad_x, cons
     return launched(ctx);
 }
 
+int gptb200_softmax_cross_entropy_inplace(gptb200_ctx *ctx, float *logits_inout, float *row_loss, const int *labels, int rows, int vocab,
+                                          int vocab_padded)
+{
+    NEED(ctx, rows >= 0 && vocab >= 0 && vocab_padded >= vocab);
+    if (rows == 0 || vocab_padded == 0) return GPTB200_OK;
+    NEED(ctx, logits_inout && row_loss && labels);
+    if (vocab_padded % 4 == 0 && vocab_padded <= 512 * 4 * 25 && vocab_padded > 1024 * 4 * 4 && aligned16_all({logits_inout}))
+        ops::softmax_ce_inplace_rowreg_kernel<512, 25><<<rows, 512, 0, ctx->stream>>>(logits_inout, row_loss, labels, rows, vocab, vocab_padded);
+    else if (vocab_padded % 4 == 0 && vocab_padded <= 1024 * 4 * 4 && aligned16_all({logits_inout}))
+        ops::softmax_ce_inplace_rowreg_kernel<1024, 4><<<rows, 1024, 0, ctx->stream>>>(logits_inout, row_loss, labels, rows, vocab, vocab_padded);
+    else
+        ops::softmax_ce_inplace_kernel<<<rows, 1024, 0, ctx->stream>>>(logits_inout, row_loss, labels, rows, vocab, vocab_padded);
+    return launched(ctx);
+}
+
+int gptb200_cross_entropy_loss_from_logits(gptb200_ctx *ctx, float *loss, float *row_loss, const float *logits, const int *labels, int rows, int vocab,
+                                           int vocab_padded)
+{
+    NEED(ctx, rows >= 0 && vocab >= 0 && vocab_padded >= vocab && loss);
+    NEED(ctx, rows == 0 || (row_loss && logits && labels));
+    if (rows > 0) ops::ce_row_loss_from_logits_kernel<<<rows, 512, 0, ctx->stream>>>(row_loss, logits, labels, vocab, vocab_padded);
+    ops::row_loss_mean_kernel<<<1, 1024, 0, ctx->stream>>>(loss, row_loss, rows);
+    return launched(ctx, rows > 0 ? 2 : 1);
+}
+
+int gptb200_row_loss_mean(gptb200_ctx *ctx, float *loss, const float *row_loss, int rows)
+{
+    NEED(ctx, rows >= 0 && loss && (rows == 0 || row_loss));
+    ops::row_loss_mean_kernel<<<1, 1024, 0, ctx->stream>>>(loss, row_loss, rows);
+    return launched(ctx);
+}
+
 int gptb200_cross_entropy_loss(gptb200_ctx *ctx, float *loss, const float *probs, const int *labels, int rows, int vocab_padded)
 {
     NEED(ctx, rows >= 0 && vocab_padded >= 0 && loss);

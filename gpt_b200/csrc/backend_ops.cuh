@@ -580,6 +580,111 @@ __global__ void cross_entropy_softmax_backward_vec_kernel(float *__restrict__ gr
     for (int i = 4 * full + threadIdx.x; i < v; i += blockDim.x) grad_x[r * vp + i] = (probs[r * vp + i] - (i == label ? 1.0f : 0.0f)) / inv;
 }
 
+// Softmax, cross-entropy backward and the row's loss term in ONE pass over the logits, in place: what the reference does with
+// device_softmax_forward (logits -> probabilities), device_cross_entropy_softmax_fused_backward (probabilities -> gradient)
+// and device_cross_entropy_loss (cpu_backend.cpp:439-509), without the probability tensor and without a second and third
+// trip through HBM.  A thread keeps its NV float4 of the row in registers: the logits are read once and overwritten by
+//   x[r, i] = (softmax(x[r, :v])[i] - (i == label)) / rows   for i < v,      x[r, i] = 0   for v <= i < vp
+// and row_loss[r] = -log(p[label] + 1e-8), the term that cross_entropy_loss averages.
+template <int THREADS, int NV>
+__global__ void __launch_bounds__(THREADS) softmax_ce_inplace_rowreg_kernel(float *__restrict__ x, float *__restrict__ row_loss,
+                                                                            const int *__restrict__ labels, int rows, int v, int vp)
+{
+    __shared__ float red[32];
+    const size_t r = blockIdx.x;
+    float4 *xr = reinterpret_cast<float4 *>(x + r * vp);
+    const int nvec = vp >> 2;
+    const int label = labels[r];
+    float4 e[NV];
+    float m = -FLT_MAX;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int c = threadIdx.x + THREADS * k;
+        e[k] = make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
+        if (c < nvec) {
+            const float4 t = xr[c];
+            const int i = 4 * c;
+            e[k].x = i < v ? t.x : -FLT_MAX;
+            e[k].y = i + 1 < v ? t.y : -FLT_MAX;
+            e[k].z = i + 2 < v ? t.z : -FLT_MAX;
+            e[k].w = i + 3 < v ? t.w : -FLT_MAX;
+        }
+        m = fmaxf(m, fmaxf(fmaxf(e[k].x, e[k].y), fmaxf(e[k].z, e[k].w)));
+    }
+    m = block_max(m, red);
+    float s = 0.0f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        e[k].x = e[k].x == -FLT_MAX ? 0.0f : expf(e[k].x - m);
+        e[k].y = e[k].y == -FLT_MAX ? 0.0f : expf(e[k].y - m);
+        e[k].z = e[k].z == -FLT_MAX ? 0.0f : expf(e[k].z - m);
+        e[k].w = e[k].w == -FLT_MAX ? 0.0f : expf(e[k].w - m);
+        s += (e[k].x + e[k].y) + (e[k].z + e[k].w);
+    }
+    s = block_sum(s, red);
+    const float inv = static_cast<float>(rows);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int c = threadIdx.x + THREADS * k;
+        if (c >= nvec) continue;
+        const int i = 4 * c;
+        float p[4] = {e[k].x / s, e[k].y / s, e[k].z / s, e[k].w / s};
+        float g[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (i + j == label) row_loss[r] = -logf(p[j] + 1e-8f);
+            g[j] = i + j < v ? (p[j] - (i + j == label ? 1.0f : 0.0f)) / inv : 0.0f;
+        }
+        xr[c] = make_float4(g[0], g[1], g[2], g[3]);
+    }
+}
+
+// The same for any row length and alignment: three passes of one block over its row (maximum, sum, write).
+__global__ void softmax_ce_inplace_kernel(float *__restrict__ x, float *__restrict__ row_loss, const int *__restrict__ labels, int rows, int v, int vp)
+{
+    __shared__ float red[32];
+    const size_t r = blockIdx.x;
+    float *xr = x + r * vp;
+    const int label = labels[r];
+    float m = -FLT_MAX;
+    for (int i = threadIdx.x; i < v; i += blockDim.x) m = fmaxf(m, xr[i]);
+    m = block_max(m, red);
+    float s = 0.0f;
+    for (int i = threadIdx.x; i < v; i += blockDim.x) s += expf(xr[i] - m);
+    s = block_sum(s, red);
+    const float inv = static_cast<float>(rows);
+    for (int i = threadIdx.x; i < vp; i += blockDim.x) {
+        const float p = i < v ? expf(xr[i] - m) / s : 0.0f;
+        if (i == label) row_loss[r] = -logf(p + 1e-8f);
+        xr[i] = i < v ? (p - (i == label ? 1.0f : 0.0f)) / inv : 0.0f;
+    }
+}
+
+// loss = mean of the row terms.  Single block, fixed order per thread.
+__global__ void row_loss_mean_kernel(float *__restrict__ loss, const float *__restrict__ row_loss, int rows)
+{
+    __shared__ float red[32];
+    float s = 0.0f;
+    for (int r = threadIdx.x; r < rows; r += blockDim.x) s += row_loss[r];
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) *loss = s / static_cast<float>(rows);
+}
+
+// The loss straight from logits (no probabilities stored): per row -log(softmax[label] + 1e-8).  One block per row.
+__global__ void ce_row_loss_from_logits_kernel(float *__restrict__ row_loss, const float *__restrict__ x, const int *__restrict__ labels, int v, int vp)
+{
+    __shared__ float red[32];
+    const size_t r = blockIdx.x;
+    const float *xr = x + r * vp;
+    float m = -FLT_MAX;
+    for (int i = threadIdx.x; i < v; i += blockDim.x) m = fmaxf(m, xr[i]);
+    m = block_max(m, red);
+    float s = 0.0f;
+    for (int i = threadIdx.x; i < v; i += blockDim.x) s += expf(xr[i] - m);
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) row_loss[r] = -logf(expf(xr[labels[r]] - m) / s + 1e-8f);
+}
+
 // loss = -(1/rows) sum_r log(p[r, label[r]] + 1e-8)   (cpu_backend.cpp:493-509).  Single block, fixed order per thread.
 __global__ void cross_entropy_loss_kernel(float *__restrict__ loss, const float *__restrict__ probs, const int *__restrict__ labels, int rows,
                                           int vp)

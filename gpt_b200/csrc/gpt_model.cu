@@ -120,14 +120,17 @@ public:
         a.ln2 = take(L * M * D); a.ln2_mean = take(L * M); a.ln2_var = take(L * M);
         a.up = take(L * M * F); a.act = take(L * M * F); a.down = take(L * M * D);
         a.lnf = take(M * D); a.lnf_mean = take(M); a.lnf_var = take(M);
-        a.logits = take(M * Vp); a.probs = take(M * Vp);
+        // fused cross-entropy: the logits become their own gradient in place; only the row terms of the loss are kept
+        const bool fused = fused_ce_ && use_grad_ && ctx_ != nullptr;
+        a.logits = take(M * Vp); a.probs = fused ? a.logits : take(M * Vp);
+        a.row_loss = take(fused ? M : 0);
         a.total = o;
         GradLayout g{};
         if (use_grad_) {
             // activation gradients are consumed right after they are produced: one set of buffers serves all layers
             o = 0;
             g.d_ln = take(M * D); g.d_res = take(M * D); g.d_x = take(M * D); g.d_qkv = take(M * 3 * D); g.d_helper = take(M * H);
-            g.d_f1 = take(M * F); g.d_f2 = take(M * F); g.d_logits = take(M * Vp);
+            g.d_f1 = take(M * F); g.d_f2 = take(M * F); g.d_logits = take(fused ? 0 : M * Vp);
             g.total = o;
         }
         // the new buffers first: if one cannot be had, nothing has changed
@@ -152,6 +155,8 @@ public:
         }
         a_ = a;
         g_ = g;
+        fused_ce_active_ = fused;
+        row_loss_valid_ = false;
         B_ = batch;
         T_ = seq;
         if (use_grad_) be_->device_memset(agrads_, 0, g_.total * sizeof(float));  // the padding columns of d_logits must be zero
@@ -194,7 +199,8 @@ public:
         be_->device_layernorm_residual_fused_forward(A + a_.lnf, A + a_.lnf_mean, A + a_.lnf_var, stream, resid, w + lay_.lnf_w, w + lay_.lnf_b, B_, T_,
                                                      c_.d_model);
         be_->device_unembedding_forward(A + a_.logits, A + a_.lnf, w + lay_.wte, B_, T_, c_.d_model, c_.vocab_padded);
-        if (use_grad_) be_->device_softmax_forward(A + a_.probs, A + a_.logits, B_, T_, c_.vocab, c_.vocab_padded);
+        if (use_grad_ && !fused_ce_active_) be_->device_softmax_forward(A + a_.probs, A + a_.logits, B_, T_, c_.vocab, c_.vocab_padded);
+        row_loss_valid_ = false;
     }
 
     // layer_done(l, user): gradients of layer l's twelve parameter tensors are complete (enqueued);
@@ -204,9 +210,17 @@ public:
         const size_t M = size_t(B_) * T_, D = c_.d_model, F = c_.d_ffn, H = c_.heads;
         float *w = weights(), *gw = grads(), *A = acts_, *G = agrads_;
         float *d_ln = G + g_.d_ln, *d_res = G + g_.d_res, *d_x = G + g_.d_x;
-        // the padding columns of d_logits are never written by the cross-entropy backward: they stay zero from set_size
-        be_->device_cross_entropy_softmax_fused_backward(G + g_.d_logits, A + a_.probs, labels, B_, T_, c_.vocab, c_.vocab_padded);
-        be_->device_unembedding_backward(d_x, gw + lay_.wte, G + g_.d_logits, A + a_.lnf, w + lay_.wte, B_, T_, c_.d_model, c_.vocab_padded);
+        float *d_logits = G + g_.d_logits;
+        if (fused_ce_active_) {
+            // softmax, its gradient and the loss terms in one pass, in place: the logits buffer now holds the gradient
+            d_logits = A + a_.logits;
+            if (gptb200_softmax_cross_entropy_inplace(ctx_, d_logits, A + a_.row_loss, labels, B_ * T_, c_.vocab, c_.vocab_padded) != 0) return;
+            row_loss_valid_ = true;
+        } else {
+            // the padding columns of d_logits are never written by the cross-entropy backward: they stay zero from set_size
+            be_->device_cross_entropy_softmax_fused_backward(d_logits, A + a_.probs, labels, B_, T_, c_.vocab, c_.vocab_padded);
+        }
+        be_->device_unembedding_backward(d_x, gw + lay_.wte, d_logits, A + a_.lnf, w + lay_.wte, B_, T_, c_.d_model, c_.vocab_padded);
         be_->device_layernorm_residual_fused_backward(d_res, gw + lay_.lnf_w, gw + lay_.lnf_b, d_x, nullptr, A + a_.down + (c_.layers - 1) * M * D,
                                                       A + a_.lnf_mean, A + a_.lnf_var, w + lay_.lnf_w, B_, T_, c_.d_model);
         if (layer_done) layer_done(c_.layers, user);
@@ -315,13 +329,23 @@ public:
     int generate_position() const { return gen_ ? gen_pos_ : -1; }
 
     void set_defer_embedding(bool on) { defer_embedding_ = on; }
+    void set_context(gptb200_ctx *ctx) { ctx_ = ctx; }
+    void set_fused_cross_entropy(bool on) { fused_ce_ = on; }
     float *embedding_grad() { return agrads_ ? agrads_ + g_.d_res : nullptr; }
     size_t wte_offset() const { return lay_.wte; }
     size_t wpe_offset() const { return lay_.wpe; }
 
     float loss(const int *labels)
     {
-        be_->device_cross_entropy_loss(loss_dev_, acts_ + a_.probs, labels, B_, T_, c_.vocab_padded);
+        if (fused_ce_active_) {
+            // after a backward pass the row terms are there; before it they are computed from the (still untouched) logits
+            if (row_loss_valid_)
+                gptb200_row_loss_mean(ctx_, loss_dev_, acts_ + a_.row_loss, B_ * T_);
+            else
+                gptb200_cross_entropy_loss_from_logits(ctx_, loss_dev_, acts_ + a_.row_loss, acts_ + a_.logits, labels, B_ * T_, c_.vocab, c_.vocab_padded);
+        } else {
+            be_->device_cross_entropy_loss(loss_dev_, acts_ + a_.probs, labels, B_, T_, c_.vocab_padded);
+        }
         float v = 0.0f;
         be_->device_memcpy_d2h(&v, loss_dev_, sizeof(float));
         return v;
@@ -384,7 +408,7 @@ private:
     }
 
     struct ActLayout {
-        size_t x_emb, ln1, ln1_mean, ln1_var, qkv, lse, attn, proj, ln2, ln2_mean, ln2_var, up, act, down, lnf, lnf_mean, lnf_var, logits, probs, total;
+        size_t x_emb, ln1, ln1_mean, ln1_var, qkv, lse, attn, proj, ln2, ln2_mean, ln2_var, up, act, down, lnf, lnf_mean, lnf_var, logits, probs, row_loss, total;
     } a_{};
     struct GradLayout {
         size_t d_ln, d_res, d_x, d_qkv, d_helper, d_f1, d_f2, d_logits, total;
@@ -399,6 +423,8 @@ private:
     size_t acts_capacity_ = 0, agrads_capacity_ = 0;
     int B_ = 0, T_ = 0, step_ = 0;
     bool defer_embedding_ = false;
+    gptb200_ctx *ctx_ = nullptr;   // the backend's context, for the operators that are not part of IGPTBackend
+    bool fused_ce_ = false, fused_ce_active_ = false, row_loss_valid_ = false;
     float *gen_ = nullptr;        // KV cache of every layer, then the step's activations, then the device copy of the position
     size_t gen_capacity_ = 0, gen_pos_off_ = 0;
     int gen_batch_ = 0, gen_max_len_ = 0, gen_pos_ = 0;
@@ -431,6 +457,7 @@ int gptb200_model_create(gptb200_model **out, const int *cfg, int device, void *
     auto *m = new gptb200_model();
     m->h.backend = new B200Backend(seed, device, stream, mode, /*abort_on_error=*/false);
     m->h.model = m->h.backend->status() == 0 ? new GptModel(m->h.backend, c, use_grad != 0) : nullptr;
+    if (m->h.model) m->h.model->set_context(m->h.backend->context());
     const int rc = m->h.backend->status();   // no device, or the parameter buffers could not be allocated
     if (rc != GPTB200_OK) {
         delete m->h.model;
@@ -548,6 +575,13 @@ int gptb200_model_backward(gptb200_model *m, const int *tokens_dev, const int *l
     if (!m || !tokens_dev || !labels_dev || m->h.model->batch() == 0) return GPTB200_ERR_INVALID_ARG;
     m->h.model->backward(tokens_dev, labels_dev, layer_done, user);
     return m->h.backend->status();
+}
+
+int gptb200_model_set_fused_cross_entropy(gptb200_model *m, int on)
+{
+    if (!m) return GPTB200_ERR_INVALID_ARG;
+    m->h.model->set_fused_cross_entropy(on != 0);
+    return GPTB200_OK;
 }
 
 int gptb200_model_generate_begin(gptb200_model *m, const int *prompt_dev, int batch, int prompt_len, int max_len)

@@ -186,6 +186,17 @@ int gptb200_softmax_forward(gptb200_ctx *ctx, float *y, const float *x, int rows
 int gptb200_cross_entropy_softmax_backward(gptb200_ctx *ctx, float *grad_x, const float *probs, const int *labels, int rows, int vocab,
                                            int vocab_padded);
 int gptb200_cross_entropy_loss(gptb200_ctx *ctx, float *loss, const float *probs, const int *labels, int rows, int vocab_padded);
+/* Softmax, cross-entropy backward and the loss terms in one pass over the logits, in place: the reference's
+ * device_softmax_forward + device_cross_entropy_softmax_fused_backward + device_cross_entropy_loss
+ * (cuda/kernels/softmax.cu:23-110, cross_entropy.cu:7-102, cpu/cpu_backend.cpp:439-509) without the probability tensor:
+ *   logits_inout[r, i] becomes (softmax(logits[r, :vocab])[i] - (i == labels[r])) / rows for i < vocab and 0 in the padding
+ *   columns; row_loss[r] = -log(softmax[labels[r]] + 1e-8).  gptb200_row_loss_mean averages the row terms into *loss (device
+ *   memory); gptb200_cross_entropy_loss_from_logits computes row terms and loss from untouched logits. */
+int gptb200_softmax_cross_entropy_inplace(gptb200_ctx *ctx, float *logits_inout, float *row_loss, const int *labels, int rows, int vocab,
+                                          int vocab_padded);
+int gptb200_row_loss_mean(gptb200_ctx *ctx, float *loss, const float *row_loss, int rows);
+int gptb200_cross_entropy_loss_from_logits(gptb200_ctx *ctx, float *loss, float *row_loss, const float *logits, const int *labels, int rows, int vocab,
+                                           int vocab_padded);
 int gptb200_adamw_step(gptb200_ctx *ctx, float *params, const float *g, float *m, float *v, size_t count, float lr, float beta1,
                        float beta2, float eps, float weight_decay, int step);
 int gptb200_scale_and_clip_grad(gptb200_ctx *ctx, float *g, size_t count, float max_norm, int accum_steps);
@@ -256,6 +267,11 @@ int gptb200_model_backward(gptb200_model *m, const int *tokens_dev, const int *l
 int gptb200_model_defer_embedding_backward(gptb200_model *m, int defer);
 float *gptb200_model_embedding_grad(gptb200_model *m);
 int gptb200_model_apply_embedding_grad(gptb200_model *m, const float *rows_dev, const int *tokens_dev, int batch, int seq, float scale);
+/* on != 0: the un-embedding's logits are turned into their gradient in place at the start of the backward pass
+ * (gptb200_softmax_cross_entropy_inplace): no probability tensor and no separate gradient tensor (2 x batch*seq x
+ * vocab_size_padded floats less), two trips through HBM less per step.  gptb200_model_logits then holds logits only between
+ * forward and backward.  Takes effect at the next gptb200_model_set_size. */
+int gptb200_model_set_fused_cross_entropy(gptb200_model *m, int on);
 int gptb200_model_loss(gptb200_model *m, const int *labels_dev, float *loss_out);
 /* KV-cached generation (the reference's loop, src/infer/infer.cpp:112-148, recomputes the prefix for every token):
  *   generate_begin  one forward pass over the prompt [batch x prompt_len] (device, int32), keys and values of every layer

@@ -158,3 +158,45 @@ def test_softmax_and_cross_entropy(env, reference, rows, v, vp):
     assert bool((p[:, v:] == 0).all())                  # padding columns are zero
     close("grad_logits", g, g_ref, max(1e-5, 2 * ref_off))
     assert abs(float(loss.item()) - float(loss_ref[0])) <= 1e-5 * abs(float(loss_ref[0]))
+
+
+@pytest.mark.parametrize("rows,v,vp", [(64, 507, 512), (8, 50257, 50304), (5, 130, 131), (16, 4097, 4100), (1, 3, 4)])
+def test_fused_softmax_cross_entropy_in_place(env, reference, rows, v, vp):
+    """gptb200_softmax_cross_entropy_inplace against the reference's three operators in sequence (softmax forward,
+    cross-entropy backward, loss: cpu_backend.cpp:439-509) on the same logits: same gradient (zero padding columns), same
+    loss; and the loss computed straight from untouched logits."""
+    torch, be, lib, ref = env
+    rng = np.random.default_rng(rows + v)
+    logits = (3.0 * rng.standard_normal((rows, vp))).astype(np.float32)
+    logits[:, v:] = 7.0                       # padding columns hold something: they must come out as zero
+    labels = rng.integers(0, v, size=rows).astype(np.int32)
+    probs = reference.softmax_forward(logits, v)
+    g_ref = reference.cross_entropy_softmax_backward(probs, labels, v)
+    loss_ref = np.zeros(1, np.float32)
+    ref.ref_cross_entropy_loss.argtypes = [_f, _f, _i, ctypes.c_int, ctypes.c_int]
+    ref.ref_cross_entropy_loss(loss_ref, probs, labels, rows, vp)
+    x, lab = dev(torch, logits), dev(torch, labels)
+    row_loss, loss = torch.empty(rows, device="cuda"), torch.zeros(1, device="cuda")
+    assert lib.gptb200_cross_entropy_loss_from_logits(be.handle, loss.data_ptr(), row_loss.data_ptr(), x.data_ptr(), lab.data_ptr(), rows, v, vp) == 0
+    be.synchronize()
+    assert abs(float(loss) - float(loss_ref[0])) <= 1e-5 * abs(float(loss_ref[0]))
+    assert np.array_equal(x.cpu().numpy(), logits)                                      # untouched
+    row_loss.zero_(); loss.zero_()
+    assert lib.gptb200_softmax_cross_entropy_inplace(be.handle, x.data_ptr(), row_loss.data_ptr(), lab.data_ptr(), rows, v, vp) == 0
+    assert lib.gptb200_row_loss_mean(be.handle, loss.data_ptr(), row_loss.data_ptr(), rows) == 0
+    be.synchronize()
+    # exact (float64) result: the reference adds the v exponentials one after the other in fp32, which at v = 50257 is itself
+    # about 1e-5 from it; a miss against the reference passes only if the GPU is within 1e-5 of the exact result AND at least as
+    # close to it as the reference is
+    z = logits[:, :v].astype(np.float64)
+    p = np.exp(z - z.max(1, keepdims=True))
+    p /= p.sum(1, keepdims=True)
+    p[np.arange(rows), labels] -= 1.0
+    exact = np.zeros((rows, vp))
+    exact[:, :v] = p / rows
+    got = x.cpu().numpy().astype(np.float64)
+    scale = np.abs(exact).max()
+    e_ref, e_gpu, e_oracle = np.abs(got - g_ref).max() / scale, np.abs(got - exact).max() / scale, np.abs(g_ref - exact).max() / scale
+    assert e_ref <= 1e-5 or (e_gpu <= 1e-5 and e_gpu <= e_oracle), (e_ref, e_gpu, e_oracle)
+    assert bool((x[:, v:] == 0).all())
+    assert abs(float(loss) - float(loss_ref[0])) <= 1e-5 * abs(float(loss_ref[0]))

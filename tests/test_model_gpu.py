@@ -380,3 +380,40 @@ def test_kv_cached_generation_matches_prefix_recomputation(lib, reference, batch
     with pytest.raises(gpt_b200.GptB200Error):
         cached.generate_step(nxt.contiguous(), step_logits)      # beyond max_len
     cached.close(); full.close()
+
+
+def test_fused_cross_entropy_gives_the_same_step_with_less_memory(lib, reference):
+    """The model driver with the logits turned into their gradient in place (no probability tensor, no separate gradient
+    tensor) against the reference CPU model: same loss (whether asked before or after the backward pass), every gradient
+    tensor within 1e-5; and against the unfused driver."""
+    import torch
+    import gpt_b200
+    cfg, tokens, weights, golden = _tiny()
+    T = cfg["max_seq_len"]
+    d_in = torch.from_numpy(tokens[:T].copy()).cuda()
+    d_lbl = torch.from_numpy(tokens[1:T + 1].copy()).cuda()
+    cpu, cpu_loss, _ = reference.gpt_forward_backward(cfg, weights, tokens[:T], tokens[1:T + 1], 1, T)
+    out = {}
+    for fused in (False, True):
+        torch.cuda.synchronize(); torch.cuda.empty_cache()
+        free0 = torch.cuda.mem_get_info()[0]
+        m = gpt_b200.Model(cfg, 0, None, gpt_b200.MODE_3XTF32)
+        m.set_fused_cross_entropy(fused)
+        m.load_weights(weights)
+        m.set_size(1, T)
+        used = free0 - torch.cuda.mem_get_info()[0]
+        m.zero_grad(); m.forward(d_in)
+        loss_before = m.loss(d_lbl)
+        m.backward(d_in, d_lbl)
+        loss_after = m.loss(d_lbl)
+        g = np.empty(m.num_params, np.float32)
+        m.read_grads(g)
+        out[fused] = (g, loss_before, loss_after, used)
+        m.close()
+    g, lb, la, used_fused = out[True]
+    assert abs(lb - cpu_loss) < 1e-5 and abs(la - cpu_loss) < 1e-5
+    a, c = split_weights(cfg, g), split_weights(cfg, cpu)
+    for name in a:
+        assert np.abs(a[name] - c[name]).max() <= 1e-5, name                       # the reference's own absolute check
+    assert np.abs(g - out[False][0]).max() <= 1e-6
+    assert used_fused <= out[False][3]

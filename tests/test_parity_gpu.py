@@ -441,6 +441,51 @@ def test_full_size_lm_head_against_oracle_samples(be, torch, oracle):
     assert bool((gw[v:] == 0).all())
 
 
+def test_full_size_lm_head_with_in_place_cross_entropy(torch, built_library, oracle, reference):
+    """BASELINE config 2 end to end in the fused form: logits = x . wte^T on the GPU, softmax + cross-entropy backward in place
+    (gptb200_softmax_cross_entropy_inplace), then grad_x and grad_wte from that buffer -- at (M, Vp) = (8192, 50304).
+    Loss, upstream gradient (sampled rows, against the reference's softmax and cross-entropy operators applied to the
+    oracle's logits), grad_x (sampled rows) and grad_wte (sampled vocabulary rows) against the CPU oracle."""
+    import ctypes
+    import gpt_b200
+    t = torch
+    g = t.Generator(device="cuda").manual_seed(3)
+    m, d, vp, v = 8192, 768, 50304, 50257
+    x = t.randn(m, d, device="cuda", generator=g)
+    wte = t.randn(vp, d, device="cuda", generator=g) * 0.02
+    wte[v:] = 0.0
+    labels = t.randint(0, v, (m,), device="cuda", generator=g, dtype=t.int32)
+    be = gpt_b200.Backend(0, None, 0)
+    buf = t.empty(m, vp, device="cuda")
+    be.device_unembedding_forward(buf, x, wte, 1, m, d, vp)
+    row_loss, loss = t.empty(m, device="cuda"), t.zeros(1, device="cuda")
+    assert be.lib.gptb200_softmax_cross_entropy_inplace(be.handle, buf.data_ptr(), row_loss.data_ptr(), labels.data_ptr(), m, v, vp) == 0
+    assert be.lib.gptb200_row_loss_mean(be.handle, loss.data_ptr(), row_loss.data_ptr(), m) == 0
+    gx, gw = t.empty(m, d, device="cuda"), t.zeros(vp, d, device="cuda")
+    be.device_unembedding_backward(gx, gw, buf, x, wte, 1, m, d, vp)
+    be.synchronize()
+    hx, hwte, hlab = x.cpu().numpy(), wte.cpu().numpy(), labels.cpu().numpy()
+    rows = np.arange(0, m, 257)
+    # the reference's operators on the oracle's logits of the sampled rows; its gradient divides by the row count it is given
+    ref_logits = oracle.unembed_forward(hx[rows], hwte)
+    probs = reference.softmax_forward(ref_logits, v)
+    gy_rows = reference.cross_entropy_softmax_backward(probs, hlab[rows], v) * (len(rows) / m)
+    check("upstream gradient rows", buf[rows].cpu().numpy(), gy_rows, 0)
+    ref_row_loss = -np.log(probs[np.arange(len(rows)), hlab[rows]].astype(np.float64) + 1e-8)
+    assert np.abs(row_loss[rows].cpu().numpy() - ref_row_loss).max() <= 1e-5 * np.abs(ref_row_loss).max()
+    assert abs(float(loss) - float(row_loss.double().mean())) <= 1e-5 * float(loss)
+    assert abs(float(loss) - np.log(v)) < 0.5                    # random logits of small scale: loss near ln(V)
+    rgx, _ = oracle.unembed_backward(gy_rows, hx[rows], hwte)
+    exact = gy_rows.astype(np.float64) @ hwte.astype(np.float64)
+    check("grad_x rows", gx[rows].cpu().numpy(), rgx, 0, exact=exact)
+    vrows = np.arange(0, vp, 499)
+    hgy_cols = buf[:, t.from_numpy(vrows).cuda()].cpu().numpy()   # the GPU's gradient (checked above) at the sampled vocabulary rows
+    _, rgw = oracle.unembed_backward(hgy_cols, hx, hwte[vrows])
+    check("grad_wte rows", gw[t.from_numpy(vrows).cuda()].cpu().numpy(), rgw, 0)
+    assert bool((gw[v:] == 0).all()) and bool((buf[:, v:] == 0).all())
+    be.close()
+
+
 @pytest.mark.parametrize("m,k,n,w_kn", [(1, 768, 3072, True), (2, 768, 768, True), (8, 3072, 768, True), (16, 768, 2304, True),
                                         (1, 768, 50304, False), (8, 768, 1024, False), (5, 40, 132, False), (2, 3072, 767 * 4, False), (3, 100, 132, False),
                                         (40, 768, 2304, True), (64, 3072, 768, True), (33, 768, 1024, False),

@@ -72,6 +72,29 @@ int make_tmap(gptb200_ctx *ctx, CUtensorMap *map, const float *base, long long r
     return GPTB200_OK;
 }
 
+// Tensor map of an operand's expanded bf16 correction matrix (split_operand_kernel), described in 4-byte words:
+//   K-major: [rows][k8 words], box 32 words x 128 rows (like the raw operand);  MN-major: [2 k8 rows][cols / 2 words], box 32 words x 64 rows.
+int make_pre_tmap(gptb200_ctx *ctx, CUtensorMap *map, const void *base, long long rows, long long words, int box_rows)
+{
+    const TmapKey key{reinterpret_cast<uintptr_t>(base), words, rows, 0, 32, box_rows, 3};
+    const auto hit = ctx->tmaps.find(key);
+    if (hit != ctx->tmaps.end()) {
+        *map = hit->second;
+        return GPTB200_OK;
+    }
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(words), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(words) * 4};
+    cuuint32_t box[2] = {32, static_cast<cuuint32_t>(box_rows)};
+    cuuint32_t estr[2] = {1, 1};
+    const CUresult r = ctx->encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    ctx->tmap_encodes++;
+    if (r != CUDA_SUCCESS) return fail(ctx, GPTB200_ERR_CUDA, "cuTensorMapEncodeTiled (correction tiles) failed (%d) rows=%lld words=%lld", int(r), rows, words);
+    if (ctx->tmaps.size() >= kTmapCacheMax) ctx->tmaps.clear();
+    ctx->tmaps.emplace(key, *map);
+    return GPTB200_OK;
+}
+
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 struct GemmCall {
@@ -115,7 +138,7 @@ cudaError_t launch_majors(gptb200_ctx *ctx, bool a_mn, bool b_mn, const CUtensor
 
 template <bool A_MN, bool B_MN, bool X3, bool DB = false>
 cudaError_t launch_pair_instance(gptb200_ctx *ctx, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &to, const CUtensorMap &tact,
-                                 const GemmParams &p, int grid)
+                                 const CUtensorMap &tpre, const GemmParams &p, int grid)
 {
     using C = PairCfg<X3>;
     auto kernel = gemm_tcgen05_pair_kernel<A_MN, B_MN, X3, DB>;
@@ -125,19 +148,19 @@ cudaError_t launch_pair_instance(gptb200_ctx *ctx, const CUtensorMap &ta, const 
         if (e != cudaSuccess) return e;
         ctx->configured.insert(key);
     }
-    kernel<<<grid, C::kThreads, C::kSmemBytes, ctx->stream>>>(ta, tb, to, tact, p);  // cluster shape (2,1,1) is a kernel attribute
+    kernel<<<grid, C::kThreads, C::kSmemBytes, ctx->stream>>>(ta, tb, to, tact, tpre, p);  // cluster shape (2,1,1) is a kernel attribute
     return cudaGetLastError();
 }
 
 template <bool X3>
 cudaError_t launch_pair(gptb200_ctx *ctx, bool a_mn, bool b_mn, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &to,
-                        const CUtensorMap &tact, const GemmParams &p, int grid)
+                        const CUtensorMap &tact, const CUtensorMap &tpre, const GemmParams &p, int grid)
 {
-    if (!a_mn && b_mn) return launch_pair_instance<false, true, X3>(ctx, ta, tb, to, tact, p, grid);
-    if (!a_mn && !b_mn) return launch_pair_instance<false, false, X3>(ctx, ta, tb, to, tact, p, grid);
+    if (!a_mn && b_mn) return launch_pair_instance<false, true, X3>(ctx, ta, tb, to, tact, tpre, p, grid);
+    if (!a_mn && !b_mn) return launch_pair_instance<false, false, X3>(ctx, ta, tb, to, tact, tpre, p, grid);
     if (a_mn && b_mn) {
-        if (p.dbias) return launch_pair_instance<true, true, X3, true>(ctx, ta, tb, to, tact, p, grid);
-        return launch_pair_instance<true, true, X3>(ctx, ta, tb, to, tact, p, grid);
+        if (p.dbias) return launch_pair_instance<true, true, X3, true>(ctx, ta, tb, to, tact, tpre, p, grid);
+        return launch_pair_instance<true, true, X3>(ctx, ta, tb, to, tact, tpre, p, grid);
     }
     return cudaErrorInvalidValue;
 }
@@ -401,6 +424,7 @@ int run_gemm(gptb200_ctx *ctx, const GemmCall &c, bool *dbias_fused = nullptr)
     const int splits = pl.splits;
     const size_t bytes_per_split = size_t(c.M) * size_t(c.N) * sizeof(float);
     GemmParams p{};
+    char *pre_buf = nullptr;   // expanded correction matrix of the operand that is split before the launch (3xTF32, CTA pairs)
     p.M = c.M;
     p.N = c.N;
     p.K = c.K;
@@ -437,6 +461,31 @@ int run_gemm(gptb200_ctx *ctx, const GemmCall &c, bool *dbias_fused = nullptr)
             p.dbias_part = ctx->ws + (pl.workspace_bytes + cut_dbias_bytes) / sizeof(float);
             p.dbias_tickets = ctx->d_pair_flags + size_t(ctx->num_sms) * 8 + 2 + kSkinnyMaxTickets;
             if (dbias_fused) *dbias_fused = true;
+        }
+        // 3xTF32: split one operand into its bf16 correction tiles before the launch when many tiles re-read it (a weight matrix
+        // is re-read by every row tile, an activation by every column tile): the operand with the larger re-use, provided it is
+        // re-read at least three times; its expanded matrix (4 bytes per element) goes behind the other scratch regions.
+        const long long tiles_m2 = (pl.tiles_m + 1) / 2;
+        if (x3 && ctx->presplit) {
+            const long long k8 = (static_cast<long long>(c.K) + 7) & ~7LL;
+            const bool a_ok = !c.a_mn || c.M % 8 == 0, b_ok = !c.b_mn || c.N % 8 == 0;
+            const long long reuse_a = a_ok ? pl.tiles_n : 0, reuse_b = b_ok ? tiles_m2 : 0;
+            int pre = 0;
+            if (std::max(reuse_a, reuse_b) >= 3) pre = reuse_b >= reuse_a ? 2 : 1;
+            if (ctx->presplit == 2 && a_ok) pre = 1;   // forced choices, for tests
+            if (ctx->presplit == 3 && b_ok) pre = 2;
+            if (pre) {
+                const long long rows = pre == 1 ? c.M : c.N;
+                const size_t pre_bytes = size_t(rows) * size_t(k8) * 4;
+                const size_t before = (pl.workspace_bytes + cut_dbias_bytes + part_bytes + 255) & ~size_t(255);
+                if (before + pre_bytes <= ctx->ws_limit) {
+                    const int rc = ensure_workspace(ctx, before + pre_bytes);
+                    if (rc != GPTB200_OK) return rc;
+                    pre_buf = reinterpret_cast<char *>(ctx->ws) + before;
+                    p.pre_operand = pre;
+                    if (fuse_dbias) p.dbias_part = ctx->ws + (pl.workspace_bytes + cut_dbias_bytes) / sizeof(float);   // the buffer may have moved
+                }
+            }
         }
         if (pl.sk_max_share > 1) {
             p.sk_slots = ctx->ws;
@@ -479,10 +528,29 @@ int run_gemm(gptb200_ctx *ctx, const GemmCall &c, bool *dbias_fused = nullptr)
         rc = make_tmap(ctx, &tb, c.b, c.N, c.K, kBK, pair ? bn / 2 : bn, false);
     if (rc != GPTB200_OK) return rc;
 
+    CUtensorMap tpre = to;
+    if (p.pre_operand) {
+        const bool pre_a = p.pre_operand == 1;
+        const bool mn = pre_a ? c.a_mn : c.b_mn;
+        const float *src = pre_a ? c.a : c.b;
+        const long long rows = pre_a ? c.M : c.N;          // free extent of that operand
+        const long long k8 = (static_cast<long long>(c.K) + 7) & ~7LL;
+        const long long units = mn ? k8 * (rows / 8) : rows * (k8 / 8);
+        const int blocks = static_cast<int>(std::min<long long>((units + 255) / 256, 1LL * ctx->num_sms * 16));
+        if (mn)
+            split_operand_kernel<true><<<blocks, 256, 0, ctx->stream>>>(reinterpret_cast<uint4 *>(pre_buf), src, c.K, rows, pre_a ? 0 : 1);
+        else
+            split_operand_kernel<false><<<blocks, 256, 0, ctx->stream>>>(reinterpret_cast<uint4 *>(pre_buf), src, rows, c.K, pre_a ? 0 : 1);
+        ctx->launches++;
+        CUDA_TRY(ctx, cudaGetLastError());
+        rc = mn ? make_pre_tmap(ctx, &tpre, pre_buf, 2 * k8, rows / 2, 64) : make_pre_tmap(ctx, &tpre, pre_buf, rows, k8, 128);
+        if (rc != GPTB200_OK) return rc;
+    }
+
     const int grid = pl.grid;
     cudaError_t e;
     if (pair)
-        e = x3 ? launch_pair<true>(ctx, c.a_mn, c.b_mn, ta, tb, to, tact, p, grid) : launch_pair<false>(ctx, c.a_mn, c.b_mn, ta, tb, to, tact, p, grid);
+        e = x3 ? launch_pair<true>(ctx, c.a_mn, c.b_mn, ta, tb, to, tact, tpre, p, grid) : launch_pair<false>(ctx, c.a_mn, c.b_mn, ta, tb, to, tact, tpre, p, grid);
     else if (bn == 256)
         e = x3 ? launch_majors<256, true>(ctx, c.a_mn, c.b_mn, ta, tb, to, tact, p, grid)
                : launch_majors<256, false>(ctx, c.a_mn, c.b_mn, ta, tb, to, tact, p, grid);
@@ -709,6 +777,11 @@ int gptb200_ctx_set_option(gptb200_ctx *ctx, const char *key, int value)
     if (!strcmp(key, "skinny_fused")) {
         if (value < -1 || value > 1) return fail(ctx, GPTB200_ERR_INVALID_ARG, "skinny_fused must be -1, 0 or 1");
         ctx->skinny_fused = value;
+        return GPTB200_OK;
+    }
+    if (!strcmp(key, "presplit")) {
+        if (value < 0 || value > 3) return fail(ctx, GPTB200_ERR_INVALID_ARG, "presplit must be 0, 1, 2 or 3");
+        ctx->presplit = value;
         return GPTB200_OK;
     }
     if (!strcmp(key, "fuse_dbias")) {

@@ -72,6 +72,11 @@ struct GemmParams {
     unsigned int *sk_flags;  // one word per pair, CTA and epilogue warp: the number of the launch whose partial tile is complete
     unsigned int *sk_state;  // [0] number of completed launches that used the flags, [1] CTAs of this launch that have finished
     long long *trace;        // optional [kTraceEvents][kTraceSlots] clock64 samples of the first k-blocks of CTA 0
+    // CTA-pair kernel, 3xTF32: the bf16 correction tiles of ONE operand (1 = A, 2 = B, 0 = neither) were written to scratch by a
+    // pass of their own before the launch (split_operand_kernel) and are fetched by TMA (fifth tensor map) straight into the
+    // correction ring; the converter warps then only split the other operand.  Pays when that operand is re-read by many
+    // tiles (a weight matrix by every row tile): half of the conversion work leaves the main loop.
+    int pre_operand;
     // CTA-pair kernel, grad_w form (both operands MN-major) only: the bias gradient rides this launch.  The tiles of one tile
     // column read the same columns of B (= grad_y [K x N], row pitch N); each of them adds up its share of the k-blocks (epilogue
     // warps, plain loads), the shares are parked in dbias_part and the last tile to finish adds them, in tile order, into dbias[N].

@@ -286,6 +286,52 @@ __device__ __forceinline__ bool bounded_flag_wait(const unsigned int *flag, unsi
     return ok != 0;
 }
 
+// The correction tiles of one whole operand, written once before a 3xTF32 launch (GemmParams::pre_operand): an expanded bf16
+// matrix with 64 k-positions per 32 k in which groups of 8 values alternate -- A: [a_lo | a], B: [b | b_lo] with
+// x_lo = x - (x truncated to TF32), the same numbers the converter warps produce in the main loop -- laid out so that a plain
+// TMA box load with the 128-byte swizzle lands the tile in the canonical layout of the operand's major-ness:
+//   K-major operand [rows][k]:  out[row][16 g + j] (first group), out[row][16 g + 8 + j] (second group), k = 8 g + j; a row has
+//                               2 * k8 bf16 (k8 = k rounded up to a multiple of 8), zero beyond k;
+//   MN-major operand [k][cols]: out[16 g + j][col] (first group), out[16 g + 8 + j][col] (second group); 2 * k8 rows of `cols`
+//                               bf16, zero rows beyond k.
+// One thread per 8 consecutive source values that share a k-group (K-major) or per 8 consecutive columns of one k (MN-major).
+template <bool MN>
+__global__ void split_operand_kernel(uint4 *__restrict__ out, const float *__restrict__ in, long long rows, long long cols, int is_b)
+{
+    // K-major: in [rows][cols = k];  MN-major: in [rows = k][cols]
+    const long long k = MN ? rows : cols, k8 = (k + 7) & ~7LL;
+    const long long units = MN ? k8 * (cols / 8) : rows * (k8 / 8);
+    for (long long u = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; u < units; u += static_cast<long long>(gridDim.x) * blockDim.x) {
+        float v[8];
+        long long o_first, o_second;   // uint4 (8 bf16) index of the first and the second group's piece
+        if (MN) {
+            const long long kk = u / (cols / 8), c8 = u % (cols / 8);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = kk < k ? in[kk * cols + c8 * 8 + e] : 0.0f;
+            const long long g = kk >> 3, j = kk & 7;
+            o_first = (16 * g + j) * (cols / 8) + c8;
+            o_second = (16 * g + 8 + j) * (cols / 8) + c8;
+        } else {
+            const long long r = u / (k8 / 8), g = u % (k8 / 8);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = 8 * g + e < k ? in[r * k + 8 * g + e] : 0.0f;
+            o_first = r * (k8 / 4) + 2 * g;
+            o_second = o_first + 1;
+        }
+        uint32_t lo[4], whole[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float l0 = v[2 * e] - __uint_as_float(__float_as_uint(v[2 * e]) & 0xFFFFE000u);
+            const float l1 = v[2 * e + 1] - __uint_as_float(__float_as_uint(v[2 * e + 1]) & 0xFFFFE000u);
+            lo[e] = ptx::pack_bf16x2(l0, l1);
+            whole[e] = ptx::pack_bf16x2(v[2 * e], v[2 * e + 1]);
+        }
+        const uint4 w4 = make_uint4(whole[0], whole[1], whole[2], whole[3]), l4 = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        out[o_first] = is_b ? w4 : l4;
+        out[o_second] = is_b ? l4 : w4;
+    }
+}
+
 // Bias gradient inside the grad_w GEMM: column sums of B (= grad_y [K x N], row pitch ld) over the k-blocks kb_first,
 // kb_first + kb_step, ... < kb_end, for 16 consecutive columns per warp.  A quarter of four lanes covers the 16 columns of one
 // row with a 16-byte load each, the eight quarters take eight consecutive rows; `s` carries the lane's running sums of its four
@@ -333,7 +379,8 @@ __device__ __forceinline__ void column_sums_finish(float4 &s)
 template <bool A_MN, bool B_MN, bool X3, bool DB = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<X3>::kThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                         const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_act, const GemmParams p)
+                         const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_act,
+                         const __grid_constant__ CUtensorMap tmap_pre, const GemmParams p)
 {
     using C = PairCfg<X3>;
     constexpr int BN = C::BN;
@@ -375,7 +422,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             ptx::mbar_init(empty_bar(s), 1);
         }
         for (int j = 0; j < NL; ++j) {
-            ptx::mbar_init(conv_bar(j), 6);   // leader: one arrival per converter warp (three of each CTA) of the group that owns the buffer
+            // leader: one arrival per converter warp (three of each CTA) of the group that owns the buffer, plus the producer's
+            // arrival that announces the bytes of a correction tile fetched by TMA (pre_operand)
+            ptx::mbar_init(conv_bar(j), (X3 && p.pre_operand) ? 7 : 6);
             ptx::mbar_init(lo_empty_bar(j), 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -388,6 +437,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         ptx::prefetch_tensormap(&tmap_a);
         ptx::prefetch_tensormap(&tmap_b);
         ptx::prefetch_tensormap(&tmap_out);
+        if (X3 && p.pre_operand) ptx::prefetch_tensormap(&tmap_pre);
     }
     if (warp == 1) {
         ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), kTmemCols);
@@ -448,8 +498,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 if (wgrp == 0 && lane == 0) trace(TRACE_CONV_BEGIN, it);
                 const uint32_t raw = smem_base + s * C::kHiBytes;
                 const uint32_t cor = lo_base + j * C::kHiBytes;
-                convert_tile<A_MN, false>(raw, cor, lane_a, wgrp, lane);
-                convert_tile<B_MN, true>(raw, cor, lane_b, wgrp_b, lane);
+                if (p.pre_operand != 1) convert_tile<A_MN, false>(raw, cor, lane_a, wgrp, lane);
+                if (p.pre_operand != 2) convert_tile<B_MN, true>(raw, cor, lane_b, p.pre_operand ? wgrp : wgrp_b, lane);
                 ptx::fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
@@ -503,6 +553,31 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                             ptx::tma_load_2d_pair(b_dst, &tmap_b, k0, n0, bar);
                     }
                     __syncwarp();
+                    if (X3 && p.pre_operand) {
+                        // The correction tile of the operand that was split before the launch: 16 KiB per CTA from the expanded
+                        // bf16 matrix (64 k-positions per 32 k) into correction buffer j, bytes reported to the leader's conv[j].
+                        //   K-major:  rows of the operand, 32 four-byte words (64 bf16) per k-block, 128-byte swizzle: one box;
+                        //   MN-major: [64 k-positions x 64 rows-of-the-operand] atoms: one box per half of the CTA's 128 rows.
+                        const int j = it % NL;
+                        const uint32_t lph = (it / NL) & 1u;
+                        if (!bounded_wait_cluster(lo_empty_bar(j), lph ^ 1u, abort_flag, p.status, DEV_TIMEOUT_PRODUCER)) {
+                            ok = false;
+                            break;
+                        }
+                        const bool pre_a = p.pre_operand == 1;
+                        const bool pre_mn = pre_a ? A_MN : B_MN;
+                        const int r0 = pre_a ? m0 : n0;   // first of this CTA's 128 rows (A) / columns (B)
+                        const uint32_t dst = lo_base + j * C::kHiBytes + (pre_a ? 0 : kATileBytes);
+                        const uint32_t cbar = ptx::map_to_cta(conv_bar(j), 0u);
+                        if (leader && lane == 0) ptx::mbar_arrive_expect_tx(conv_bar(j), 2 * kATileBytes);
+                        __syncwarp();
+                        if (pre_mn) {
+                            if (lane < 2) ptx::tma_load_2d_pair(dst + lane * 8192, &tmap_pre, (r0 + 64 * lane) / 2, 2 * k0, cbar);
+                        } else {
+                            if (lane == 0) ptx::tma_load_2d_pair(dst, &tmap_pre, k0, r0, cbar);
+                        }
+                        __syncwarp();
+                    }
                 }
             }
         } else if (warp == 1) {

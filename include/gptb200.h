@@ -76,6 +76,11 @@ int gptb200_ctx_set_stream(gptb200_ctx *ctx, void *cuda_stream);
  * immediately before a decode-shaped forward call on the same stream (an optimizer step does: leave this off when training)),
  * "skinny_fused" (the k-split kernel adds its partial sums itself instead of in a second launch: 1 = always, 0 = with at most
  * two splits (default), -1 = never; same bits either way),
+ * "presplit" (3xTF32 mode, CTA-pair kernel: the bf16 correction tiles of the operand that most tiles re-read -- the weight matrix
+ * in forward and grad_x, the activations in grad_w -- are written to scratch by a small kernel before the GEMM and fetched by
+ * TMA, instead of being recomputed by every tile in the main loop: 0 = off (default), 1 = automatic choice of the operand,
+ * 2 / 3 = always A / B; same bits either way.  Measured: 8-11 % fewer SM cycles per k-block on the GPT-2 FFN shapes but the same
+ * time, because the kernel runs at the board's power limit and the clock drops by as much; one more launch per GEMM),
  * "fuse_dbias" (weight-gradient launches of the CTA-pair kernel also produce the bias gradient: 1 = on (default), 0 = the
  * separate column-sum kernels; results differ only in summation order),
  * "max_sms" (0 = all SMs; otherwise the GEMM kernels occupy at most this many, which leaves SMs to a collective that runs

@@ -29,14 +29,19 @@ def torch():
 # (precision mode, kernel choice, k-range cutting): automatic choice in both modes, plus the CTA-pair (cta_group::2) kernel
 # and the one-CTA kernel forced, so that every shape below runs through both GEMM kernels; the pair kernel once with whole
 # tiles per pair and once with every pair's k-block range cut as finely as possible (tiles summed from several pairs' parts).
-@pytest.fixture(scope="module", params=[(0, 0, 0), (1, 0, 0), (0, 1, -1), (1, 1, -1), (0, 1, 1), (1, 1, 1), (0, -1, 0)],
-                ids=["3xTF32", "TF32", "3xTF32-pair", "TF32-pair", "3xTF32-pair-cut", "TF32-pair-cut", "3xTF32-single"])
+# Two more variants force the 3xTF32 pair kernel to take the correction tiles of operand A, or of operand B, from the pass that
+# splits an operand before the launch (option "presplit"), whatever the shape; the automatic choice runs in the others.
+@pytest.fixture(scope="module", params=[(0, 0, 0, 0), (1, 0, 0, 0), (0, 1, -1, 0), (1, 1, -1, 0), (0, 1, 1, 0), (1, 1, 1, 0), (0, -1, 0, 0),
+                                        (0, 1, 1, 2), (0, 1, -1, 3), (0, 1, 0, 1)],
+                ids=["3xTF32", "TF32", "3xTF32-pair", "TF32-pair", "3xTF32-pair-cut", "TF32-pair-cut", "3xTF32-single",
+                     "3xTF32-pair-cut-splitA", "3xTF32-pair-splitB", "3xTF32-pair-autosplit"])
 def be(request, torch, built_library):
     import gpt_b200
-    mode, pair, stream_k = request.param
+    mode, pair, stream_k, presplit = request.param
     b = gpt_b200.Backend(0, None, mode)
     b.set_option("pair", pair)
     b.set_option("stream_k", stream_k)
+    b.set_option("presplit", presplit)
     b.mode = mode
     yield b
     b.close()

@@ -522,6 +522,7 @@ def train_record(torch, dist, world, rank, dev, mode_name="3xtf32", global_batch
     model = gpt_b200.Model(cfg, dev.index, stream.cuda_stream, mode, seed=42)
     model.init(0.0, 0.02)           # same seed on every rank: identical replicas
     model.set_fused_cross_entropy(os.environ.get("GPTB200_FUSED_CE", "1") != "0")   # logits -> their gradient in place, no probability tensor
+    model.set_fused_gelu_backward(os.environ.get("GPTB200_FUSED_GELU", "1") != "0")  # GELU' in the epilogue of the down projection's grad_x GEMM
     model.set_size(B, T)
 
     class _Raw:   # torch view of the packed gradient buffer (no copy) for the collectives

@@ -28,6 +28,7 @@ EXPORTED_SYMBOLS = [
     "gptb200_ctx_set_stream", "gptb200_ctx_set_option", "gptb200_ctx_synchronize", "gptb200_ctx_launch_count", "gptb200_ctx_tensor_map_encodes", "gptb200_ctx_read_trace",
     "gptb200_status_string", "gptb200_last_error", "gptb200_plan_gemm", "gptb200_plan_decode", "gptb200_selftest_wait_timeout",
     "gptb200_linear_forward", "gptb200_linear_backward", "gptb200_linear_backward_weights", "gptb200_linear_backward_input",
+    "gptb200_linear_backward_input_gelu",
     "gptb200_gelu_backward",
     "gptb200_unembed_forward", "gptb200_unembed_backward",
     "gptb200_malloc", "gptb200_free", "gptb200_memset", "gptb200_memcpy_h2d", "gptb200_memcpy_d2h",
@@ -81,6 +82,7 @@ def load_library(path: str | None = None) -> ctypes.CDLL:
         "gptb200_linear_backward": (i, [vp, fp, fp, fp, fp, fp, fp, i, i, i]),
         "gptb200_linear_backward_weights": (i, [vp, fp, fp, fp, fp, i, i, i]),
         "gptb200_linear_backward_input": (i, [vp, fp, fp, fp, i, i, i]),
+        "gptb200_linear_backward_input_gelu": (i, [vp, fp, fp, fp, fp, i, i, i]),
         "gptb200_gelu_backward": (i, [vp, fp, fp, fp, i, i]),
         "gptb200_unembed_forward": (i, [vp, fp, fp, fp, i, i, i]),
         "gptb200_unembed_backward": (i, [vp, fp, fp, fp, fp, fp, i, i, i]),
@@ -260,6 +262,11 @@ class Backend:
         self._check(self._lib.gptb200_linear_backward_input(self._ctx, _ptr(grad_x), _ptr(grad_y), _ptr(w), m, k, n),
                     "gptb200_linear_backward_input")
 
+    def linear_backward_input_gelu(self, grad_x, grad_y, w, pre_act, m: int, k: int, n: int) -> None:
+        """grad_x = (grad_y . w^T) * gelu_tanh'(pre_act): device_linear_backward's input half and device_activation_backward in one."""
+        self._check(self._lib.gptb200_linear_backward_input_gelu(self._ctx, _ptr(grad_x), _ptr(grad_y), _ptr(w), _ptr(pre_act), m, k, n),
+                    "gptb200_linear_backward_input_gelu")
+
     def device_activation_backward(self, grad_x, grad_y, x, batch_size: int, seq_len: int, output_size: int) -> None:
         self._check(self._lib.gptb200_gelu_backward(self._ctx, _ptr(grad_x), _ptr(grad_y), _ptr(x), batch_size * seq_len,
                                                     output_size), "gptb200_gelu_backward")
@@ -330,6 +337,7 @@ def _declare_model(lib: ctypes.CDLL) -> None:
         "gptb200_model_optimizer_step": (i, [vp, f32, f32, f32, f32]),
         "gptb200_model_clip_and_optimizer_step": (i, [vp, f32, i, f32, f32, f32, f32]),
         "gptb200_model_set_fused_cross_entropy": (i, [vp, i]),
+        "gptb200_model_set_fused_gelu_backward": (i, [vp, i]),
         "gptb200_model_generate_begin": (i, [vp, vp, i, i, i]),
         "gptb200_model_generate_step": (i, [vp, vp, vp]),
         "gptb200_model_generate_position": (i, [vp]),
@@ -462,6 +470,10 @@ class Model:
         """The logits become their gradient in place at the start of the backward pass (no probability / gradient tensors);
         takes effect at the next set_size."""
         self._check(self._lib.gptb200_model_set_fused_cross_entropy(self._m, int(on)))
+
+    def set_fused_gelu_backward(self, on: bool) -> None:
+        """The FFN's GELU derivative rides the epilogue of the down projection's grad_x GEMM."""
+        self._check(self._lib.gptb200_model_set_fused_gelu_backward(self._m, int(on)))
 
     def generate_begin(self, prompt_tokens, batch_size: int, prompt_len: int, max_len: int) -> None:
         """Forward pass over the prompt [batch x prompt_len] and the keys / values of every layer into a cache for max_len positions."""

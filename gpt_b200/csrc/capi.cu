@@ -108,6 +108,7 @@ struct GemmCall {
     const float *bias;
     bool accumulate;  // out += result
     float *dbias = nullptr;  // grad_w form only: dbias[N] += column sums of b, inside the same launch when the CTA-pair kernel runs
+    const float *gelu_src = nullptr;  // out = result * gelu_tanh'(gelu_src) element by element, when the CTA-pair kernel runs
 };
 
 template <int BN, bool A_MN, bool B_MN, bool X3>
@@ -399,9 +400,11 @@ GemmPlanInput plan_input(const gptb200_ctx *ctx, const GemmCall &c)
 
 // *dbias_fused (optional) reports whether c.dbias was computed inside the GEMM launch; if not, the caller runs the
 // separate column-sum kernels.
-int run_gemm(gptb200_ctx *ctx, const GemmCall &c, bool *dbias_fused = nullptr)
+// *gelu_fused (optional): whether c.gelu_src was applied inside the launch (CTA-pair kernel only).
+int run_gemm(gptb200_ctx *ctx, const GemmCall &c, bool *dbias_fused = nullptr, bool *gelu_fused = nullptr)
 {
     if (dbias_fused) *dbias_fused = false;
+    if (gelu_fused) *gelu_fused = false;
     const GemmPlan pl = plan_gemm(plan_input(ctx, c));
     if (pl.kernel == KERNEL_NONE) return GPTB200_OK;
     if (pl.kernel == KERNEL_SKINNY) return run_skinny(ctx, c, pl);
@@ -439,6 +442,10 @@ int run_gemm(gptb200_ctx *ctx, const GemmCall &c, bool *dbias_fused = nullptr)
     if (pair && ctx->d_trace) {
         CUDA_TRY(ctx, cudaMemsetAsync(ctx->d_trace, 0, sizeof(long long) * kTraceEvents * kTraceSlots, ctx->stream));
         p.trace = ctx->d_trace;
+    }
+    if (pair && c.gelu_src && !c.accumulate && aligned16(c.gelu_src)) {
+        p.gelu_src = c.gelu_src;
+        if (gelu_fused) *gelu_fused = true;
     }
     if (pair) {
         p.sk_total = pl.sk_total;
@@ -887,6 +894,24 @@ int gptb200_linear_backward_input(gptb200_ctx *ctx, float *grad_x, const float *
     // grad_x[m x k] = grad_y[m x n] . w^T : A = grad_y (K-major), B = w stored [k x n] = [N' x K'] (K-major)
     GemmCall dx{m, k, n, grad_y, false, w, false, grad_x, nullptr, nullptr, false};
     return run_gemm(ctx, dx);
+}
+
+int gptb200_linear_backward_input_gelu(gptb200_ctx *ctx, float *grad_x, const float *grad_y, const float *w, const float *pre_act, int m, int k, int n)
+{
+    int rc = check_dims(ctx, m, k, n);
+    if (rc) return rc;
+    if (1LL * m * k == 0) return GPTB200_OK;
+    if (!grad_x || !pre_act || (n > 0 && (!grad_y || !w))) return fail(ctx, GPTB200_ERR_INVALID_ARG, "null tensor pointer");
+    if (n == 0) {
+        CUDA_TRY(ctx, cudaMemsetAsync(grad_x, 0, size_t(m) * k * sizeof(float), ctx->stream));
+        return GPTB200_OK;
+    }
+    GemmCall dx{m, k, n, grad_y, false, w, false, grad_x, nullptr, nullptr, false, nullptr, pre_act};
+    bool fused = false;
+    rc = run_gemm(ctx, dx, nullptr, &fused);
+    if (rc || fused) return rc;
+    // shapes that do not run the CTA-pair kernel: the derivative as a pass of its own, in place
+    return gptb200_gelu_backward(ctx, grad_x, grad_x, pre_act, m, k);
 }
 
 int gptb200_linear_backward_weights(gptb200_ctx *ctx, float *grad_w, float *grad_b, const float *grad_y, const float *x, int m, int k, int n)

@@ -72,6 +72,9 @@ struct GemmParams {
     unsigned int *sk_flags;  // one word per pair, CTA and epilogue warp: the number of the launch whose partial tile is complete
     unsigned int *sk_state;  // [0] number of completed launches that used the flags, [1] CTAs of this launch that have finished
     long long *trace;        // optional [kTraceEvents][kTraceSlots] clock64 samples of the first k-blocks of CTA 0
+    // CTA-pair kernel, store epilogue: out = acc * gelu_tanh'(gelu_src) element by element (gelu_src [M x N], row pitch N): the
+    // GELU derivative of the FFN rides the grad_x GEMM of the layer behind it instead of a pass of its own over HBM.
+    const float *gelu_src;
     // CTA-pair kernel, 3xTF32: the bf16 correction tiles of ONE operand (1 = A, 2 = B, 0 = neither) were written to scratch by a
     // pass of their own before the launch (split_operand_kernel) and are fetched by TMA (fifth tensor map) straight into the
     // correction ring; the converter warps then only split the other operand.  Pays when that operand is re-read by many
@@ -159,6 +162,17 @@ __device__ __forceinline__ float gelu_tanh(float x)
 {
     const float u = 0.79788456f * (x + 0.044715f * x * x * x);
     return __fdividef(x, 1.0f + __expf(-2.0f * u));
+}
+
+// d/dx of gelu_tanh(x) = 0.5 x (1 + tanh u), u = 0.79788456 (x + 0.044715 x^3):
+//   0.5 (1 + t) + 0.5 x (1 - t^2) * 0.79788456 (1 + 3 * 0.044715 x^2),  t = tanh u = 1 - 2 / (1 + exp(2u))
+// (the reference's constants, linear.cu:162-187; exp and division in their fast forms, 1-2 ulp, far inside the 1e-5 bound;
+// exp(2u) = +inf for large u gives t = 1 exactly).
+__device__ __forceinline__ float gelu_tanh_grad_fast(float x)
+{
+    const float u = 0.79788456f * (x + 0.044715f * x * x * x);
+    const float t = 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * u));
+    return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * (0.79788456f + 0.107032f * x * x);
 }
 
 // One epilogue warp's staging state: `kBufs` swizzled [32 x 32] fp32 tiles and the count of TMA stores

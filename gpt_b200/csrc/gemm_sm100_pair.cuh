@@ -682,6 +682,24 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, bias_lane, j);
             }
+            if (p.gelu_src && p.epi_mode == EPI_STORE && row0 + lane < p.M) {
+                // this thread's row of the pre-activation, 128 contiguous bytes, a quarter at a time (register budget of the chunked form)
+                const float4 *src = reinterpret_cast<const float4 *>(p.gelu_src + static_cast<long long>(row0 + lane) * p.N + col0);
+#pragma unroll
+                for (int qt = 0; qt < 4; ++qt) {
+                    const bool in = col0 + 8 * qt < p.N;      // N is a multiple of 4: a 16-byte piece is inside or outside as a whole
+                    const float4 xa = in ? __ldg(src + 2 * qt) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    const float4 xb = (col0 + 8 * qt + 4 < p.N) ? __ldg(src + 2 * qt + 1) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    v[8 * qt] *= gelu_tanh_grad_fast(xa.x);
+                    v[8 * qt + 1] *= gelu_tanh_grad_fast(xa.y);
+                    v[8 * qt + 2] *= gelu_tanh_grad_fast(xa.z);
+                    v[8 * qt + 3] *= gelu_tanh_grad_fast(xa.w);
+                    v[8 * qt + 4] *= gelu_tanh_grad_fast(xb.x);
+                    v[8 * qt + 5] *= gelu_tanh_grad_fast(xb.y);
+                    v[8 * qt + 6] *= gelu_tanh_grad_fast(xb.z);
+                    v[8 * qt + 7] *= gelu_tanh_grad_fast(xb.w);
+                }
+            }
             constexpr int kPieces = 32 / C::kStageCols;
 #pragma unroll
             for (int h = 0; h < kPieces; ++h) {

@@ -226,9 +226,18 @@ public:
         if (layer_done) layer_done(c_.layers, user);
         // d_res holds the gradient of the residual stream at the output of layer l
         for (int l = c_.layers - 1; l >= 0; --l) {
-            be_->device_linear_backward(G + g_.d_f1, gw + lay_.down_w + l * F * D, gw + lay_.down_b + l * D, d_res, A + a_.act + l * M * F,
-                                        w + lay_.down_w + l * F * D, B_, T_, c_.d_ffn, c_.d_model);
-            be_->device_activation_backward(G + g_.d_f2, G + g_.d_f1, A + a_.up + l * M * F, B_, T_, c_.d_ffn);
+            if (fused_gelu_ && ctx_) {
+                // the down projection's two halves apart: grad_x comes out already multiplied by the GELU derivative
+                if (gptb200_linear_backward_weights(ctx_, gw + lay_.down_w + l * F * D, gw + lay_.down_b + l * D, d_res, A + a_.act + l * M * F,
+                                                    static_cast<int>(M), c_.d_ffn, c_.d_model) != 0 ||
+                    gptb200_linear_backward_input_gelu(ctx_, G + g_.d_f2, d_res, w + lay_.down_w + l * F * D, A + a_.up + l * M * F, static_cast<int>(M),
+                                                       c_.d_ffn, c_.d_model) != 0)
+                    return;
+            } else {
+                be_->device_linear_backward(G + g_.d_f1, gw + lay_.down_w + l * F * D, gw + lay_.down_b + l * D, d_res, A + a_.act + l * M * F,
+                                            w + lay_.down_w + l * F * D, B_, T_, c_.d_ffn, c_.d_model);
+                be_->device_activation_backward(G + g_.d_f2, G + g_.d_f1, A + a_.up + l * M * F, B_, T_, c_.d_ffn);
+            }
             be_->device_linear_backward(d_x, gw + lay_.up_w + l * D * F, gw + lay_.up_b + l * F, G + g_.d_f2, A + a_.ln2 + l * M * D,
                                         w + lay_.up_w + l * D * F, B_, T_, c_.d_model, c_.d_ffn);
             be_->device_layernorm_residual_fused_backward(d_ln, gw + lay_.ln2_w + l * D, gw + lay_.ln2_b + l * D, d_x, d_res, A + a_.proj + l * M * D,
@@ -331,6 +340,7 @@ public:
     void set_defer_embedding(bool on) { defer_embedding_ = on; }
     void set_context(gptb200_ctx *ctx) { ctx_ = ctx; }
     void set_fused_cross_entropy(bool on) { fused_ce_ = on; }
+    void set_fused_gelu_backward(bool on) { fused_gelu_ = on; }
     float *embedding_grad() { return agrads_ ? agrads_ + g_.d_res : nullptr; }
     size_t wte_offset() const { return lay_.wte; }
     size_t wpe_offset() const { return lay_.wpe; }
@@ -425,6 +435,7 @@ private:
     bool defer_embedding_ = false;
     gptb200_ctx *ctx_ = nullptr;   // the backend's context, for the operators that are not part of IGPTBackend
     bool fused_ce_ = false, fused_ce_active_ = false, row_loss_valid_ = false;
+    bool fused_gelu_ = false;
     float *gen_ = nullptr;        // KV cache of every layer, then the step's activations, then the device copy of the position
     size_t gen_capacity_ = 0, gen_pos_off_ = 0;
     int gen_batch_ = 0, gen_max_len_ = 0, gen_pos_ = 0;
@@ -581,6 +592,13 @@ int gptb200_model_set_fused_cross_entropy(gptb200_model *m, int on)
 {
     if (!m) return GPTB200_ERR_INVALID_ARG;
     m->h.model->set_fused_cross_entropy(on != 0);
+    return GPTB200_OK;
+}
+
+int gptb200_model_set_fused_gelu_backward(gptb200_model *m, int on)
+{
+    if (!m) return GPTB200_ERR_INVALID_ARG;
+    m->h.model->set_fused_gelu_backward(on != 0);
     return GPTB200_OK;
 }
 

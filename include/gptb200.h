@@ -140,6 +140,13 @@ int gptb200_linear_backward(gptb200_ctx *ctx, float *grad_x, float *grad_w, floa
 int gptb200_linear_backward_weights(gptb200_ctx *ctx, float *grad_w, float *grad_b, const float *grad_y, const float *x, int m, int k, int n);
 int gptb200_linear_backward_input(gptb200_ctx *ctx, float *grad_x, const float *grad_y, const float *w, int m, int k, int n);
 
+/* The input half with the GELU derivative of the layer in FRONT of this one folded into its epilogue:
+ *   grad_x[m x k] = (grad_y[m x n] . w^T) * gelu_tanh'(pre_act[m x k])  element by element,
+ * i.e. device_linear_backward's grad_x followed by device_activation_backward (linear.cu:116-203, gpt.cpp:565-571: the FFN's
+ * down projection and its GELU) without the gradient of the activation making a round trip through HBM.  Same values as the
+ * two calls up to the rounding of the derivative (fast exp / division, 1-2 ulp). */
+int gptb200_linear_backward_input_gelu(gptb200_ctx *ctx, float *grad_x, const float *grad_y, const float *w, const float *pre_act, int m, int k, int n);
+
 /* ---- IGPTBackend::device_activation_backward
  *      (backend_interface.h:150-159, cuda/kernels/linear.cu:162-203, cpu/cpu_backend.cpp:268-287)
  *   grad_x = grad_y * gelu_tanh'(x), all [m x n]. */
@@ -277,6 +284,9 @@ int gptb200_model_apply_embedding_grad(gptb200_model *m, const float *rows_dev, 
  * vocab_size_padded floats less), two trips through HBM less per step.  gptb200_model_logits then holds logits only between
  * forward and backward.  Takes effect at the next gptb200_model_set_size. */
 int gptb200_model_set_fused_cross_entropy(gptb200_model *m, int on);
+/* on != 0: the FFN's GELU derivative is applied in the epilogue of the down projection's grad_x GEMM
+ * (gptb200_linear_backward_input_gelu) instead of by device_activation_backward. */
+int gptb200_model_set_fused_gelu_backward(gptb200_model *m, int on);
 int gptb200_model_loss(gptb200_model *m, const int *labels_dev, float *loss_out);
 /* KV-cached generation (the reference's loop, src/infer/infer.cpp:112-148, recomputes the prefix for every token):
  *   generate_begin  one forward pass over the prompt [batch x prompt_len] (device, int32), keys and values of every layer

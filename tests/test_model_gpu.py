@@ -417,3 +417,31 @@ def test_fused_cross_entropy_gives_the_same_step_with_less_memory(lib, reference
         assert np.abs(a[name] - c[name]).max() <= 1e-5, name                       # the reference's own absolute check
     assert np.abs(g - out[False][0]).max() <= 1e-6
     assert used_fused <= out[False][3]
+
+
+def test_fused_gelu_backward_in_the_model_driver(lib, reference):
+    """The model driver with the GELU derivative folded into the down projection's grad_x GEMM: every gradient tensor still
+    within the reference's absolute 1e-5 of the CPU model, and within 1e-6 of the unfused driver."""
+    import torch
+    import gpt_b200
+    cfg, tokens, weights, _ = _tiny()
+    T = cfg["max_seq_len"]
+    d_in = torch.from_numpy(tokens[:T].copy()).cuda()
+    d_lbl = torch.from_numpy(tokens[1:T + 1].copy()).cuda()
+    cpu, cpu_loss, _ = reference.gpt_forward_backward(cfg, weights, tokens[:T], tokens[1:T + 1], 1, T)
+    grads = {}
+    for fused in (False, True):
+        m = gpt_b200.Model(cfg, 0, None, gpt_b200.MODE_3XTF32)
+        m.set_fused_gelu_backward(fused)
+        m.set_option("pair", 1)                 # the tiny shapes would otherwise not reach the kernel with the fused epilogue
+        m.load_weights(weights)
+        m.set_size(1, T)
+        m.zero_grad(); m.forward(d_in); m.backward(d_in, d_lbl)
+        g = np.empty(m.num_params, np.float32)
+        m.read_grads(g)
+        grads[fused] = g
+        m.close()
+    a, c = split_weights(cfg, grads[True]), split_weights(cfg, cpu)
+    for name in a:
+        assert np.abs(a[name] - c[name]).max() <= 1e-5, name
+    assert np.abs(grads[True] - grads[False]).max() <= 1e-6

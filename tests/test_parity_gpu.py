@@ -714,3 +714,22 @@ def test_decode_chain_with_early_launch_matches_plain_launches(torch, built_libr
     finally:
         be.synchronize()
         be.close()
+
+
+@pytest.mark.parametrize("m,k,n", [(2048, 3072, 768), (300, 420, 100), (64, 3072, 768), (129, 260, 36)], ids=lambda v: str(v))
+def test_gelu_derivative_rides_the_input_gradient_gemm(be, torch, oracle, m, k, n):
+    """gptb200_linear_backward_input_gelu: grad_x = (grad_y . w^T) * gelu'(pre_act) in one call, against the oracle's
+    device_linear_backward followed by device_activation_backward (cpu_backend.cpp:241-287) -- through the CTA-pair kernel
+    (derivative in the epilogue) and, for the shapes that run another kernel, its two-step form."""
+    rng = np.random.default_rng(m + k)
+    w = (0.02 * rng.standard_normal((k, n))).astype(np.float32)
+    gy = rng.standard_normal((m, n), dtype=np.float32)
+    pre = (1.5 * rng.standard_normal((m, k))).astype(np.float32)
+    gx_lin, _, _ = oracle.linear_backward(gy, np.zeros((m, k), np.float32), w)
+    ref = oracle.gelu_backward(gx_lin, pre)
+    d = Dev(torch)
+    gx = d.nan(m, k)
+    be.linear_backward_input_gelu(gx, d.put(gy), d.put(w), d.put(pre), m, k, n)
+    be.synchronize()
+    d.check_canaries()
+    check(f"grad_x {m}x{k}x{n}", gx.cpu().numpy(), ref, be.mode)

@@ -96,11 +96,12 @@ class DataParallelStep:
         self.comm_stream = torch.cuda.Stream(priority=-1) if (world_size > 1 and self.on_gpu) else None
         self._all_reduce = all_reduce or (lambda t: dist.all_reduce(t, op=dist.ReduceOp.AVG))
         self.collectives = 0
-        # While collectives are in flight the persistent GEMM kernels leave `comm_sms` SMs free: NCCL's CTAs otherwise wait for
-        # a GEMM CTA to finish, and the GEMM's equal k-block ranges assume that all of its CTAs run at once (measured on the
-        # FFN step at 2 GPUs: 0.55 ms per step with all SMs claimed, 0.50 ms with 16 left free, 0.48 ms without any collective).
+        # While collectives are in flight the persistent GEMM kernels can leave `comm_sms` SMs free: NCCL's CTAs otherwise wait for
+        # a GEMM CTA to finish, and the GEMM's equal k-block ranges assume that all of its CTAs run at once.  That pays when one
+        # collective overlaps one GEMM (the FFN micro-step: 0.55 ms per step with all SMs claimed, 0.50 ms with 16 left free at 2
+        # GPUs); in the whole training step, where dozens of kernels pass while a bucket is reduced, it does not.
         if comm_sms is None:
-            comm_sms = 0 if world_size <= 2 else 32   # NCCL uses more channels with more ranks (measured: training step at 2 GPUs, FFN step at 8)
+            comm_sms = 0   # measured on the training step at 2 and 4 GPUs: ceding 16 or 32 SMs costs more GEMM time than NCCL's waiting CTAs do
         self.comm_sms = comm_sms if world_size > 1 else 0
         self._sms_limited = False
         # early reduction of wte (module text): needs the model driver's hooks and device tensors

@@ -206,7 +206,28 @@ inline GemmPlan plan_gemm(const GemmPlanInput &in)
     const long long pair_kb = pair_tiles * p.num_kb;
     // pairs that can be given at least eight k-blocks each
     const long long pairs_busy = std::min<long long>(max_pairs, std::max<long long>(pair_tiles, pair_kb / 8));
-    const bool pair = in.opt_pair > 0 || (in.opt_pair == 0 && in.opt_tile_n == 0 && in.M > kPlanBM && in.N > 128 && pairs_busy * 20 >= 9LL * in.num_sms);
+    bool pair = in.opt_pair > 0 || (in.opt_pair == 0 && in.opt_tile_n == 0 && in.M > kPlanBM && in.N > 128 && pairs_busy * 20 >= 9LL * in.num_sms);
+    // Small problems (measured on the GPT-2 layer shapes at 1024 and 2048 rows, both precision modes): cutting tiles between
+    // pairs costs a fixed 10 - 20 us per launch (a partner's partial tile is complete only at the end of its range, and the
+    // owner's epilogue comes after it), which only a long main loop pays back.
+    //   * one wave of 128 x 128 one-CTA tiles with at most 32 k-blocks each beats every CTA-pair plan (qkv forward at 1024 rows
+    //     16.5 against 23.1 us in TF32 mode, 28.8 against 45.4 us in 3xTF32 mode);
+    //   * when the pairs would outnumber the tiles four to one or more, every tile would be added up from four or more partial
+    //     tiles by its one owner: split-K over one-CTA tiles with its parallel reduction kernel is faster (attention projection
+    //     grad_w at 2048 rows 24.8 against 37.9 us, FFN-up grad_x at 1024 rows 18.9 against 30.9 us) -- where the epilogue
+    //     allows split-K at all.
+    const bool automatic = in.opt_pair == 0 && in.opt_tile_n == 0 && in.opt_stream_k == 0 && in.opt_max_splits == 0;
+    const long long tiles128 = 1LL * ((in.M + kPlanBM - 1) / kPlanBM) * ((in.N + 127) / 128);
+    bool force128 = false;
+    if (pair && automatic) {
+        const long long kb_each = std::max<long long>(1, pair_kb / pairs_busy);
+        if (!in.accumulate && p.num_kb <= 32 && tiles128 <= in.num_sms) {
+            pair = false;
+            force128 = true;
+        } else if (pair_tiles < max_pairs && p.num_kb >= 4 * kb_each && split_allowed) {
+            pair = false;
+        }
+    }
     if (pair) {
         p.kernel = KERNEL_PAIR;
         p.tile_n = 256;
@@ -219,8 +240,11 @@ inline GemmPlan plan_gemm(const GemmPlanInput &in)
         const long long rounds = (pair_tiles + whole_pairs - 1) / whole_pairs;
         const double whole_eff = double(pair_tiles) / double(rounds * pairs_busy);   // share of the usable pairs kept busy by whole tiles
         long long pairs;
-        // Whole tiles per pair only when they keep at least 97 % of the usable pairs busy.
-        if (in.opt_stream_k < 0 || (in.opt_stream_k == 0 && whole_eff >= 0.97)) {
+        // Whole tiles per pair when they keep at least 97 % of the usable pairs busy -- or when the tiles are short (at most 32
+        // k-blocks), fit one round and occupy at least half of the pairs: the main loop a cut would save is then shorter than the
+        // cut's fixed cost (FFN-up forward at 1024 rows: 22.7 against 28.5 us in TF32 mode, 37.0 against 56.2 us in 3xTF32 mode).
+        const bool short_single_round = automatic && pair_tiles <= max_pairs && p.num_kb <= 32 && 2 * pair_tiles >= max_pairs;
+        if (in.opt_stream_k < 0 || (in.opt_stream_k == 0 && (whole_eff >= 0.97 || short_single_round))) {
             p.sk_unit = p.num_kb;   // whole tiles, as evenly as they go
             pairs = whole_pairs;
             p.sk_max_share = 1;
@@ -273,7 +297,7 @@ inline GemmPlan plan_gemm(const GemmPlanInput &in)
     int bn = in.opt_tile_n;
     if (bn != 128 && bn != 256) {
         const long long tiles256 = 1LL * ((in.M + kPlanBM - 1) / kPlanBM) * ((in.N + 255) / 256);
-        bn = (in.N <= 128 || tiles256 < in.num_sms / 2) ? 128 : 256;
+        bn = (force128 || in.N <= 128 || tiles256 < in.num_sms / 2) ? 128 : 256;
     }
     p.kernel = KERNEL_SINGLE;
     p.tile_n = bn;

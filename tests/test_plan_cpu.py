@@ -35,6 +35,32 @@ def test_gpt2_124m_shapes_use_the_cta_pair_kernel_at_m_8192(plan):
     assert dw["kernel"] == "pair" and dw["grid"] == 144 and dw["splits"] == 2
 
 
+def test_small_problems_avoid_the_fixed_cost_of_cut_ranges(plan):
+    """The GPT-2 layer shapes at 1024 and 2048 rows (the per-GPU shards of the data-parallel step): the choices measured
+    fastest -- one wave of 128 x 128 one-CTA tiles, split-K instead of tiles added up from four or more partial tiles, whole
+    tiles when they are short and fit one round -- and cut ranges where the main loop is long enough to pay for them."""
+    D, F = 768, 3072
+    # one wave of 128 x 128 tiles, at most 32 k-blocks: qkv forward at 1024 rows (144 tiles), attention projection at 2048 rows (96)
+    for m, n in ((1024, 3 * D), (2048, D)):
+        p = plan(SMS, m, n, D, False, True, has_epilogue=True)
+        assert p["kernel"] == "single" and p["tile_n"] == 128 and p["splits"] == 1
+    assert plan(SMS, 2048, D, D, False, False)["kernel"] == "single"           # ... and its grad_x
+    # the pairs would outnumber the tiles four to one: split-K over one-CTA tiles
+    dx = plan(SMS, 1024, D, F, False, False)                                   # FFN-up grad_x at 1024 rows: 12 pair tiles of 96 k-blocks
+    assert dx["kernel"] == "single" and dx["splits"] > 1
+    dw = plan(SMS, D, D, 2048, True, True, accumulate=True)                    # attention projection grad_w at 2048 rows: 9 pair tiles
+    assert dw["kernel"] == "single" and dw["splits"] > 1
+    # ... but not where the epilogue rules split-K out: FFN-down forward keeps the cut ranges
+    down = plan(SMS, 1024, D, F, False, True, has_epilogue=True)
+    assert down["kernel"] == "pair" and down["splits"] >= 2
+    # short tiles that fit one round and occupy more than half of the pairs: whole tiles
+    up = plan(SMS, 1024, F, D, False, True, has_epilogue=True)                 # 48 tiles of 24 k-blocks on 74 pairs
+    assert up["kernel"] == "pair" and up["splits"] == 1 and up["grid"] == 96 and up["scratch_kib"] == 0
+    # long main loops still get equal ranges: FFN-up forward at 2048 rows (96 tiles), grad_w at 1024 rows (36 tiles of 32 k-blocks)
+    assert plan(SMS, 2048, F, D, False, True, has_epilogue=True)["splits"] >= 2
+    assert plan(SMS, D, F, 1024, True, True, accumulate=True)["kernel"] == "pair"
+
+
 def test_small_and_odd_shapes(plan):
     assert plan(SMS, 64, 96, 32, False, True, True)["kernel"] == "single"      # the reference's test shapes: ragged tiles
     assert plan(SMS, 64, 32, 256, False, True, True)["grid"] == 1

@@ -224,8 +224,8 @@ inline GemmPlan plan_gemm(const GemmPlanInput &in)
         if (!in.accumulate && p.num_kb <= 32 && tiles128 <= in.num_sms) {
             pair = false;
             force128 = true;
-        } else if (pair_tiles < max_pairs && p.num_kb >= 4 * kb_each && split_allowed) {
-            pair = false;
+        } else if (pair_tiles < max_pairs && p.num_kb >= 4 * kb_each && kb_each <= 16 && split_allowed) {
+            pair = false;   // (with longer ranges the pair kernel's better main loop wins again: attention projection grad_w at 8192 rows)
         }
     }
     if (pair) {

@@ -59,6 +59,7 @@ def test_small_problems_avoid_the_fixed_cost_of_cut_ranges(plan):
     # long main loops still get equal ranges: FFN-up forward at 2048 rows (96 tiles), grad_w at 1024 rows (36 tiles of 32 k-blocks)
     assert plan(SMS, 2048, F, D, False, True, has_epilogue=True)["splits"] >= 2
     assert plan(SMS, D, F, 1024, True, True, accumulate=True)["kernel"] == "pair"
+    assert plan(SMS, D, D, 8192, True, True, accumulate=True)["kernel"] == "pair"   # 9 tiles, but 32 k-blocks per pair: worth cutting
 
 
 def test_small_and_odd_shapes(plan):

@@ -28,7 +28,7 @@ EXPORTED_SYMBOLS = [
     "gptb200_ctx_set_stream", "gptb200_ctx_set_option", "gptb200_ctx_synchronize", "gptb200_ctx_launch_count", "gptb200_ctx_tensor_map_encodes", "gptb200_ctx_read_trace",
     "gptb200_status_string", "gptb200_last_error", "gptb200_plan_gemm", "gptb200_plan_decode", "gptb200_selftest_wait_timeout",
     "gptb200_linear_forward", "gptb200_linear_backward", "gptb200_linear_backward_weights", "gptb200_linear_backward_input",
-    "gptb200_linear_backward_input_gelu",
+    "gptb200_linear_backward_input_gelu", "gptb200_gemm_batched",
     "gptb200_gelu_backward",
     "gptb200_unembed_forward", "gptb200_unembed_backward",
     "gptb200_malloc", "gptb200_free", "gptb200_memset", "gptb200_memcpy_h2d", "gptb200_memcpy_d2h",
@@ -83,6 +83,8 @@ def load_library(path: str | None = None) -> ctypes.CDLL:
         "gptb200_linear_backward_weights": (i, [vp, fp, fp, fp, fp, i, i, i]),
         "gptb200_linear_backward_input": (i, [vp, fp, fp, fp, i, i, i]),
         "gptb200_linear_backward_input_gelu": (i, [vp, fp, fp, fp, fp, i, i, i]),
+        "gptb200_gemm_batched": (i, [vp, fp, fp, fp, i, i, i, i, i, i, i, ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(ctypes.c_longlong),
+                                     ctypes.POINTER(ctypes.c_longlong)]),
         "gptb200_gelu_backward": (i, [vp, fp, fp, fp, i, i]),
         "gptb200_unembed_forward": (i, [vp, fp, fp, fp, i, i, i]),
         "gptb200_unembed_backward": (i, [vp, fp, fp, fp, fp, fp, i, i, i]),
@@ -266,6 +268,13 @@ class Backend:
         """grad_x = (grad_y . w^T) * gelu_tanh'(pre_act): device_linear_backward's input half and device_activation_backward in one."""
         self._check(self._lib.gptb200_linear_backward_input_gelu(self._ctx, _ptr(grad_x), _ptr(grad_y), _ptr(w), _ptr(pre_act), m, k, n),
                     "gptb200_linear_backward_input_gelu")
+
+    def gemm_batched(self, out, a, b, m: int, n: int, k: int, a_mn: bool, b_mn: bool, batch_inner: int, batch_outer: int, a_strides, b_strides,
+                     out_strides) -> None:
+        """batch_inner * batch_outer products out[z] = a[z] . b[z] in one launch; strides = (row pitch, inner, outer) in floats."""
+        arr = lambda s: (ctypes.c_longlong * 3)(*[int(v) for v in s])
+        self._check(self._lib.gptb200_gemm_batched(self._ctx, _ptr(out), _ptr(a), _ptr(b), m, n, k, int(a_mn), int(b_mn), batch_inner, batch_outer,
+                                                   arr(a_strides), arr(b_strides), arr(out_strides)), "gptb200_gemm_batched")
 
     def device_activation_backward(self, grad_x, grad_y, x, batch_size: int, seq_len: int, output_size: int) -> None:
         self._check(self._lib.gptb200_gelu_backward(self._ctx, _ptr(grad_x), _ptr(grad_y), _ptr(x), batch_size * seq_len,

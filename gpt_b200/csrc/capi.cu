@@ -95,6 +95,28 @@ int make_pre_tmap(gptb200_ctx *ctx, CUtensorMap *map, const void *base, long lon
     return GPTB200_OK;
 }
 
+// 4-D tensor map of a batched operand or output: (cols, inner batch, rows, outer batch) with element strides (1, stride_inner,
+// ld, stride_outer); box cols x rows of one batch.  swizzle: 0 = 128-byte (K-major operands, outputs), 1 = 128-byte with 32-byte
+// atoms (MN-major operands).
+int make_batched_tmap(gptb200_ctx *ctx, CUtensorMap *map, const float *base, long long cols, long long rows, long long inner, long long outer,
+                      long long ld, long long stride_inner, long long stride_outer, int box_cols, int box_rows, int swizzle)
+{
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(outer)};
+    if (inner == 1) stride_inner = ld;   // the coordinate is always 0: keep the strides in growing order
+    if (outer == 1) stride_outer = ld * rows;
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(stride_inner) * 4, static_cast<cuuint64_t>(ld) * 4, static_cast<cuuint64_t>(stride_outer) * 4};
+    cuuint32_t box[4] = {static_cast<cuuint32_t>(box_cols), 1, static_cast<cuuint32_t>(box_rows), 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    const CUresult r = ctx->encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                   swizzle ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    ctx->tmap_encodes++;
+    if (r != CUDA_SUCCESS)
+        return fail(ctx, GPTB200_ERR_CUDA, "cuTensorMapEncodeTiled (batched) failed (%d) cols=%lld rows=%lld batches=%lldx%lld strides=%lld,%lld,%lld", int(r), cols,
+                    rows, inner, outer, stride_inner, ld, stride_outer);
+    return GPTB200_OK;
+}
+
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 struct GemmCall {
@@ -596,6 +618,51 @@ int run_bias_grad(gptb200_ctx *ctx, float *gb, const float *gy, int M, int N)
     return GPTB200_OK;
 }
 
+// `batches` GEMMs of one shape in one launch of the CTA-pair kernel (whole tiles per pair, store epilogue).  Operands are
+// described as stored: a K-major operand has `rows` = its free extent and k columns, an MN-major operand k rows and its free
+// extent as columns; ld = row pitch, stride_inner / stride_outer = distance between consecutive inner / outer batches (floats).
+struct BatchedOperand {
+    const float *base;
+    bool mn;
+    long long ld, stride_inner, stride_outer;
+};
+
+int run_gemm_batched(gptb200_ctx *ctx, float *out, long long out_ld, long long out_si, long long out_so, const BatchedOperand &a, const BatchedOperand &b,
+                     int M, int N, int K, int inner, int outer)
+{
+    if (M <= 0 || N <= 0 || K <= 0 || inner <= 0 || outer <= 0) return fail(ctx, GPTB200_ERR_INVALID_ARG, "batched GEMM with an empty dimension");
+    if (a.mn && !b.mn) return fail(ctx, GPTB200_ERR_INVALID_ARG, "operand forms (MN-major, K-major) do not occur");
+    const bool x3 = ctx->mode == GPTB200_MODE_3XTF32;
+    GemmParams p{};
+    p.M = M; p.N = N; p.K = K;
+    p.tiles_m = (M + kBM - 1) / kBM;
+    p.tiles_n = (N + 255) / 256;
+    p.num_kb = (K + kBK - 1) / kBK;
+    p.kb_per_split = p.num_kb;
+    p.splits = 1;
+    p.status = ctx->d_status;
+    p.epi_mode = EPI_STORE;
+    p.batches = inner * outer;
+    p.batch_inner = inner;
+    const long long tiles = 1LL * ((p.tiles_m + 1) / 2) * p.tiles_n * p.batches;
+    p.sk_total = tiles * p.num_kb;
+    p.sk_unit = p.num_kb;                                   // whole tiles per pair
+    const int pairs = static_cast<int>(std::min<long long>(std::max(1, ctx->num_sms / 2), tiles));
+    CUtensorMap ta, tb, to;
+    int rc = a.mn ? make_batched_tmap(ctx, &ta, a.base, M, K, inner, outer, a.ld, a.stride_inner, a.stride_outer, 32, kBK, 1)
+                  : make_batched_tmap(ctx, &ta, a.base, K, M, inner, outer, a.ld, a.stride_inner, a.stride_outer, kBK, kBM, 0);
+    if (rc) return rc;
+    rc = b.mn ? make_batched_tmap(ctx, &tb, b.base, N, K, inner, outer, b.ld, b.stride_inner, b.stride_outer, 32, kBK, 1)
+              : make_batched_tmap(ctx, &tb, b.base, K, N, inner, outer, b.ld, b.stride_inner, b.stride_outer, kBK, 128, 0);
+    if (rc) return rc;
+    rc = make_batched_tmap(ctx, &to, out, N, M, inner, outer, out_ld, out_si, out_so, PairCfg<false>::kStageCols, 32, 0);
+    if (rc) return rc;
+    const cudaError_t e = x3 ? launch_pair<true>(ctx, a.mn, b.mn, ta, tb, to, to, to, p, 2 * pairs) : launch_pair<false>(ctx, a.mn, b.mn, ta, tb, to, to, to, p, 2 * pairs);
+    ctx->launches++;
+    CUDA_TRY(ctx, e);
+    return GPTB200_OK;
+}
+
 int check_dims(gptb200_ctx *ctx, int m, int a, int b)
 {
     if (!ctx) return GPTB200_ERR_INVALID_ARG;
@@ -941,6 +1008,16 @@ int gptb200_linear_backward(gptb200_ctx *ctx, float *grad_x, float *grad_w, floa
     rc = gptb200_linear_backward_input(ctx, grad_x, grad_y, w, m, k, n);
     if (rc) return rc;
     return gptb200_linear_backward_weights(ctx, grad_w, grad_b, grad_y, x, m, k, n);
+}
+
+int gptb200_gemm_batched(gptb200_ctx *ctx, float *out, const float *a, const float *b, int m, int n, int k, int a_mn_major, int b_mn_major, int batch_inner,
+                         int batch_outer, const long long *a_strides3, const long long *b_strides3, const long long *out_strides3)
+{
+    if (!ctx) return GPTB200_ERR_INVALID_ARG;
+    if (!out || !a || !b || !a_strides3 || !b_strides3 || !out_strides3) return fail(ctx, GPTB200_ERR_INVALID_ARG, "null pointer");
+    const BatchedOperand oa{a, a_mn_major != 0, a_strides3[0], a_strides3[1], a_strides3[2]};
+    const BatchedOperand ob{b, b_mn_major != 0, b_strides3[0], b_strides3[1], b_strides3[2]};
+    return run_gemm_batched(ctx, out, out_strides3[0], out_strides3[1], out_strides3[2], oa, ob, m, n, k, batch_inner, batch_outer);
 }
 
 int gptb200_gelu_backward(gptb200_ctx *ctx, float *grad_x, const float *grad_y, const float *x, int m, int n)

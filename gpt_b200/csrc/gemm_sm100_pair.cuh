@@ -522,6 +522,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             PairWork work = my_work();
             int tm2, tn, kb0, kb1;
             while (ok && work.next(tm2, tn, kb0, kb1)) {
+                const int z = p.batches > 1 ? tn / p.tiles_n : 0;                     // batched form: the tile columns of all batches are numbered through
+                if (p.batches > 1) tn -= z * p.tiles_n;
+                const int zi = p.batches > 1 ? z % p.batch_inner : 0, zo = p.batches > 1 ? z / p.batch_inner : 0;
                 const int m0 = tm2 * 2 * kBM + static_cast<int>(rank) * kBM;          // the rows this CTA owns
                 const int n0 = tn * BN + static_cast<int>(rank) * C::kBRows;          // the half of B this CTA loads
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
@@ -540,7 +543,20 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     const uint32_t a_dst = smem_base + s * C::kHiBytes;
                     const uint32_t b_dst = a_dst + kATileBytes;
                     const int k0 = kb * kBK;
-                    if (lane < kBoxesA) {
+                    if (p.batches > 1) {
+                        if (lane < kBoxesA) {
+                            if (A_MN)
+                                ptx::tma_load_4d_pair(a_dst + lane * kBoxBytesMN, &tmap_a, m0 + 32 * lane, zi, k0, zo, bar);
+                            else
+                                ptx::tma_load_4d_pair(a_dst, &tmap_a, k0, zi, m0, zo, bar);
+                        } else if (lane < kBoxesA + kBoxesB) {
+                            const int j = lane - kBoxesA;
+                            if (B_MN)
+                                ptx::tma_load_4d_pair(b_dst + j * kBoxBytesMN, &tmap_b, n0 + 32 * j, zi, k0, zo, bar);
+                            else
+                                ptx::tma_load_4d_pair(b_dst, &tmap_b, k0, zi, n0, zo, bar);
+                        }
+                    } else if (lane < kBoxesA) {
                         if (A_MN)
                             ptx::tma_load_2d_pair(a_dst + lane * kBoxBytesMN, &tmap_a, m0 + 32 * lane, k0, bar);
                         else
@@ -676,6 +692,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         const unsigned int sk_epoch = p.sk_flags ? __ldcg(p.sk_state) + 1u : 0u;
         const uint32_t leader_tmem_empty[2] = {ptx::map_to_cta(tmem_empty_bar(0), 0u), ptx::map_to_cta(tmem_empty_bar(1), 0u)};
 
+        int ezi = 0, ezo = 0;   // batched form: batch coordinates of the tile being written
         // bias_lane: bias[col0 + lane], fetched when the tile was started
         auto emit = [&](float (&v)[32], int row0, int col0, float bias_lane) {
             if (p.bias && p.epi_mode == EPI_STORE) {
@@ -709,7 +726,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 __syncwarp();
                 if (lane == 0) {
                     if (row0 < p.M && col0 + h * C::kStageCols < p.N) {
-                        if (p.epi_mode == EPI_ACCUM)
+                        if (p.batches > 1)
+                            ptx::tma_store_4d(&tmap_out, col0 + h * C::kStageCols, ezi, row0, ezo, buf);
+                        else if (p.epi_mode == EPI_ACCUM)
                             ptx::tma_reduce_add_3d(&tmap_out, col0 + h * C::kStageCols, row0, 0, buf);
                         else
                             ptx::tma_store_3d(&tmap_out, col0 + h * C::kStageCols, row0, 0, buf);
@@ -739,6 +758,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         PairWork work = my_work();
         int tm2, tn, kb0, kb1;
         while (ok && work.next(tm2, tn, kb0, kb1)) {
+            if (p.batches > 1) {
+                const int z = tn / p.tiles_n;
+                tn -= z * p.tiles_n;
+                ezi = z % p.batch_inner;
+                ezo = z / p.batch_inner;
+            }
             const int row0 = tm2 * 2 * kBM + static_cast<int>(rank) * kBM + q * 32;
             const int n0 = tn * BN + col_base;
             const bool owner = kb0 == 0;              // this pair writes the tile's output

@@ -125,6 +125,26 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void *tmap,
         : "memory");
 }
 
+// The same for a 4-D tensor map (x innermost): batched GEMMs address (column, row, inner batch index, outer batch index).
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const void *tmap, int32_t x, int32_t y, int32_t z, int32_t w, uint32_t cluster_bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+        :
+        : "r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(z), "r"(w), "r"(cluster_bar)
+        : "memory");
+}
+
+// 4-D tiled store shared -> global (bulk async group).
+__device__ __forceinline__ void tma_store_4d(const void *tmap, int32_t x, int32_t y, int32_t z, int32_t w, uint32_t src)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];"
+        :
+        : "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(z), "r"(w), "r"(src)
+        : "memory");
+}
+
 // 3-D tiled store shared -> global (bulk async group); elements outside the tensor are dropped.
 __device__ __forceinline__ void tma_store_3d(const void *tmap, int32_t x, int32_t y, int32_t z, uint32_t src)
 {

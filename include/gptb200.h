@@ -147,6 +147,15 @@ int gptb200_linear_backward_input(gptb200_ctx *ctx, float *grad_x, const float *
  * two calls up to the rounding of the derivative (fast exp / division, 1-2 ulp). */
 int gptb200_linear_backward_input_gelu(gptb200_ctx *ctx, float *grad_x, const float *grad_y, const float *w, const float *pre_act, int m, int k, int n);
 
+/* batch_inner * batch_outer independent products out[z] = a[z] . b[z] of one shape (m x n x k) in ONE launch of the CTA-pair
+ * tensor-core kernel, in the context's precision mode (no counterpart in the reference, whose attention is scalar code:
+ * cuda/kernels/attention.cu).  An operand is described as stored: K-major (a: [m][k], b: [n][k]) or MN-major (a: [k][m],
+ * b: [k][n]); strides3 = {row pitch, distance between consecutive inner batches, distance between consecutive outer batches}
+ * in floats, each a multiple of 4, in growing order -- which lets an operand be one head of packed rows (inner batch = head,
+ * stride 64; row pitch 3 * d_model; outer batch = sequence).  out [m][n] is overwritten. */
+int gptb200_gemm_batched(gptb200_ctx *ctx, float *out, const float *a, const float *b, int m, int n, int k, int a_mn_major, int b_mn_major, int batch_inner,
+                         int batch_outer, const long long *a_strides3, const long long *b_strides3, const long long *out_strides3);
+
 /* ---- IGPTBackend::device_activation_backward
  *      (backend_interface.h:150-159, cuda/kernels/linear.cu:162-203, cpu/cpu_backend.cpp:268-287)
  *   grad_x = grad_y * gelu_tanh'(x), all [m x n]. */

@@ -289,6 +289,9 @@ def run_ours(args):
     be = gpt_b200.Backend(local_rank, stream.cuda_stream, mode)
     if args.max_sms:
         be.set_option("max_sms", args.max_sms)
+    for kv in args.ctx_option:
+        key, _, value = kv.partition("=")
+        be.set_option(key, int(value))
     M, K, N = args.m_per_gpu, K_IN, N_OUT
     flops_per_step = 6.0 * M * K * N
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
@@ -523,6 +526,8 @@ def train_record(torch, dist, world, rank, dev, mode_name="3xtf32", global_batch
     model.init(0.0, 0.02)           # same seed on every rank: identical replicas
     model.set_fused_cross_entropy(os.environ.get("GPTB200_FUSED_CE", "1") != "0")   # logits -> their gradient in place, no probability tensor
     model.set_fused_gelu_backward(os.environ.get("GPTB200_FUSED_GELU", "1") != "0")  # GELU' in the epilogue of the down projection's grad_x GEMM
+    for kv in filter(None, os.environ.get("GPTB200_CTX_OPTIONS", "").split(",")):   # experiments: gptb200_ctx_set_option pairs key=value
+        model.set_option(kv.partition("=")[0], int(kv.partition("=")[2]))
     model.set_size(B, T)
 
     class _Raw:   # torch view of the packed gradient buffer (no copy) for the collectives

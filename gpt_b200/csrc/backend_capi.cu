@@ -6,6 +6,7 @@
 
 #include "ctx_internal.h"
 #include "backend_ops.cuh"
+#include "attention_gemm.cuh"
 #include "attention_tiled.cuh"
 #include "layernorm_warp.cuh"
 #include "optimizer_fused.cuh"
@@ -102,6 +103,114 @@ int attention64_backward(gptb200_ctx *ctx, float *gqkv, float *dcache, const flo
     ops::attention64_backward_dq_kernel<<<grid, ops::kFaThreads, ops::kFaDqSmem, ctx->stream>>>(gqkv, dcache, lse, gy, qkv, seq_len, d, heads);
     ops::attention64_backward_dkv_kernel<<<grid, ops::kFaThreads, ops::kFaDkvSmem, ctx->stream>>>(gqkv, dcache, lse, gy, qkv, seq_len, d, heads);
     return launched(ctx, 3);
+}
+
+// Scratch of the tensor-core attention: `bytes` of device memory, kept by the context.  false (and no error left behind) when the
+// device cannot give it: the caller then takes the fp32 FMA kernels, which need none.
+bool attention_scratch(gptb200_ctx *ctx, size_t bytes)
+{
+    if (bytes <= ctx->attn_ws_bytes) return true;
+    if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) return false;   // queued launches may still use the old buffer
+    if (ctx->attn_ws) cudaFree(ctx->attn_ws);
+    ctx->attn_ws = nullptr;
+    ctx->attn_ws_bytes = 0;
+    if (cudaMalloc(&ctx->attn_ws, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        ctx->attn_ws = nullptr;
+        return false;
+    }
+    ctx->attn_ws_bytes = bytes;
+    return true;
+}
+
+bool attention_gemm_applies(const gptb200_ctx *ctx, int seq_len, int d, int heads)
+{
+    // automatic (1): with the linear layers in TF32 mode, whose accuracy these products then share; in 3xTF32 mode the products are
+    // about 2e-6 from the exact result where the fp32 FMA kernels are 7e-7, which a whole-model gradient check to 1e-5 does not absorb
+    const bool on = ctx->attention_gemm == 2 || (ctx->attention_gemm == 1 && ctx->mode == GPTB200_MODE_TF32);
+    return on && d / heads == 64 && seq_len % 4 == 0 && seq_len >= 4 && seq_len <= 1024;
+}
+
+// Sequences per group of launches: bounds the scratch (one score buffer forward, two backward).  Groups small enough for the
+// scores to stay in L2 were measured slower than one group (GPT-2 124M, 64 sequences of 256 tokens, TF32: forward 196 us in one
+// group, 251 us in groups of 50 MB): these launches are bound by their epilogues and fixed costs, not by DRAM.
+int attention_group(const gptb200_ctx *ctx, int batch, int seq_len, int heads, int buffers)
+{
+    const double per_seq = 4.0 * heads * seq_len * seq_len * buffers;
+    const long long g = static_cast<long long>(ctx->attention_group_mb * 1048576.0 / per_seq);
+    return static_cast<int>(std::max(1LL, std::min<long long>(batch, g)));
+}
+
+// Head slices of packed rows and the score buffer s[b][q][h][k] as batched operands (row pitch, head stride, sequence stride).
+BatchedOperand head_slice(const float *base, bool mn, int row_floats, int seq_len) { return {base, mn, row_floats, 64, 1LL * seq_len * row_floats}; }
+BatchedOperand score_rows(const float *s, bool mn, int seq_len, int heads) { return {s, mn, 1LL * heads * seq_len, seq_len, 1LL * seq_len * heads * seq_len}; }
+
+template <typename... Args>
+void launch_scores_softmax(gptb200_ctx *ctx, int T, unsigned blocks, Args... args)
+{
+    if (T <= 256)
+        ops::attention_scores_softmax_kernel<2><<<blocks, ops::kScoreRowsPerBlock * 32, 0, ctx->stream>>>(args...);
+    else if (T <= 512)
+        ops::attention_scores_softmax_kernel<4><<<blocks, ops::kScoreRowsPerBlock * 32, 0, ctx->stream>>>(args...);
+    else
+        ops::attention_scores_softmax_kernel<8><<<blocks, ops::kScoreRowsPerBlock * 32, 0, ctx->stream>>>(args...);
+}
+
+int attention_gemm_forward(gptb200_ctx *ctx, float *y, float *lse, const float *qkv, int batch, int seq_len, int d, int heads)
+{
+    const int T = seq_len, G = attention_group(ctx, batch, T, heads, 1);
+    if (!attention_scratch(ctx, sizeof(float) * G * T * heads * T)) return -1;
+    float *s = ctx->attn_ws;
+    const long long sl = 1LL * heads * T, so = 1LL * T * heads * T;
+    for (int b0 = 0; b0 < batch; b0 += G) {
+        const int nb = std::min(G, batch - b0);
+        const float *x = qkv + 1LL * b0 * T * 3 * d;
+        int rc = run_gemm_batched(ctx, s, sl, T, so, head_slice(x, false, 3 * d, T), head_slice(x + d, false, 3 * d, T), T, T, 64, heads, nb);
+        if (rc) return rc;
+        const long long rows = 1LL * nb * T * heads;
+        const unsigned blocks = static_cast<unsigned>((rows + ops::kScoreRowsPerBlock - 1) / ops::kScoreRowsPerBlock);
+        launch_scores_softmax(ctx, T, blocks, s, lse + 1LL * b0 * T * heads, T, heads, 0.125f, rows);
+        rc = launched(ctx);
+        if (rc) return rc;
+        rc = run_gemm_batched(ctx, y + 1LL * b0 * T * d, d, 64, 1LL * T * d, score_rows(s, false, T, heads), head_slice(x + 2 * d, true, 3 * d, T), T, 64, T, heads, nb);
+        if (rc) return rc;
+    }
+    return GPTB200_OK;
+}
+
+int attention_gemm_backward(gptb200_ctx *ctx, float *gqkv, float *dcache, const float *lse, const float *gy, const float *y, const float *qkv, int batch,
+                            int seq_len, int d, int heads)
+{
+    const int T = seq_len, G = attention_group(ctx, batch, T, heads, 2);
+    if (!attention_scratch(ctx, 2 * sizeof(float) * G * T * heads * T)) return -1;
+    float *s = ctx->attn_ws, *dp = ctx->attn_ws + 1LL * G * T * heads * T;
+    ops::attention64_rowsum_kernel<<<static_cast<unsigned>((1LL * batch * T + 7) / 8), 256, 0, ctx->stream>>>(dcache, gy, y, 1LL * batch * T, d, heads);
+    int rc = launched(ctx);
+    if (rc) return rc;
+    const long long sl = 1LL * heads * T, so = 1LL * T * heads * T, xo = 1LL * T * 3 * d;
+    for (int b0 = 0; b0 < batch; b0 += G) {
+        const int nb = std::min(G, batch - b0);
+        const float *x = qkv + b0 * xo, *g = gy + 1LL * b0 * T * d;
+        float *gx = gqkv + b0 * xo;
+        rc = run_gemm_batched(ctx, s, sl, T, so, head_slice(x, false, 3 * d, T), head_slice(x + d, false, 3 * d, T), T, T, 64, heads, nb);
+        if (rc) return rc;
+        rc = run_gemm_batched(ctx, dp, sl, T, so, head_slice(g, false, d, T), head_slice(x + 2 * d, false, 3 * d, T), T, T, 64, heads, nb);
+        if (rc) return rc;
+        const long long rows = 1LL * nb * T * heads;
+        const unsigned blocks = static_cast<unsigned>((rows + ops::kScoreRowsPerBlock - 1) / ops::kScoreRowsPerBlock);
+        ops::attention_scores_backward_kernel<<<blocks, ops::kScoreRowsPerBlock * 32, 0, ctx->stream>>>(s, dp, lse + 1LL * b0 * T * heads,
+                                                                                                     dcache + 1LL * b0 * T * heads, T, heads, 0.125f, rows);
+        rc = launched(ctx);
+        if (rc) return rc;
+        // grad_v = P^T . grad_y,  grad_k = dS^T . Q,  grad_q = dS . K  (dS carries the 1 / 8)
+        rc = run_gemm_batched(ctx, gx + 2 * d, 3 * d, 64, xo, score_rows(s, true, T, heads), head_slice(g, true, d, T), T, 64, T, heads, nb);
+        if (rc) return rc;
+        rc = run_gemm_batched(ctx, gx + d, 3 * d, 64, xo, score_rows(dp, true, T, heads), head_slice(x, true, 3 * d, T), T, 64, T, heads, nb);
+        if (rc) return rc;
+        rc = run_gemm_batched(ctx, gx, 3 * d, 64, xo, score_rows(dp, false, T, heads), head_slice(x + d, true, 3 * d, T), T, 64, T, heads, nb);
+        if (rc) return rc;
+    }
+    return GPTB200_OK;
 }
 
 }  // namespace
@@ -236,6 +345,10 @@ int gptb200_attention_forward(gptb200_ctx *ctx, float *y, float *logsumexp, cons
         case 16: return attention_forward_t<16, 1>(ctx, y, logsumexp, qkv, batch, seq_len, d, heads);
         case 32: return attention_forward_t<32, 1>(ctx, y, logsumexp, qkv, batch, seq_len, d, heads);
         case 64:
+            if (attention_gemm_applies(ctx, seq_len, d, heads) && aligned16_all({y, qkv})) {
+                const int rc = attention_gemm_forward(ctx, y, logsumexp, qkv, batch, seq_len, d, heads);
+                if (rc >= 0) return rc;   // -1: no memory for the score matrices; the FMA kernels need none
+            }
             if (ctx->attention_tiled && d % 4 == 0 && aligned16_all({y, qkv})) return attention64_forward(ctx, y, logsumexp, qkv, batch, seq_len, d, heads);
             return attention_forward_t<64, 2>(ctx, y, logsumexp, qkv, batch, seq_len, d, heads);
         case 128: return attention_forward_t<128, 4>(ctx, y, logsumexp, qkv, batch, seq_len, d, heads);
@@ -249,6 +362,10 @@ int gptb200_attention_backward(gptb200_ctx *ctx, float *grad_qkv, float *d_cache
     NEED(ctx, batch >= 0 && seq_len >= 0 && d >= 0 && heads > 0 && d % heads == 0);
     if (1LL * batch * seq_len * d == 0) return GPTB200_OK;
     NEED(ctx, grad_qkv && d_cache && logsumexp && grad_y && y && qkv && batch <= 65535 && heads <= 65535);
+    if (attention_gemm_applies(ctx, seq_len, d, heads) && aligned16_all({grad_qkv, grad_y, y, qkv})) {
+        const int rc = attention_gemm_backward(ctx, grad_qkv, d_cache, logsumexp, grad_y, y, qkv, batch, seq_len, d, heads);
+        if (rc >= 0) return rc;
+    }
     if (d / heads == 64 && ctx->attention_tiled && d % 4 == 0 && aligned16_all({grad_qkv, grad_y, y, qkv}))
         return attention64_backward(ctx, grad_qkv, d_cache, logsumexp, grad_y, y, qkv, batch, seq_len, d, heads);
     const long long rh = 1LL * batch * seq_len * heads;

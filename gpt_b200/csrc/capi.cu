@@ -101,9 +101,15 @@ int make_pre_tmap(gptb200_ctx *ctx, CUtensorMap *map, const void *base, long lon
 int make_batched_tmap(gptb200_ctx *ctx, CUtensorMap *map, const float *base, long long cols, long long rows, long long inner, long long outer,
                       long long ld, long long stride_inner, long long stride_outer, int box_cols, int box_rows, int swizzle)
 {
-    cuuint64_t dims[4] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(outer)};
     if (inner == 1) stride_inner = ld;   // the coordinate is always 0: keep the strides in growing order
     if (outer == 1) stride_outer = ld * rows;
+    const TmapKey key{reinterpret_cast<uintptr_t>(base), cols, rows, ld, box_cols, box_rows, 4 + swizzle, inner, outer, stride_inner, stride_outer};
+    const auto hit = ctx->tmaps.find(key);
+    if (hit != ctx->tmaps.end()) {
+        *map = hit->second;
+        return GPTB200_OK;
+    }
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(outer)};
     cuuint64_t strides[3] = {static_cast<cuuint64_t>(stride_inner) * 4, static_cast<cuuint64_t>(ld) * 4, static_cast<cuuint64_t>(stride_outer) * 4};
     cuuint32_t box[4] = {static_cast<cuuint32_t>(box_cols), 1, static_cast<cuuint32_t>(box_rows), 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
@@ -114,8 +120,12 @@ int make_batched_tmap(gptb200_ctx *ctx, CUtensorMap *map, const float *base, lon
     if (r != CUDA_SUCCESS)
         return fail(ctx, GPTB200_ERR_CUDA, "cuTensorMapEncodeTiled (batched) failed (%d) cols=%lld rows=%lld batches=%lldx%lld strides=%lld,%lld,%lld", int(r), cols,
                     rows, inner, outer, stride_inner, ld, stride_outer);
+    if (ctx->tmaps.size() >= kTmapCacheMax) ctx->tmaps.clear();
+    ctx->tmaps.emplace(key, *map);
     return GPTB200_OK;
 }
+
+constexpr double kExact3xFlops = 6.0e9;   // launches up to this size take the TF32 correction terms when "exact3x" is automatic
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -516,6 +526,10 @@ int run_gemm(gptb200_ctx *ctx, const GemmCall &c, bool *dbias_fused = nullptr, b
                 }
             }
         }
+        // 3xTF32 correction terms: as TF32 products of fp32 low-part tiles (error about 2^-22 per term, 12 instructions per k-block)
+        // for launches too small to be bound by the tensor pipe or the power limit, where the extra instructions cost a few
+        // percent; as one bf16 chain (2^-20, 8 instructions) for the large ones, where they cost 8 %.
+        if (x3 && !p.pre_operand && (ctx->exact3x == 1 || (ctx->exact3x == 2 && 2.0 * c.M * c.N * c.K <= kExact3xFlops))) p.exact3x = 1;
         if (pl.sk_max_share > 1) {
             p.sk_slots = ctx->ws;
             p.sk_dbias = ctx->ws + pl.workspace_bytes / sizeof(float);
@@ -618,17 +632,9 @@ int run_bias_grad(gptb200_ctx *ctx, float *gb, const float *gy, int M, int N)
     return GPTB200_OK;
 }
 
-// `batches` GEMMs of one shape in one launch of the CTA-pair kernel (whole tiles per pair, store epilogue).  Operands are
-// described as stored: a K-major operand has `rows` = its free extent and k columns, an MN-major operand k rows and its free
-// extent as columns; ld = row pitch, stride_inner / stride_outer = distance between consecutive inner / outer batches (floats).
-struct BatchedOperand {
-    const float *base;
-    bool mn;
-    long long ld, stride_inner, stride_outer;
-};
-
-int run_gemm_batched(gptb200_ctx *ctx, float *out, long long out_ld, long long out_si, long long out_so, const BatchedOperand &a, const BatchedOperand &b,
-                     int M, int N, int K, int inner, int outer)
+// `batches` GEMMs of one shape in one launch of the CTA-pair kernel (whole tiles per pair, store epilogue).
+int run_gemm_batched_impl(gptb200_ctx *ctx, float *out, long long out_ld, long long out_si, long long out_so, const BatchedOperand &a,
+                          const BatchedOperand &b, int M, int N, int K, int inner, int outer)
 {
     if (M <= 0 || N <= 0 || K <= 0 || inner <= 0 || outer <= 0) return fail(ctx, GPTB200_ERR_INVALID_ARG, "batched GEMM with an empty dimension");
     if (a.mn && !b.mn) return fail(ctx, GPTB200_ERR_INVALID_ARG, "operand forms (MN-major, K-major) do not occur");
@@ -644,6 +650,8 @@ int run_gemm_batched(gptb200_ctx *ctx, float *out, long long out_ld, long long o
     p.epi_mode = EPI_STORE;
     p.batches = inner * outer;
     p.batch_inner = inner;
+    if (N <= 128) p.mma_n = (N + 31) / 32 * 32;
+    p.exact3x = (x3 && ctx->batched_exact3x) ? 1 : 0;
     const long long tiles = 1LL * ((p.tiles_m + 1) / 2) * p.tiles_n * p.batches;
     p.sk_total = tiles * p.num_kb;
     p.sk_unit = p.num_kb;                                   // whole tiles per pair
@@ -674,6 +682,14 @@ int check_dims(gptb200_ctx *ctx, int m, int a, int b)
 }
 
 }  // namespace
+
+namespace gptb200 {
+int run_gemm_batched(gptb200_ctx *ctx, float *out, long long out_ld, long long out_si, long long out_so, const BatchedOperand &a, const BatchedOperand &b,
+                     int M, int N, int K, int inner, int outer)
+{
+    return run_gemm_batched_impl(ctx, out, out_ld, out_si, out_so, a, b, M, N, K, inner, outer);
+}
+}  // namespace gptb200
 
 extern "C" {
 
@@ -738,6 +754,7 @@ int gptb200_ctx_destroy(gptb200_ctx *ctx)
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->ws) cudaFree(ctx->ws);
+    if (ctx->attn_ws) cudaFree(ctx->attn_ws);
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->d_pair_flags) cudaFree(ctx->d_pair_flags);
     if (ctx->d_trace) cudaFree(ctx->d_trace);
@@ -777,6 +794,24 @@ int gptb200_ctx_set_option(gptb200_ctx *ctx, const char *key, int value)
     if (!strcmp(key, "max_sms")) {
         if (value < 0) return fail(ctx, GPTB200_ERR_INVALID_ARG, "max_sms must be >= 0");
         ctx->max_sms = value;
+        return GPTB200_OK;
+    }
+    if (!strcmp(key, "exact3x")) {
+        if (value < 0 || value > 2) return fail(ctx, GPTB200_ERR_INVALID_ARG, "exact3x: 0 never, 1 always, 2 automatic");
+        ctx->exact3x = value;
+        return GPTB200_OK;
+    }
+    if (!strcmp(key, "batched_exact3x")) {
+        ctx->batched_exact3x = value != 0;
+        return GPTB200_OK;
+    }
+    if (!strcmp(key, "attention_group_mb")) {
+        if (value < 1) return fail(ctx, GPTB200_ERR_INVALID_ARG, "attention_group_mb must be positive");
+        ctx->attention_group_mb = value;
+        return GPTB200_OK;
+    }
+    if (!strcmp(key, "attention_gemm")) {
+        ctx->attention_gemm = value;
         return GPTB200_OK;
     }
     if (!strcmp(key, "attention_tiled")) {

@@ -22,14 +22,20 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
 struct TmapKey {
     uintptr_t base;
     long long d0, d1, d2;   // extents (innermost first; d2 = 0 for 2-D maps)
-    int box0, box1, kind;   // kind: 0 K-major operand, 1 MN-major operand, 2 output
-    bool operator==(const TmapKey &o) const { return base == o.base && d0 == o.d0 && d1 == o.d1 && d2 == o.d2 && box0 == o.box0 && box1 == o.box1 && kind == o.kind; }
+    int box0, box1, kind;   // kind: 0 K-major operand, 1 MN-major operand, 2 output, 3 pre-split operand, 4 / 5 batched (4-D) with either swizzle
+    long long b0 = 0, b1 = 0, b2 = 0, b3 = 0;   // batched maps: inner and outer batch counts (d2 = row pitch), inner and outer batch strides
+    bool operator==(const TmapKey &o) const
+    {
+        return base == o.base && d0 == o.d0 && d1 == o.d1 && d2 == o.d2 && box0 == o.box0 && box1 == o.box1 && kind == o.kind && b0 == o.b0 && b1 == o.b1 &&
+               b2 == o.b2 && b3 == o.b3;
+    }
 };
 struct TmapKeyHash {
     size_t operator()(const TmapKey &k) const
     {
         uint64_t h = k.base * 0x9E3779B97F4A7C15ull;
-        for (uint64_t v : {uint64_t(k.d0), uint64_t(k.d1), uint64_t(k.d2), uint64_t(k.box0) << 32 | uint64_t(k.box1) << 8 | uint64_t(k.kind)})
+        for (uint64_t v : {uint64_t(k.d0), uint64_t(k.d1), uint64_t(k.d2), uint64_t(k.box0) << 32 | uint64_t(k.box1) << 8 | uint64_t(k.kind), uint64_t(k.b0), uint64_t(k.b1),
+                           uint64_t(k.b2), uint64_t(k.b3)})
             h = (h ^ v) * 0x100000001B3ull + (h >> 29);
         return size_t(h);
     }
@@ -70,6 +76,13 @@ struct gptb200_ctx {
                                            // then the decode kernel's tickets (one per column block, zero between launches)
     float *ws = nullptr;  // scratch: split-K partial tiles, partial rows of column reductions
     size_t ws_bytes = 0;
+    float *attn_ws = nullptr;   // scratch of the tensor-core attention: score and score-gradient matrices of all heads
+    size_t attn_ws_bytes = 0;
+    int exact3x = 2;               // 3xTF32 CTA-pair kernel: correction terms as TF32 products of fp32 low-part tiles instead of one bf16 chain:
+                                   // 0 never, 1 always, 2 for launches of at most 6 GFLOP
+    bool batched_exact3x = true;   // 3xTF32 batched products: TF32 correction terms (GemmParams::exact3x)
+    int attention_group_mb = 8192; // ... in groups of sequences whose score matrices take at most this many MB of scratch (fewer, larger launches are faster)
+    int attention_gemm = 1;     // head size 64: attention as batched tensor-core products + row kernels: 2 always, 1 in TF32 mode, 0 never (the fp32 FMA kernels)
     size_t ws_limit = size_t(1) << 30;
     EncodeTiledFn encode = nullptr;
     long long launches = 0;
@@ -93,6 +106,17 @@ inline int fail(gptb200_ctx *ctx, int code, const char *fmt, ...)
     }
     return code;
 }
+
+// out[z] = a[z] . b[z] for inner * outer batches in one launch of the CTA-pair kernel (capi.cu).  Operands as stored: K-major
+// (rows = free extent, k columns) or MN-major (k rows, free extent as columns); ld = row pitch, stride_inner / stride_outer =
+// distance between consecutive inner / outer batches, all in floats.
+struct BatchedOperand {
+    const float *base;
+    bool mn;
+    long long ld, stride_inner, stride_outer;
+};
+int run_gemm_batched(gptb200_ctx *ctx, float *out, long long out_ld, long long out_si, long long out_so, const BatchedOperand &a, const BatchedOperand &b,
+                     int M, int N, int K, int inner, int outer);
 
 // Grows the context's scratch buffer to at least `bytes` (waits for queued work before replacing it).
 int ensure_workspace(gptb200_ctx *ctx, size_t bytes);

@@ -72,12 +72,18 @@ struct GemmParams {
     unsigned int *sk_flags;  // one word per pair, CTA and epilogue warp: the number of the launch whose partial tile is complete
     unsigned int *sk_state;  // [0] number of completed launches that used the flags, [1] CTAs of this launch that have finished
     long long *trace;        // optional [kTraceEvents][kTraceSlots] clock64 samples of the first k-blocks of CTA 0
-    // CTA-pair kernel, batched form (batches > 1): `batches` independent GEMMs of the same shape in one launch, whole tiles per
+    // CTA-pair kernel, batched form (batches > 0): `batches` independent GEMMs of the same shape in one launch, whole tiles per
     // pair.  The three tensor maps are then 4-D -- (innermost, inner batch index, row, outer batch index), the order of growing
     // strides for a head slice of packed rows -- so that an operand may be a strided slice of a larger tensor (one head of the
     // packed qkv rows); batch z = outer * batch_inner + inner.
     // Store epilogue only.
     int batches, batch_inner;
+    // batched form with n <= 128: width of the tensor-core instruction (a multiple of 32); each CTA of a pair then supplies mma_n / 2
+    // columns of B and only the first mma_n accumulator columns are written.  0 = the full 256.
+    int mma_n;
+    // 3xTF32, batched form: the correction terms a_lo.b + a.b_lo run as TF32 products of fp32 low-part tiles (relative error about
+    // 2^-22 per term) instead of one bf16 chain (2^-20): 12 instead of 8 instructions per k-block.
+    int exact3x;
     // CTA-pair kernel, store epilogue: out = acc * gelu_tanh'(gelu_src) element by element (gelu_src [M x N], row pitch N): the
     // GELU derivative of the FFN rides the grad_x GEMM of the layer behind it instead of a pass of its own over HBM.
     const float *gelu_src;

@@ -498,8 +498,21 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 if (wgrp == 0 && lane == 0) trace(TRACE_CONV_BEGIN, it);
                 const uint32_t raw = smem_base + s * C::kHiBytes;
                 const uint32_t cor = lo_base + j * C::kHiBytes;
-                if (p.pre_operand != 1) convert_tile<A_MN, false>(raw, cor, lane_a, wgrp, lane);
-                if (p.pre_operand != 2) convert_tile<B_MN, true>(raw, cor, lane_b, p.pre_operand ? wgrp : wgrp_b, lane);
+                if (p.exact3x) {
+                    // low parts as fp32 tiles in the raw tiles' own layout: every 16-byte piece of the stage, a third per warp
+#pragma unroll 1
+                    for (uint32_t off = (wgrp * 32 + lane) * 16; off < C::kHiBytes; off += 96 * 16) {
+                        float4 v = ptx::lds128(raw + off);
+                        v.x -= __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
+                        v.y -= __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
+                        v.z -= __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
+                        v.w -= __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
+                        ptx::sts128(cor + off, __float_as_uint(v.x), __float_as_uint(v.y), __float_as_uint(v.z), __float_as_uint(v.w));
+                    }
+                } else {
+                    if (p.pre_operand != 1) convert_tile<A_MN, false>(raw, cor, lane_a, wgrp, lane);
+                    if (p.pre_operand != 2) convert_tile<B_MN, true>(raw, cor, lane_b, p.pre_operand ? wgrp : wgrp_b, lane);
+                }
                 ptx::fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
@@ -522,11 +535,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             PairWork work = my_work();
             int tm2, tn, kb0, kb1;
             while (ok && work.next(tm2, tn, kb0, kb1)) {
-                const int z = p.batches > 1 ? tn / p.tiles_n : 0;                     // batched form: the tile columns of all batches are numbered through
-                if (p.batches > 1) tn -= z * p.tiles_n;
-                const int zi = p.batches > 1 ? z % p.batch_inner : 0, zo = p.batches > 1 ? z / p.batch_inner : 0;
+                const int z = p.batches > 0 ? tn / p.tiles_n : 0;                     // batched form: the tile columns of all batches are numbered through
+                if (p.batches > 0) tn -= z * p.tiles_n;
+                const int zi = p.batches > 0 ? z % p.batch_inner : 0, zo = p.batches > 0 ? z / p.batch_inner : 0;
                 const int m0 = tm2 * 2 * kBM + static_cast<int>(rank) * kBM;          // the rows this CTA owns
-                const int n0 = tn * BN + static_cast<int>(rank) * C::kBRows;          // the half of B this CTA loads
+                const int n0 = tn * BN + static_cast<int>(rank) * (p.mma_n ? p.mma_n / 2 : C::kBRows);   // the half of B this CTA loads
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
@@ -543,7 +556,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     const uint32_t a_dst = smem_base + s * C::kHiBytes;
                     const uint32_t b_dst = a_dst + kATileBytes;
                     const int k0 = kb * kBK;
-                    if (p.batches > 1) {
+                    if (p.batches > 0) {
                         if (lane < kBoxesA) {
                             if (A_MN)
                                 ptx::tma_load_4d_pair(a_dst + lane * kBoxBytesMN, &tmap_a, m0 + 32 * lane, zi, k0, zo, bar);
@@ -603,6 +616,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 bool ok = true;
                 PairWork work = my_work();
                 int tm2, tn, kb0, kb1;
+                const uint32_t idesc = p.mma_n ? ptx::make_idesc_tf32(2 * kBM, p.mma_n, A_MN, B_MN) : kIdesc;
+                const uint32_t idesc_corr = p.mma_n ? ptx::make_idesc_bf16(2 * kBM, p.mma_n, A_MN, B_MN) : kIdescCorr;
                 while (ok && work.next(tm2, tn, kb0, kb1)) {
                     int kb = kb0;
                     while (ok && kb < kb1) {
@@ -636,7 +651,21 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                             constexpr uint32_t b_lbo = B_MN ? kBoxBytesMN : 16, b_sbo = B_MN ? 512 : 1024;
                             constexpr uint32_t a_lay = A_MN ? ptx::kLayoutSw128Base32B : ptx::kLayoutSw128;
                             constexpr uint32_t b_lay = B_MN ? ptx::kLayoutSw128Base32B : ptx::kLayoutSw128;
-                            if (X3) {
+                            if (X3 && p.exact3x) {
+                                // correction terms in TF32 as well: a_lo.b + a.b_lo with fp32 low-part tiles laid out like the raw ones
+#pragma unroll
+                                for (int k = 0; k < kBK / kUmmaK; ++k) {
+                                    const uint32_t a_off = A_MN ? k * 1024 : k * 32;
+                                    const uint32_t b_off = B_MN ? k * 1024 : k * 32;
+                                    const uint64_t da_hi = ptx::make_smem_desc(a_hi + a_off, a_lbo, a_sbo, a_lay);
+                                    const uint64_t db_hi = ptx::make_smem_desc(b_hi + b_off, b_lbo, b_sbo, b_lay);
+                                    const uint64_t da_lo = ptx::make_smem_desc(a_lo + a_off, a_lbo, a_sbo, a_lay);
+                                    const uint64_t db_lo = ptx::make_smem_desc(b_lo + b_off, b_lbo, b_sbo, b_lay);
+                                    ptx::mma_tf32_ss_pair(d_tmem, da_lo, db_hi, idesc, accumulate);
+                                    ptx::mma_tf32_ss_pair(d_tmem, da_hi, db_lo, idesc, 1u);
+                                    accumulate = 1u;
+                                }
+                            } else if (X3) {
                                 // correction terms a_lo.b + a.b_lo: bf16 tiles with 64 k-positions (low parts and whole values
                                 // side by side), 16 of them per instruction.  K-major: 128-byte rows, +32 bytes per step;
                                 // MN-major: [8 k x 64 m] atoms, 1 KiB per group of 8 k, 8 KiB to the next 64 rows.
@@ -644,7 +673,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                                 for (int k = 0; k < 4; ++k) {
                                     const uint64_t da = ptx::make_smem_desc(a_lo + (A_MN ? k * 2048 : k * 32), A_MN ? 8192 : 16, 1024, ptx::kLayoutSw128);
                                     const uint64_t db = ptx::make_smem_desc(b_lo + (B_MN ? k * 2048 : k * 32), B_MN ? 8192 : 16, 1024, ptx::kLayoutSw128);
-                                    ptx::mma_f16_ss_pair(d_tmem, da, db, kIdescCorr, accumulate);
+                                    ptx::mma_f16_ss_pair(d_tmem, da, db, idesc_corr, accumulate);
                                     accumulate = 1u;
                                 }
                             }
@@ -654,7 +683,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                                 const uint32_t b_off = B_MN ? k * 1024 : k * 32;
                                 const uint64_t da_hi = ptx::make_smem_desc(a_hi + a_off, a_lbo, a_sbo, a_lay);
                                 const uint64_t db_hi = ptx::make_smem_desc(b_hi + b_off, b_lbo, b_sbo, b_lay);
-                                ptx::mma_tf32_ss_pair(d_tmem, da_hi, db_hi, kIdesc, accumulate);
+                                ptx::mma_tf32_ss_pair(d_tmem, da_hi, db_hi, idesc, accumulate);
                                 accumulate = 1u;
                             }
                             // the stage is free in both CTAs once these MMAs have read it
@@ -695,6 +724,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         int ezi = 0, ezo = 0;   // batched form: batch coordinates of the tile being written
         // bias_lane: bias[col0 + lane], fetched when the tile was started
         auto emit = [&](float (&v)[32], int row0, int col0, float bias_lane) {
+            if (p.mma_n && col0 >= p.mma_n) return;   // narrow batched form: these accumulator columns were not computed
             if (p.bias && p.epi_mode == EPI_STORE) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, bias_lane, j);
@@ -726,7 +756,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 __syncwarp();
                 if (lane == 0) {
                     if (row0 < p.M && col0 + h * C::kStageCols < p.N) {
-                        if (p.batches > 1)
+                        if (p.batches > 0)
                             ptx::tma_store_4d(&tmap_out, col0 + h * C::kStageCols, ezi, row0, ezo, buf);
                         else if (p.epi_mode == EPI_ACCUM)
                             ptx::tma_reduce_add_3d(&tmap_out, col0 + h * C::kStageCols, row0, 0, buf);
@@ -758,7 +788,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         PairWork work = my_work();
         int tm2, tn, kb0, kb1;
         while (ok && work.next(tm2, tn, kb0, kb1)) {
-            if (p.batches > 1) {
+            if (p.batches > 0) {
                 const int z = tn / p.tiles_n;
                 tn -= z * p.tiles_n;
                 ezi = z % p.batch_inner;

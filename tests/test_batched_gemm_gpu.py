@@ -32,7 +32,7 @@ def rel_err(a, ref):
 
 
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)], ids=["K.K", "K.MN", "MN.MN"])
-@pytest.mark.parametrize("batches,m,n,k", [(3, 256, 256, 64), (5, 200, 136, 100), (12, 1024, 1024, 64), (2, 1024, 64, 1024), (150, 64, 64, 32)])
+@pytest.mark.parametrize("batches,m,n,k", [(1, 600, 300, 72), (3, 256, 256, 64), (5, 200, 136, 100), (4, 256, 96, 256), (2, 300, 32, 64), (12, 1024, 1024, 64), (2, 1024, 64, 1024), (150, 64, 64, 32)])
 def test_contiguous_batches(be, torch, a_mn, b_mn, batches, m, n, k):
     g = torch.Generator(device="cuda").manual_seed(batches * 1000 + m + n + k)
     a = torch.randn(batches, k, m, device="cuda", generator=g) if a_mn else torch.randn(batches, m, k, device="cuda", generator=g)

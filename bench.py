@@ -29,7 +29,9 @@ Beside those headline keys the default line carries sub-records, each a few hund
                  in the reference's form (the whole prefix recomputed per token);
   train_step     (every N) the full GPT-2 124M training step at a global batch of 64 x 256 tokens sharded over the ranks
                  (strong scaling): tokens/s, phase times, collectives per step, and dp_parity -- the distance per gradient
-                 tensor between the all-reduced N-rank gradients and rank 0 computing the whole batch alone.
+                 tensor between the all-reduced N-rank gradients and rank 0 computing the whole batch alone;
+  train_step_tf32 (every N) the same step with the linear layers in single-pass TF32 (the precision of the reference's CUDA
+                 backend, whose step reference_gpu times) and attention as batched tensor-core products.
 
 --impl reference times the reference's own CPU implementation (unmodified sources, oracle/_ref) of the same
 step on the host, on a bounded row sample per step (its cost is exactly linear in M).
@@ -464,6 +466,10 @@ def run_ours(args):
             sub["generate"] = generate_record(torch, dev, "3xtf32")
             torch.cuda.empty_cache()
         sub["train_step"] = train_record(torch, dist, world, rank, dev, "3xtf32", 64, 5, 2, sampler, parity=True)
+        torch.cuda.empty_cache()
+        # the same step with the linear layers in single-pass TF32 -- the precision of the reference's own CUDA backend (cuBLAS
+        # TF32 tensor ops), whose step reference_gpu times -- and attention on the tensor cores, the default of that mode
+        sub["train_step_tf32"] = train_record(torch, dist, world, rank, dev, "tf32", 64, 5, 2, sampler, parity=False)
         torch.cuda.empty_cache()
         if world == 1 and rank == 0:
             sub["reference_gpu"] = reference_gpu_record()

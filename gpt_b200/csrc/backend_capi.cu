@@ -165,7 +165,7 @@ int attention_gemm_forward(gptb200_ctx *ctx, float *y, float *lse, const float *
     for (int b0 = 0; b0 < batch; b0 += G) {
         const int nb = std::min(G, batch - b0);
         const float *x = qkv + 1LL * b0 * T * 3 * d;
-        int rc = run_gemm_batched(ctx, s, sl, T, so, head_slice(x, false, 3 * d, T), head_slice(x + d, false, 3 * d, T), T, T, 64, heads, nb);
+        int rc = run_gemm_batched(ctx, s, sl, T, so, head_slice(x, false, 3 * d, T), head_slice(x + d, false, 3 * d, T), T, T, 64, heads, nb, true);   // the row kernel reads columns <= row only
         if (rc) return rc;
         const long long rows = 1LL * nb * T * heads;
         const unsigned blocks = static_cast<unsigned>((rows + ops::kScoreRowsPerBlock - 1) / ops::kScoreRowsPerBlock);
@@ -192,9 +192,9 @@ int attention_gemm_backward(gptb200_ctx *ctx, float *gqkv, float *dcache, const 
         const int nb = std::min(G, batch - b0);
         const float *x = qkv + b0 * xo, *g = gy + 1LL * b0 * T * d;
         float *gx = gqkv + b0 * xo;
-        rc = run_gemm_batched(ctx, s, sl, T, so, head_slice(x, false, 3 * d, T), head_slice(x + d, false, 3 * d, T), T, T, 64, heads, nb);
+        rc = run_gemm_batched(ctx, s, sl, T, so, head_slice(x, false, 3 * d, T), head_slice(x + d, false, 3 * d, T), T, T, 64, heads, nb, true);   // the row kernel reads columns <= row only
         if (rc) return rc;
-        rc = run_gemm_batched(ctx, dp, sl, T, so, head_slice(g, false, d, T), head_slice(x + 2 * d, false, 3 * d, T), T, T, 64, heads, nb);
+        rc = run_gemm_batched(ctx, dp, sl, T, so, head_slice(g, false, d, T), head_slice(x + 2 * d, false, 3 * d, T), T, T, 64, heads, nb, true);   // the row kernel reads columns <= row only
         if (rc) return rc;
         const long long rows = 1LL * nb * T * heads;
         const unsigned blocks = static_cast<unsigned>((rows + ops::kScoreRowsPerBlock - 1) / ops::kScoreRowsPerBlock);

@@ -634,7 +634,7 @@ int run_bias_grad(gptb200_ctx *ctx, float *gb, const float *gy, int M, int N)
 
 // `batches` GEMMs of one shape in one launch of the CTA-pair kernel (whole tiles per pair, store epilogue).
 int run_gemm_batched_impl(gptb200_ctx *ctx, float *out, long long out_ld, long long out_si, long long out_so, const BatchedOperand &a,
-                          const BatchedOperand &b, int M, int N, int K, int inner, int outer)
+                          const BatchedOperand &b, int M, int N, int K, int inner, int outer, bool causal)
 {
     if (M <= 0 || N <= 0 || K <= 0 || inner <= 0 || outer <= 0) return fail(ctx, GPTB200_ERR_INVALID_ARG, "batched GEMM with an empty dimension");
     if (a.mn && !b.mn) return fail(ctx, GPTB200_ERR_INVALID_ARG, "operand forms (MN-major, K-major) do not occur");
@@ -652,6 +652,7 @@ int run_gemm_batched_impl(gptb200_ctx *ctx, float *out, long long out_ld, long l
     p.batch_inner = inner;
     if (N <= 128) p.mma_n = (N + 31) / 32 * 32;
     p.exact3x = (x3 && ctx->batched_exact3x) ? 1 : 0;
+    p.causal_skip = (causal && M == N) ? 1 : 0;
     const long long tiles = 1LL * ((p.tiles_m + 1) / 2) * p.tiles_n * p.batches;
     p.sk_total = tiles * p.num_kb;
     p.sk_unit = p.num_kb;                                   // whole tiles per pair
@@ -685,9 +686,9 @@ int check_dims(gptb200_ctx *ctx, int m, int a, int b)
 
 namespace gptb200 {
 int run_gemm_batched(gptb200_ctx *ctx, float *out, long long out_ld, long long out_si, long long out_so, const BatchedOperand &a, const BatchedOperand &b,
-                     int M, int N, int K, int inner, int outer)
+                     int M, int N, int K, int inner, int outer, bool causal)
 {
-    return run_gemm_batched_impl(ctx, out, out_ld, out_si, out_so, a, b, M, N, K, inner, outer);
+    return run_gemm_batched_impl(ctx, out, out_ld, out_si, out_so, a, b, M, N, K, inner, outer, causal);
 }
 }  // namespace gptb200
 
@@ -1052,7 +1053,7 @@ int gptb200_gemm_batched(gptb200_ctx *ctx, float *out, const float *a, const flo
     if (!out || !a || !b || !a_strides3 || !b_strides3 || !out_strides3) return fail(ctx, GPTB200_ERR_INVALID_ARG, "null pointer");
     const BatchedOperand oa{a, a_mn_major != 0, a_strides3[0], a_strides3[1], a_strides3[2]};
     const BatchedOperand ob{b, b_mn_major != 0, b_strides3[0], b_strides3[1], b_strides3[2]};
-    return run_gemm_batched(ctx, out, out_strides3[0], out_strides3[1], out_strides3[2], oa, ob, m, n, k, batch_inner, batch_outer);
+    return run_gemm_batched_impl(ctx, out, out_strides3[0], out_strides3[1], out_strides3[2], oa, ob, m, n, k, batch_inner, batch_outer, false);
 }
 
 int gptb200_gelu_backward(gptb200_ctx *ctx, float *grad_x, const float *grad_y, const float *x, int m, int n)

@@ -115,8 +115,9 @@ struct BatchedOperand {
     bool mn;
     long long ld, stride_inner, stride_outer;
 };
+// causal: the consumer of a square product reads only columns <= row, so output pieces wholly beyond the diagonal may stay unwritten
 int run_gemm_batched(gptb200_ctx *ctx, float *out, long long out_ld, long long out_si, long long out_so, const BatchedOperand &a, const BatchedOperand &b,
-                     int M, int N, int K, int inner, int outer);
+                     int M, int N, int K, int inner, int outer, bool causal = false);
 
 // Grows the context's scratch buffer to at least `bytes` (waits for queued work before replacing it).
 int ensure_workspace(gptb200_ctx *ctx, size_t bytes);

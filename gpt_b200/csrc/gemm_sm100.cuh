@@ -84,6 +84,9 @@ struct GemmParams {
     // 3xTF32, batched form: the correction terms a_lo.b + a.b_lo run as TF32 products of fp32 low-part tiles (relative error about
     // 2^-22 per term) instead of one bf16 chain (2^-20): 12 instead of 8 instructions per k-block.
     int exact3x;
+    // Batched form, square products whose consumer only reads columns <= row (causal attention scores): 32-column pieces that lie
+    // wholly beyond the diagonal for the 32 rows of an epilogue warp are not written.
+    int causal_skip;
     // CTA-pair kernel, store epilogue: out = acc * gelu_tanh'(gelu_src) element by element (gelu_src [M x N], row pitch N): the
     // GELU derivative of the FFN rides the grad_x GEMM of the layer behind it instead of a pass of its own over HBM.
     const float *gelu_src;

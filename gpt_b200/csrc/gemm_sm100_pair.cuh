@@ -725,6 +725,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         // bias_lane: bias[col0 + lane], fetched when the tile was started
         auto emit = [&](float (&v)[32], int row0, int col0, float bias_lane) {
             if (p.mma_n && col0 >= p.mma_n) return;   // narrow batched form: these accumulator columns were not computed
+            if (p.causal_skip && col0 > row0 + 31) return;   // nobody reads these
             if (p.bias && p.epi_mode == EPI_STORE) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] += __shfl_sync(0xffffffffu, bias_lane, j);

@@ -86,7 +86,16 @@ int gptb200_ctx_set_stream(gptb200_ctx *ctx, void *cuda_stream);
  * "max_sms" (0 = all SMs; otherwise the GEMM kernels occupy at most this many, which leaves SMs to a collective that runs
  * at the same time on another stream),
  * "trace" (record a kernel-phase trace of each CTA-pair GEMM launch: 1 = on, 0 = off (default)),
- * "attention_tiled" (attention with head size 64: register-tiled kernels, 1 = on (default), 0 = one row per thread group). */
+ * "exact3x" (3xTF32 mode, CTA-pair kernel: form of the correction terms a_lo.b + a.b_lo -- 0 = one bf16 chain (error about 2^-20
+ * per term, 8 tensor-core instructions per k-block), 1 = TF32 products of fp32 low-part tiles (2^-22, 12 instructions: 8 % slower
+ * where the launch is bound by the tensor pipe or the power limit), 2 = the latter for launches of at most 6 GFLOP (default)),
+ * "batched_exact3x" (the same choice for gptb200_gemm_batched and the attention products: 1 = TF32 products (default), 0 = bf16 chain),
+ * "attention_gemm" (attention with head size 64 and a sequence length that is a multiple of 4, at most 1024: batched tensor-core
+ * products on head slices of the packed qkv rows plus two row kernels, in the context's precision mode -- 0 = never, 1 = when the
+ * mode is TF32 (default), 2 = always; needs 2 * batch * heads * seq_len^2 floats of scratch, otherwise the kernels below run),
+ * "attention_group_mb" (that form works through the sequences in groups whose score matrices take at most this many MB of
+ * scratch: default 8192; fewer, larger launches are faster),
+ * "attention_tiled" (attention with head size 64 on fp32 FMAs: register-tiled kernels, 1 = on (default), 0 = one row per thread group). */
 int gptb200_ctx_set_option(gptb200_ctx *ctx, const char *key, int value);
 /* Kernel-phase trace (option "trace" = 1): the most recent CTA-pair GEMM launch recorded the SM clock at 11 events,
  * [event][slot] with 128 slots per event.  Events 0-5 are taken in the launch's first CTA, slot = k-block (the first 128):

@@ -911,6 +911,74 @@ def generate_record(torch, dev, mode_name="3xtf32", batches=(1, 8, 64), with_pre
                 note="tokens/s counts generated tokens; host-side sampling with torch is inside the time")
 
 
+def attention_record(torch, dev, mode_name="tf32", batch=64, steps=20, warmup=3):
+    """Causal attention of one GPT-2 124M layer (12 heads of 64, 256 tokens per sequence) through gptb200_attention_forward /
+    _backward (the reference's device_flash_attention_forward / _backward, cuda/kernels/attention.cu): microseconds per call as
+    batched tensor-core products + row kernels in the given precision mode, and as the fp32 FMA kernels."""
+    import gpt_b200
+    T, D, H = 256, 768, 12
+    be = gpt_b200.Backend(dev.index, torch.cuda.current_stream().cuda_stream, gpt_b200.MODE_TF32 if mode_name == "tf32" else gpt_b200.MODE_3XTF32)
+    lib = be.lib
+    gen = torch.Generator(device=dev).manual_seed(11)
+    qkv = torch.randn(batch, T, 3 * D, device=dev, generator=gen)
+    gy = torch.randn(batch, T, D, device=dev, generator=gen)
+    y, lse = torch.empty(batch, T, D, device=dev), torch.empty(batch, T, H, device=dev)
+    gq, dc = torch.empty(batch, T, 3 * D, device=dev), torch.empty(batch, T, H, device=dev)
+
+    def fwd():
+        assert lib.gptb200_attention_forward(be.handle, y.data_ptr(), lse.data_ptr(), qkv.data_ptr(), batch, T, D, H) == 0
+
+    def bwd():
+        assert lib.gptb200_attention_backward(be.handle, gq.data_ptr(), dc.data_ptr(), lse.data_ptr(), gy.data_ptr(), y.data_ptr(), qkv.data_ptr(), batch, T, D, H) == 0
+
+    out, launches = {}, 0
+    for form, option in (("tensor_core", 2), ("fp32_fma", 0)):
+        be.set_option("attention_gemm", option)
+        rec = {}
+        for name, fn in (("forward", fwd), ("backward", bwd)):
+            for _ in range(warmup):
+                fn()
+            torch.cuda.synchronize()
+            l0 = be.launch_count()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            launches += be.launch_count() - l0
+            rec[name + "_us"] = e0.elapsed_time(e1) / steps * 1e3
+            rec[name + "_launches"] = (be.launch_count() - l0) // steps
+        out[form] = rec
+    be.close()
+    # both causal halves of the five products count as algorithmic work: 2 * T * T * 64 flops per product, head and sequence / 2
+    flops = {"forward": 2 * 2.0 * T * T * 64 * H * batch / 2, "backward": 5 * 2.0 * T * T * 64 * H * batch / 2}
+    for rec in out.values():
+        for name in ("forward", "backward"):
+            rec[name + "_tflops"] = flops[name] / (rec[name + "_us"] * 1e-6) / 1e12
+    return dict(forms=out, batch=batch, seq_len=T, heads=H, head_size=64, mode=mode_name, gpu_launches=int(launches))
+
+
+def run_attention(args):
+    """--workload attention: see attention_record; the JSON `value` is forward + backward of the tensor-core form."""
+    import torch
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    sampler = ClockSampler(0)
+    t_begin = time.time()
+    rec = attention_record(torch, dev, args.mode, args.global_batch, args.steps, args.warmup)
+    clocks = sampler.stop(t_begin, time.time())
+    tc = rec["forms"]["tensor_core"]
+    us = tc["forward_us"] + tc["backward_us"]
+    out = dict(metric="attention_layer_us", value=us, unit="us", n_gpus=1, steps=args.steps, warmup=args.warmup, ms_per_step=us * 1e-3,
+               higher_is_better=False, scaling="weak", vs_baseline=None, dtype="tf32" if args.mode == "tf32" else "tf32x3 (fp32-accurate split)",
+               data="synthetic", impl="ours",
+               config=dict(workload="causal attention of one GPT-2 124M layer, forward + backward", batch=rec["batch"], seq_len=rec["seq_len"], heads=rec["heads"],
+                           head_size=64, mode=args.mode, l2="qkv, outputs and score matrices of 64 sequences (> 700 MB) exceed the 126 MB L2"),
+               forms=rec["forms"], gpu_launches=rec["gpu_launches"], clocks=clocks)
+    print(json.dumps(out), flush=True)
+
+
 def run_generate(args):
     """--workload generate: see generate_record; the JSON `value` is the batch-8 KV-cached figure."""
     import torch
@@ -1012,9 +1080,9 @@ def main():
     ap.add_argument("--cpu-rows", type=int, default=256, help="rows of the workload the cpu_baseline leg runs")
     ap.add_argument("--ref-rows", type=int, default=32, help="rows per step of the --impl reference arm")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", choices=["ffn", "train", "decode", "generate"], default="ffn",
+    ap.add_argument("--workload", choices=["ffn", "train", "decode", "generate", "attention"], default="ffn",
                     help="ffn: BASELINE configs[1] (default); train: configs[3]; decode: configs[4] (linear layers of a decode step); generate: configs[4] end to end")
-    ap.add_argument("--global-batch", type=int, default=64, help="sequences per step over all GPUs (train workload)")
+    ap.add_argument("--global-batch", type=int, default=64, help="sequences per step over all GPUs (train workload); sequences of the attention workload")
     ap.add_argument("--m-per-gpu", type=int, default=M_PER_GPU, help="tokens per GPU (smaller for profiler captures)")
     ap.add_argument("--max-sms", type=int, default=0, help="SMs the GEMM kernels may occupy (0 = all; experiments)")
     ap.add_argument("--comm-sms", type=int, default=-1,
@@ -1036,6 +1104,8 @@ def main():
         run_train(args)
     elif args.workload == "decode":
         run_decode(args)
+    elif args.workload == "attention":
+        run_attention(args)
     elif args.workload == "generate":
         run_generate(args)
     else:

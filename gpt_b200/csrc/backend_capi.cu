@@ -11,6 +11,7 @@
 #include "layernorm_warp.cuh"
 #include "optimizer_fused.cuh"
 #include "decode_ops.cuh"
+#include "softmax_stream.cuh"
 
 using namespace gptb200;
 
@@ -63,6 +64,13 @@ cudaError_t allow_smem(gptb200_ctx *ctx, Kernel kernel, int bytes)
     const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (e == cudaSuccess) ctx->configured.insert(key);
     return e;
+}
+
+// Long rows of logits (16 K - 51 K floats, 16-byte aligned) and more rows than SMs: the persistent row kernels of softmax_stream.cuh.
+bool row_stream_applies(const gptb200_ctx *ctx, int rows, int vocab_padded)
+{
+    return ctx->softmax_stream && vocab_padded % 4 == 0 && vocab_padded > 1024 * 4 * 4 && vocab_padded <= ops::kRowStreamThreads * 4 * ops::kRowStreamVecs &&
+           rows > ctx->num_sms;
 }
 
 // Head size 64 with 16-byte aligned tensors: the register-tiled kernels of attention_tiled.cuh.
@@ -386,7 +394,11 @@ int gptb200_softmax_forward(gptb200_ctx *ctx, float *y, const float *x, int rows
     NEED(ctx, rows >= 0 && vocab >= 0 && vocab_padded >= vocab);
     if (rows == 0 || vocab_padded == 0) return GPTB200_OK;
     NEED(ctx, y && x);
-    if (vocab_padded % 4 == 0 && vocab_padded <= 512 * 4 * 25 && vocab_padded > 1024 * 4 * 4 && aligned16_all({y, x}))
+    if (row_stream_applies(ctx, rows, vocab_padded) && aligned16_all({y, x})) {
+        CUDA_TRY(ctx, allow_smem(ctx, ops::softmax_row_stream_kernel<0>, ops::kRowStreamSmem));
+        ops::softmax_row_stream_kernel<0><<<std::min(rows, ctx->num_sms), ops::kRowStreamThreads, ops::kRowStreamSmem, ctx->stream>>>(
+            y, const_cast<float *>(x), nullptr, nullptr, rows, vocab, vocab_padded, ctx->d_status);
+    } else if (vocab_padded % 4 == 0 && vocab_padded <= 512 * 4 * 25 && vocab_padded > 1024 * 4 * 4 && aligned16_all({y, x}))
         ops::softmax_forward_rowreg_kernel<512, 25><<<rows, 512, 0, ctx->stream>>>(y, x, vocab, vocab_padded);
     else if (vocab_padded % 4 == 0 && vocab_padded <= 1024 * 4 * 4 && aligned16_all({y, x}))
         ops::softmax_forward_rowreg_kernel<1024, 4><<<rows, 1024, 0, ctx->stream>>>(y, x, vocab, vocab_padded);
@@ -414,7 +426,11 @@ int gptb200_softmax_cross_entropy_inplace(gptb200_ctx *ctx, float *logits_inout,
     NEED(ctx, rows >= 0 && vocab >= 0 && vocab_padded >= vocab);
     if (rows == 0 || vocab_padded == 0) return GPTB200_OK;
     NEED(ctx, logits_inout && row_loss && labels);
-    if (vocab_padded % 4 == 0 && vocab_padded <= 512 * 4 * 25 && vocab_padded > 1024 * 4 * 4 && aligned16_all({logits_inout}))
+    if (row_stream_applies(ctx, rows, vocab_padded) && aligned16_all({logits_inout})) {
+        CUDA_TRY(ctx, allow_smem(ctx, ops::softmax_row_stream_kernel<1>, ops::kRowStreamSmem));
+        ops::softmax_row_stream_kernel<1><<<std::min(rows, ctx->num_sms), ops::kRowStreamThreads, ops::kRowStreamSmem, ctx->stream>>>(
+            nullptr, logits_inout, row_loss, labels, rows, vocab, vocab_padded, ctx->d_status);
+    } else if (vocab_padded % 4 == 0 && vocab_padded <= 512 * 4 * 25 && vocab_padded > 1024 * 4 * 4 && aligned16_all({logits_inout}))
         ops::softmax_ce_inplace_rowreg_kernel<512, 25><<<rows, 512, 0, ctx->stream>>>(logits_inout, row_loss, labels, rows, vocab, vocab_padded);
     else if (vocab_padded % 4 == 0 && vocab_padded <= 1024 * 4 * 4 && aligned16_all({logits_inout}))
         ops::softmax_ce_inplace_rowreg_kernel<1024, 4><<<rows, 1024, 0, ctx->stream>>>(logits_inout, row_loss, labels, rows, vocab, vocab_padded);

@@ -543,10 +543,11 @@ __global__ void __launch_bounds__(THREADS) softmax_forward_rowreg_kernel(float *
         s += (e[k].x + e[k].y) + (e[k].z + e[k].w);
     }
     s = block_sum(s, red);
+    const float rs = 1.0f / s;   // one division per row: a hundred per thread would make the kernel instruction-bound
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
         const int c = threadIdx.x + THREADS * k;
-        if (c < nvec) yr[c] = make_float4(e[k].x / s, e[k].y / s, e[k].z / s, e[k].w / s);   // masked and padding columns: 0 / s = 0
+        if (c < nvec) yr[c] = make_float4(e[k].x * rs, e[k].y * rs, e[k].z * rs, e[k].w * rs);   // masked and padding columns: 0
     }
 }
 
@@ -567,17 +568,17 @@ __global__ void cross_entropy_softmax_backward_vec_kernel(float *__restrict__ gr
 {
     const size_t r = blockIdx.x;
     const int label = labels[r];
-    const float inv = static_cast<float>(rows);
+    const float inv = 1.0f / static_cast<float>(rows);
     const float4 *p = reinterpret_cast<const float4 *>(probs + r * vp);
     float4 *g = reinterpret_cast<float4 *>(grad_x + r * vp);
     const int full = v >> 2;
     for (int c = threadIdx.x; c < full; c += blockDim.x) {
         const float4 t = __ldg(p + c);
         const int i = 4 * c;
-        g[c] = make_float4((t.x - (i == label ? 1.0f : 0.0f)) / inv, (t.y - (i + 1 == label ? 1.0f : 0.0f)) / inv,
-                           (t.z - (i + 2 == label ? 1.0f : 0.0f)) / inv, (t.w - (i + 3 == label ? 1.0f : 0.0f)) / inv);
+        g[c] = make_float4((t.x - (i == label ? 1.0f : 0.0f)) * inv, (t.y - (i + 1 == label ? 1.0f : 0.0f)) * inv,
+                           (t.z - (i + 2 == label ? 1.0f : 0.0f)) * inv, (t.w - (i + 3 == label ? 1.0f : 0.0f)) * inv);
     }
-    for (int i = 4 * full + threadIdx.x; i < v; i += blockDim.x) grad_x[r * vp + i] = (probs[r * vp + i] - (i == label ? 1.0f : 0.0f)) / inv;
+    for (int i = 4 * full + threadIdx.x; i < v; i += blockDim.x) grad_x[r * vp + i] = (probs[r * vp + i] - (i == label ? 1.0f : 0.0f)) * inv;
 }
 
 // Softmax, cross-entropy backward and the row's loss term in ONE pass over the logits, in place: what the reference does with
@@ -622,18 +623,18 @@ __global__ void __launch_bounds__(THREADS) softmax_ce_inplace_rowreg_kernel(floa
         s += (e[k].x + e[k].y) + (e[k].z + e[k].w);
     }
     s = block_sum(s, red);
-    const float inv = static_cast<float>(rows);
+    const float inv = 1.0f / static_cast<float>(rows), rs = 1.0f / s;   // two divisions per row instead of two per element
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
         const int c = threadIdx.x + THREADS * k;
         if (c >= nvec) continue;
         const int i = 4 * c;
-        float p[4] = {e[k].x / s, e[k].y / s, e[k].z / s, e[k].w / s};
+        float p[4] = {e[k].x * rs, e[k].y * rs, e[k].z * rs, e[k].w * rs};
         float g[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             if (i + j == label) row_loss[r] = -logf(p[j] + 1e-8f);
-            g[j] = i + j < v ? (p[j] - (i + j == label ? 1.0f : 0.0f)) / inv : 0.0f;
+            g[j] = i + j < v ? (p[j] - (i + j == label ? 1.0f : 0.0f)) * inv : 0.0f;
         }
         xr[c] = make_float4(g[0], g[1], g[2], g[3]);
     }

@@ -815,6 +815,10 @@ int gptb200_ctx_set_option(gptb200_ctx *ctx, const char *key, int value)
         ctx->attention_gemm = value;
         return GPTB200_OK;
     }
+    if (!strcmp(key, "softmax_stream")) {
+        ctx->softmax_stream = value != 0;
+        return GPTB200_OK;
+    }
     if (!strcmp(key, "attention_tiled")) {
         ctx->attention_tiled = value != 0;
         return GPTB200_OK;

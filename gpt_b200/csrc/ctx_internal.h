@@ -64,6 +64,7 @@ struct gptb200_ctx {
     int skinny_rowwise_rows = 8;  // ... for calls with at most this many rows (beyond: the register-tiled kernel)
     bool skinny_pipelined = true;  // k-split kernel, 16-row groups, W stored [k][n]: weight loads pipelined through shared memory
     int skinny_fused = 0;  // that kernel adds its partial sums itself (one launch): 1 = always, 0 = with at most two splits, -1 = never
+    bool softmax_stream = true;   // long rows of logits: persistent softmax kernels that prefetch the next row (false: one block per row)
     bool attention_tiled = true;  // head size 64: register-tiled attention kernels (false: the one-row-per-thread-group kernels)
     int presplit = 0;        // 3xTF32, CTA pairs: split the operand that many tiles re-read before the launch (0 off, 1 automatic, 2 / 3 force A / B)
     bool fuse_dbias = true;  // grad_w launches of the CTA-pair kernel also produce the bias gradient (false: separate column-sum kernels)

@@ -400,6 +400,14 @@ __host__ __device__ constexpr uint32_t make_idesc_tf32(int m, int n, bool a_mn_m
            (static_cast<uint32_t>(m >> 4) << 24);
 }
 
+// Untiled bulk copy global -> this CTA's shared memory; both addresses 16-byte aligned, bytes a multiple of 16; completion is
+// reported to the mbarrier as transferred bytes.
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
 __device__ __forceinline__ float4 lds128(uint32_t addr)
 {
     float4 v;

@@ -911,7 +911,7 @@ def generate_record(torch, dev, mode_name="3xtf32", batches=(1, 8, 64), with_pre
                 note="tokens/s counts generated tokens; host-side sampling with torch is inside the time")
 
 
-def attention_record(torch, dev, mode_name="tf32", batch=64, steps=20, warmup=3):
+def attention_record(torch, dev, mode_name="tf32", batch=64, steps=20, warmup=3, ctx_options=()):
     """Causal attention of one GPT-2 124M layer (12 heads of 64, 256 tokens per sequence) through gptb200_attention_forward /
     _backward (the reference's device_flash_attention_forward / _backward, cuda/kernels/attention.cu): microseconds per call as
     batched tensor-core products + row kernels in the given precision mode, and as the fp32 FMA kernels."""
@@ -919,6 +919,8 @@ def attention_record(torch, dev, mode_name="tf32", batch=64, steps=20, warmup=3)
     T, D, H = 256, 768, 12
     be = gpt_b200.Backend(dev.index, torch.cuda.current_stream().cuda_stream, gpt_b200.MODE_TF32 if mode_name == "tf32" else gpt_b200.MODE_3XTF32)
     lib = be.lib
+    for kv in ctx_options:
+        be.set_option(kv.partition("=")[0], int(kv.partition("=")[2]))
     gen = torch.Generator(device=dev).manual_seed(11)
     qkv = torch.randn(batch, T, 3 * D, device=dev, generator=gen)
     gy = torch.randn(batch, T, D, device=dev, generator=gen)
@@ -932,7 +934,7 @@ def attention_record(torch, dev, mode_name="tf32", batch=64, steps=20, warmup=3)
         assert lib.gptb200_attention_backward(be.handle, gq.data_ptr(), dc.data_ptr(), lse.data_ptr(), gy.data_ptr(), y.data_ptr(), qkv.data_ptr(), batch, T, D, H) == 0
 
     out, launches = {}, 0
-    for form, option in (("tensor_core", 2), ("fp32_fma", 0)):
+    for form, option in (("tensor_core", 1), ("fp32_fma", 0)):
         be.set_option("attention_gemm", option)
         rec = {}
         for name, fn in (("forward", fwd), ("backward", bwd)):
@@ -966,7 +968,7 @@ def run_attention(args):
     dev = torch.device("cuda", 0)
     sampler = ClockSampler(0)
     t_begin = time.time()
-    rec = attention_record(torch, dev, args.mode, args.global_batch, args.steps, args.warmup)
+    rec = attention_record(torch, dev, args.mode, args.global_batch, args.steps, args.warmup, args.ctx_option)
     clocks = sampler.stop(t_begin, time.time())
     tc = rec["forms"]["tensor_core"]
     us = tc["forward_us"] + tc["backward_us"]

@@ -133,9 +133,7 @@ bool attention_scratch(gptb200_ctx *ctx, size_t bytes)
 
 bool attention_gemm_applies(const gptb200_ctx *ctx, int seq_len, int d, int heads)
 {
-    // automatic (1): with the linear layers in TF32 mode, whose accuracy these products then share; in 3xTF32 mode the products are
-    // about 2e-6 from the exact result where the fp32 FMA kernels are 7e-7, which a whole-model gradient check to 1e-5 does not absorb
-    const bool on = ctx->attention_gemm == 2 || (ctx->attention_gemm == 1 && ctx->mode == GPTB200_MODE_TF32);
+    const bool on = ctx->attention_gemm != 0;
     return on && d / heads == 64 && seq_len % 4 == 0 && seq_len >= 4 && seq_len <= 1024;
 }
 

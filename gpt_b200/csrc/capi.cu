@@ -653,6 +653,7 @@ int run_gemm_batched_impl(gptb200_ctx *ctx, float *out, long long out_ld, long l
     if (N <= 128) p.mma_n = (N + 31) / 32 * 32;
     p.exact3x = (x3 && ctx->batched_exact3x) ? 1 : 0;
     p.causal_skip = (causal && M == N) ? 1 : 0;
+    p.chunk_kb = ctx->batched_chunk_kb;
     const long long tiles = 1LL * ((p.tiles_m + 1) / 2) * p.tiles_n * p.batches;
     p.sk_total = tiles * p.num_kb;
     p.sk_unit = p.num_kb;                                   // whole tiles per pair
@@ -800,6 +801,11 @@ int gptb200_ctx_set_option(gptb200_ctx *ctx, const char *key, int value)
     if (!strcmp(key, "exact3x")) {
         if (value < 0 || value > 2) return fail(ctx, GPTB200_ERR_INVALID_ARG, "exact3x: 0 never, 1 always, 2 automatic");
         ctx->exact3x = value;
+        return GPTB200_OK;
+    }
+    if (!strcmp(key, "batched_chunk_kb")) {
+        if (value < 0 || value > 4) return fail(ctx, GPTB200_ERR_INVALID_ARG, "batched_chunk_kb: 0 (default) to 4");
+        ctx->batched_chunk_kb = value;
         return GPTB200_OK;
     }
     if (!strcmp(key, "batched_exact3x")) {

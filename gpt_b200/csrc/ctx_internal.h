@@ -81,9 +81,11 @@ struct gptb200_ctx {
     size_t attn_ws_bytes = 0;
     int exact3x = 2;               // 3xTF32 CTA-pair kernel: correction terms as TF32 products of fp32 low-part tiles instead of one bf16 chain:
                                    // 0 never, 1 always, 2 for launches of at most 6 GFLOP
+    int batched_chunk_kb = 1;      // 3xTF32 batched products: k-blocks per accumulator hand-off (0 = as the other launches: 4); 1: the attention
+                                   // products then match the fp32 FMA kernels' accuracy (the accumulator's truncating adds are the main error)
     bool batched_exact3x = true;   // 3xTF32 batched products: TF32 correction terms (GemmParams::exact3x)
     int attention_group_mb = 8192; // ... in groups of sequences whose score matrices take at most this many MB of scratch (fewer, larger launches are faster)
-    int attention_gemm = 1;     // head size 64: attention as batched tensor-core products + row kernels: 2 always, 1 in TF32 mode, 0 never (the fp32 FMA kernels)
+    int attention_gemm = 1;     // head size 64: attention as batched tensor-core products + row kernels (0: the fp32 FMA kernels)
     size_t ws_limit = size_t(1) << 30;
     EncodeTiledFn encode = nullptr;
     long long launches = 0;

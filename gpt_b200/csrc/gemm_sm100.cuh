@@ -87,6 +87,8 @@ struct GemmParams {
     // Batched form, square products whose consumer only reads columns <= row (causal attention scores): 32-column pieces that lie
     // wholly beyond the diagonal for the 32 rows of an epilogue warp are not written.
     int causal_skip;
+    // 3xTF32, batched form: k-blocks per accumulator hand-off (0 = kChunkKB); shorter chunks leave less to the accumulator's truncating adds
+    int chunk_kb;
     // CTA-pair kernel, store epilogue: out = acc * gelu_tanh'(gelu_src) element by element (gelu_src [M x N], row pitch N): the
     // GELU derivative of the FFN rides the grad_x GEMM of the layer behind it instead of a pass of its own over HBM.
     const float *gelu_src;

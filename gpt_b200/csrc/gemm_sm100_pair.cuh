@@ -621,7 +621,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 while (ok && work.next(tm2, tn, kb0, kb1)) {
                     int kb = kb0;
                     while (ok && kb < kb1) {
-                        const int kend = C::kChunked ? min(kb + pair_chunk_kb(kb == kb0), kb1) : kb1;
+                        const int kend = C::kChunked ? min(kb + (p.chunk_kb ? p.chunk_kb : pair_chunk_kb(kb == kb0)), kb1) : kb1;
                         const uint32_t buf = g & 1u;
                         const uint32_t use = (g >> 1) & 1u;
                         if (!bounded_wait_cluster(tmem_empty_bar(buf), use ^ 1u, abort_flag, p.status, DEV_TIMEOUT_MMA_TMEM)) {
@@ -860,7 +860,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 float acc[128];
 #pragma unroll
                 for (int j = 0; j < 128; ++j) acc[j] = 0.0f;
-                for (int kb = kb0; ok && kb < kb1; kb += pair_chunk_kb(kb == kb0), ++g) {
+                for (int kb = kb0; ok && kb < kb1; kb += (p.chunk_kb ? p.chunk_kb : pair_chunk_kb(kb == kb0)), ++g) {
                     const uint32_t buf = g & 1u;
                     const uint32_t use = (g >> 1) & 1u;
                     if (!bounded_wait_cluster(tmem_full_bar(buf), use, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE)) {

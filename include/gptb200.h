@@ -90,9 +90,11 @@ int gptb200_ctx_set_stream(gptb200_ctx *ctx, void *cuda_stream);
  * per term, 8 tensor-core instructions per k-block), 1 = TF32 products of fp32 low-part tiles (2^-22, 12 instructions: 8 % slower
  * where the launch is bound by the tensor pipe or the power limit), 2 = the latter for launches of at most 6 GFLOP (default)),
  * "batched_exact3x" (the same choice for gptb200_gemm_batched and the attention products: 1 = TF32 products (default), 0 = bf16 chain),
+ * "batched_chunk_kb" (3xTF32 mode, gptb200_gemm_batched and the attention products: k-blocks per hand-off of the accumulator to the
+ * fp32 running sums, 1 (default) to 4, 0 = 4; the tensor core's truncating accumulation is the main error of these products),
  * "attention_gemm" (attention with head size 64 and a sequence length that is a multiple of 4, at most 1024: batched tensor-core
- * products on head slices of the packed qkv rows plus two row kernels, in the context's precision mode -- 0 = never, 1 = when the
- * mode is TF32 (default), 2 = always; needs 2 * batch * heads * seq_len^2 floats of scratch, otherwise the kernels below run),
+ * products on head slices of the packed qkv rows plus two row kernels, in the context's precision mode -- 1 = on (default),
+ * 0 = the fp32 FMA kernels below; needs 2 * batch * heads * seq_len^2 floats of scratch, otherwise those kernels run too),
  * "attention_group_mb" (that form works through the sequences in groups whose score matrices take at most this many MB of
  * scratch: default 8192; fewer, larger launches are faster),
  * "attention_tiled" (attention with head size 64 on fp32 FMAs: register-tiled kernels, 1 = on (default), 0 = one row per thread group). */

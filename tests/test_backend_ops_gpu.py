@@ -105,7 +105,7 @@ def test_attention(env, batch, seq, d, heads, kernels):
     torch, be, lib, ref = env
     if kernels.startswith("gemm") and (d // heads != 64 or seq % 4):
         pytest.skip("the tensor-core form covers head size 64 and sequence lengths that are multiples of 4")
-    be.set_option("attention_gemm", 2 if kernels.startswith("gemm") else 0)
+    be.set_option("attention_gemm", 1 if kernels.startswith("gemm") else 0)
     be.set_option("attention_tiled", int(kernels != "rows"))
     be.set_option("attention_group_mb", 1 if kernels == "gemm-grouped" else 8192)   # 1 MB: a few sequences (or one) per group of launches
     tol = 2e-3 if kernels == "gemm-tf32" else 1e-5

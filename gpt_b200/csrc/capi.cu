@@ -663,7 +663,7 @@ int run_gemm_batched_impl(gptb200_ctx *ctx, float *out, long long out_ld, long l
                   : make_batched_tmap(ctx, &ta, a.base, K, M, inner, outer, a.ld, a.stride_inner, a.stride_outer, kBK, kBM, 0);
     if (rc) return rc;
     rc = b.mn ? make_batched_tmap(ctx, &tb, b.base, N, K, inner, outer, b.ld, b.stride_inner, b.stride_outer, 32, kBK, 1)
-              : make_batched_tmap(ctx, &tb, b.base, K, N, inner, outer, b.ld, b.stride_inner, b.stride_outer, kBK, 128, 0);
+              : make_batched_tmap(ctx, &tb, b.base, K, N, inner, outer, b.ld, b.stride_inner, b.stride_outer, kBK, N <= 128 ? (N + 31) / 32 * 16 : 128, 0);
     if (rc) return rc;
     rc = make_batched_tmap(ctx, &to, out, N, M, inner, outer, out_ld, out_si, out_so, PairCfg<false>::kStageCols, 32, 0);
     if (rc) return rc;

@@ -450,6 +450,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     const uint32_t tmem_base = *tmem_slot;
 
     const int tiles_m2 = (p.tiles_m + 1) / 2;   // pairs of 128-row tiles
+    // narrow batched form: only the first mma_n / 2 columns of this CTA's B tile are loaded, split and read (K-major: that many
+    // 128-byte rows, the box of the tensor map has exactly them; MN-major: the 32-column boxes that hold them)
+    const uint32_t b_boxes = p.mma_n ? static_cast<uint32_t>((p.mma_n / 2 + 31) / 32) : static_cast<uint32_t>(C::kBRows / 32);
+    const uint32_t b_used = !p.mma_n ? static_cast<uint32_t>(C::kBTileBytes) : B_MN ? b_boxes * kBoxBytesMN : static_cast<uint32_t>(p.mma_n / 2) * 128u;
     const long long num_pairs = gridDim.x >> 1;
     const long long pair_id = blockIdx.x >> 1;
     auto trace = [&](int event, uint32_t slot) {
@@ -501,7 +505,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 if (p.exact3x) {
                     // low parts as fp32 tiles in the raw tiles' own layout: every 16-byte piece of the stage, a third per warp
 #pragma unroll 1
-                    for (uint32_t off = (wgrp * 32 + lane) * 16; off < C::kHiBytes; off += 96 * 16) {
+                    for (uint32_t idx = wgrp * 32 + lane; idx < (kATileBytes + b_used) / 16; idx += 96) {
+                        const uint32_t off = idx * 16;   // the A tile, then the part of the B tile that the instruction reads
                         float4 v = ptx::lds128(raw + off);
                         v.x -= __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
                         v.y -= __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
@@ -551,7 +556,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     // TF32: every load of the pair reports to the leader's barrier, armed by the leader for both CTAs.
                     // 3xTF32: each CTA's loads report to its own barrier (its converter warps wait on it).
                     const uint32_t bar = X3 ? full_bar(s) : ptx::map_to_cta(full_bar(s), 0u);
-                    if (lane == 0 && (X3 || leader)) ptx::mbar_arrive_expect_tx(full_bar(s), X3 ? C::kHiBytes : 2 * C::kHiBytes);
+                    if (lane == 0 && (X3 || leader)) ptx::mbar_arrive_expect_tx(full_bar(s), (X3 ? 1u : 2u) * (kATileBytes + b_used));
                     __syncwarp();
                     const uint32_t a_dst = smem_base + s * C::kHiBytes;
                     const uint32_t b_dst = a_dst + kATileBytes;
@@ -562,7 +567,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                                 ptx::tma_load_4d_pair(a_dst + lane * kBoxBytesMN, &tmap_a, m0 + 32 * lane, zi, k0, zo, bar);
                             else
                                 ptx::tma_load_4d_pair(a_dst, &tmap_a, k0, zi, m0, zo, bar);
-                        } else if (lane < kBoxesA + kBoxesB) {
+                        } else if (lane < kBoxesA + (B_MN ? static_cast<int>(b_boxes) : 1)) {
                             const int j = lane - kBoxesA;
                             if (B_MN)
                                 ptx::tma_load_4d_pair(b_dst + j * kBoxBytesMN, &tmap_b, n0 + 32 * j, zi, k0, zo, bar);

@@ -653,6 +653,10 @@ int run_gemm_batched_impl(gptb200_ctx *ctx, float *out, long long out_ld, long l
     if (N <= 128) p.mma_n = (N + 31) / 32 * 32;
     p.exact3x = (x3 && ctx->batched_exact3x) ? 1 : 0;
     p.causal_skip = (causal && M == N) ? 1 : 0;
+    if (ctx->d_trace) {   // option "trace": the first CTA pair records its pipeline events
+        CUDA_TRY(ctx, cudaMemsetAsync(ctx->d_trace, 0, sizeof(long long) * kTraceEvents * kTraceSlots, ctx->stream));
+        p.trace = ctx->d_trace;
+    }
     p.chunk_kb = ctx->batched_chunk_kb;
     const long long tiles = 1LL * ((p.tiles_m + 1) / 2) * p.tiles_n * p.batches;
     p.sk_total = tiles * p.num_kb;

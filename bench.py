@@ -27,6 +27,8 @@ Beside those headline keys the default line carries sub-records, each a few hund
   decode         (N = 1) the linear layers of a decode step at batch 1 / 8 / 64: GB/s of weight stream and fraction of HBM peak;
   generate       (N = 1) generation of 192 tokens after a 64-token prompt at batch 1 / 8 / 64: tokens/s with the KV cache and
                  in the reference's form (the whole prefix recomputed per token);
+  attention      (N = 1) causal attention of one layer at 64 x 256 tokens, forward and backward, in both modes: the batched tensor-core
+                 products + row kernels against the fp32 FMA kernels;
   train_step     (every N) the full GPT-2 124M training step at a global batch of 64 x 256 tokens sharded over the ranks
                  (strong scaling): tokens/s, phase times, collectives per step, and dp_parity -- the distance per gradient
                  tensor between the all-reduced N-rank gradients and rank 0 computing the whole batch alone;
@@ -464,6 +466,8 @@ def run_ours(args):
             sub["decode"]["frac"] = {k: v["hbm_frac"] for k, v in sub["decode"]["per_batch"].items()}
             torch.cuda.empty_cache()
             sub["generate"] = generate_record(torch, dev, "3xtf32")
+            torch.cuda.empty_cache()
+            sub["attention"] = {m: attention_record(torch, dev, m, 64, 10, 3) for m in ("3xtf32", "tf32")}
             torch.cuda.empty_cache()
         sub["train_step"] = train_record(torch, dist, world, rank, dev, "3xtf32", 64, 5, 2, sampler, parity=True)
         torch.cuda.empty_cache()

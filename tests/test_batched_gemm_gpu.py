@@ -51,7 +51,7 @@ def test_contiguous_batches(be, torch, a_mn, b_mn, batches, m, n, k):
 
 
 @pytest.mark.parametrize("B,T,H", [(2, 256, 12), (3, 200, 4), (1, 1024, 12)])
-def test_head_slices_of_packed_rows(be, torch, B, T, H):
+def test_head_slices_of_packed_rows(be, torch, oracle, B, T, H):
     """The products of causal attention taken straight from the packed [B, T, 3 * D] qkv rows: S = Q . K^T per (sequence, head)
     into [B][T][H][T] scores, then O = S . V back into [B, T, D] rows (no softmax here: the addressing is what is tested)."""
     hd = 64
@@ -72,6 +72,17 @@ def test_head_slices_of_packed_rows(be, torch, B, T, H):
     assert rel_err(s.permute(0, 2, 1, 3), s_ref) <= TOL[be.mode]
     o_ref = (s.permute(0, 2, 1, 3).double() @ vh).permute(0, 2, 1, 3).reshape(B, T, D)
     assert rel_err(o, o_ref) <= TOL[be.mode]
+    # the same two products of single heads by the oracle's linear operator (the reference's summation order)
+    for b, h in ((0, 0), (B - 1, H - 1)):
+        q_bh = np.ascontiguousarray(q[b, :, h * hd:(h + 1) * hd].cpu().numpy())
+        k_bh = np.ascontiguousarray(k[b, :, h * hd:(h + 1) * hd].cpu().numpy())
+        v_bh = np.ascontiguousarray(v[b, :, h * hd:(h + 1) * hd].cpu().numpy())
+        s_or, _ = oracle.linear_forward(q_bh, np.ascontiguousarray(k_bh.T), np.zeros(T, np.float32), False)
+        got = s[b, :, h, :].cpu().numpy().astype(np.float64)
+        assert np.abs(got - s_or).max() / np.abs(s_or).max() <= TOL[be.mode]
+        o_or, _ = oracle.linear_forward(np.ascontiguousarray(s[b, :, h, :].cpu().numpy()), v_bh, np.zeros(hd, np.float32), False)
+        got = o[b, :, h * hd:(h + 1) * hd].cpu().numpy().astype(np.float64)
+        assert np.abs(got - o_or).max() / np.abs(o_or).max() <= TOL[be.mode]
 
 
 def test_bad_arguments_are_refused(be, torch):

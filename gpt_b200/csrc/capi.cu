@@ -661,7 +661,8 @@ int run_gemm_batched_impl(gptb200_ctx *ctx, float *out, long long out_ld, long l
     const long long tiles = 1LL * ((p.tiles_m + 1) / 2) * p.tiles_n * p.batches;
     p.sk_total = tiles * p.num_kb;
     p.sk_unit = p.num_kb;                                   // whole tiles per pair
-    const int pairs = static_cast<int>(std::min<long long>(std::max(1, ctx->num_sms / 2), tiles));
+    const int sms = ctx->max_sms > 0 ? std::min(ctx->max_sms, ctx->num_sms) : ctx->num_sms;   // option "max_sms" bounds these launches too
+    const int pairs = static_cast<int>(std::min<long long>(std::max(1, sms / 2), tiles));
     CUtensorMap ta, tb, to;
     int rc = a.mn ? make_batched_tmap(ctx, &ta, a.base, M, K, inner, outer, a.ld, a.stride_inner, a.stride_outer, 32, kBK, 1)
                   : make_batched_tmap(ctx, &ta, a.base, K, M, inner, outer, a.ld, a.stride_inner, a.stride_outer, kBK, kBM, 0);

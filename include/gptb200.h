@@ -162,8 +162,9 @@ int gptb200_linear_backward_input_gelu(gptb200_ctx *ctx, float *grad_x, const fl
  * tensor-core kernel, in the context's precision mode (no counterpart in the reference, whose attention is scalar code:
  * cuda/kernels/attention.cu).  An operand is described as stored: K-major (a: [m][k], b: [n][k]) or MN-major (a: [k][m],
  * b: [k][n]); strides3 = {row pitch, distance between consecutive inner batches, distance between consecutive outer batches}
- * in floats, each a multiple of 4, in growing order -- which lets an operand be one head of packed rows (inner batch = head,
- * stride 64; row pitch 3 * d_model; outer batch = sequence).  out [m][n] is overwritten. */
+ * in floats, each a multiple of 4 and in any order of size -- which lets an operand be one head of packed rows (inner batch = head,
+ * stride 64; row pitch 3 * d_model; outer batch = sequence).  Base addresses 16-byte aligned.  (a MN-major, b K-major) does not
+ * occur and is refused.  out [m][n] is overwritten. */
 int gptb200_gemm_batched(gptb200_ctx *ctx, float *out, const float *a, const float *b, int m, int n, int k, int a_mn_major, int b_mn_major, int batch_inner,
                          int batch_outer, const long long *a_strides3, const long long *b_strides3, const long long *out_strides3);
 
